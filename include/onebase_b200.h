@@ -1,0 +1,168 @@
+/*
+ * onebase_b200 -- C ABI of the B200 (sm_100a) implementation of OneBase's fused multi-tenant LoRA + low-precision
+ * base GEMM projection.
+ *
+ * The reference (fatebreaker/onebase) has no native layer: its host code launches Triton kernels directly from
+ * Python.  Every entry point below therefore replaces a Python->Triton launch site of the reference; each comment
+ * names that site as `file:line` inside the reference checkout.
+ *
+ * Conventions
+ *   - every function returns an int status: 0 = OB_OK, < 0 = argument / geometry rejected BEFORE any launch,
+ *     > 0 = a cudaError_t (or 1000 + CUresult for driver calls) from the launch path.  Nothing throws.
+ *   - every pointer inside the structs is a borrowed DEVICE pointer that the caller keeps alive; the library never
+ *     allocates or frees device memory and never synchronizes (except ob_read_status, which copies 64 bytes back).
+ *   - scratch ("workspace") is one caller-allocated, zero-initialized device buffer per device, sized by
+ *     ob_workspace_bytes() for the largest layer that will use it; layers share it and run one after another on one
+ *     stream (as the reference's shared `Scratch`, lowbit_lora/kernels/fp8_lora_vllm.py:315-346).  Kernels return its
+ *     counters to zero, so a captured CUDA graph can be replayed.
+ *   - device-side waits are bounded: a wait that runs out sets status word 0 of the workspace (see ob_read_status)
+ *     and the kernel returns without writing out of bounds.
+ *   - reentrant per (device, stream); two calls that share a workspace must not overlap on the GPU.
+ */
+#ifndef ONEBASE_B200_H
+#define ONEBASE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define OB_ABI_VERSION 1
+
+/* status codes (< 0: rejected before any launch) */
+#define OB_OK 0
+#define OB_ERR_NULL (-1)         /* a required pointer is null */
+#define OB_ERR_SHAPE (-2)        /* unsupported N / K / R / S / L / widths */
+#define OB_ERR_ALIGN (-3)        /* a pointer or pitch is not 16-byte aligned */
+#define OB_ERR_WORKSPACE (-4)    /* the workspace is too small for this call */
+#define OB_ERR_TILE (-5)         /* the tile configuration is not valid for this shape */
+#define OB_ERR_FORMAT (-6)       /* unknown base / adapter format, or a format this entry point does not serve */
+#define OB_ERR_BATCH (-7)        /* M out of range (0 < M <= max_m) */
+#define OB_ERR_DRIVER (-8)       /* the CUDA driver entry points could not be resolved (no GPU / no driver) */
+#define OB_ERR_TOO_LARGE (-9)    /* the request exceeds a fixed capacity of the entry point */
+
+/* device-side status word 0 (ob_read_status) */
+#define OB_DEV_OK 0
+#define OB_DEV_WAIT_TIMEOUT 1    /* a bounded wait ran out; words 1..7 say where */
+
+enum { OB_BASE_FP8 = 0, OB_BASE_NVFP4 = 1 };
+enum { OB_LORA_BF16 = 0, OB_LORA_FP8 = 1, OB_LORA_NVFP4 = 2 };
+
+#define OB_MAX_SLICES 4
+#define OB_STATUS_WORDS 16
+
+/* One LoRA linear layer: the constructor arguments of the reference's op objects
+ *   VllmFusedFP8LoRA(w_q, s_w, a_stacked, b_stacked, max_m, lora_fp8=, lora_fp4=)
+ *       lowbit_lora/kernels/fp8_lora_vllm.py:416-496
+ *   VllmFusedNVFP4LoRA(w_q, w_sf, w_global, x_global, a_stacked, b_stacked, max_m, lora_fmt=)
+ *       lowbit_lora/kernels/nvfp4_lora_vllm.py:437-502
+ * with vLLM's per-slice stacked adapter buffers a[s] = [L,1,R,K], b[s] = [L,1,N_s,R]. */
+typedef struct ObLayerDesc {
+    int32_t base_fmt;                /* OB_BASE_* */
+    int32_t lora_fmt;                /* OB_LORA_* */
+    int32_t N, K;                    /* output / input features of this (shard of the) projection */
+    int32_t S;                       /* slices (1..4): q/k/v, gate/up */
+    int32_t L;                       /* adapter slots */
+    int32_t R;                       /* LoRA rank: 16, 32, 64, 128 or 256 */
+    int32_t widths[OB_MAX_SLICES];   /* N_s, sum = N */
+    int32_t max_m;                   /* largest token count of a call */
+    const void* w_q;                 /* FP8: [N,K] e4m3.  NVFP4: [N,K/2] packed e2m1, element 2i in the low nibble */
+    const void* w_sf;                /* NVFP4: [N,K/16] ue4m3 block scales, linear (checkpoint) layout.  FP8: null */
+    const float* s_w;                /* FP8: [1] per-tensor weight scale */
+    const float* x_global;           /* NVFP4: [1] static activation global scale (1 / input_scale) */
+    const float* alpha;              /* NVFP4: [1] 1 / (x_global * w_global) */
+    const void* a[OB_MAX_SLICES];    /* adapter A per slice: bf16 [L,1,R,K] | e4m3 [L,1,R,K] | packed [L,1,R,K/2] */
+    const void* b[OB_MAX_SLICES];    /* adapter B per slice: bf16 [L,1,N_s,R] | e4m3 | packed [L,1,N_s,R/2] */
+    const void* sa[OB_MAX_SLICES];   /* FP8: fp32 [L,R] row scales.  NVFP4: ue4m3 [L,1,R,K/16] block scales */
+    const void* sb[OB_MAX_SLICES];   /* FP8: fp32 [L,N_s].           NVFP4: ue4m3 [L,1,N_s,R/16] */
+    const float* ag;                 /* NVFP4 adapters: fp32 [S,L] inverse global scales of A */
+    const float* bg;                 /* NVFP4 adapters: fp32 [S,L] inverse global scales of B */
+} ObLayerDesc;
+
+/* One call's inputs and output: the arguments of `op(x, meta_args, out=...)`
+ * (lowbit_lora/kernels/fp8_lora_vllm.py:619-629) with vLLM's LoRAKernelMeta tensors
+ * (vllm/lora/ops/triton_ops/lora_kernel_metadata.py:170-200), all int32 on the device. */
+typedef struct ObBatch {
+    int32_t M;                       /* tokens in this call (rows of x and y), 0 < M <= max_m */
+    const void* x;                   /* [M,K] bf16, row pitch ldx elements */
+    int64_t ldx;
+    void* y;                         /* [M,N] bf16, row pitch ldy elements */
+    int64_t ldy;
+    const int32_t* tok;              /* [M]   token -> slot id (-1: none)            token_lora_mapping */
+    const int32_t* srt;              /* [M]   token indices sorted by slot id        token_indices_sorted_by_lora_ids */
+    const int32_t* seg_n;            /* [L+1] tokens per segment                     num_tokens_per_lora */
+    const int32_t* seg_start;        /* [L+2] segment start offsets                  lora_token_start_loc */
+    const int32_t* seg_ids;          /* [L+1] slot id per segment, -1 padded         active_lora_ids */
+} ObBatch;
+
+/* Capacity of a shared workspace (what the reference's Scratch.ensure / _Work.ensure grow,
+ * lowbit_lora/kernels/fp8_lora_vllm.py:329-346, lowbit_lora/kernels/fp8_lora_pdl.py:620-643). */
+typedef struct ObWorkspaceShape {
+    int32_t max_m;                   /* tokens */
+    int32_t max_k;                   /* largest K */
+    int32_t max_n;                   /* largest N */
+    int32_t max_sr;                  /* largest S*R */
+    int32_t max_split1;              /* largest split-K of the shrink */
+    int32_t max_split2;              /* largest split-K of the GEMM */
+} ObWorkspaceShape;
+
+/* Per-call tile choice (what the reference's pick_cfg / plugin_cfg return,
+ * lowbit_lora/kernels/fp8_lora_vllm.py:287-312, lowbit_lora/hopper_pdl.py:268-298).  0 = library default. */
+typedef struct ObTileCfg {
+    int32_t tn;                      /* tokens per GEMM tile (the MMA's N): 16, 32, 64, 128 or 256 */
+    int32_t split2;                  /* GEMM split-K (1..16) */
+    int32_t split1;                  /* shrink split-K (1..32) */
+    int32_t stages;                  /* shared-memory ring depth of the GEMM (2..12) */
+    int32_t wait_ms;                 /* bound of every device-side wait in milliseconds (default 2000) */
+} ObTileCfg;
+
+typedef struct ObLayer ObLayer;      /* opaque: validated descriptor + TMA tensor maps (host memory only) */
+
+int ob_version(void);
+const char* ob_status_string(int status);
+
+/* Bytes of the shared workspace for `shape`.  Replaces Scratch.ensure (fp8_lora_vllm.py:329-346). */
+int ob_workspace_bytes(const ObWorkspaceShape* shape, size_t* bytes);
+
+/* Byte offsets of the workspace regions, for inspection (the reference exposes them as Scratch.xq / .sx / .hp,
+ * fp8_lora_vllm.py:321-327): out[0..6] = status words, split-K counters, s_x [max_m] fp32, x_q codes (row pitch = the
+ * calling layer's K; rows are adapter-sorted POSITIONS), NVFP4 activation block scales, shrink partials
+ * [split1][S][max_m][R] fp32, GEMM split-K partials. */
+int ob_workspace_offsets(const ObWorkspaceShape* shape, size_t out[7]);
+
+/* Validate a layer and build its TMA descriptors.  Replaces VllmFusedFP8LoRA.__init__ / VllmFusedNVFP4LoRA.__init__
+ * (fp8_lora_vllm.py:425-496, nvfp4_lora_vllm.py:446-502): pointer tables, slice ends, format flags. */
+int ob_layer_create(const ObLayerDesc* desc, ObLayer** out);
+int ob_layer_destroy(ObLayer* layer);
+
+/* K1, FP8 base: per-token dynamic e4m3 quantization of x (codes + scales into the workspace, at each token's
+ * adapter-sorted position) fused with every tenant's shrink h = x A^T (split-K partials into the workspace).
+ * Replaces the launch `_shrink_vllm[grid]` (fp8_lora_vllm.py:732-745) / `_shrink_pdl` (lowbit_lora/hopper_pdl.py:153-165). */
+int ob_k1_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape,
+              const ObTileCfg* cfg, void* cuda_stream);
+
+/* K2, FP8 base: TMA-fed tcgen05 e4m3 GEMM over the adapter-sorted tokens K1 wrote, scaled by s_x*s_w, plus each
+ * tenant's expand h B^T, bf16 out.  Replaces `_gemm_vllm[grid]` (fp8_lora_vllm.py:747-765) / `_gemm_pdl`
+ * (lowbit_lora/hopper_pdl.py:167-174).  `pdl` != 0 launches it with programmatic stream serialization. */
+int ob_k2_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape,
+              const ObTileCfg* cfg, int pdl, void* cuda_stream);
+
+/* K1 then K2 linked by programmatic dependent launch: the decode chain `run_pdl` (lowbit_lora/hopper_pdl.py:104-175). */
+int ob_chain_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape,
+                 const ObTileCfg* cfg, void* cuda_stream);
+
+/* Token sort + segment index on the device: vLLM's LoRAKernelMeta.prepare_tensors
+ * (vllm/lora/ops/triton_ops/lora_kernel_metadata.py:110-168) incl. its stale-on-no-adapter behaviour.
+ * token_lora [M] int32 in; the five metadata tensors out (tok/srt of capacity >= M, seg_* of L+1 / L+2 / L+1). */
+int ob_segment_index(const int32_t* token_lora, int32_t M, int32_t L, int32_t* tok, int32_t* srt, int32_t* seg_n,
+                     int32_t* seg_start, int32_t* seg_ids, void* cuda_stream);
+
+/* Copy the workspace's OB_STATUS_WORDS status words to host memory (synchronizes the stream) and clear them. */
+int ob_read_status(void* workspace, int32_t* host_out, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ONEBASE_B200_H */

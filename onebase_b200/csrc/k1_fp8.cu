@@ -1,0 +1,221 @@
+// K1 (FP8 base): per-token dynamic e4m3 quantization of the activations, fused in one launch with every tenant's LoRA
+// shrink h = x A^T.
+//
+// One launch, two kinds of CTA (256 threads each):
+//   * CTAs [0, M): quantize one tile POSITION each.  Position p stands for row `position_row(p)` of x: the adapter-sorted
+//     order whenever the batch has an adapter, so that K2 can fetch contiguous rows by TMA.  amax over the row in fp32,
+//     s_x = max(amax / 448, 1/(448*512)) and code = e4m3_rn(clamp(x / s_x)) with IEEE divisions and ONE rounding step:
+//     the rule of lowbit_lora/kernels/fp8_lora_vllm.py:47-71 (vLLM's dynamic per-token quantization), bit for bit.
+//   * the remaining CTAs: 8 independent warps each; a warp owns (block of 1 or 4 sorted positions, slice, 8 rank rows,
+//     K split) and streams that [8, K/split] block of the positions' adapter A from HBM with 16-byte loads, multiplying it
+//     into up to 4 tokens at a time (their x rows come from L2; tokens of one tenant handled by different warps re-read
+//     A through L2, not HBM).  The 32 lane-partial sums per warp (8 rank rows x 4 tokens) are
+//     reduced with a transposing butterfly -- 31 shuffles for 32 sums, lane i ends up with sum i -- and written as
+//     split-K partials hp[split][slice][position][rank] (fp32), which K2 adds in split order (deterministic).
+//     Computes what lowbit_lora/kernels/fp8_lora_vllm.py:72-120 computes per adapter segment.
+// The kernel starts with griddepcontrol.launch_dependents so that a dependent K2 may begin streaming W at once.
+#include "ob_common.cuh"
+#include "ob_ptx.cuh"
+
+namespace ob {
+
+constexpr int kK1Threads = 256;
+constexpr int kQuantCache = 8;      // 16-byte vectors of the row a thread keeps in registers between the two passes
+constexpr float kFp8Max = 448.0f;
+constexpr float kMinTokenScale = 1.0f / (448.0f * 512.0f);
+
+__device__ __forceinline__ float amax8(const uint4& v) {
+    float m = fmaxf(fabsf(bf16_lo(v.x)), fabsf(bf16_hi(v.x)));
+    m = fmaxf(m, fmaxf(fabsf(bf16_lo(v.y)), fabsf(bf16_hi(v.y))));
+    m = fmaxf(m, fmaxf(fabsf(bf16_lo(v.z)), fabsf(bf16_hi(v.z))));
+    return fmaxf(m, fmaxf(fabsf(bf16_lo(v.w)), fabsf(bf16_hi(v.w))));
+}
+
+__device__ __forceinline__ float q1(float v, float sx) {
+    return fminf(fmaxf(__fdiv_rn(v, sx), -kFp8Max), kFp8Max);
+}
+
+__device__ __forceinline__ uint2 quant8(const uint4& v, float sx) {
+    uint2 o;
+    o.x = (uint32_t)cvt_e4m3x2(q1(bf16_lo(v.x), sx), q1(bf16_hi(v.x), sx)) |
+          ((uint32_t)cvt_e4m3x2(q1(bf16_lo(v.y), sx), q1(bf16_hi(v.y), sx)) << 16);
+    o.y = (uint32_t)cvt_e4m3x2(q1(bf16_lo(v.z), sx), q1(bf16_hi(v.z), sx)) |
+          ((uint32_t)cvt_e4m3x2(q1(bf16_lo(v.w), sx), q1(bf16_hi(v.w), sx)) << 16);
+    return o;
+}
+
+__device__ void quantize_position(const K1Params& p, int pos) {
+    __shared__ float s_part[kK1Threads / 32];
+    __shared__ float s_scale;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int n_all, n_ad;
+    segment_totals(p.meta, p.L, lane, n_all, n_ad);
+    n_all = min(n_all, p.M);
+    const int row = position_row(p.meta, pos, p.M, n_all, n_ad);
+    const uint4* xr = reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.ldx);
+    const int nvec = p.K >> 3;
+    uint4 cache[kQuantCache];
+    float amax = 0.0f;
+#pragma unroll
+    for (int c = 0; c < kQuantCache; ++c) {
+        const int i = tid + c * kK1Threads;
+        if (i < nvec) {
+            cache[c] = __ldg(xr + i);
+            amax = fmaxf(amax, amax8(cache[c]));
+        }
+    }
+    for (int i = tid + kQuantCache * kK1Threads; i < nvec; i += kK1Threads) amax = fmaxf(amax, amax8(__ldg(xr + i)));
+#pragma unroll
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) s_part[warp] = amax;
+    __syncthreads();
+    if (tid == 0) {
+        float m = s_part[0];
+        for (int w = 1; w < kK1Threads / 32; ++w) m = fmaxf(m, s_part[w]);
+        const float sx = fmaxf(__fdiv_rn(m, kFp8Max), kMinTokenScale);
+        s_scale = sx;
+        p.sx[pos] = sx;
+    }
+    __syncthreads();
+    const float sx = s_scale;
+    uint2* out = reinterpret_cast<uint2*>(p.xq + (size_t)pos * (size_t)p.K);
+#pragma unroll
+    for (int c = 0; c < kQuantCache; ++c) {
+        const int i = tid + c * kK1Threads;
+        if (i < nvec) out[i] = quant8(cache[c], sx);
+    }
+    for (int i = tid + kQuantCache * kK1Threads; i < nvec; i += kK1Threads) out[i] = quant8(__ldg(xr + i), sx);
+}
+
+// 32 lane-partial values per lane -> lane i holds the warp-wide sum of value i (31 shuffles).
+__device__ __forceinline__ float transpose_reduce32(float (&v)[32], int lane) {
+#pragma unroll
+    for (int off = 16, n = 32; off >= 1; off >>= 1, n >>= 1) {
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+            const float send = upper ? v[i] : v[i + n / 2];
+            const float keep = upper ? v[i + n / 2] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+    }
+    return v[0];
+}
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+    f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+
+// One pass of a warp: 8 rank rows [k0, k1) of adapter `lora`, slice s, times the `nt` (<= 4) tokens at sorted positions
+// pos0 .. pos0+nt-1; writes the split-K partial hp[j][s][pos][rg*8 .. +8].  bf16 adapters.
+__device__ __forceinline__ void shrink_pass_bf16(const K1Params& p, int lora, int s, int rg, int j, int k0, int k1, int pos0,
+                                                 int nt, int lane) {
+    const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(p.a[s]) + ((size_t)lora * p.R + (size_t)rg * 8) * p.K;
+    const __nv_bfloat16* xrow[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        int r = (t < nt) ? p.meta.srt[pos0 + t] : 0;
+        r = r < 0 ? 0 : (r > p.M - 1 ? p.M - 1 : r);
+        xrow[t] = p.x + (int64_t)r * p.ldx;
+    }
+    float acc[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
+    for (int kk = k0; kk < k1; kk += 256) {
+        const int k = kk + lane * 8;
+        if (k < k1) {
+            uint4 av[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) av[r] = __ldg(reinterpret_cast<const uint4*>(a + (size_t)r * p.K + k));
+            float xf[4][8];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                if (t < nt) {
+                    unpack8(__ldg(reinterpret_cast<const uint4*>(xrow[t] + k)), xf[t]);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) xf[t][e] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                float af[8];
+                unpack8(av[r], af);
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {
+                    float sacc = acc[r * 4 + t];
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) sacc = fmaf(af[e], xf[t][e], sacc);
+                    acc[r * 4 + t] = sacc;
+                }
+            }
+        }
+    }
+    const float total = transpose_reduce32(acc, lane);
+    const int r = lane >> 2, t = lane & 3;
+    if (t < nt) p.hp[(((size_t)j * p.S + s) * p.max_m + (pos0 + t)) * p.R + rg * 8 + r] = total;
+}
+
+// One warp: block `pb` of p.pb consecutive sorted positions, unit `u` -> (slice, group of 8 rank rows, K split).
+// The warp looks up which segment each of its positions lies in (one warp-wide read of the segment index) and runs
+// one pass per run of positions that share an adapter.
+__device__ void shrink_unit(const K1Params& p, int pb, int u, int lane) {
+    int n_all, n_ad;
+    segment_totals(p.meta, p.L, lane, n_all, n_ad);
+    n_all = min(n_all, p.M);
+    if (n_ad <= 0) return;
+    const int p0 = pb * p.pb;
+    const int np = min(p.pb, n_all - p0);
+    if (np <= 0) return;
+    int lora_of[4] = {-1, -1, -1, -1};
+    for (int base = 0; base <= p.L; base += 32) {
+        const int i = base + lane;
+        int id = -1, st = 0, en = 0;
+        if (i <= p.L) {
+            id = p.meta.seg_ids[i];
+            st = p.meta.seg_start[i];
+            en = st + p.meta.seg_n[i];
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const bool hit = q < np && id >= 0 && id < p.L && st <= p0 + q && p0 + q < en;
+            const uint32_t m = __ballot_sync(0xffffffffu, hit);
+            if (m) lora_of[q] = __shfl_sync(0xffffffffu, id, __ffs(m) - 1);
+        }
+    }
+    const int groups = p.R >> 3;
+    const int j = u % p.split1;
+    const int rg = (u / p.split1) % groups;
+    const int s = u / (p.split1 * groups);
+    const int k0 = j * p.k_per_split;
+    const int k1 = min(p.K, k0 + p.k_per_split);
+    int q = 0;
+    while (q < np) {
+        const int lora = lora_of[q];
+        int nt = 1;
+        while (q + nt < np && lora_of[q + nt] == lora) ++nt;
+        if (lora >= 0) shrink_pass_bf16(p, lora, s, rg, j, k0, k1, p0 + q, nt, lane);
+        q += nt;
+    }
+}
+
+__global__ void __launch_bounds__(kK1Threads) k1_fp8_kernel(const K1Params p) {
+    griddep_launch_dependents();
+    if ((int)blockIdx.x < p.n_quant_ctas) {
+        quantize_position(p, blockIdx.x);
+        return;
+    }
+    const int lane = threadIdx.x & 31;
+    const int w = ((int)blockIdx.x - p.n_quant_ctas) * (kK1Threads / 32) + (threadIdx.x >> 5);
+    const int pb = w / p.units_per_block;
+    if (pb >= p.n_pblocks) return;
+    shrink_unit(p, pb, w % p.units_per_block, lane);
+}
+
+cudaError_t launch_k1_fp8(const K1Params& p, int grid, cudaStream_t stream) {
+    k1_fp8_kernel<<<grid, kK1Threads, 0, stream>>>(p);
+    return cudaGetLastError();
+}
+
+}  // namespace ob

@@ -1,0 +1,430 @@
+// K2 (FP8 base): y = bf16( s_x * s_w * (x_q W_q^T) + sum over tenants of h B^T ), one CTA per (128 output features,
+// token tile, K split), hand-written for sm_100a:
+//
+//   swap-AB orientation -- the 128 rows of the W tile sit on the MMA's M side, the tokens (16..256 per tile, adapter-
+//   sorted positions written by K1) on its N side, so a decode batch of 1..32 tokens wastes no tensor-core rows and the
+//   kernel is a pure stream of W from HBM.
+//
+//   warp 0   TMA producer: W tiles [128 x 128 B] (128-byte swizzle) into a shared-memory ring, then -- through the same
+//            ring -- each expand step's B tile [128 x rank chunk] (bf16).  Independent of K1, so under programmatic
+//            dependent launch the whole ring fills while K1 is still running.
+//   warp 2   TMA producer of the x_q tiles [tokens x 128 B]; waits for K1 (griddepcontrol.wait) first.
+//   warp 1   allocates TMEM and issues tcgen05.mma: kind::f8f6f4 (e4m3 x e4m3, fp32) into accumulator 0 for the base
+//            GEMM, kind::f16 (bf16) into accumulator 1 for the LoRA expand; tcgen05.commit releases ring slots.
+//   warps 4-7  read vLLM's segment index, list the (segment, rank chunk) expand steps of this tile, and after K1 build each
+//            step's masked H tile (bf16(sum of K1's split-K partials) on the segment's token rows, zero elsewhere) in
+//            shared memory in the UMMA layout; finally the epilogue: tcgen05.ld both accumulators, scale, add, and store
+//            bf16 rows scattered back through the sort.  With split-K > 1 they write fp32 partials instead and the last
+//            CTA to arrive adds them in split order (deterministic) and resets the arrival counter.
+//
+// What it computes is lowbit_lora/kernels/fp8_lora_vllm.py:123-284 (`_gemm_vllm`, BASE=True) and the decode-chain GEMM
+// lowbit_lora/kernels/fp8_lora_pdl.py:324-495; positions, padding and stale metadata follow fp8_lora_vllm.py:147-163.
+// Every wait is bounded (wait_ms); a wait that runs out records where in the workspace status words and the CTA leaves
+// without storing.
+#include "ob_common.cuh"
+#include "ob_ptx.cuh"
+
+namespace ob {
+
+constexpr int kK2Threads = 256;
+constexpr int kWTileBytes = kTileN * kBlockK;   // 16 KB
+constexpr int kCtrlBytes = 16384;
+
+struct LoraStep {
+    int lora;     // adapter slot
+    int lo, hi;   // tile-local token rows [lo, hi) of the segment
+    int chunk;    // rank chunk index
+};
+
+struct K2Ctrl {
+    uint64_t full_w[12];
+    uint64_t full_x[12];
+    uint64_t empty[12];
+    uint64_t h_full[2];
+    uint64_t h_empty[2];
+    uint64_t list_ready;
+    uint64_t acc_full;
+    uint32_t tmem_base;
+    volatile int abort_flag;
+    int n_steps;          // expand steps of this CTA
+    int last_flag;
+    int go_flag;          // the epilogue warps' shared continue / stop decision
+    float sx[256];
+    int rowmap[256];
+    LoraStep steps[kMaxLoraIters];
+};
+static_assert(sizeof(K2Ctrl) <= kCtrlBytes, "control block too large");
+
+__device__ __forceinline__ void record_timeout(const K2Params& p, K2Ctrl* c, int where, int it) {
+    c->abort_flag = 1;
+    if (atomicCAS(p.status, OB_DEV_OK, OB_DEV_WAIT_TIMEOUT) == OB_DEV_OK) {
+        p.status[1] = where;
+        p.status[2] = blockIdx.x;
+        p.status[3] = blockIdx.y;
+        p.status[4] = blockIdx.z;
+        p.status[5] = it;
+    }
+}
+
+#define OB_WAIT(bar, parity, where, it)                   \
+    if (!mbar_wait((bar), (parity), limit_ns)) {          \
+        record_timeout(p, ctrl, (where), (it));           \
+        break;                                            \
+    }
+
+__global__ void __launch_bounds__(kK2Threads, 1)
+k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+              const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
+              const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_b3) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int tn = p.tn;
+    const int stage_bytes = kWTileBytes + tn * kBlockK;
+    const int h_bytes = (int)align_up((size_t)tn * p.rc * 2, 1024);
+    uint8_t* ring = smem;
+    uint8_t* hbuf = ring + (size_t)p.stages * stage_bytes;
+    K2Ctrl* ctrl = reinterpret_cast<K2Ctrl*>(hbuf + 2 * h_bytes);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint64_t limit_ns = (uint64_t)p.wait_ms * 1000000ull;
+
+    // ---- tile coordinates: blockIdx.x walks the slices' 128-wide tiles, .y the K splits, .z the token tiles
+    int s = 0, n_tile = blockIdx.x, slice_off = 0;
+    while (s < p.S - 1 && n_tile >= (p.widths[s] + kTileN - 1) / kTileN) {
+        n_tile -= (p.widths[s] + kTileN - 1) / kTileN;
+        slice_off += p.widths[s];
+        ++s;
+    }
+    const int n_s = p.widths[s];
+    const int n0_local = n_tile * kTileN;
+    const int j = blockIdx.y;
+    const int t0 = blockIdx.z * tn;
+    const int kb0 = (int)(((int64_t)p.kblocks * j) / p.split2);
+    const int kb1 = (int)(((int64_t)p.kblocks * (j + 1)) / p.split2);
+    const int n_base = kb1 - kb0;
+    const int n_chunks = p.R / p.rc;
+    const int tile_lin = blockIdx.z * gridDim.x + blockIdx.x;
+
+    // ---- one-time setup
+    if (tid == 0) {
+        for (int i = 0; i < p.stages; ++i) {
+            mbar_init(&ctrl->full_w[i], 1);
+            mbar_init(&ctrl->full_x[i], 1);
+            mbar_init(&ctrl->empty[i], 1);
+        }
+        mbar_init(&ctrl->h_full[0], 1);
+        mbar_init(&ctrl->h_full[1], 1);
+        mbar_init(&ctrl->h_empty[0], 1);
+        mbar_init(&ctrl->h_empty[1], 1);
+        mbar_init(&ctrl->list_ready, 1);
+        mbar_init(&ctrl->acc_full, 1);
+        ctrl->abort_flag = 0;
+        ctrl->n_steps = 0;
+        ctrl->last_flag = 0;
+        fence_mbar_init();
+    }
+    const uint32_t tmem_cols = (2 * tn <= 32) ? 32u : (uint32_t)(2 * tn);
+    if (warp == 1) {
+        tmem_alloc(&ctrl->tmem_base, tmem_cols);
+        tmem_relinquish();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tm_w);
+        tma_prefetch_desc(&tm_x);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctrl->tmem_base;
+    const uint32_t acc0 = tmem_base, acc1 = tmem_base + (uint32_t)tn;
+
+    if (warp == 0) {
+        // =========================================================== W / B-tile producer
+        if (lane == 0) {
+            const uint64_t pol = l2_policy_evict_first();
+            int it = 0;
+            for (; it < n_base; ++it) {
+                const int st = it % p.stages, use = it / p.stages;
+                if (ctrl->abort_flag) break;
+                if (use > 0) OB_WAIT(&ctrl->empty[st], (uint32_t)((use - 1) & 1), 1, it)
+                mbar_arrive_expect_tx(&ctrl->full_w[st], kWTileBytes);
+                tma_load_2d_hint(ring + (size_t)st * stage_bytes, &tm_w, &ctrl->full_w[st], (kb0 + it) * kBlockK,
+                                 slice_off + n0_local, pol);
+            }
+            if (it == n_base && !ctrl->abort_flag) {
+                bool ok = mbar_wait(&ctrl->list_ready, 0, limit_ns);
+                if (!ok) record_timeout(p, ctrl, 2, 0);
+                const int n_steps = ok ? ctrl->n_steps : 0;
+                const CUtensorMap* tmb = (s == 0) ? &tm_b0 : (s == 1) ? &tm_b1 : (s == 2) ? &tm_b2 : &tm_b3;
+                const uint32_t b_bytes = (uint32_t)kTileN * p.rc * 2;
+                for (int li = 0; li < n_steps; ++li, ++it) {
+                    const int st = it % p.stages, use = it / p.stages;
+                    if (ctrl->abort_flag) break;
+                    if (use > 0) OB_WAIT(&ctrl->empty[st], (uint32_t)((use - 1) & 1), 3, it)
+                    const LoraStep e = ctrl->steps[li];
+                    mbar_arrive_expect_tx(&ctrl->full_w[st], b_bytes);
+                    tma_load_2d(ring + (size_t)st * stage_bytes, tmb, &ctrl->full_w[st], e.chunk * p.rc,
+                                e.lora * n_s + n0_local);
+                }
+            }
+        }
+    } else if (warp == 2) {
+        // =========================================================== x_q producer (depends on K1)
+        if (lane == 0) {
+            griddep_wait();
+            for (int it = 0; it < n_base; ++it) {
+                const int st = it % p.stages, use = it / p.stages;
+                if (ctrl->abort_flag) break;
+                if (use > 0) OB_WAIT(&ctrl->empty[st], (uint32_t)((use - 1) & 1), 4, it)
+                mbar_arrive_expect_tx(&ctrl->full_x[st], (uint32_t)tn * kBlockK);
+                tma_load_2d(ring + (size_t)st * stage_bytes + kWTileBytes, &tm_x, &ctrl->full_x[st], (kb0 + it) * kBlockK, t0);
+            }
+        }
+    } else if (warp == 1) {
+        // =========================================================== MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc8 = umma_idesc(0, 0, kTileN, (uint32_t)tn);
+            const uint32_t idesc16 = umma_idesc(1, 1, kTileN, (uint32_t)tn);
+            int it = 0;
+            for (; it < n_base; ++it) {
+                const int st = it % p.stages, use = it / p.stages;
+                if (ctrl->abort_flag) break;
+                OB_WAIT(&ctrl->full_w[st], (uint32_t)(use & 1), 5, it)
+                OB_WAIT(&ctrl->full_x[st], (uint32_t)(use & 1), 6, it)
+                tc_fence_after();
+                const uint32_t wa = smem_u32(ring + (size_t)st * stage_bytes);
+                const uint64_t dw = umma_smem_desc(wa, 1024, 2);
+                const uint64_t dx = umma_smem_desc(wa + kWTileBytes, 1024, 2);
+#pragma unroll
+                for (int k = 0; k < kBlockK / 32; ++k)
+                    umma_f8f6f4(acc0, dw + (uint64_t)(k * 2), dx + (uint64_t)(k * 2), idesc8, (it > 0 || k > 0) ? 1u : 0u);
+                umma_commit(&ctrl->empty[st]);
+            }
+            if (it == n_base && !ctrl->abort_flag) {
+                bool ok = mbar_wait(&ctrl->list_ready, 0, limit_ns);
+                if (!ok) record_timeout(p, ctrl, 7, 0);
+                const int n_steps = ok ? ctrl->n_steps : 0;
+                const uint32_t row_bytes = (uint32_t)p.rc * 2;                 // 32, 64 or 128
+                const uint32_t lt = row_bytes == 128 ? 2u : row_bytes == 64 ? 4u : 6u;
+                const uint32_t sbo = row_bytes * 8;
+                int li = 0;
+                for (; li < n_steps; ++li, ++it) {
+                    const int st = it % p.stages, use = it / p.stages;
+                    const int hb = li & 1, hu = li >> 1;
+                    if (ctrl->abort_flag) break;
+                    OB_WAIT(&ctrl->full_w[st], (uint32_t)(use & 1), 8, it)
+                    OB_WAIT(&ctrl->h_full[hb], (uint32_t)(hu & 1), 9, it)
+                    tc_fence_after();
+                    const uint64_t db = umma_smem_desc(smem_u32(ring + (size_t)st * stage_bytes), sbo, lt);
+                    const uint64_t dh = umma_smem_desc(smem_u32(hbuf + (size_t)hb * h_bytes), sbo, lt);
+                    for (int k = 0; k < p.rc / 16; ++k)
+                        umma_f16(acc1, db + (uint64_t)(k * 2), dh + (uint64_t)(k * 2), idesc16, (li > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&ctrl->empty[st]);
+                    umma_commit(&ctrl->h_empty[hb]);
+                }
+                if (li == n_steps && !ctrl->abort_flag) umma_commit(&ctrl->acc_full);
+            }
+        }
+    } else if (warp >= 4) {
+        // =========================================================== segment index, H tiles, epilogue
+        const int te = tid - 128;
+        int n_all, n_ad;
+        segment_totals(p.meta, p.L, lane, n_all, n_ad);
+        n_all = min(n_all, p.M);
+        for (int c = te; c < tn; c += 128) {
+            const int pos = t0 + c;
+            ctrl->rowmap[c] = pos < p.M ? position_row(p.meta, pos, p.M, n_all, n_ad) : -1;
+        }
+        if (warp == 4) {
+            int total = 0;                                   // (segment, chunk) steps of this tile so far, all splits
+            if (n_ad > 0) {
+                for (int base = 0; base <= p.L; base += 32) {
+                    const int i = base + lane;
+                    int lora = -1, lo = 0, hi = 0;
+                    if (i <= p.L) {
+                        lora = p.meta.seg_ids[i];
+                        const int cnt = p.meta.seg_n[i], sst = p.meta.seg_start[i];
+                        lo = max(sst, t0);
+                        hi = min(min(sst + cnt, t0 + tn), n_all);
+                        if (cnt <= 0 || sst < 0) lora = -1;
+                    }
+                    const bool ok = lora >= 0 && lora < p.L && lo < hi;
+                    const uint32_t mask = __ballot_sync(0xffffffffu, ok);
+                    if (ok) {
+                        const int idx = total / n_chunks + __popc(mask & ((1u << lane) - 1u));
+                        for (int c = 0; c < n_chunks; ++c) {
+                            const int e = idx * n_chunks + c;
+                            if (e % p.split2 == j) {
+                                const int li = e / p.split2;
+                                if (li < kMaxLoraIters) ctrl->steps[li] = LoraStep{lora, lo - t0, hi - t0, c};
+                            }
+                        }
+                    }
+                    total += __popc(mask) * n_chunks;
+                }
+            }
+            if (lane == 0) {
+                int mine = total > j ? (total - j + p.split2 - 1) / p.split2 : 0;
+                ctrl->n_steps = min(mine, kMaxLoraIters);
+            }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (te == 0) mbar_arrive(&ctrl->list_ready);
+        const int n_steps = ctrl->n_steps;
+
+        griddep_wait();                                       // K1's s_x and shrink partials from here on
+        for (int c = te; c < tn; c += 128) ctrl->sx[c] = (t0 + c < p.M) ? p.sx[t0 + c] : 0.0f;
+
+        const int row_bytes = p.rc * 2;
+        const int cpr = row_bytes / 16;                       // 16-byte chunks per H row
+        const uint32_t swz = (uint32_t)cpr - 1u;
+        for (int li = 0; li < n_steps; ++li) {
+            const int hb = li & 1, hu = li >> 1;
+            if (te == 0) {                                    // one thread decides, so that all 128 leave together
+                int go = ctrl->abort_flag ? 0 : 1;
+                if (go && hu > 0 && !mbar_wait(&ctrl->h_empty[hb], (uint32_t)((hu - 1) & 1), limit_ns)) {
+                    record_timeout(p, ctrl, 10, li);
+                    go = 0;
+                }
+                ctrl->go_flag = go;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (!ctrl->go_flag) break;
+            const LoraStep e = ctrl->steps[li];
+            uint8_t* hdst = hbuf + (size_t)hb * h_bytes;
+            for (int ch = te; ch < tn * cpr; ch += 128) {
+                const int row = ch / cpr, cc = ch % cpr;
+                uint4 out = make_uint4(0u, 0u, 0u, 0u);
+                if (row >= e.lo && row < e.hi) {
+                    float acc[8];
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) acc[q] = 0.0f;
+                    const size_t col = (size_t)e.chunk * p.rc + (size_t)cc * 8;
+                    for (int j1 = 0; j1 < p.split1; ++j1) {
+                        const float4* src = reinterpret_cast<const float4*>(
+                            p.hp + (((size_t)j1 * p.S + s) * p.max_m + (size_t)(t0 + row)) * p.R + col);
+                        const float4 u0 = __ldcg(src), u1 = __ldcg(src + 1);
+                        acc[0] += u0.x; acc[1] += u0.y; acc[2] += u0.z; acc[3] += u0.w;
+                        acc[4] += u1.x; acc[5] += u1.y; acc[6] += u1.z; acc[7] += u1.w;
+                    }
+                    __nv_bfloat162 b0 = __floats2bfloat162_rn(acc[0], acc[1]);
+                    __nv_bfloat162 b1 = __floats2bfloat162_rn(acc[2], acc[3]);
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(acc[4], acc[5]);
+                    __nv_bfloat162 b3 = __floats2bfloat162_rn(acc[6], acc[7]);
+                    out.x = *reinterpret_cast<uint32_t*>(&b0);
+                    out.y = *reinterpret_cast<uint32_t*>(&b1);
+                    out.z = *reinterpret_cast<uint32_t*>(&b2);
+                    out.w = *reinterpret_cast<uint32_t*>(&b3);
+                }
+                uint32_t off = (uint32_t)row * (uint32_t)row_bytes + (uint32_t)cc * 16u;
+                off ^= ((off >> 7) & swz) << 4;
+                *reinterpret_cast<uint4*>(hdst + off) = out;
+            }
+            fence_proxy_async_smem();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (te == 0) mbar_arrive(&ctrl->h_full[hb]);
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");        // sx / rowmap visible to all epilogue threads
+
+        // ---- epilogue
+        if (te == 0) {
+            int go = ctrl->abort_flag ? 0 : 1;
+            if (go && !mbar_wait(&ctrl->acc_full, 0u, limit_ns)) {
+                record_timeout(p, ctrl, 11, 0);
+                go = 0;
+            }
+            ctrl->go_flag = go;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const bool done = ctrl->go_flag != 0;
+        tc_fence_after();
+        if (done) {
+            const int q = warp & 3;
+            const int n_local = q * 32 + lane;
+            const bool n_ok = n0_local + n_local < n_s;
+            const int n_glob = slice_off + n0_local + n_local;
+            const float s_w = __ldg(p.s_w);
+            const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+            const bool has_lora = n_steps > 0;
+            float* part = p.part + ((size_t)tile_lin * p.split2 + j) * (size_t)tn * kTileN;
+            for (int c0 = 0; c0 < tn; c0 += 16) {
+                uint32_t r0[16], r1[16];
+                tmem_ld16(acc0 + lane_addr + (uint32_t)c0, r0);
+                if (has_lora) tmem_ld16(acc1 + lane_addr + (uint32_t)c0, r1);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 16; ++c) {
+                    const int row = ctrl->rowmap[c0 + c];
+                    float v = __uint_as_float(r0[c]) * (ctrl->sx[c0 + c] * s_w);
+                    if (has_lora) v += __uint_as_float(r1[c]);
+                    if (p.split2 == 1) {
+                        if (row >= 0 && n_ok) p.y[(int64_t)row * p.ldy + n_glob] = __float2bfloat16_rn(v);
+                    } else {
+                        part[(size_t)(c0 + c) * kTileN + n_local] = v;
+                    }
+                }
+            }
+            if (p.split2 > 1) {
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (te == 0) {
+                    const int old = atomicAdd(p.counters + tile_lin, 1);
+                    ctrl->last_flag = (old == p.split2 - 1) ? 1 : 0;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (ctrl->last_flag) {
+                    __threadfence();
+                    const float* pbase = p.part + (size_t)tile_lin * p.split2 * (size_t)tn * kTileN;
+                    for (int c = 0; c < tn; ++c) {
+                        const int row = ctrl->rowmap[c];
+                        if (row < 0) continue;
+                        float v = 0.0f;
+                        for (int jj = 0; jj < p.split2; ++jj)
+                            v += __ldcg(pbase + ((size_t)jj * tn + c) * kTileN + n_local);
+                        if (n_ok) p.y[(int64_t)row * p.ldy + n_glob] = __float2bfloat16_rn(v);
+                    }
+                    if (te == 0) p.counters[tile_lin] = 0;
+                }
+            }
+        }
+    }
+
+    // ---- teardown: nobody leaves while TMEM is in use or copies may still land in this CTA's shared memory
+    if (ctrl->abort_flag) __nanosleep(200000);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+size_t k2_fp8_smem_bytes(int tn, int stages, int rc) {
+    return 1024 + (size_t)stages * (kWTileBytes + (size_t)tn * kBlockK) + 2 * align_up((size_t)tn * rc * 2, 1024) + kCtrlBytes;
+}
+
+cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
+                          dim3 grid, size_t smem, int pdl, cudaStream_t stream) {
+    static int configured_for[64] = {0};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && !configured_for[dev]) {
+        e = cudaFuncSetAttribute(k2_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return e;
+        configured_for[dev] = 1;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kK2Threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, k2_fp8_kernel, p, tm_w, tm_x, tm_b[0], tm_b[1], tm_b[2], tm_b[3]);
+}
+
+}  // namespace ob

@@ -1,0 +1,403 @@
+// The C ABI (include/onebase_b200.h): argument validation, launch geometry, TMA descriptor construction, launches.
+// Host code only allocates host memory; device memory always belongs to the caller.
+#include <mutex>
+#include <new>
+#include <vector>
+
+#include "ob_common.cuh"
+
+namespace ob {
+cudaError_t launch_k1_fp8(const K1Params& p, int grid, cudaStream_t stream);
+size_t k2_fp8_smem_bytes(int tn, int stages, int rc);
+cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
+                          dim3 grid, size_t smem, int pdl, cudaStream_t stream);
+cudaError_t launch_segment_index(const int32_t* token_lora, int M, int L, int32_t* tok, int32_t* srt, int32_t* seg_n,
+                                 int32_t* seg_start, int32_t* seg_ids, cudaStream_t stream);
+}  // namespace ob
+
+using namespace ob;
+
+namespace {
+
+constexpr size_t kSmemLimit = 227 * 1024;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+        else
+            (void)cudaGetLastError();
+    });
+    return fn;
+}
+
+// 2-D row-major tensor [rows, inner] of `elem_bytes` elements -> tiled map with box [box_rows, box_inner], swizzle by the
+// box's inner bytes (32 / 64 / 128).
+int encode_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t inner, uint64_t rows,
+              uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return OB_ERR_DRIVER;
+    const uint32_t inner_bytes = box_inner * (uint32_t)elem_bytes;
+    CUtensorMapSwizzle sw = inner_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                            : inner_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                            : inner_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                                : CU_TENSOR_MAP_SWIZZLE_NONE;
+    if (sw == CU_TENSOR_MAP_SWIZZLE_NONE) return OB_ERR_SHAPE;
+    cuuint64_t gdim[2] = {inner, rows};
+    cuuint64_t gstride[1] = {pitch_bytes};
+    cuuint32_t box[2] = {box_inner, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(tm, dt, 2, const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? OB_OK : 1000 + (int)r;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+struct XMap {
+    const void* base;
+    int rows, tn;
+    CUtensorMap tm;
+};
+
+}  // namespace
+
+struct ObLayer {
+    ObLayerDesc d;
+    int rc;                       // rank chunk of an expand step
+    int n_tiles;                  // 128-wide output tiles over all slices
+    CUtensorMap tm_w;
+    CUtensorMap tm_b[OB_MAX_SLICES];
+    std::mutex mu;
+    std::vector<XMap> xmaps;      // x_q maps by (workspace region, rows, token tile)
+};
+
+namespace {
+
+int validate_desc(const ObLayerDesc* d) {
+    if (!d) return OB_ERR_NULL;
+    if (d->base_fmt != OB_BASE_FP8 && d->base_fmt != OB_BASE_NVFP4) return OB_ERR_FORMAT;
+    if (d->lora_fmt != OB_LORA_BF16 && d->lora_fmt != OB_LORA_FP8 && d->lora_fmt != OB_LORA_NVFP4) return OB_ERR_FORMAT;
+    if (d->N <= 0 || d->K <= 0 || d->K % 16 != 0 || d->S < 1 || d->S > OB_MAX_SLICES || d->L < 1 || d->L > 256 ||
+        d->max_m < 1)
+        return OB_ERR_SHAPE;
+    if (!(d->R == 16 || d->R == 32 || d->R == 64 || d->R == 128 || d->R == 256)) return OB_ERR_SHAPE;
+    int sum = 0;
+    for (int s = 0; s < d->S; ++s) {
+        if (d->widths[s] <= 0) return OB_ERR_SHAPE;
+        sum += d->widths[s];
+    }
+    if (sum != d->N) return OB_ERR_SHAPE;
+    if (!d->w_q) return OB_ERR_NULL;
+    if (d->base_fmt == OB_BASE_FP8 && !d->s_w) return OB_ERR_NULL;
+    if (d->base_fmt == OB_BASE_NVFP4 && (!d->w_sf || !d->x_global || !d->alpha)) return OB_ERR_NULL;
+    if (!aligned16(d->w_q) || (d->w_sf && !aligned16(d->w_sf))) return OB_ERR_ALIGN;
+    for (int s = 0; s < d->S; ++s) {
+        if (!d->a[s] || !d->b[s]) return OB_ERR_NULL;
+        if (!aligned16(d->a[s]) || !aligned16(d->b[s])) return OB_ERR_ALIGN;
+        if (d->lora_fmt != OB_LORA_BF16 && (!d->sa[s] || !d->sb[s])) return OB_ERR_NULL;
+    }
+    if (d->lora_fmt == OB_LORA_NVFP4 && (!d->ag || !d->bg)) return OB_ERR_NULL;
+    return OB_OK;
+}
+
+int validate_batch(const ObLayer* l, const ObBatch* b) {
+    if (!l || !b) return OB_ERR_NULL;
+    if (b->M < 1 || b->M > l->d.max_m) return OB_ERR_BATCH;
+    if (!b->x || !b->y || !b->tok || !b->srt || !b->seg_n || !b->seg_start || !b->seg_ids) return OB_ERR_NULL;
+    if (!aligned16(b->x) || b->ldx < l->d.K || b->ldx % 8 != 0) return OB_ERR_ALIGN;
+    if ((reinterpret_cast<uintptr_t>(b->y) & 1u) || b->ldy < l->d.N) return OB_ERR_ALIGN;
+    return OB_OK;
+}
+
+int validate_workspace(const ObLayer* l, const void* ws, const ObWorkspaceShape* sh, int split1, int split2) {
+    if (!ws || !sh) return OB_ERR_NULL;
+    if ((reinterpret_cast<uintptr_t>(ws) & 1023u) != 0) return OB_ERR_ALIGN;
+    if (sh->max_m < l->d.max_m || sh->max_k < l->d.K || sh->max_n < l->d.N || sh->max_sr < l->d.S * l->d.R ||
+        sh->max_split1 < split1 || sh->max_split2 < split2)
+        return OB_ERR_WORKSPACE;
+    return OB_OK;
+}
+
+struct Resolved {
+    int tn, split1, split2, stages, m_tiles, k_per_split, pb;
+    uint32_t wait_ms;
+};
+
+int default_tn(int M) {
+    int tn = 16;
+    while (tn < M && tn < 256) tn *= 2;
+    return tn;
+}
+
+int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
+    const ObLayerDesc& d = l->d;
+    const int kblocks = (d.K + kBlockK - 1) / kBlockK;
+    r->tn = (cfg && cfg->tn) ? cfg->tn : default_tn(M);
+    if (!(r->tn == 16 || r->tn == 32 || r->tn == 64 || r->tn == 128 || r->tn == 256)) return OB_ERR_TILE;
+    r->m_tiles = (M + r->tn - 1) / r->tn;
+    int split2 = (cfg && cfg->split2) ? cfg->split2 : 0;
+    if (split2 == 0) {
+        split2 = r->m_tiles > 1 ? 1 : 148 / (l->n_tiles > 0 ? l->n_tiles : 1);
+        if (split2 < 1) split2 = 1;
+        if (split2 > 8) split2 = 8;
+        if (split2 > kblocks) split2 = kblocks;
+    }
+    if (split2 < 1 || split2 > 16 || split2 > kblocks || (split2 > 1 && r->m_tiles > 1)) return OB_ERR_TILE;
+    if ((long long)l->n_tiles * r->m_tiles > kCounterSlots) return OB_ERR_TOO_LARGE;
+    r->split2 = split2;
+    int split1 = (cfg && cfg->split1) ? cfg->split1 : 0;
+    if (split1 == 0) {
+        split1 = d.K / 512;
+        if (split1 < 1) split1 = 1;
+        if (split1 > 16) split1 = 16;
+        if (M > 512) split1 = 1;
+    }
+    if (split1 < 1 || split1 > 32) return OB_ERR_TILE;
+    r->split1 = split1;
+    r->k_per_split = (int)align_up((size_t)(d.K + split1 - 1) / split1, 256);
+    r->pb = M <= 32 ? 1 : 4;
+    const int rc = l->rc;
+    int stages = (cfg && cfg->stages) ? cfg->stages : 12;
+    if (stages < 2 || stages > 12) return OB_ERR_TILE;
+    while (stages > 2 && k2_fp8_smem_bytes(r->tn, stages, rc) > kSmemLimit) --stages;
+    if (k2_fp8_smem_bytes(r->tn, stages, rc) > kSmemLimit) return OB_ERR_TILE;
+    r->stages = stages;
+    if ((long long)(d.L < r->tn ? d.L : r->tn) * (d.R / rc) > kMaxLoraIters) return OB_ERR_TOO_LARGE;
+    r->wait_ms = (cfg && cfg->wait_ms > 0) ? (uint32_t)cfg->wait_ms : 2000u;
+    return OB_OK;
+}
+
+Meta meta_of(const ObBatch* b) { return Meta{b->tok, b->srt, b->seg_n, b->seg_start, b->seg_ids}; }
+
+int get_xmap(ObLayer* l, const void* xq, int rows, int tn, CUtensorMap* out) {
+    std::lock_guard<std::mutex> g(l->mu);
+    for (const XMap& m : l->xmaps)
+        if (m.base == xq && m.rows == rows && m.tn == tn) {
+            *out = m.tm;
+            return OB_OK;
+        }
+    XMap m;
+    m.base = xq;
+    m.rows = rows;
+    m.tn = tn;
+    int st = encode_2d(&m.tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, (uint64_t)l->d.K, (uint64_t)rows, (uint64_t)l->d.K,
+                       kBlockK, (uint32_t)tn);
+    if (st != OB_OK) return st;
+    l->xmaps.push_back(m);
+    *out = m.tm;
+    return OB_OK;
+}
+
+int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, cudaStream_t stream) {
+    const ObLayerDesc& d = l->d;
+    const WorkspaceLayout lay = workspace_layout(*sh);
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    K1Params p = {};
+    p.M = b->M; p.K = d.K; p.S = d.S; p.R = d.R; p.L = d.L;
+    p.lora_fmt = d.lora_fmt;
+    p.split1 = r.split1;
+    p.k_per_split = r.k_per_split;
+    p.n_quant_ctas = b->M;
+    p.pb = r.pb;
+    p.n_pblocks = (b->M + r.pb - 1) / r.pb;
+    p.units_per_block = d.S * (d.R / 8) * r.split1;
+    p.x = static_cast<const __nv_bfloat16*>(b->x);
+    p.ldx = b->ldx;
+    p.meta = meta_of(b);
+    for (int s = 0; s < d.S; ++s) { p.a[s] = d.a[s]; p.sa[s] = d.sa[s]; }
+    p.ag = d.ag;
+    p.xq = base + lay.xq;
+    p.sx = reinterpret_cast<float*>(base + lay.sx);
+    p.hp = reinterpret_cast<float*>(base + lay.hp);
+    p.max_m = sh->max_m;
+    const long long warps = (long long)p.n_pblocks * p.units_per_block;
+    const long long grid = p.n_quant_ctas + (warps + 7) / 8;
+    if (grid > 0x7fffffffLL) return OB_ERR_TOO_LARGE;
+    cudaError_t e = launch_k1_fp8(p, (int)grid, stream);
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
+
+int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, int pdl,
+                cudaStream_t stream) {
+    const ObLayerDesc& d = l->d;
+    const WorkspaceLayout lay = workspace_layout(*sh);
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    CUtensorMap tm_x;
+    int st = get_xmap(l, base + lay.xq, sh->max_m, r.tn, &tm_x);
+    if (st != OB_OK) return st;
+    K2Params p = {};
+    p.M = b->M; p.N = d.N; p.K = d.K; p.S = d.S; p.R = d.R; p.L = d.L;
+    for (int s = 0; s < OB_MAX_SLICES; ++s) p.widths[s] = s < d.S ? d.widths[s] : 0;
+    p.lora_fmt = d.lora_fmt;
+    p.tn = r.tn;
+    p.split2 = r.split2;
+    p.split1 = r.split1;
+    p.kblocks = (d.K + kBlockK - 1) / kBlockK;
+    p.stages = r.stages;
+    p.rc = l->rc;
+    p.max_m = sh->max_m;
+    p.wait_ms = r.wait_ms;
+    p.s_w = d.s_w;
+    p.sx = reinterpret_cast<const float*>(base + lay.sx);
+    p.hp = reinterpret_cast<const float*>(base + lay.hp);
+    p.meta = meta_of(b);
+    p.y = static_cast<__nv_bfloat16*>(b->y);
+    p.ldy = b->ldy;
+    p.part = reinterpret_cast<float*>(base + lay.part);
+    p.counters = reinterpret_cast<int32_t*>(base + lay.counters);
+    p.status = reinterpret_cast<int32_t*>(base + lay.status);
+    for (int s = 0; s < d.S; ++s) { p.b[s] = d.b[s]; p.sb[s] = d.sb[s]; }
+    p.bg = d.bg;
+    if (r.split2 > 1) {   // the partials of this call must fit the workspace's split-K region
+        const size_t need = (size_t)r.split2 * (size_t)l->n_tiles * (size_t)r.tn * kTileN * sizeof(float);
+        if (lay.part + need > lay.total) return OB_ERR_WORKSPACE;
+    }
+    dim3 grid((unsigned)l->n_tiles, (unsigned)r.split2, (unsigned)r.m_tiles);
+    cudaError_t e = launch_k2_fp8(p, l->tm_w, tm_x, l->tm_b, grid, k2_fp8_smem_bytes(r.tn, r.stages, l->rc), pdl, stream);
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
+
+int prepare_call(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const ObTileCfg* cfg, Resolved* r) {
+    int st = validate_batch(l, b);
+    if (st != OB_OK) return st;
+    if (l->d.base_fmt != OB_BASE_FP8 || l->d.lora_fmt != OB_LORA_BF16) return OB_ERR_FORMAT;
+    st = resolve_cfg(l, b->M, cfg, r);
+    if (st != OB_OK) return st;
+    return validate_workspace(l, ws, sh, r->split1, r->split2);
+}
+
+}  // namespace
+
+extern "C" {
+
+int ob_version(void) { return OB_ABI_VERSION; }
+
+const char* ob_status_string(int status) {
+    switch (status) {
+        case OB_OK: return "ok";
+        case OB_ERR_NULL: return "a required pointer is null";
+        case OB_ERR_SHAPE: return "unsupported layer shape";
+        case OB_ERR_ALIGN: return "pointer or pitch not aligned";
+        case OB_ERR_WORKSPACE: return "workspace too small";
+        case OB_ERR_TILE: return "invalid tile configuration";
+        case OB_ERR_FORMAT: return "format not served by this entry point";
+        case OB_ERR_BATCH: return "token count out of range";
+        case OB_ERR_DRIVER: return "CUDA driver entry points unavailable";
+        case OB_ERR_TOO_LARGE: return "request exceeds a fixed capacity";
+        default: break;
+    }
+    if (status >= 1000) return "CUDA driver error (status - 1000 is the CUresult)";
+    if (status > 0) return cudaGetErrorString((cudaError_t)status);
+    return "unknown status";
+}
+
+int ob_workspace_bytes(const ObWorkspaceShape* shape, size_t* bytes) {
+    if (!shape || !bytes) return OB_ERR_NULL;
+    if (shape->max_m < 1 || shape->max_k < 16 || shape->max_k % 16 != 0 || shape->max_n < 1 || shape->max_sr < 16 ||
+        shape->max_split1 < 1 || shape->max_split1 > 32 || shape->max_split2 < 1 || shape->max_split2 > 16)
+        return OB_ERR_SHAPE;
+    *bytes = workspace_layout(*shape).total;
+    return OB_OK;
+}
+
+int ob_workspace_offsets(const ObWorkspaceShape* shape, size_t out[7]) {
+    size_t total;
+    int st = ob_workspace_bytes(shape, &total);
+    if (st != OB_OK) return st;
+    if (!out) return OB_ERR_NULL;
+    const WorkspaceLayout l = workspace_layout(*shape);
+    out[0] = l.status; out[1] = l.counters; out[2] = l.sx; out[3] = l.xq; out[4] = l.xsf; out[5] = l.hp; out[6] = l.part;
+    return OB_OK;
+}
+
+int ob_layer_create(const ObLayerDesc* desc, ObLayer** out) {
+    if (!out) return OB_ERR_NULL;
+    *out = nullptr;
+    int st = validate_desc(desc);
+    if (st != OB_OK) return st;
+    ObLayer* l = new (std::nothrow) ObLayer();
+    if (!l) return (int)cudaErrorMemoryAllocation;
+    l->d = *desc;
+    l->rc = desc->R < 64 ? desc->R : 64;
+    l->n_tiles = 0;
+    for (int s = 0; s < desc->S; ++s) l->n_tiles += (desc->widths[s] + kTileN - 1) / kTileN;
+    if (desc->base_fmt == OB_BASE_FP8) {
+        st = encode_2d(&l->tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, desc->w_q, (uint64_t)desc->K, (uint64_t)desc->N,
+                       (uint64_t)desc->K, kBlockK, kTileN);
+        if (st == OB_OK && desc->lora_fmt == OB_LORA_BF16) {
+            for (int s = 0; s < OB_MAX_SLICES && st == OB_OK; ++s) {
+                const int ss = s < desc->S ? s : 0;   // unused slots repeat slice 0 so every kernel argument is a valid map
+                st = encode_2d(&l->tm_b[s], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, desc->b[ss], (uint64_t)desc->R,
+                               (uint64_t)desc->L * (uint64_t)desc->widths[ss], (uint64_t)desc->R * 2, (uint32_t)l->rc, kTileN);
+            }
+        }
+    }
+    if (st != OB_OK) {
+        delete l;
+        return st;
+    }
+    *out = l;
+    return OB_OK;
+}
+
+int ob_layer_destroy(ObLayer* layer) {
+    delete layer;
+    return OB_OK;
+}
+
+int ob_k1_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape, const ObTileCfg* cfg,
+              void* cuda_stream) {
+    Resolved r;
+    int st = prepare_call(layer, batch, workspace, shape, cfg, &r);
+    if (st != OB_OK) return st;
+    return k1_fp8_impl(layer, batch, workspace, shape, r, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int ob_k2_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape, const ObTileCfg* cfg,
+              int pdl, void* cuda_stream) {
+    Resolved r;
+    int st = prepare_call(layer, batch, workspace, shape, cfg, &r);
+    if (st != OB_OK) return st;
+    return k2_fp8_impl(layer, batch, workspace, shape, r, pdl, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int ob_chain_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape, const ObTileCfg* cfg,
+                 void* cuda_stream) {
+    Resolved r;
+    int st = prepare_call(layer, batch, workspace, shape, cfg, &r);
+    if (st != OB_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    st = k1_fp8_impl(layer, batch, workspace, shape, r, stream);
+    if (st != OB_OK) return st;
+    return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
+}
+
+int ob_segment_index(const int32_t* token_lora, int32_t M, int32_t L, int32_t* tok, int32_t* srt, int32_t* seg_n,
+                     int32_t* seg_start, int32_t* seg_ids, void* cuda_stream) {
+    if (!token_lora || !tok || !srt || !seg_n || !seg_start || !seg_ids) return OB_ERR_NULL;
+    if (M < 1 || L < 1 || L > 1023) return OB_ERR_SHAPE;
+    cudaError_t e = launch_segment_index(token_lora, M, L, tok, srt, seg_n, seg_start, seg_ids,
+                                         static_cast<cudaStream_t>(cuda_stream));
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
+
+int ob_read_status(void* workspace, int32_t* host_out, void* cuda_stream) {
+    if (!workspace || !host_out) return OB_ERR_NULL;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    cudaError_t e = cudaMemcpyAsync(host_out, workspace, sizeof(int32_t) * OB_STATUS_WORDS, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(workspace, 0, sizeof(int32_t) * OB_STATUS_WORDS, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
+
+}  // extern "C"

@@ -1,0 +1,134 @@
+// Shared between the kernels and the C-ABI: the workspace layout, kernel parameter blocks and the position rule.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/onebase_b200.h"
+
+namespace ob {
+
+constexpr int kTileN = 128;          // output features per GEMM tile (rows of W; the MMA's M)
+constexpr int kBlockK = 128;         // bytes of K per ring stage row (one 128-byte swizzle row)
+constexpr int kMaxLoraIters = 512;   // capacity of a CTA's list of (segment, rank chunk) expand steps
+constexpr int kCounterSlots = 4096;  // split-K arrival counters in the workspace
+
+__host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Offsets of the regions inside the shared workspace (bytes).  All regions are 1024-byte aligned.
+struct WorkspaceLayout {
+    size_t status;     // int32 [OB_STATUS_WORDS]
+    size_t counters;   // int32 [kCounterSlots]   zero between launches
+    size_t sx;         // fp32  [max_m]           per-position activation scale
+    size_t xq;         // bytes [max_m * max_k]   quantized activations, row pitch = the calling layer's K (FP8) or K/2
+    size_t xsf;        // bytes [max_m * max_k/16] NVFP4 activation block scales
+    size_t hp;         // fp32  [max_split1 * max_sr * max_m]  shrink partials [split][slice][position][rank]
+    size_t part;       // fp32  [max_split2 * token tile * (max_n rounded to tiles)]  GEMM split-K partials
+    size_t total;
+};
+
+__host__ __device__ inline WorkspaceLayout workspace_layout(const ObWorkspaceShape& s) {
+    WorkspaceLayout l;
+    size_t off = 0;
+    l.status = off;   off = align_up(off + sizeof(int32_t) * OB_STATUS_WORDS, 1024);
+    l.counters = off; off = align_up(off + sizeof(int32_t) * kCounterSlots, 1024);
+    l.sx = off;       off = align_up(off + sizeof(float) * (size_t)s.max_m, 1024);
+    l.xq = off;       off = align_up(off + (size_t)s.max_m * (size_t)s.max_k, 1024);
+    l.xsf = off;      off = align_up(off + (size_t)s.max_m * (size_t)(s.max_k / 16 + 16), 1024);
+    l.hp = off;       off = align_up(off + sizeof(float) * (size_t)s.max_split1 * (size_t)s.max_sr * (size_t)s.max_m, 1024);
+    const size_t n_pad = align_up((size_t)s.max_n, kTileN) + (size_t)OB_MAX_SLICES * kTileN;
+    size_t m_pad = 16;                                        // split-K serves one token tile: min(max_m, 256) tokens
+    while (m_pad < (size_t)s.max_m && m_pad < 256) m_pad *= 2;
+    l.part = off;     off = align_up(off + sizeof(float) * (s.max_split2 > 1 ? (size_t)s.max_split2 * m_pad * n_pad : 0), 1024);
+    l.total = off;
+    return l;
+}
+
+// vLLM's five metadata tensors.
+struct Meta {
+    const int32_t* tok;
+    const int32_t* srt;
+    const int32_t* seg_n;
+    const int32_t* seg_start;
+    const int32_t* seg_ids;
+};
+
+enum : int { kLoraBf16 = OB_LORA_BF16, kLoraFp8 = OB_LORA_FP8, kLoraNvfp4 = OB_LORA_NVFP4 };
+
+struct K1Params {
+    int M, K, S, R, L;
+    int lora_fmt;
+    int split1;            // K splits of the shrink
+    int k_per_split;       // elements of K per split (multiple of the warp's K step)
+    int n_quant_ctas;      // leading CTAs that quantize (one position each)
+    int pb;                // sorted positions per shrink warp: 1 (decode) or 4
+    int n_pblocks;         // ceil(M / pb)
+    int units_per_block;   // shrink warps per position block: S * (R / 8) * split1
+    const __nv_bfloat16* x;
+    int64_t ldx;
+    Meta meta;
+    const void* a[OB_MAX_SLICES];
+    const void* sa[OB_MAX_SLICES];
+    const float* ag;
+    uint8_t* xq;           // [M, K] codes at sorted positions
+    float* sx;             // [M]
+    float* hp;             // [split1][S][max_m][R]
+    int max_m;
+};
+
+struct K2Params {
+    int M, N, K, S, R, L;
+    int widths[OB_MAX_SLICES];
+    int lora_fmt;
+    int tn;                // tokens per tile (MMA N)
+    int split2;            // GEMM split-K
+    int split1;            // shrink partials to sum
+    int kblocks;           // ceil(K / 128)
+    int stages;
+    int rc;                // rank chunk per expand step: min(R, 64)
+    int max_m;
+    uint32_t wait_ms;
+    const float* s_w;
+    const float* sx;
+    const float* hp;
+    Meta meta;
+    __nv_bfloat16* y;
+    int64_t ldy;
+    float* part;
+    int32_t* counters;
+    int32_t* status;
+    const void* b[OB_MAX_SLICES];
+    const void* sb[OB_MAX_SLICES];
+    const float* bg;
+};
+
+// Warp-wide: n_all = sum of seg_n, n_ad = sum of seg_n over segments whose slot id >= 0 (L+1 segments).
+__device__ __forceinline__ void segment_totals(const Meta& m, int L, int lane, int& n_all, int& n_ad) {
+    int a = 0, d = 0;
+    for (int i = lane; i <= L; i += 32) {
+        const int c = m.seg_n[i];
+        a += c;
+        d += (m.seg_ids[i] >= 0) ? c : 0;
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        a += __shfl_xor_sync(0xffffffffu, a, o);
+        d += __shfl_xor_sync(0xffffffffu, d, o);
+    }
+    n_all = a;
+    n_ad = d;
+}
+
+// Row of x / y that tile position p stands for: the adapter-sorted order when the batch has an adapter and p is a real
+// token, else the position itself (no-adapter batches, CUDA-graph padding).  Indices are clamped as a last guard.
+__device__ __forceinline__ int position_row(const Meta& m, int p, int M, int n_all, int n_ad) {
+    if (n_ad > 0 && p < n_all) {
+        int r = m.srt[p];
+        return r < 0 ? 0 : (r > M - 1 ? M - 1 : r);
+    }
+    return p;
+}
+
+}  // namespace ob
