@@ -1,0 +1,295 @@
+"""Benchmark of the fused FP8 + multi-tenant LoRA decoder layer (the decode chain K1 -> K2 per projection).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--m M] [--impl reference]
+
+Workload (N = 1): one Qwen3-8B-shaped decoder layer, FP8 per-tensor base (qkv 4096->6144, o 4096->4096, gate_up
+4096->2x12288, down 12288->4096), decode batch M = 32 tokens, 32 bf16 tenants of rank 64 with slot ids uniform random
+per token, the four projections' K1 -> K2 chains captured in ONE CUDA graph; a "step" is one replay of that graph.
+Synthetic data with the shapes and distributions of that configuration (random-init weights; no dataset).
+Timing: CUDA events around each replay on the replay's stream, a 256 MB write flushes L2 before every replay (outside
+the timed events), W >= 3 warm-up replays, max over ranks.  Prints ONE JSON line (rank 0).
+
+`value`   tokens/s through the layer with inputs resident in HBM (M / mean replay time).
+`e2e`     the same through the public op call with HOST buffers: every step copies the four projections' activations from
+          pinned host memory, runs the layer, and copies the four outputs back (copies inside the timed region).
+`roofline` for the dominant kernel (K2 of gate_up): algorithmic bytes (W + x + the distinct tenants' B + y) / its
+          CUDA-event time when launched alone, against the measured HBM copy bandwidth.
+`cpu_baseline` the CPU oracle (a torch port of the reference's dequantize-and-matmul path) on this host's cores.
+`--impl reference` times only that CPU path and prints the same line shape with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+PROJECTIONS = {"qkv": (4096, (4096, 1024, 1024)), "o": (4096, (4096,)), "gate_up": (4096, (12288, 12288)),
+               "down": (12288, (4096,))}
+L_SLOTS, RANK = 32, 64
+METRIC = "decode tok/s at 32 tenants through one fused FP8+LoRA decoder layer (layer us and HBM roofline % alongside)"
+
+
+def measured_peaks() -> tuple[float, str]:
+    f = ROOT / "MEASURED_PEAKS.json"
+    if f.exists():
+        return float(json.loads(f.read_text())["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.stop_flag, self.max_mhz = index, [], set(), False, None
+
+    def run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            names = {nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap", nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                     nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+                     nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown"}
+            while not self.stop_flag:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for bit, name in names.items():
+                    if r & bit:
+                        self.reasons.add(name)
+                time.sleep(0.002)
+        except Exception as e:   # noqa: BLE001 - clocks are reported as unavailable, the measurement itself stands
+            self.reasons.add(f"nvml-unavailable:{type(e).__name__}")
+
+    def result(self) -> dict:
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(s)}
+
+
+def physical_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except (ValueError, IndexError):
+            return local
+    return local
+
+
+def make_layer(M: int, device, seed: int = 0, tp: int = 1, rank: int = 0):
+    """Random-init layer with the configuration's distributions, generated on the device (values do not matter for
+    timing; the parity tests use CPU-drawn inputs).  Returns {proj: (op, x, meta)} plus the ids."""
+    from onebase_b200.kernels.fp8_lora_vllm import VllmFusedFP8LoRA
+    g = torch.Generator(device=device).manual_seed(seed)
+    ids = torch.randint(0, L_SLOTS, (M,), generator=torch.Generator().manual_seed(seed), dtype=torch.int32)
+    from onebase_b200.metadata import KernelMeta
+    km = KernelMeta.make(L_SLOTS, M, device)
+    km.prepare_tensors(ids.to(device))
+    meta = km.meta_args(M)
+    layer = {}
+    for name, (K, widths) in PROJECTIONS.items():
+        N = sum(widths)
+        w = torch.randn(N, K, device=device, generator=g) * 0.02
+        s_w = (w.abs().max() / 448.0).reshape(1).float()
+        w_q = (w / s_w).to(torch.float8_e4m3fn)
+        del w
+        a_st = tuple(((torch.rand(L_SLOTS, 1, RANK, K, device=device, generator=g) * 2 - 1) / K ** 0.5).to(torch.bfloat16)
+                     for _ in widths)
+        b_st = tuple((torch.randn(L_SLOTS, 1, n, RANK, device=device, generator=g) * 0.01).to(torch.bfloat16) for n in widths)
+        x = torch.randn(M, K, device=device, generator=g).to(torch.bfloat16)
+        op = VllmFusedFP8LoRA(w_q, s_w, a_st, b_st, max_m=M)
+        layer[name] = (op, x, torch.empty(M, N, dtype=torch.bfloat16, device=device))
+    return layer, meta, ids
+
+
+def layer_bytes(M: int, distinct: int) -> dict:
+    """Algorithmic bytes per projection: W + x + the distinct tenants' A and B + y (bf16 adapters)."""
+    out = {}
+    for name, (K, widths) in PROJECTIONS.items():
+        N, S = sum(widths), len(widths)
+        out[name] = {"w": N * K, "x": M * K * 2, "y": M * N * 2, "a": distinct * S * RANK * K * 2, "b": distinct * N * RANK * 2}
+        out[name]["total"] = sum(out[name].values())
+    return out
+
+
+def run_layer(layer, meta):
+    for name in ("qkv", "o", "gate_up", "down"):
+        op, x, y = layer[name]
+        op(x, meta, out=y)
+
+
+def time_events(fn, steps: int, warmup: int, flush) -> list[float]:
+    for _ in range(warmup):
+        flush.fill_(1)
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(steps):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return ts   # milliseconds
+
+
+def cpu_layer_seconds(M: int, reps: int, threads: int) -> tuple[float, str]:
+    """The CPU oracle on one layer (all four projections), same shapes and distributions; median seconds per pass."""
+    from oracle import configs, fp8 as ofp8
+    torch.set_num_threads(threads)
+    ds = {}
+    for i, (name, (K, widths)) in enumerate(PROJECTIONS.items()):
+        d = configs.with_fp8_base(configs.draw(K, widths, RANK, L_SLOTS, M, seed=i, ids_low=0))
+        d["A"], d["B"] = ofp8.stack_slices(d["a_stacked"], d["b_stacked"])
+        ds[name] = d
+    ts = []
+    for r in range(reps + 1):
+        t0 = time.perf_counter()
+        for name, d in ds.items():
+            ofp8.fused_projection(d["x"], d["ids"], d["w_q"], d["s_w"], d["A"], d["B"], d["widths"])
+        if r:
+            ts.append(time.perf_counter() - t0)
+    return statistics.median(ts), f"one Qwen3-8B layer (4 projections), M={M}, 32 slots rank 64, {reps} timed passes after 1 warm-up"
+
+
+def reference_arm(args, rank: int) -> None:
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    M = args.m
+    steps = max(1, min(args.steps, 3))
+    sec, sample = cpu_layer_seconds(M, steps, threads)
+    value = M / sec
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps,
+            "warmup": 1, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp32 (CPU dequantize-and-matmul)", "data": "synthetic",
+            "config": {"workload": f"Qwen3-8B decoder layer, FP8 base, decode M={M}, 32 tenants rank 64"},
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--m", type=int, default=32, help="decode batch (tokens per step)")
+    ap.add_argument("--impl", default="onebase_b200")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        reference_arm(args, rank)
+        return
+    if world > 1:
+        from onebase_b200.tp import bench_tp
+        bench_tp(args, rank, world, local, METRIC)
+        return
+
+    warmup = max(3, args.warmup)
+    M = args.m
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    layer, meta, ids = make_layer(M, dev)
+    distinct = int(torch.unique(ids).numel())
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    run_layer(layer, meta)                                   # scratch reaches its final size before capture
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        run_layer(layer, meta)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run_layer(layer, meta)
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(physical_index(local))
+    sampler.start()
+    ts = time_events(graph.replay, args.steps, warmup, flush)
+    ms = statistics.fmean(ts)
+
+    # per-projection chain time and the dominant kernel (K2 of gate_up) alone
+    per_proj = {}
+    for name in PROJECTIONS:
+        op, x, y = layer[name]
+        g1 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g1):
+            op(x, meta, out=y)
+        per_proj[name] = statistics.median(time_events(g1.replay, 30, 5, flush)) * 1e3
+    op, x, y = layer["gate_up"]
+    op(x, meta, out=y)
+    k2_ms = statistics.fmean(time_events(lambda: op(x, meta, out=y, shrink=False, pdl=False), 50, 5, flush))
+    k1_ms = statistics.fmean(time_events(lambda: op(x, meta, out=y, gemm=False), 50, 5, flush))
+
+    # end to end: host buffers in, host buffers out, copies inside the timed region
+    host_x = {n: layer[n][1].cpu().pin_memory() for n in PROJECTIONS}
+    host_y = {n: torch.empty(layer[n][2].shape, dtype=torch.bfloat16).pin_memory() for n in PROJECTIONS}
+    h2d = sum(t.numel() * 2 for t in host_x.values())
+    d2h = sum(t.numel() * 2 for t in host_y.values())
+
+    def e2e_step():
+        for n in PROJECTIONS:
+            layer[n][1].copy_(host_x[n], non_blocking=True)
+        graph.replay()
+        for n in PROJECTIONS:
+            host_y[n].copy_(layer[n][2], non_blocking=True)
+
+    e2e_ms = statistics.fmean(time_events(e2e_step, args.steps, warmup, flush))
+    sampler.stop_flag = True
+    sampler.join(timeout=2)
+    status = layer["qkv"][0].scratch.status()
+    assert status[0] == 0, f"device status {status[:8]}"
+
+    by = layer_bytes(M, distinct)
+    total_bytes = sum(v["total"] for v in by.values())
+    peak, peak_kind = measured_peaks()
+    gu = by["gate_up"]
+    k2_bytes = gu["w"] + gu["x"] + gu["b"] + gu["y"]
+    k2_gbs = k2_bytes / (k2_ms * 1e-3) / 1e9
+    line = {
+        "metric": METRIC, "value": M / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3",
+        "data": "synthetic",
+        "config": {"workload": f"Qwen3-8B decoder layer (qkv, o, gate_up, down), FP8 per-tensor base, decode M={M}, "
+                               f"32 bf16 tenants rank 64 ({distinct} distinct in the batch), K1->K2 PDL chains in one CUDA graph",
+                   "l2": "flushed by a 256 MB write before every timed replay"},
+        "layer_us": ms * 1e3, "layer_us_median": statistics.median(ts) * 1e3, "projection_us": per_proj,
+        "layer_bytes": total_bytes, "layer_gbs": total_bytes / (ms * 1e-3) / 1e9,
+        "layer_frac_of_peak": total_bytes / (ms * 1e-3) / 1e9 / peak,
+        "roofline": {"kernel": "k2_fp8_kernel (gate_up, launched alone)", "bound": "hbm", "achieved": k2_gbs, "peak": peak,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": k2_gbs / peak, "traffic": None, "bytes": k2_bytes,
+                     "us": k2_ms * 1e3, "k1_us_alone": k1_ms * 1e3},
+        "e2e": {"value": M / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": e2e_ms},
+        "gpu_launches": 8 * args.steps,
+        "clocks": sampler.result(),
+    }
+    if not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        sec, sample = cpu_layer_seconds(M, 2, threads)
+        line["cpu_baseline"] = {"value": M / sec, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()
