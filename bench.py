@@ -148,6 +148,28 @@ def time_events(fn, steps: int, warmup: int, flush) -> list[float]:
     return ts   # milliseconds
 
 
+def profile_case(args, dev) -> None:
+    """One projection, K1 and K2 launched separately (no graph, no PDL) so that a profiler can pick either kernel."""
+    global PROJECTIONS
+    keep = {args.profile: PROJECTIONS[args.profile]}
+    saved, PROJECTIONS = PROJECTIONS, keep
+    try:
+        layer, meta, ids = make_layer(args.m, dev)
+    finally:
+        PROJECTIONS = saved
+    op, x, y = layer[args.profile]
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    op(x, meta, out=y)
+    torch.cuda.synchronize()
+    k1 = time_events(lambda: op(x, meta, out=y, gemm=False), args.steps, 2, flush)
+    k2 = time_events(lambda: op(x, meta, out=y, shrink=False, pdl=False), args.steps, 2, flush)
+    chain = time_events(lambda: op(x, meta, out=y), args.steps, 2, flush)
+    by = layer_bytes(args.m, int(torch.unique(ids).numel()))[args.profile]
+    print(json.dumps({"profile": args.profile, "M": args.m, "distinct": int(torch.unique(ids).numel()),
+                      "k1_us": statistics.fmean(k1) * 1e3, "k2_us": statistics.fmean(k2) * 1e3,
+                      "chain_us": statistics.fmean(chain) * 1e3, "bytes": by}))
+
+
 def cpu_layer_seconds(M: int, reps: int, threads: int) -> tuple[float, str]:
     """The CPU oracle on one layer (all four projections), same shapes and distributions; median seconds per pass."""
     from oracle import configs, fp8 as ofp8
@@ -192,6 +214,9 @@ def main() -> None:
     ap.add_argument("--m", type=int, default=32, help="decode batch (tokens per step)")
     ap.add_argument("--impl", default="onebase_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--profile", default=None, metavar="PROJ",
+                    help="small profiling case: build only this projection (qkv|o|gate_up|down) and launch K1 and K2 "
+                         "separately --steps times each (for ncu captures); prints their mean times")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -208,6 +233,9 @@ def main() -> None:
     M = args.m
     dev = torch.device(f"cuda:{local}")
     torch.cuda.set_device(dev)
+    if args.profile:
+        profile_case(args, dev)
+        return
     layer, meta, ids = make_layer(M, dev)
     distinct = int(torch.unique(ids).numel())
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
