@@ -163,11 +163,24 @@ def profile_case(args, dev) -> None:
     torch.cuda.synchronize()
     k1 = time_events(lambda: op(x, meta, out=y, gemm=False), args.steps, 2, flush)
     k2 = time_events(lambda: op(x, meta, out=y, shrink=False, pdl=False), args.steps, 2, flush)
-    chain = time_events(lambda: op(x, meta, out=y), args.steps, 2, flush)
+    chain = time_events(graph_of(lambda: op(x, meta, out=y)).replay, args.steps, 2, flush)
     by = layer_bytes(args.m, int(torch.unique(ids).numel()))[args.profile]
     print(json.dumps({"profile": args.profile, "M": args.m, "distinct": int(torch.unique(ids).numel()),
                       "k1_us": statistics.fmean(k1) * 1e3, "k2_us": statistics.fmean(k2) * 1e3,
                       "chain_us": statistics.fmean(chain) * 1e3, "bytes": by}))
+
+
+def graph_of(fn) -> "torch.cuda.CUDAGraph":
+    """Capture fn's launches in a CUDA graph (replays carry no host launch latency)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return g
 
 
 def cpu_layer_seconds(M: int, reps: int, threads: int) -> tuple[float, str]:
@@ -266,8 +279,8 @@ def main() -> None:
         per_proj[name] = statistics.median(time_events(g1.replay, 30, 5, flush)) * 1e3
     op, x, y = layer["gate_up"]
     op(x, meta, out=y)
-    k2_ms = statistics.fmean(time_events(lambda: op(x, meta, out=y, shrink=False, pdl=False), 50, 5, flush))
-    k1_ms = statistics.fmean(time_events(lambda: op(x, meta, out=y, gemm=False), 50, 5, flush))
+    k2_ms = statistics.fmean(time_events(graph_of(lambda: op(x, meta, out=y, shrink=False, pdl=False)).replay, 50, 5, flush))
+    k1_ms = statistics.fmean(time_events(graph_of(lambda: op(x, meta, out=y, gemm=False)).replay, 50, 5, flush))
 
     # end to end: host buffers in, host buffers out, copies inside the timed region
     host_x = {n: layer[n][1].cpu().pin_memory() for n in PROJECTIONS}

@@ -13,7 +13,9 @@
 //     reduced with a transposing butterfly -- 31 shuffles for 32 sums, lane i ends up with sum i -- and written as
 //     split-K partials hp[split][slice][position][rank] (fp32), which K2 adds in split order (deterministic).
 //     Computes what lowbit_lora/kernels/fp8_lora_vllm.py:72-120 computes per adapter segment.
-// The kernel starts with griddepcontrol.launch_dependents so that a dependent K2 may begin streaming W at once.
+// The kernel starts with griddepcontrol.launch_dependents so that a dependent K2 may begin streaming W at once, and it
+// may itself be launched as a programmatic dependent of the preceding kernel: it reads the segment index and requests
+// its first block of A before griddepcontrol.wait, and touches x and the scratch only after it.
 #include "ob_common.cuh"
 #include "ob_ptx.cuh"
 
@@ -52,6 +54,7 @@ __device__ void quantize_position(const K1Params& p, int pos) {
     segment_totals(p.meta, p.L, lane, n_all, n_ad);
     n_all = min(n_all, p.M);
     const int row = position_row(p.meta, pos, p.M, n_all, n_ad);
+    griddep_wait();                                   // x comes from the preceding kernel; the scratch may still be read by it
     const uint4* xr = reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.ldx);
     const int nvec = p.K >> 3;
     uint4 cache[kQuantCache];
@@ -107,50 +110,52 @@ __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
     f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
 }
 
-// One pass of a warp: 8 rank rows [k0, k1) of adapter `lora`, slice s, times the `nt` (<= 4) tokens at sorted positions
-// pos0 .. pos0+nt-1; writes the split-K partial hp[j][s][pos][rg*8 .. +8].  bf16 adapters.
+__device__ __forceinline__ void load_a8(uint4 (&av)[8], const __nv_bfloat16* a, int K, int k, bool act) {
+#pragma unroll
+    for (int r = 0; r < 8; ++r) av[r] = act ? __ldg(reinterpret_cast<const uint4*>(a + (size_t)r * K + k)) : make_uint4(0u, 0u, 0u, 0u);
+}
+
+// One pass of a warp: 8 rank rows [k0, k1) of adapter `lora`, slice s, times the `nt` (<= 4) tokens whose x rows are
+// rows[0..nt); writes the split-K partial hp[j][s][pos0 + t][rg*8 .. +8].  bf16 adapters.  The first block of A is
+// requested before the wait on the preceding kernel (A is static); x is read and hp written only after it.
 __device__ __forceinline__ void shrink_pass_bf16(const K1Params& p, int lora, int s, int rg, int j, int k0, int k1, int pos0,
-                                                 int nt, int lane) {
+                                                 const int* rows, int nt, int lane) {
     const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(p.a[s]) + ((size_t)lora * p.R + (size_t)rg * 8) * p.K;
+    uint4 av[8];
+    load_a8(av, a, p.K, k0 + lane * 8, k0 + lane * 8 < k1);
+    griddep_wait();
     const __nv_bfloat16* xrow[4];
 #pragma unroll
-    for (int t = 0; t < 4; ++t) {
-        int r = (t < nt) ? p.meta.srt[pos0 + t] : 0;
-        r = r < 0 ? 0 : (r > p.M - 1 ? p.M - 1 : r);
-        xrow[t] = p.x + (int64_t)r * p.ldx;
-    }
+    for (int t = 0; t < 4; ++t) xrow[t] = p.x + (int64_t)rows[t < nt ? t : 0] * p.ldx;
     float acc[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
     for (int kk = k0; kk < k1; kk += 256) {
         const int k = kk + lane * 8;
-        if (k < k1) {
-            uint4 av[8];
+        const bool act = k < k1;
+        float xf[4][8];
 #pragma unroll
-            for (int r = 0; r < 8; ++r) av[r] = __ldg(reinterpret_cast<const uint4*>(a + (size_t)r * p.K + k));
-            float xf[4][8];
+        for (int t = 0; t < 4; ++t) {
+            if (t < nt && act) {
+                unpack8(__ldg(reinterpret_cast<const uint4*>(xrow[t] + k)), xf[t]);
+            } else {
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                if (t < nt) {
-                    unpack8(__ldg(reinterpret_cast<const uint4*>(xrow[t] + k)), xf[t]);
-                } else {
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) xf[t][e] = 0.0f;
-                }
-            }
-#pragma unroll
-            for (int r = 0; r < 8; ++r) {
-                float af[8];
-                unpack8(av[r], af);
-#pragma unroll
-                for (int t = 0; t < 4; ++t) {
-                    float sacc = acc[r * 4 + t];
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) sacc = fmaf(af[e], xf[t][e], sacc);
-                    acc[r * 4 + t] = sacc;
-                }
+                for (int e = 0; e < 8; ++e) xf[t][e] = 0.0f;
             }
         }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            float af[8];
+            unpack8(av[r], af);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                float sacc = acc[r * 4 + t];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sacc = fmaf(af[e], xf[t][e], sacc);
+                acc[r * 4 + t] = sacc;
+            }
+        }
+        if (kk + 256 < k1) load_a8(av, a, p.K, k + 256, k + 256 < k1);
     }
     const float total = transpose_reduce32(acc, lane);
     const int r = lane >> 2, t = lane & 3;
@@ -158,14 +163,20 @@ __device__ __forceinline__ void shrink_pass_bf16(const K1Params& p, int lora, in
 }
 
 // One warp: block `pb` of p.pb consecutive sorted positions, unit `u` -> (slice, group of 8 rank rows, K split).
-// The warp looks up which segment each of its positions lies in (one warp-wide read of the segment index) and runs
-// one pass per run of positions that share an adapter.
+// The warp looks up which segment each of its positions lies in (one warp-wide read of the segment index, together with
+// the positions' token rows) and runs one pass per run of positions that share an adapter.
 __device__ void shrink_unit(const K1Params& p, int pb, int u, int lane) {
+    const int p0 = pb * p.pb;
+    int rows[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+        int r = (q < p.pb && p0 + q < p.M) ? p.meta.srt[p0 + q] : 0;
+        rows[q] = r < 0 ? 0 : (r > p.M - 1 ? p.M - 1 : r);
+    }
     int n_all, n_ad;
     segment_totals(p.meta, p.L, lane, n_all, n_ad);
     n_all = min(n_all, p.M);
     if (n_ad <= 0) return;
-    const int p0 = pb * p.pb;
     const int np = min(p.pb, n_all - p0);
     if (np <= 0) return;
     int lora_of[4] = {-1, -1, -1, -1};
@@ -195,7 +206,7 @@ __device__ void shrink_unit(const K1Params& p, int pb, int u, int lane) {
         const int lora = lora_of[q];
         int nt = 1;
         while (q + nt < np && lora_of[q + nt] == lora) ++nt;
-        if (lora >= 0) shrink_pass_bf16(p, lora, s, rg, j, k0, k1, p0 + q, nt, lane);
+        if (lora >= 0) shrink_pass_bf16(p, lora, s, rg, j, k0, k1, p0 + q, rows + q, nt, lane);
         q += nt;
     }
 }
@@ -213,9 +224,18 @@ __global__ void __launch_bounds__(kK1Threads) k1_fp8_kernel(const K1Params p) {
     shrink_unit(p, pb, w % p.units_per_block, lane);
 }
 
-cudaError_t launch_k1_fp8(const K1Params& p, int grid, cudaStream_t stream) {
-    k1_fp8_kernel<<<grid, kK1Threads, 0, stream>>>(p);
-    return cudaGetLastError();
+cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kK1Threads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, k1_fp8_kernel, p);
 }
 
 }  // namespace ob

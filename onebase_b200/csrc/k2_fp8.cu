@@ -11,11 +11,15 @@
 //   warp 2   TMA producer of the x_q tiles [tokens x 128 B]; waits for K1 (griddepcontrol.wait) first.
 //   warp 1   allocates TMEM and issues tcgen05.mma: kind::f8f6f4 (e4m3 x e4m3, fp32) into accumulator 0 for the base
 //            GEMM, kind::f16 (bf16) into accumulator 1 for the LoRA expand; tcgen05.commit releases ring slots.
-//   warps 4-7  read vLLM's segment index, list the (segment, rank chunk) expand steps of this tile, and after K1 build each
-//            step's masked H tile (bf16(sum of K1's split-K partials) on the segment's token rows, zero elsewhere) in
-//            shared memory in the UMMA layout; finally the epilogue: tcgen05.ld both accumulators, scale, add, and store
-//            bf16 rows scattered back through the sort.  With split-K > 1 they write fp32 partials instead and the last
-//            CTA to arrive adds them in split order (deterministic) and resets the arrival counter.
+//   warps 4-7  read vLLM's segment index and list the (segment, rank chunk) expand steps of this tile.  After K1:
+//            * token tiles of 16 / 32 (decode): they sum K1's split-K partials once into a bf16 h table in shared memory and
+//              do the expand themselves on the CUDA cores, straight from the B tiles as these arrive in the ring -- thread
+//              n keeps its 32 token sums in registers, no per-step tile building, nothing on the tensor pipe's path;
+//            * larger token tiles (prefill): they build each step's masked H tile (the tenant's rows, zero elsewhere) in the
+//              UMMA layout and warp 1 issues the bf16 MMAs into accumulator 1.
+//            Finally the epilogue: tcgen05.ld, s_x*s_w*acc0 + LoRA, bf16 rows scattered back through the sort.  With
+//            split-K > 1 they write fp32 partials instead and the last CTA to arrive adds them in split order
+//            (deterministic) and resets the arrival counter.
 //
 // What it computes is lowbit_lora/kernels/fp8_lora_vllm.py:123-284 (`_gemm_vllm`, BASE=True) and the decode-chain GEMM
 // lowbit_lora/kernels/fp8_lora_pdl.py:324-495; positions, padding and stale metadata follow fp8_lora_vllm.py:147-163.
@@ -28,12 +32,12 @@ namespace ob {
 
 constexpr int kK2Threads = 256;
 constexpr int kWTileBytes = kTileN * kBlockK;   // 16 KB
-constexpr int kCtrlBytes = 16384;
+constexpr int kCtrlBytes = 8192;
 
 struct LoraStep {
-    int lora;     // adapter slot
-    int lo, hi;   // tile-local token rows [lo, hi) of the segment
-    int chunk;    // rank chunk index
+    uint16_t lora;    // adapter slot
+    uint16_t chunk;   // rank chunk index
+    uint16_t lo, hi;  // tile-local token rows [lo, hi) of the segment
 };
 
 struct K2Ctrl {
@@ -72,7 +76,7 @@ __device__ __forceinline__ void record_timeout(const K2Params& p, K2Ctrl* c, int
         break;                                            \
     }
 
-__global__ void __launch_bounds__(kK2Threads, 1)
+__global__ void __launch_bounds__(kK2Threads, 2)
 k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
               const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
               const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_b3) {
@@ -80,12 +84,14 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tn = p.tn;
     const int stage_bytes = kWTileBytes + tn * kBlockK;
+    const bool cc = p.expand_cc != 0;                          // expand on the CUDA cores (token tiles of 16 / 32)
     const int h_bytes = (int)align_up((size_t)tn * p.rc * 2, 1024);
     uint8_t* ring = smem;
-    uint8_t* hbuf = ring + (size_t)p.stages * stage_bytes;
-    K2Ctrl* ctrl = reinterpret_cast<K2Ctrl*>(hbuf + 2 * h_bytes);
+    uint8_t* hbuf = ring + (size_t)p.stages * stage_bytes;    // cc: the bf16 h table [tn][R]; else two masked H tiles
+    K2Ctrl* ctrl = reinterpret_cast<K2Ctrl*>(hbuf + (cc ? align_up((size_t)tn * p.R * 2, 1024) : 2 * (size_t)h_bytes));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    griddep_launch_dependents();                               // the next kernel in the stream may start its own prologue
     const uint64_t limit_ns = (uint64_t)p.wait_ms * 1000000ull;
 
     // ---- tile coordinates: blockIdx.x walks the slices' 128-wide tiles, .y the K splits, .z the token tiles
@@ -200,7 +206,9 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                     umma_f8f6f4(acc0, dw + (uint64_t)(k * 2), dx + (uint64_t)(k * 2), idesc8, (it > 0 || k > 0) ? 1u : 0u);
                 umma_commit(&ctrl->empty[st]);
             }
-            if (it == n_base && !ctrl->abort_flag) {
+            if (cc) {
+                if (it == n_base && !ctrl->abort_flag) umma_commit(&ctrl->acc_full);
+            } else if (it == n_base && !ctrl->abort_flag) {
                 bool ok = mbar_wait(&ctrl->list_ready, 0, limit_ns);
                 if (!ok) record_timeout(p, ctrl, 7, 0);
                 const int n_steps = ok ? ctrl->n_steps : 0;
@@ -256,7 +264,8 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                             const int e = idx * n_chunks + c;
                             if (e % p.split2 == j) {
                                 const int li = e / p.split2;
-                                if (li < kMaxLoraIters) ctrl->steps[li] = LoraStep{lora, lo - t0, hi - t0, c};
+                                if (li < kMaxLoraIters)
+                                    ctrl->steps[li] = LoraStep{(uint16_t)lora, (uint16_t)c, (uint16_t)(lo - t0), (uint16_t)(hi - t0)};
                             }
                         }
                     }
@@ -276,55 +285,144 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
         for (int c = te; c < tn; c += 128) ctrl->sx[c] = (t0 + c < p.M) ? p.sx[t0 + c] : 0.0f;
 
         const int row_bytes = p.rc * 2;
-        const int cpr = row_bytes / 16;                       // 16-byte chunks per H row
+        const int cpr = row_bytes / 16;                       // 16-byte chunks per tile row
         const uint32_t swz = (uint32_t)cpr - 1u;
-        for (int li = 0; li < n_steps; ++li) {
-            const int hb = li & 1, hu = li >> 1;
-            if (te == 0) {                                    // one thread decides, so that all 128 leave together
-                int go = ctrl->abort_flag ? 0 : 1;
-                if (go && hu > 0 && !mbar_wait(&ctrl->h_empty[hb], (uint32_t)((hu - 1) & 1), limit_ns)) {
-                    record_timeout(p, ctrl, 10, li);
-                    go = 0;
-                }
-                ctrl->go_flag = go;
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (!ctrl->go_flag) break;
-            const LoraStep e = ctrl->steps[li];
-            uint8_t* hdst = hbuf + (size_t)hb * h_bytes;
-            for (int ch = te; ch < tn * cpr; ch += 128) {
-                const int row = ch / cpr, cc = ch % cpr;
-                uint4 out = make_uint4(0u, 0u, 0u, 0u);
-                if (row >= e.lo && row < e.hi) {
+        const int q = warp & 3;
+        const int n_local = q * 32 + lane;
+        float accl[32];                                       // cc mode: this thread's LoRA sums, one per token of the tile
+#pragma unroll
+        for (int c = 0; c < 32; ++c) accl[c] = 0.0f;
+
+        if (cc) {
+            // ---- h table: bf16( sum over K1's splits, in split order ) for every token of the tile, once
+            if (n_steps > 0) {
+                const int groups = p.R / 8;
+                __nv_bfloat16* htab = reinterpret_cast<__nv_bfloat16*>(hbuf);
+                for (int idx = te; idx < tn * groups; idx += 128) {
+                    const int row = idx / groups, g8 = idx % groups;
                     float acc[8];
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) acc[q] = 0.0f;
-                    const size_t col = (size_t)e.chunk * p.rc + (size_t)cc * 8;
-                    for (int j1 = 0; j1 < p.split1; ++j1) {
-                        const float4* src = reinterpret_cast<const float4*>(
-                            p.hp + (((size_t)j1 * p.S + s) * p.max_m + (size_t)(t0 + row)) * p.R + col);
-                        const float4 u0 = __ldcg(src), u1 = __ldcg(src + 1);
-                        acc[0] += u0.x; acc[1] += u0.y; acc[2] += u0.z; acc[3] += u0.w;
-                        acc[4] += u1.x; acc[5] += u1.y; acc[6] += u1.z; acc[7] += u1.w;
+                    for (int u = 0; u < 8; ++u) acc[u] = 0.0f;
+                    if (t0 + row < n_all) {
+                        for (int j1 = 0; j1 < p.split1; ++j1) {
+                            const float4* src = reinterpret_cast<const float4*>(
+                                p.hp + (((size_t)j1 * p.S + s) * p.max_m + (size_t)(t0 + row)) * p.R + (size_t)g8 * 8);
+                            const float4 u0 = __ldcg(src), u1 = __ldcg(src + 1);
+                            acc[0] += u0.x; acc[1] += u0.y; acc[2] += u0.z; acc[3] += u0.w;
+                            acc[4] += u1.x; acc[5] += u1.y; acc[6] += u1.z; acc[7] += u1.w;
+                        }
                     }
                     __nv_bfloat162 b0 = __floats2bfloat162_rn(acc[0], acc[1]);
                     __nv_bfloat162 b1 = __floats2bfloat162_rn(acc[2], acc[3]);
                     __nv_bfloat162 b2 = __floats2bfloat162_rn(acc[4], acc[5]);
                     __nv_bfloat162 b3 = __floats2bfloat162_rn(acc[6], acc[7]);
+                    uint4 out;
                     out.x = *reinterpret_cast<uint32_t*>(&b0);
                     out.y = *reinterpret_cast<uint32_t*>(&b1);
                     out.z = *reinterpret_cast<uint32_t*>(&b2);
                     out.w = *reinterpret_cast<uint32_t*>(&b3);
+                    *reinterpret_cast<uint4*>(htab + (size_t)row * p.R + (size_t)g8 * 8) = out;
                 }
-                uint32_t off = (uint32_t)row * (uint32_t)row_bytes + (uint32_t)cc * 16u;
-                off ^= ((off >> 7) & swz) << 4;
-                *reinterpret_cast<uint4*>(hdst + off) = out;
             }
-            fence_proxy_async_smem();
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (te == 0) mbar_arrive(&ctrl->h_full[hb]);
+            // ---- expand steps: B tiles arrive in the ring behind the W tiles; 16 rank columns at a time
+            for (int li = 0; li < n_steps; ++li) {
+                const int it = n_base + li;
+                const int st = it % p.stages, use = it / p.stages;
+                if (te == 0) {
+                    int go = ctrl->abort_flag ? 0 : 1;
+                    if (go && !mbar_wait(&ctrl->full_w[st], (uint32_t)(use & 1), limit_ns)) {
+                        record_timeout(p, ctrl, 12, it);
+                        go = 0;
+                    }
+                    ctrl->go_flag = go;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (!ctrl->go_flag) break;
+                const LoraStep e = ctrl->steps[li];
+                const uint8_t* btile = ring + (size_t)st * stage_bytes;
+                const uint8_t* hrow0 = hbuf + (size_t)e.chunk * p.rc * 2;
+                for (int g = 0; g < p.rc / 16; ++g) {
+                    uint32_t off = (uint32_t)n_local * (uint32_t)row_bytes + (uint32_t)g * 32u;
+                    uint32_t o0 = off ^ (((off >> 7) & swz) << 4);
+                    uint32_t o1 = (off + 16u) ^ ((((off + 16u) >> 7) & swz) << 4);
+                    const uint4 bq0 = *reinterpret_cast<const uint4*>(btile + o0);
+                    const uint4 bq1 = *reinterpret_cast<const uint4*>(btile + o1);
+                    float bf[16];
+                    bf[0] = bf16_lo(bq0.x); bf[1] = bf16_hi(bq0.x); bf[2] = bf16_lo(bq0.y); bf[3] = bf16_hi(bq0.y);
+                    bf[4] = bf16_lo(bq0.z); bf[5] = bf16_hi(bq0.z); bf[6] = bf16_lo(bq0.w); bf[7] = bf16_hi(bq0.w);
+                    bf[8] = bf16_lo(bq1.x); bf[9] = bf16_hi(bq1.x); bf[10] = bf16_lo(bq1.y); bf[11] = bf16_hi(bq1.y);
+                    bf[12] = bf16_lo(bq1.z); bf[13] = bf16_hi(bq1.z); bf[14] = bf16_lo(bq1.w); bf[15] = bf16_hi(bq1.w);
+#pragma unroll
+                    for (int t = 0; t < 32; ++t) {
+                        if (t >= (int)e.lo && t < (int)e.hi) {
+                            const uint4* hp4 = reinterpret_cast<const uint4*>(hrow0 + (size_t)t * p.R * 2 + (size_t)g * 32);
+                            const uint4 h0 = hp4[0], h1 = hp4[1];
+                            float a = accl[t];
+                            a = fmaf(bf[0], bf16_lo(h0.x), a); a = fmaf(bf[1], bf16_hi(h0.x), a);
+                            a = fmaf(bf[2], bf16_lo(h0.y), a); a = fmaf(bf[3], bf16_hi(h0.y), a);
+                            a = fmaf(bf[4], bf16_lo(h0.z), a); a = fmaf(bf[5], bf16_hi(h0.z), a);
+                            a = fmaf(bf[6], bf16_lo(h0.w), a); a = fmaf(bf[7], bf16_hi(h0.w), a);
+                            a = fmaf(bf[8], bf16_lo(h1.x), a); a = fmaf(bf[9], bf16_hi(h1.x), a);
+                            a = fmaf(bf[10], bf16_lo(h1.y), a); a = fmaf(bf[11], bf16_hi(h1.y), a);
+                            a = fmaf(bf[12], bf16_lo(h1.z), a); a = fmaf(bf[13], bf16_hi(h1.z), a);
+                            a = fmaf(bf[14], bf16_lo(h1.w), a); a = fmaf(bf[15], bf16_hi(h1.w), a);
+                            accl[t] = a;
+                        }
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");    // every thread has read its B row: the slot is free
+                if (te == 0) mbar_arrive(&ctrl->empty[st]);
+            }
+        } else {
+            for (int li = 0; li < n_steps; ++li) {
+                const int hb = li & 1, hu = li >> 1;
+                if (te == 0) {                                    // one thread decides, so that all 128 leave together
+                    int go = ctrl->abort_flag ? 0 : 1;
+                    if (go && hu > 0 && !mbar_wait(&ctrl->h_empty[hb], (uint32_t)((hu - 1) & 1), limit_ns)) {
+                        record_timeout(p, ctrl, 10, li);
+                        go = 0;
+                    }
+                    ctrl->go_flag = go;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (!ctrl->go_flag) break;
+                const LoraStep e = ctrl->steps[li];
+                uint8_t* hdst = hbuf + (size_t)hb * h_bytes;
+                for (int ch = te; ch < tn * cpr; ch += 128) {
+                    const int row = ch / cpr, c16 = ch % cpr;
+                    uint4 out = make_uint4(0u, 0u, 0u, 0u);
+                    if (row >= (int)e.lo && row < (int)e.hi) {
+                        float acc[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) acc[u] = 0.0f;
+                        const size_t col = (size_t)e.chunk * p.rc + (size_t)c16 * 8;
+                        for (int j1 = 0; j1 < p.split1; ++j1) {
+                            const float4* src = reinterpret_cast<const float4*>(
+                                p.hp + (((size_t)j1 * p.S + s) * p.max_m + (size_t)(t0 + row)) * p.R + col);
+                            const float4 u0 = __ldcg(src), u1 = __ldcg(src + 1);
+                            acc[0] += u0.x; acc[1] += u0.y; acc[2] += u0.z; acc[3] += u0.w;
+                            acc[4] += u1.x; acc[5] += u1.y; acc[6] += u1.z; acc[7] += u1.w;
+                        }
+                        __nv_bfloat162 b0 = __floats2bfloat162_rn(acc[0], acc[1]);
+                        __nv_bfloat162 b1 = __floats2bfloat162_rn(acc[2], acc[3]);
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(acc[4], acc[5]);
+                        __nv_bfloat162 b3 = __floats2bfloat162_rn(acc[6], acc[7]);
+                        out.x = *reinterpret_cast<uint32_t*>(&b0);
+                        out.y = *reinterpret_cast<uint32_t*>(&b1);
+                        out.z = *reinterpret_cast<uint32_t*>(&b2);
+                        out.w = *reinterpret_cast<uint32_t*>(&b3);
+                    }
+                    uint32_t off = (uint32_t)row * (uint32_t)row_bytes + (uint32_t)c16 * 16u;
+                    off ^= ((off >> 7) & swz) << 4;
+                    *reinterpret_cast<uint4*>(hdst + off) = out;
+                }
+                fence_proxy_async_smem();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (te == 0) mbar_arrive(&ctrl->h_full[hb]);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");        // sx / rowmap visible to all epilogue threads
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");        // sx / rowmap visible to all epilogue threads
 
         // ---- epilogue
         if (te == 0) {
@@ -339,28 +437,47 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
         const bool done = ctrl->go_flag != 0;
         tc_fence_after();
         if (done) {
-            const int q = warp & 3;
-            const int n_local = q * 32 + lane;
             const bool n_ok = n0_local + n_local < n_s;
             const int n_glob = slice_off + n0_local + n_local;
             const float s_w = __ldg(p.s_w);
             const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
             const bool has_lora = n_steps > 0;
             float* part = p.part + ((size_t)tile_lin * p.split2 + j) * (size_t)tn * kTileN;
-            for (int c0 = 0; c0 < tn; c0 += 16) {
-                uint32_t r0[16], r1[16];
-                tmem_ld16(acc0 + lane_addr + (uint32_t)c0, r0);
-                if (has_lora) tmem_ld16(acc1 + lane_addr + (uint32_t)c0, r1);
-                tmem_ld_wait();
+            if (cc) {
 #pragma unroll
-                for (int c = 0; c < 16; ++c) {
-                    const int row = ctrl->rowmap[c0 + c];
-                    float v = __uint_as_float(r0[c]) * (ctrl->sx[c0 + c] * s_w);
-                    if (has_lora) v += __uint_as_float(r1[c]);
-                    if (p.split2 == 1) {
-                        if (row >= 0 && n_ok) p.y[(int64_t)row * p.ldy + n_glob] = __float2bfloat16_rn(v);
-                    } else {
-                        part[(size_t)(c0 + c) * kTileN + n_local] = v;
+                for (int c0 = 0; c0 < 32; c0 += 16) {
+                    if (c0 < tn) {
+                        uint32_t r0[16];
+                        tmem_ld16(acc0 + lane_addr + (uint32_t)c0, r0);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            const int row = ctrl->rowmap[c0 + c];
+                            const float v = fmaf(__uint_as_float(r0[c]), ctrl->sx[c0 + c] * s_w, accl[c0 + c]);
+                            if (p.split2 == 1) {
+                                if (row >= 0 && n_ok) p.y[(int64_t)row * p.ldy + n_glob] = __float2bfloat16_rn(v);
+                            } else {
+                                part[(size_t)(c0 + c) * kTileN + n_local] = v;
+                            }
+                        }
+                    }
+                }
+            } else {
+                for (int c0 = 0; c0 < tn; c0 += 16) {
+                    uint32_t r0[16], r1[16];
+                    tmem_ld16(acc0 + lane_addr + (uint32_t)c0, r0);
+                    if (has_lora) tmem_ld16(acc1 + lane_addr + (uint32_t)c0, r1);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const int row = ctrl->rowmap[c0 + c];
+                        float v = __uint_as_float(r0[c]) * (ctrl->sx[c0 + c] * s_w);
+                        if (has_lora) v += __uint_as_float(r1[c]);
+                        if (p.split2 == 1) {
+                            if (row >= 0 && n_ok) p.y[(int64_t)row * p.ldy + n_glob] = __float2bfloat16_rn(v);
+                        } else {
+                            part[(size_t)(c0 + c) * kTileN + n_local] = v;
+                        }
                     }
                 }
             }
@@ -399,8 +516,9 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
     }
 }
 
-size_t k2_fp8_smem_bytes(int tn, int stages, int rc) {
-    return 1024 + (size_t)stages * (kWTileBytes + (size_t)tn * kBlockK) + 2 * align_up((size_t)tn * rc * 2, 1024) + kCtrlBytes;
+size_t k2_fp8_smem_bytes(int tn, int stages, int rc, int R) {
+    const size_t aux = tn <= 32 ? align_up((size_t)tn * R * 2, 1024) : 2 * align_up((size_t)tn * rc * 2, 1024);
+    return 1024 + (size_t)stages * (kWTileBytes + (size_t)tn * kBlockK) + aux + kCtrlBytes;
 }
 
 cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,

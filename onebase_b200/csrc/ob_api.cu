@@ -7,8 +7,8 @@
 #include "ob_common.cuh"
 
 namespace ob {
-cudaError_t launch_k1_fp8(const K1Params& p, int grid, cudaStream_t stream);
-size_t k2_fp8_smem_bytes(int tn, int stages, int rc);
+size_t k2_fp8_smem_bytes(int tn, int stages, int rc, int R);
+cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream);
 cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                           dim3 grid, size_t smem, int pdl, cudaStream_t stream);
 cudaError_t launch_segment_index(const int32_t* token_lora, int M, int L, int32_t* tok, int32_t* srt, int32_t* seg_n,
@@ -20,6 +20,7 @@ using namespace ob;
 namespace {
 
 constexpr size_t kSmemLimit = 227 * 1024;
+constexpr size_t kSmemTwoPerSm = 112 * 1024;   // two CTAs of this size (+1 KB reserved each) fit one SM's 228 KB
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -146,11 +147,19 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     if (!(r->tn == 16 || r->tn == 32 || r->tn == 64 || r->tn == 128 || r->tn == 256)) return OB_ERR_TILE;
     r->m_tiles = (M + r->tn - 1) / r->tn;
     int split2 = (cfg && cfg->split2) ? cfg->split2 : 0;
-    if (split2 == 0) {
-        split2 = r->m_tiles > 1 ? 1 : 148 / (l->n_tiles > 0 ? l->n_tiles : 1);
-        if (split2 < 1) split2 = 1;
-        if (split2 > 8) split2 = 8;
-        if (split2 > kblocks) split2 = kblocks;
+    if (split2 == 0) {   // fill the GPU's 2 x 148 CTA slots as evenly as possible, at least 4 K blocks per CTA
+        split2 = 1;
+        if (r->m_tiles == 1) {
+            double best = 0.0;
+            for (int c = 1; c <= 8 && c <= kblocks && (c == 1 || kblocks / c >= 4); ++c) {
+                const int ctas = l->n_tiles * c;
+                const double eff = (double)ctas / (double)(((ctas + 295) / 296) * 296);
+                if (eff > best + 0.02) {
+                    best = eff;
+                    split2 = c;
+                }
+            }
+        }
     }
     if (split2 < 1 || split2 > 16 || split2 > kblocks || (split2 > 1 && r->m_tiles > 1)) return OB_ERR_TILE;
     if ((long long)l->n_tiles * r->m_tiles > kCounterSlots) return OB_ERR_TOO_LARGE;
@@ -167,10 +176,15 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     r->k_per_split = (int)align_up((size_t)(d.K + split1 - 1) / split1, 256);
     r->pb = M <= 32 ? 1 : 4;
     const int rc = l->rc;
-    int stages = (cfg && cfg->stages) ? cfg->stages : 12;
+    int stages = (cfg && cfg->stages) ? cfg->stages : 0;
+    if (stages == 0) {   // prefer a footprint that lets two CTAs share an SM (3+ stages), else the deepest ring that fits
+        stages = 12;
+        while (stages > 3 && k2_fp8_smem_bytes(r->tn, stages, rc, d.R) > kSmemTwoPerSm) --stages;
+        if (k2_fp8_smem_bytes(r->tn, stages, rc, d.R) > kSmemTwoPerSm) stages = 12;
+    }
     if (stages < 2 || stages > 12) return OB_ERR_TILE;
-    while (stages > 2 && k2_fp8_smem_bytes(r->tn, stages, rc) > kSmemLimit) --stages;
-    if (k2_fp8_smem_bytes(r->tn, stages, rc) > kSmemLimit) return OB_ERR_TILE;
+    while (stages > 2 && k2_fp8_smem_bytes(r->tn, stages, rc, d.R) > kSmemLimit) --stages;
+    if (k2_fp8_smem_bytes(r->tn, stages, rc, d.R) > kSmemLimit) return OB_ERR_TILE;
     r->stages = stages;
     if ((long long)(d.L < r->tn ? d.L : r->tn) * (d.R / rc) > kMaxLoraIters) return OB_ERR_TOO_LARGE;
     r->wait_ms = (cfg && cfg->wait_ms > 0) ? (uint32_t)cfg->wait_ms : 2000u;
@@ -198,7 +212,8 @@ int get_xmap(ObLayer* l, const void* xq, int rows, int tn, CUtensorMap* out) {
     return OB_OK;
 }
 
-int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, cudaStream_t stream) {
+int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, int pdl,
+                cudaStream_t stream) {
     const ObLayerDesc& d = l->d;
     const WorkspaceLayout lay = workspace_layout(*sh);
     uint8_t* base = static_cast<uint8_t*>(ws);
@@ -223,7 +238,7 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     const long long warps = (long long)p.n_pblocks * p.units_per_block;
     const long long grid = p.n_quant_ctas + (warps + 7) / 8;
     if (grid > 0x7fffffffLL) return OB_ERR_TOO_LARGE;
-    cudaError_t e = launch_k1_fp8(p, (int)grid, stream);
+    cudaError_t e = launch_k1_fp8(p, (int)grid, pdl, stream);
     return e == cudaSuccess ? OB_OK : (int)e;
 }
 
@@ -245,6 +260,7 @@ int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     p.kblocks = (d.K + kBlockK - 1) / kBlockK;
     p.stages = r.stages;
     p.rc = l->rc;
+    p.expand_cc = r.tn <= 32 ? 1 : 0;
     p.max_m = sh->max_m;
     p.wait_ms = r.wait_ms;
     p.s_w = d.s_w;
@@ -263,7 +279,7 @@ int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
         if (lay.part + need > lay.total) return OB_ERR_WORKSPACE;
     }
     dim3 grid((unsigned)l->n_tiles, (unsigned)r.split2, (unsigned)r.m_tiles);
-    cudaError_t e = launch_k2_fp8(p, l->tm_w, tm_x, l->tm_b, grid, k2_fp8_smem_bytes(r.tn, r.stages, l->rc), pdl, stream);
+    cudaError_t e = launch_k2_fp8(p, l->tm_w, tm_x, l->tm_b, grid, k2_fp8_smem_bytes(r.tn, r.stages, l->rc, d.R), pdl, stream);
     return e == cudaSuccess ? OB_OK : (int)e;
 }
 
@@ -360,7 +376,7 @@ int ob_k1_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWor
     Resolved r;
     int st = prepare_call(layer, batch, workspace, shape, cfg, &r);
     if (st != OB_OK) return st;
-    return k1_fp8_impl(layer, batch, workspace, shape, r, static_cast<cudaStream_t>(cuda_stream));
+    return k1_fp8_impl(layer, batch, workspace, shape, r, 0, static_cast<cudaStream_t>(cuda_stream));
 }
 
 int ob_k2_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape, const ObTileCfg* cfg,
@@ -377,7 +393,7 @@ int ob_chain_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const Ob
     int st = prepare_call(layer, batch, workspace, shape, cfg, &r);
     if (st != OB_OK) return st;
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-    st = k1_fp8_impl(layer, batch, workspace, shape, r, stream);
+    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
     if (st != OB_OK) return st;
     return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
 }
