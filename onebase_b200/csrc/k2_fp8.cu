@@ -43,6 +43,7 @@ struct LoraStep {
 struct K2Ctrl {
     uint64_t full_w[12];
     uint64_t full_x[12];
+    uint64_t full_b[12];   // B tiles of the expand steps: own barriers, so their consumers need not follow the base phases
     uint64_t empty[12];
     uint64_t h_full[2];
     uint64_t h_empty[2];
@@ -116,6 +117,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
         for (int i = 0; i < p.stages; ++i) {
             mbar_init(&ctrl->full_w[i], 1);
             mbar_init(&ctrl->full_x[i], 1);
+            mbar_init(&ctrl->full_b[i], 1);
             mbar_init(&ctrl->empty[i], 1);
         }
         mbar_init(&ctrl->h_full[0], 1);
@@ -168,8 +170,8 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                     if (ctrl->abort_flag) break;
                     if (use > 0) OB_WAIT(&ctrl->empty[st], (uint32_t)((use - 1) & 1), 3, it)
                     const LoraStep e = ctrl->steps[li];
-                    mbar_arrive_expect_tx(&ctrl->full_w[st], b_bytes);
-                    tma_load_2d(ring + (size_t)st * stage_bytes, tmb, &ctrl->full_w[st], e.chunk * p.rc,
+                    mbar_arrive_expect_tx(&ctrl->full_b[st], b_bytes);
+                    tma_load_2d(ring + (size_t)st * stage_bytes, tmb, &ctrl->full_b[st], e.chunk * p.rc,
                                 e.lora * n_s + n0_local);
                 }
             }
@@ -217,10 +219,10 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                 const uint32_t sbo = row_bytes * 8;
                 int li = 0;
                 for (; li < n_steps; ++li, ++it) {
-                    const int st = it % p.stages, use = it / p.stages;
+                    const int st = it % p.stages;
                     const int hb = li & 1, hu = li >> 1;
                     if (ctrl->abort_flag) break;
-                    OB_WAIT(&ctrl->full_w[st], (uint32_t)(use & 1), 8, it)
+                    OB_WAIT(&ctrl->full_b[st], (uint32_t)((li / p.stages) & 1), 8, it)
                     OB_WAIT(&ctrl->h_full[hb], (uint32_t)(hu & 1), 9, it)
                     tc_fence_after();
                     const uint64_t db = umma_smem_desc(smem_u32(ring + (size_t)st * stage_bytes), sbo, lt);
@@ -328,10 +330,10 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
             // ---- expand steps: B tiles arrive in the ring behind the W tiles; 16 rank columns at a time
             for (int li = 0; li < n_steps; ++li) {
                 const int it = n_base + li;
-                const int st = it % p.stages, use = it / p.stages;
+                const int st = it % p.stages;
                 if (te == 0) {
                     int go = ctrl->abort_flag ? 0 : 1;
-                    if (go && !mbar_wait(&ctrl->full_w[st], (uint32_t)(use & 1), limit_ns)) {
+                    if (go && !mbar_wait(&ctrl->full_b[st], (uint32_t)((li / p.stages) & 1), limit_ns)) {
                         record_timeout(p, ctrl, 12, it);
                         go = 0;
                     }
