@@ -159,6 +159,13 @@ int ob_chain_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const Ob
 int ob_segment_index(const int32_t* token_lora, int32_t M, int32_t L, int32_t* tok, int32_t* srt, int32_t* seg_n,
                      int32_t* seg_start, int32_t* seg_ids, void* cuda_stream);
 
+/* In-kernel timeline for profiling (the reference has no counterpart: it profiles with torch.profiler only,
+ * bench/overhead.py:111-113).  While a buffer is set, every K2 CTA stores OB_TRACE_EVENTS global-timer stamps (ns) at
+ * buffer[cta * OB_TRACE_EVENTS + event], cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z); CTAs beyond
+ * `max_ctas` store nothing.  Pass a null pointer to switch it off (the default).  Process-wide, not thread-safe. */
+#define OB_TRACE_EVENTS 16
+int ob_trace_buffer(void* device_u64_buffer, int64_t max_ctas);
+
 /* Copy the workspace's OB_STATUS_WORDS status words to host memory (synchronizes the stream) and clear them. */
 int ob_read_status(void* workspace, int32_t* host_out, void* cuda_stream);
 

@@ -67,6 +67,7 @@ SYMBOLS = {
                                C.POINTER(ObTileCfg), C.c_void_p]),
     "ob_segment_index": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                    C.c_void_p, C.c_void_p]),
+    "ob_trace_buffer": (C.c_int, [C.c_void_p, C.c_int64]),
     "ob_read_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p]),
 }
 

@@ -71,6 +71,10 @@ __device__ __forceinline__ void record_timeout(const K2Params& p, K2Ctrl* c, int
     }
 }
 
+// Timeline stamp `ev` of this CTA (profiling only; off unless a trace buffer is set).
+#define OB_TRACE(ev)                                                                                      \
+    if (p.trace != nullptr && trace_cta < p.trace_ctas) p.trace[trace_cta * OB_TRACE_EVENTS + (ev)] = global_timer_ns();
+
 #define OB_WAIT(bar, parity, where, it)                   \
     if (!mbar_wait((bar), (parity), limit_ns)) {          \
         record_timeout(p, ctrl, (where), (it));           \
@@ -88,8 +92,8 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
     const bool cc = p.expand_cc != 0;                          // expand on the CUDA cores (token tiles of 16 / 32)
     const int h_bytes = (int)align_up((size_t)tn * p.rc * 2, 1024);
     uint8_t* ring = smem;
-    uint8_t* hbuf = ring + (size_t)p.stages * stage_bytes;    // cc: the bf16 h table [tn][R]; else two masked H tiles
-    K2Ctrl* ctrl = reinterpret_cast<K2Ctrl*>(hbuf + (cc ? align_up((size_t)tn * p.R * 2, 1024) : 2 * (size_t)h_bytes));
+    uint8_t* hbuf = ring + (size_t)p.stages * stage_bytes;    // cc: the fp32 h table [tn][R]; else two masked H tiles
+    K2Ctrl* ctrl = reinterpret_cast<K2Ctrl*>(hbuf + (cc ? align_up((size_t)tn * p.R * 4, 1024) : 2 * (size_t)h_bytes));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     griddep_launch_dependents();                               // the next kernel in the stream may start its own prologue
@@ -111,6 +115,8 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
     const int n_base = kb1 - kb0;
     const int n_chunks = p.R / p.rc;
     const int tile_lin = blockIdx.z * gridDim.x + blockIdx.x;
+    const long long trace_cta = blockIdx.x + (long long)gridDim.x * (blockIdx.y + (long long)gridDim.y * blockIdx.z);
+    if (tid == 0) { OB_TRACE(0) }
 
     // ---- one-time setup
     if (tid == 0) {
@@ -144,6 +150,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = ctrl->tmem_base;
+    if (tid == 0) { OB_TRACE(1) }
     const uint32_t acc0 = tmem_base, acc1 = tmem_base + (uint32_t)tn;
 
     if (warp == 0) {
@@ -159,6 +166,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                 tma_load_2d_hint(ring + (size_t)st * stage_bytes, &tm_w, &ctrl->full_w[st], (kb0 + it) * kBlockK,
                                  slice_off + n0_local, pol);
             }
+            OB_TRACE(2)
             if (it == n_base && !ctrl->abort_flag) {
                 bool ok = mbar_wait(&ctrl->list_ready, 0, limit_ns);
                 if (!ok) record_timeout(p, ctrl, 2, 0);
@@ -174,12 +182,14 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                     tma_load_2d(ring + (size_t)st * stage_bytes, tmb, &ctrl->full_b[st], e.chunk * p.rc,
                                 e.lora * n_s + n0_local);
                 }
+                OB_TRACE(3)
             }
         }
     } else if (warp == 2) {
         // =========================================================== x_q producer (depends on K1)
         if (lane == 0) {
             griddep_wait();
+            OB_TRACE(4)
             for (int it = 0; it < n_base; ++it) {
                 const int st = it % p.stages, use = it / p.stages;
                 if (ctrl->abort_flag) break;
@@ -199,6 +209,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                 if (ctrl->abort_flag) break;
                 OB_WAIT(&ctrl->full_w[st], (uint32_t)(use & 1), 5, it)
                 OB_WAIT(&ctrl->full_x[st], (uint32_t)(use & 1), 6, it)
+                if (it == 0) { OB_TRACE(5) }
                 tc_fence_after();
                 const uint32_t wa = smem_u32(ring + (size_t)st * stage_bytes);
                 const uint64_t dw = umma_smem_desc(wa, 1024, 2);
@@ -208,6 +219,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                     umma_f8f6f4(acc0, dw + (uint64_t)(k * 2), dx + (uint64_t)(k * 2), idesc8, (it > 0 || k > 0) ? 1u : 0u);
                 umma_commit(&ctrl->empty[st]);
             }
+            OB_TRACE(6)
             if (cc) {
                 if (it == n_base && !ctrl->abort_flag) umma_commit(&ctrl->acc_full);
             } else if (it == n_base && !ctrl->abort_flag) {
@@ -280,10 +292,11 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
             }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (te == 0) mbar_arrive(&ctrl->list_ready);
+        if (te == 0) { mbar_arrive(&ctrl->list_ready); OB_TRACE(7) }
         const int n_steps = ctrl->n_steps;
 
         griddep_wait();                                       // K1's s_x and shrink partials from here on
+        if (te == 0) { OB_TRACE(8) }
         for (int c = te; c < tn; c += 128) ctrl->sx[c] = (t0 + c < p.M) ? p.sx[t0 + c] : 0.0f;
 
         const int row_bytes = p.rc * 2;
@@ -296,37 +309,29 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
         for (int c = 0; c < 32; ++c) accl[c] = 0.0f;
 
         if (cc) {
-            // ---- h table: bf16( sum over K1's splits, in split order ) for every token of the tile, once
+            // ---- h table: bf16( sum over K1's splits, in split order ), widened back to fp32, for every token of the tile
+            float* htab = reinterpret_cast<float*>(hbuf);
             if (n_steps > 0) {
-                const int groups = p.R / 8;
-                __nv_bfloat16* htab = reinterpret_cast<__nv_bfloat16*>(hbuf);
+                const int groups = p.R / 4;
                 for (int idx = te; idx < tn * groups; idx += 128) {
-                    const int row = idx / groups, g8 = idx % groups;
-                    float acc[8];
-#pragma unroll
-                    for (int u = 0; u < 8; ++u) acc[u] = 0.0f;
+                    const int row = idx / groups, g4 = idx % groups;
+                    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
                     if (t0 + row < n_all) {
                         for (int j1 = 0; j1 < p.split1; ++j1) {
-                            const float4* src = reinterpret_cast<const float4*>(
-                                p.hp + (((size_t)j1 * p.S + s) * p.max_m + (size_t)(t0 + row)) * p.R + (size_t)g8 * 8);
-                            const float4 u0 = __ldcg(src), u1 = __ldcg(src + 1);
-                            acc[0] += u0.x; acc[1] += u0.y; acc[2] += u0.z; acc[3] += u0.w;
-                            acc[4] += u1.x; acc[5] += u1.y; acc[6] += u1.z; acc[7] += u1.w;
+                            const float4 u = __ldcg(reinterpret_cast<const float4*>(
+                                p.hp + (((size_t)j1 * p.S + s) * p.max_m + (size_t)(t0 + row)) * p.R + (size_t)g4 * 4));
+                            acc.x += u.x; acc.y += u.y; acc.z += u.z; acc.w += u.w;
                         }
                     }
-                    __nv_bfloat162 b0 = __floats2bfloat162_rn(acc[0], acc[1]);
-                    __nv_bfloat162 b1 = __floats2bfloat162_rn(acc[2], acc[3]);
-                    __nv_bfloat162 b2 = __floats2bfloat162_rn(acc[4], acc[5]);
-                    __nv_bfloat162 b3 = __floats2bfloat162_rn(acc[6], acc[7]);
-                    uint4 out;
-                    out.x = *reinterpret_cast<uint32_t*>(&b0);
-                    out.y = *reinterpret_cast<uint32_t*>(&b1);
-                    out.z = *reinterpret_cast<uint32_t*>(&b2);
-                    out.w = *reinterpret_cast<uint32_t*>(&b3);
-                    *reinterpret_cast<uint4*>(htab + (size_t)row * p.R + (size_t)g8 * 8) = out;
+                    acc.x = __bfloat162float(__float2bfloat16_rn(acc.x));
+                    acc.y = __bfloat162float(__float2bfloat16_rn(acc.y));
+                    acc.z = __bfloat162float(__float2bfloat16_rn(acc.z));
+                    acc.w = __bfloat162float(__float2bfloat16_rn(acc.w));
+                    *reinterpret_cast<float4*>(htab + (size_t)row * p.R + (size_t)g4 * 4) = acc;
                 }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (te == 0) { OB_TRACE(9) }
             // ---- expand steps: B tiles arrive in the ring behind the W tiles; 16 rank columns at a time
             for (int li = 0; li < n_steps; ++li) {
                 const int it = n_base + li;
@@ -343,35 +348,27 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                 if (!ctrl->go_flag) break;
                 const LoraStep e = ctrl->steps[li];
                 const uint8_t* btile = ring + (size_t)st * stage_bytes;
-                const uint8_t* hrow0 = hbuf + (size_t)e.chunk * p.rc * 2;
-                for (int g = 0; g < p.rc / 16; ++g) {
-                    uint32_t off = (uint32_t)n_local * (uint32_t)row_bytes + (uint32_t)g * 32u;
-                    uint32_t o0 = off ^ (((off >> 7) & swz) << 4);
-                    uint32_t o1 = (off + 16u) ^ ((((off + 16u) >> 7) & swz) << 4);
-                    const uint4 bq0 = *reinterpret_cast<const uint4*>(btile + o0);
-                    const uint4 bq1 = *reinterpret_cast<const uint4*>(btile + o1);
-                    float bf[16];
-                    bf[0] = bf16_lo(bq0.x); bf[1] = bf16_hi(bq0.x); bf[2] = bf16_lo(bq0.y); bf[3] = bf16_hi(bq0.y);
-                    bf[4] = bf16_lo(bq0.z); bf[5] = bf16_hi(bq0.z); bf[6] = bf16_lo(bq0.w); bf[7] = bf16_hi(bq0.w);
-                    bf[8] = bf16_lo(bq1.x); bf[9] = bf16_hi(bq1.x); bf[10] = bf16_lo(bq1.y); bf[11] = bf16_hi(bq1.y);
-                    bf[12] = bf16_lo(bq1.z); bf[13] = bf16_hi(bq1.z); bf[14] = bf16_lo(bq1.w); bf[15] = bf16_hi(bq1.w);
-#pragma unroll
-                    for (int t = 0; t < 32; ++t) {
-                        if (t >= (int)e.lo && t < (int)e.hi) {
-                            const uint4* hp4 = reinterpret_cast<const uint4*>(hrow0 + (size_t)t * p.R * 2 + (size_t)g * 32);
-                            const uint4 h0 = hp4[0], h1 = hp4[1];
-                            float a = accl[t];
-                            a = fmaf(bf[0], bf16_lo(h0.x), a); a = fmaf(bf[1], bf16_hi(h0.x), a);
-                            a = fmaf(bf[2], bf16_lo(h0.y), a); a = fmaf(bf[3], bf16_hi(h0.y), a);
-                            a = fmaf(bf[4], bf16_lo(h0.z), a); a = fmaf(bf[5], bf16_hi(h0.z), a);
-                            a = fmaf(bf[6], bf16_lo(h0.w), a); a = fmaf(bf[7], bf16_hi(h0.w), a);
-                            a = fmaf(bf[8], bf16_lo(h1.x), a); a = fmaf(bf[9], bf16_hi(h1.x), a);
-                            a = fmaf(bf[10], bf16_lo(h1.y), a); a = fmaf(bf[11], bf16_hi(h1.y), a);
-                            a = fmaf(bf[12], bf16_lo(h1.z), a); a = fmaf(bf[13], bf16_hi(h1.z), a);
-                            a = fmaf(bf[14], bf16_lo(h1.w), a); a = fmaf(bf[15], bf16_hi(h1.w), a);
-                            accl[t] = a;
-                        }
+                const uint32_t row_off = (uint32_t)n_local * (uint32_t)row_bytes;
+                for (int t = e.lo; t < (int)e.hi; ++t) {      // the tenant's tokens in this tile (1-2 in a mixed decode batch)
+                    const float4* hrow = reinterpret_cast<const float4*>(htab + (size_t)t * p.R + (size_t)e.chunk * p.rc);
+                    float a0 = 0.0f, a1 = 0.0f;
+                    for (int g = 0; g < p.rc / 16; ++g) {
+                        const uint32_t off = row_off + (uint32_t)g * 32u;
+                        const uint4 bq0 = *reinterpret_cast<const uint4*>(btile + (off ^ (((off >> 7) & swz) << 4)));
+                        const uint4 bq1 = *reinterpret_cast<const uint4*>(btile + ((off + 16u) ^ ((((off + 16u) >> 7) & swz) << 4)));
+                        const float4 h0 = hrow[g * 4 + 0], h1 = hrow[g * 4 + 1], h2 = hrow[g * 4 + 2], h3 = hrow[g * 4 + 3];
+                        a0 = fmaf(bf16_lo(bq0.x), h0.x, a0); a1 = fmaf(bf16_hi(bq0.x), h0.y, a1);
+                        a0 = fmaf(bf16_lo(bq0.y), h0.z, a0); a1 = fmaf(bf16_hi(bq0.y), h0.w, a1);
+                        a0 = fmaf(bf16_lo(bq0.z), h1.x, a0); a1 = fmaf(bf16_hi(bq0.z), h1.y, a1);
+                        a0 = fmaf(bf16_lo(bq0.w), h1.z, a0); a1 = fmaf(bf16_hi(bq0.w), h1.w, a1);
+                        a0 = fmaf(bf16_lo(bq1.x), h2.x, a0); a1 = fmaf(bf16_hi(bq1.x), h2.y, a1);
+                        a0 = fmaf(bf16_lo(bq1.y), h2.z, a0); a1 = fmaf(bf16_hi(bq1.y), h2.w, a1);
+                        a0 = fmaf(bf16_lo(bq1.z), h3.x, a0); a1 = fmaf(bf16_hi(bq1.z), h3.y, a1);
+                        a0 = fmaf(bf16_lo(bq1.w), h3.z, a0); a1 = fmaf(bf16_hi(bq1.w), h3.w, a1);
                     }
+                    const float a = a0 + a1;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) accl[c] += (c == t) ? a : 0.0f;   // keeps the sums in registers
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");    // every thread has read its B row: the slot is free
                 if (te == 0) mbar_arrive(&ctrl->empty[st]);
@@ -427,6 +424,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
         }
 
         // ---- epilogue
+        if (te == 0) { OB_TRACE(10) }
         if (te == 0) {
             int go = ctrl->abort_flag ? 0 : 1;
             if (go && !mbar_wait(&ctrl->acc_full, 0u, limit_ns)) {
@@ -438,6 +436,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const bool done = ctrl->go_flag != 0;
         tc_fence_after();
+        if (te == 0) { OB_TRACE(11) }
         if (done) {
             const bool n_ok = n0_local + n_local < n_s;
             const int n_glob = slice_off + n0_local + n_local;
@@ -483,6 +482,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                     }
                 }
             }
+            if (te == 0) { OB_TRACE(12) }
             if (p.split2 > 1) {
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -508,6 +508,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
         }
     }
 
+    if (tid == 128) { OB_TRACE(13) }
     // ---- teardown: nobody leaves while TMEM is in use or copies may still land in this CTA's shared memory
     if (ctrl->abort_flag) __nanosleep(200000);
     tc_fence_before();
@@ -516,10 +517,11 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);
     }
+    if (tid == 0) { OB_TRACE(14) }
 }
 
 size_t k2_fp8_smem_bytes(int tn, int stages, int rc, int R) {
-    const size_t aux = tn <= 32 ? align_up((size_t)tn * R * 2, 1024) : 2 * align_up((size_t)tn * rc * 2, 1024);
+    const size_t aux = tn <= 32 ? align_up((size_t)tn * R * 4, 1024) : 2 * align_up((size_t)tn * rc * 2, 1024);
     return 1024 + (size_t)stages * (kWTileBytes + (size_t)tn * kBlockK) + aux + kCtrlBytes;
 }
 

@@ -62,6 +62,9 @@ int encode_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const voi
     return r == CUDA_SUCCESS ? OB_OK : 1000 + (int)r;
 }
 
+unsigned long long* g_trace = nullptr;
+long long g_trace_ctas = 0;
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 struct XMap {
@@ -147,19 +150,10 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     if (!(r->tn == 16 || r->tn == 32 || r->tn == 64 || r->tn == 128 || r->tn == 256)) return OB_ERR_TILE;
     r->m_tiles = (M + r->tn - 1) / r->tn;
     int split2 = (cfg && cfg->split2) ? cfg->split2 : 0;
-    if (split2 == 0) {   // fill the GPU's 2 x 148 CTA slots as evenly as possible, at least 4 K blocks per CTA
+    if (split2 == 0) {   // one co-resident wave: as many CTAs as fit the GPU's 2 x 148 slots, at least 4 K blocks each
         split2 = 1;
-        if (r->m_tiles == 1) {
-            double best = 0.0;
-            for (int c = 1; c <= 8 && c <= kblocks && (c == 1 || kblocks / c >= 4); ++c) {
-                const int ctas = l->n_tiles * c;
-                const double eff = (double)ctas / (double)(((ctas + 295) / 296) * 296);
-                if (eff > best + 0.02) {
-                    best = eff;
-                    split2 = c;
-                }
-            }
-        }
+        if (r->m_tiles == 1)
+            while (split2 < 8 && l->n_tiles * (split2 + 1) <= 296 && kblocks / (split2 + 1) >= 4) ++split2;
     }
     if (split2 < 1 || split2 > 16 || split2 > kblocks || (split2 > 1 && r->m_tiles > 1)) return OB_ERR_TILE;
     if ((long long)l->n_tiles * r->m_tiles > kCounterSlots) return OB_ERR_TOO_LARGE;
@@ -274,6 +268,8 @@ int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     p.status = reinterpret_cast<int32_t*>(base + lay.status);
     for (int s = 0; s < d.S; ++s) { p.b[s] = d.b[s]; p.sb[s] = d.sb[s]; }
     p.bg = d.bg;
+    p.trace = g_trace;
+    p.trace_ctas = g_trace_ctas;
     if (r.split2 > 1) {   // the partials of this call must fit the workspace's split-K region
         const size_t need = (size_t)r.split2 * (size_t)l->n_tiles * (size_t)r.tn * kTileN * sizeof(float);
         if (lay.part + need > lay.total) return OB_ERR_WORKSPACE;
@@ -405,6 +401,12 @@ int ob_segment_index(const int32_t* token_lora, int32_t M, int32_t L, int32_t* t
     cudaError_t e = launch_segment_index(token_lora, M, L, tok, srt, seg_n, seg_start, seg_ids,
                                          static_cast<cudaStream_t>(cuda_stream));
     return e == cudaSuccess ? OB_OK : (int)e;
+}
+
+int ob_trace_buffer(void* device_u64_buffer, int64_t max_ctas) {
+    g_trace = static_cast<unsigned long long*>(device_u64_buffer);
+    g_trace_ctas = device_u64_buffer ? max_ctas : 0;
+    return OB_OK;
 }
 
 int ob_read_status(void* workspace, int32_t* host_out, void* cuda_stream) {

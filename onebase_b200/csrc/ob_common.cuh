@@ -103,6 +103,8 @@ struct K2Params {
     const void* b[OB_MAX_SLICES];
     const void* sb[OB_MAX_SLICES];
     const float* bg;
+    unsigned long long* trace;   // optional timeline buffer (null: off)
+    long long trace_ctas;
 };
 
 // Warp-wide: n_all = sum of seg_n, n_ad = sum of seg_n over segments whose slot id >= 0 (L+1 segments).
