@@ -162,7 +162,9 @@ int ob_segment_index(const int32_t* token_lora, int32_t M, int32_t L, int32_t* t
 /* In-kernel timeline for profiling (the reference has no counterpart: it profiles with torch.profiler only,
  * bench/overhead.py:111-113).  While a buffer is set, every K2 CTA stores OB_TRACE_EVENTS global-timer stamps (ns) at
  * buffer[cta * OB_TRACE_EVENTS + event], cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z); CTAs beyond
- * `max_ctas` store nothing.  Pass a null pointer to switch it off (the default).  Process-wide, not thread-safe. */
+ * `max_ctas` store nothing.  K1 CTAs store 4 stamps each (start, segment index read, dependency wait passed, end of
+ * warp 0) in a second region of the same size that follows the first: the buffer holds 2 * max_ctas * OB_TRACE_EVENTS
+ * 64-bit words.  Pass a null pointer to switch it off (the default).  Process-wide, not thread-safe. */
 #define OB_TRACE_EVENTS 16
 int ob_trace_buffer(void* device_u64_buffer, int64_t max_ctas);
 

@@ -21,6 +21,10 @@
 
 namespace ob {
 
+#define OB_TRACE1(ev) \
+    if (p.trace != nullptr && (long long)blockIdx.x < p.trace_ctas && threadIdx.x == 0) \
+        p.trace[(long long)blockIdx.x * OB_TRACE_EVENTS + (ev)] = global_timer_ns();
+
 constexpr int kK1Threads = 256;
 constexpr int kQuantCache = 8;      // 16-byte vectors of the row a thread keeps in registers between the two passes
 constexpr float kFp8Max = 448.0f;
@@ -50,10 +54,11 @@ __device__ void quantize_position(const K1Params& p, int pos) {
     __shared__ float s_part[kK1Threads / 32];
     __shared__ float s_scale;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int sorted_row = p.meta.srt[pos];            // requested together with the segment index (one latency, not two)
     int n_all, n_ad;
     segment_totals(p.meta, p.L, lane, n_all, n_ad);
     n_all = min(n_all, p.M);
-    const int row = position_row(p.meta, pos, p.M, n_all, n_ad);
+    const int row = (n_ad > 0 && pos < n_all) ? min(max(sorted_row, 0), p.M - 1) : pos;
     griddep_wait();                                   // x comes from the preceding kernel; the scratch may still be read by it
     const uint4* xr = reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.ldx);
     const int nvec = p.K >> 3;
@@ -123,7 +128,9 @@ __device__ __forceinline__ void shrink_pass_bf16(const K1Params& p, int lora, in
     const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(p.a[s]) + ((size_t)lora * p.R + (size_t)rg * 8) * p.K;
     uint4 av[8];
     load_a8(av, a, p.K, k0 + lane * 8, k0 + lane * 8 < k1);
+    OB_TRACE1(1)
     griddep_wait();
+    OB_TRACE1(2)
     const __nv_bfloat16* xrow[4];
 #pragma unroll
     for (int t = 0; t < 4; ++t) xrow[t] = p.x + (int64_t)rows[t < nt ? t : 0] * p.ldx;
@@ -162,9 +169,70 @@ __device__ __forceinline__ void shrink_pass_bf16(const K1Params& p, int lora, in
     if (t < nt) p.hp[(((size_t)j * p.S + s) * p.max_m + (pos0 + t)) * p.R + rg * 8 + r] = total;
 }
 
+__device__ __forceinline__ void fma8(float (&acc)[8], const uint4 (&av)[8], const float (&xf)[8]) {
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        float af[8];
+        unpack8(av[r], af);
+        float sacc = acc[r];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) sacc = fmaf(af[e], xf[e], sacc);
+        acc[r] = sacc;
+    }
+}
+
+// Decode form of the pass (one token): two K steps of A in flight per lane (8 KB per warp), both requested before the wait
+// on the preceding kernel.  8 lane-partials -> lanes 0..7 hold the 8 rank rows' sums (2 butterfly + 3 transposing steps).
+__device__ __forceinline__ void shrink_pass1_bf16(const K1Params& p, int lora, int s, int rg, int j, int k0, int k1, int pos,
+                                                  int row, int lane) {
+    const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(p.a[s]) + ((size_t)lora * p.R + (size_t)rg * 8) * p.K;
+    const int kl = k0 + lane * 8;
+    uint4 a0[8], a1[8];
+    load_a8(a0, a, p.K, kl, kl < k1);
+    load_a8(a1, a, p.K, kl + 256, kl + 256 < k1);
+    OB_TRACE1(1)
+    griddep_wait();
+    OB_TRACE1(2)
+    const __nv_bfloat16* xrow = p.x + (int64_t)row * p.ldx;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+    for (int k = kl; k < k1; k += 512) {
+        float x0[8], x1[8];
+        unpack8(__ldg(reinterpret_cast<const uint4*>(xrow + k)), x0);
+        if (k + 256 < k1) {
+            unpack8(__ldg(reinterpret_cast<const uint4*>(xrow + k + 256)), x1);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x1[e] = 0.0f;
+        }
+        fma8(acc, a0, x0);
+        load_a8(a0, a, p.K, k + 512, k + 512 < k1);
+        fma8(acc, a1, x1);
+        load_a8(a1, a, p.K, k + 768, k + 768 < k1);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 16);
+        acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 8);
+    }
+#pragma unroll
+    for (int off = 4, n = 8; off >= 1; off >>= 1, n >>= 1) {
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+            const float send = upper ? acc[i] : acc[i + n / 2];
+            const float keep = upper ? acc[i + n / 2] : acc[i];
+            acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+    }
+    if (lane < 8) p.hp[(((size_t)j * p.S + s) * p.max_m + pos) * p.R + rg * 8 + lane] = acc[0];
+}
+
 // One warp: block `pb` of p.pb consecutive sorted positions, unit `u` -> (slice, group of 8 rank rows, K split).
-// The warp looks up which segment each of its positions lies in (one warp-wide read of the segment index, together with
-// the positions' token rows) and runs one pass per run of positions that share an adapter.
+// One warp-wide read of the segment index gives the batch totals and the segment (adapter) of each of the warp's
+// positions; the positions' token rows are requested at the same time.  Then one pass per run of positions that share
+// an adapter.
 __device__ void shrink_unit(const K1Params& p, int pb, int u, int lane) {
     const int p0 = pb * p.pb;
     int rows[4];
@@ -173,34 +241,44 @@ __device__ void shrink_unit(const K1Params& p, int pb, int u, int lane) {
         int r = (q < p.pb && p0 + q < p.M) ? p.meta.srt[p0 + q] : 0;
         rows[q] = r < 0 ? 0 : (r > p.M - 1 ? p.M - 1 : r);
     }
-    int n_all, n_ad;
-    segment_totals(p.meta, p.L, lane, n_all, n_ad);
-    n_all = min(n_all, p.M);
-    if (n_ad <= 0) return;
-    const int np = min(p.pb, n_all - p0);
-    if (np <= 0) return;
     int lora_of[4] = {-1, -1, -1, -1};
+    int n_all = 0, n_ad = 0;
     for (int base = 0; base <= p.L; base += 32) {
         const int i = base + lane;
-        int id = -1, st = 0, en = 0;
+        int id = -1, st = 0, cnt = 0;
         if (i <= p.L) {
             id = p.meta.seg_ids[i];
             st = p.meta.seg_start[i];
-            en = st + p.meta.seg_n[i];
+            cnt = p.meta.seg_n[i];
         }
+        n_all += cnt;
+        n_ad += id >= 0 ? cnt : 0;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
-            const bool hit = q < np && id >= 0 && id < p.L && st <= p0 + q && p0 + q < en;
+            const bool hit = q < p.pb && id >= 0 && id < p.L && st <= p0 + q && p0 + q < st + cnt;
             const uint32_t m = __ballot_sync(0xffffffffu, hit);
             if (m) lora_of[q] = __shfl_sync(0xffffffffu, id, __ffs(m) - 1);
         }
     }
+#pragma unroll
+    for (int o = 16; o; o >>= 1) {
+        n_all += __shfl_xor_sync(0xffffffffu, n_all, o);
+        n_ad += __shfl_xor_sync(0xffffffffu, n_ad, o);
+    }
+    n_all = min(n_all, p.M);
+    if (n_ad <= 0) return;
+    const int np = min(p.pb, n_all - p0);
+    if (np <= 0) return;
     const int groups = p.R >> 3;
     const int j = u % p.split1;
     const int rg = (u / p.split1) % groups;
     const int s = u / (p.split1 * groups);
     const int k0 = j * p.k_per_split;
     const int k1 = min(p.K, k0 + p.k_per_split);
+    if (p.pb == 1) {
+        if (lora_of[0] >= 0) shrink_pass1_bf16(p, lora_of[0], s, rg, j, k0, k1, p0, rows[0], lane);
+        return;
+    }
     int q = 0;
     while (q < np) {
         const int lora = lora_of[q];
@@ -213,8 +291,10 @@ __device__ void shrink_unit(const K1Params& p, int pb, int u, int lane) {
 
 __global__ void __launch_bounds__(kK1Threads) k1_fp8_kernel(const K1Params p) {
     griddep_launch_dependents();
+    OB_TRACE1(0)
     if ((int)blockIdx.x < p.n_quant_ctas) {
         quantize_position(p, blockIdx.x);
+        OB_TRACE1(3)
         return;
     }
     const int lane = threadIdx.x & 31;
@@ -222,6 +302,7 @@ __global__ void __launch_bounds__(kK1Threads) k1_fp8_kernel(const K1Params p) {
     const int pb = w / p.units_per_block;
     if (pb >= p.n_pblocks) return;
     shrink_unit(p, pb, w % p.units_per_block, lane);
+    OB_TRACE1(3)
 }
 
 cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream) {

@@ -45,6 +45,7 @@ struct K2Ctrl {
     uint64_t full_x[12];
     uint64_t full_b[12];   // B tiles of the expand steps: own barriers, so their consumers need not follow the base phases
     uint64_t empty[12];
+    uint64_t empty_b[12];  // release of a slot that held a B tile (4 arrivals: one per expanding warp; 1 from the MMA warp)
     uint64_t h_full[2];
     uint64_t h_empty[2];
     uint64_t list_ready;
@@ -125,6 +126,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
             mbar_init(&ctrl->full_x[i], 1);
             mbar_init(&ctrl->full_b[i], 1);
             mbar_init(&ctrl->empty[i], 1);
+            mbar_init(&ctrl->empty_b[i], cc ? 4 : 1);
         }
         mbar_init(&ctrl->h_full[0], 1);
         mbar_init(&ctrl->h_full[1], 1);
@@ -174,9 +176,13 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                 const CUtensorMap* tmb = (s == 0) ? &tm_b0 : (s == 1) ? &tm_b1 : (s == 2) ? &tm_b2 : &tm_b3;
                 const uint32_t b_bytes = (uint32_t)kTileN * p.rc * 2;
                 for (int li = 0; li < n_steps; ++li, ++it) {
-                    const int st = it % p.stages, use = it / p.stages;
+                    const int st = it % p.stages, prev = it - p.stages;
                     if (ctrl->abort_flag) break;
-                    if (use > 0) OB_WAIT(&ctrl->empty[st], (uint32_t)((use - 1) & 1), 3, it)
+                    if (prev >= n_base) {          // the slot last held a B tile
+                        OB_WAIT(&ctrl->empty_b[st], (uint32_t)((li / p.stages - 1) & 1), 3, it)
+                    } else if (prev >= 0) {        // the slot last held a W tile
+                        OB_WAIT(&ctrl->empty[st], (uint32_t)((prev / p.stages) & 1), 3, it)
+                    }
                     const LoraStep e = ctrl->steps[li];
                     mbar_arrive_expect_tx(&ctrl->full_b[st], b_bytes);
                     tma_load_2d(ring + (size_t)st * stage_bytes, tmb, &ctrl->full_b[st], e.chunk * p.rc,
@@ -241,7 +247,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                     const uint64_t dh = umma_smem_desc(smem_u32(hbuf + (size_t)hb * h_bytes), sbo, lt);
                     for (int k = 0; k < p.rc / 16; ++k)
                         umma_f16(acc1, db + (uint64_t)(k * 2), dh + (uint64_t)(k * 2), idesc16, (li > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(&ctrl->empty[st]);
+                    umma_commit(&ctrl->empty_b[st]);
                     umma_commit(&ctrl->h_empty[hb]);
                 }
                 if (li == n_steps && !ctrl->abort_flag) umma_commit(&ctrl->acc_full);
@@ -332,20 +338,16 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (te == 0) { OB_TRACE(9) }
-            // ---- expand steps: B tiles arrive in the ring behind the W tiles; 16 rank columns at a time
+            // ---- expand steps: B tiles arrive in the ring behind the W tiles.  Each warp follows the barriers on its own
+            //      (no CTA-wide sync per step) and frees the slot with one arrival per warp.
             for (int li = 0; li < n_steps; ++li) {
                 const int it = n_base + li;
                 const int st = it % p.stages;
-                if (te == 0) {
-                    int go = ctrl->abort_flag ? 0 : 1;
-                    if (go && !mbar_wait(&ctrl->full_b[st], (uint32_t)((li / p.stages) & 1), limit_ns)) {
-                        record_timeout(p, ctrl, 12, it);
-                        go = 0;
-                    }
-                    ctrl->go_flag = go;
+                if (ctrl->abort_flag) break;
+                if (!mbar_wait(&ctrl->full_b[st], (uint32_t)((li / p.stages) & 1), limit_ns)) {
+                    if (lane == 0) record_timeout(p, ctrl, 12, it);
+                    break;
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (!ctrl->go_flag) break;
                 const LoraStep e = ctrl->steps[li];
                 const uint8_t* btile = ring + (size_t)st * stage_bytes;
                 const uint32_t row_off = (uint32_t)n_local * (uint32_t)row_bytes;
@@ -370,9 +372,10 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
 #pragma unroll
                     for (int c = 0; c < 32; ++c) accl[c] += (c == t) ? a : 0.0f;   // keeps the sums in registers
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");    // every thread has read its B row: the slot is free
-                if (te == 0) mbar_arrive(&ctrl->empty[st]);
+                __syncwarp();                                     // every lane has read its B row
+                if (lane == 0) mbar_arrive(&ctrl->empty_b[st]);
             }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
         } else {
             for (int li = 0; li < n_steps; ++li) {
                 const int hb = li & 1, hu = li >> 1;
@@ -492,15 +495,38 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (ctrl->last_flag) {
+                    // The last CTA of the tile adds the partials in split order.  Thread = 4 output features x every 4th
+                    // token; 8 tokens' loads are in flight per split so the sum is not a chain of dependent L2 round trips.
                     __threadfence();
                     const float* pbase = p.part + (size_t)tile_lin * p.split2 * (size_t)tn * kTileN;
-                    for (int c = 0; c < tn; ++c) {
-                        const int row = ctrl->rowmap[c];
-                        if (row < 0) continue;
-                        float v = 0.0f;
-                        for (int jj = 0; jj < p.split2; ++jj)
-                            v += __ldcg(pbase + ((size_t)jj * tn + c) * kTileN + n_local);
-                        if (n_ok) p.y[(int64_t)row * p.ldy + n_glob] = __float2bfloat16_rn(v);
+                    const int tg = te >> 5, n4 = (te & 31) * 4;
+                    for (int cb = 0; cb < tn; cb += 32) {
+                        float4 acc[8];
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) acc[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                        for (int jj = 0; jj < p.split2; ++jj) {
+#pragma unroll
+                            for (int u = 0; u < 8; ++u) {
+                                const int c = cb + u * 4 + tg;
+                                if (c < tn) {
+                                    const float4 v = __ldcg(reinterpret_cast<const float4*>(pbase + ((size_t)jj * tn + c) * kTileN + n4));
+                                    acc[u].x += v.x; acc[u].y += v.y; acc[u].z += v.z; acc[u].w += v.w;
+                                }
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const int c = cb + u * 4 + tg;
+                            const int row = c < tn ? ctrl->rowmap[c] : -1;
+                            if (row >= 0) {
+                                __nv_bfloat16* yr = p.y + (int64_t)row * p.ldy + slice_off + n0_local + n4;
+                                const int left = n_s - (n0_local + n4);
+                                if (left > 0) yr[0] = __float2bfloat16_rn(acc[u].x);
+                                if (left > 1) yr[1] = __float2bfloat16_rn(acc[u].y);
+                                if (left > 2) yr[2] = __float2bfloat16_rn(acc[u].z);
+                                if (left > 3) yr[3] = __float2bfloat16_rn(acc[u].w);
+                            }
+                        }
                     }
                     if (te == 0) p.counters[tile_lin] = 0;
                 }

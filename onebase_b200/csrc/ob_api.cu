@@ -159,16 +159,16 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     if ((long long)l->n_tiles * r->m_tiles > kCounterSlots) return OB_ERR_TOO_LARGE;
     r->split2 = split2;
     int split1 = (cfg && cfg->split1) ? cfg->split1 : 0;
-    if (split1 == 0) {
-        split1 = d.K / 512;
-        if (split1 < 1) split1 = 1;
-        if (split1 > 16) split1 = 16;
-        if (M > 512) split1 = 1;
+    const int pb = M <= 32 ? 1 : 4;
+    if (split1 == 0) {   // as many K splits as keep the whole shrink in one wave of the GPU's 2 x 148 CTA slots (8 warps each)
+        const long long units = (long long)((M + pb - 1) / pb) * d.S * (d.R / 8);
+        split1 = 1;
+        while (split1 < 16 && d.K / (split1 * 2) >= 512 && (units * split1 * 2 + 7) / 8 + M <= 296) split1 *= 2;
     }
     if (split1 < 1 || split1 > 32) return OB_ERR_TILE;
     r->split1 = split1;
     r->k_per_split = (int)align_up((size_t)(d.K + split1 - 1) / split1, 256);
-    r->pb = M <= 32 ? 1 : 4;
+    r->pb = pb;
     const int rc = l->rc;
     int stages = (cfg && cfg->stages) ? cfg->stages : 0;
     if (stages == 0) {   // prefer a footprint that lets two CTAs share an SM (3+ stages), else the deepest ring that fits
@@ -229,6 +229,8 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     p.sx = reinterpret_cast<float*>(base + lay.sx);
     p.hp = reinterpret_cast<float*>(base + lay.hp);
     p.max_m = sh->max_m;
+    p.trace = g_trace ? g_trace + g_trace_ctas * OB_TRACE_EVENTS : nullptr;   // K1's stamps follow K2's
+    p.trace_ctas = g_trace_ctas;
     const long long warps = (long long)p.n_pblocks * p.units_per_block;
     const long long grid = p.n_quant_ctas + (warps + 7) / 8;
     if (grid > 0x7fffffffLL) return OB_ERR_TOO_LARGE;

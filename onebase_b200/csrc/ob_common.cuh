@@ -76,6 +76,8 @@ struct K1Params {
     float* sx;             // [M]
     float* hp;             // [split1][S][max_m][R]
     int max_m;
+    unsigned long long* trace;   // optional timeline buffer (null: off); K1 stamps go after K2's region
+    long long trace_ctas;
 };
 
 struct K2Params {
