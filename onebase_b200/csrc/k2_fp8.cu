@@ -42,7 +42,6 @@ struct LoraStep {
 
 struct K2Ctrl {
     uint64_t full_w[12];
-    uint64_t full_x[12];
     uint64_t full_b[12];   // B tiles of the expand steps: own barriers, so their consumers need not follow the base phases
     uint64_t empty[12];
     uint64_t empty_b[12];  // release of a slot that held a B tile (4 arrivals: one per expanding warp; 1 from the MMA warp)
@@ -60,6 +59,21 @@ struct K2Ctrl {
     LoraStep steps[kMaxLoraIters];
 };
 static_assert(sizeof(K2Ctrl) <= kCtrlBytes, "control block too large");
+
+// The ring's slot sequence, identical in every role.  Slot `it` (ring position it % stages) holds either the next W
+// k-block together with its x_q tile, or the next expand step's B tile: every third slot is a B tile while expand steps
+// remain, and once one kind is exhausted the other takes every slot.  B tiles thus stream in between the W tiles instead
+// of after them.  The number of expand steps is only needed from the first slot that could be a B tile.
+struct SlotWalk {
+    int it = 0, k = 0, li = 0;
+    __device__ bool needs_list(int n_base) const { return it % 3 == 2 || k >= n_base; }
+    __device__ bool is_b(int n_base, int n_steps) const { return li < n_steps && (k >= n_base || it % 3 == 2); }
+    __device__ bool done(int n_base, int n_steps) const { return k >= n_base && li >= n_steps; }
+    __device__ void advance(bool was_b) {
+        ++it;
+        if (was_b) ++li; else ++k;
+    }
+};
 
 __device__ __forceinline__ void record_timeout(const K2Params& p, K2Ctrl* c, int where, int it) {
     c->abort_flag = 1;
@@ -123,7 +137,6 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
     if (tid == 0) {
         for (int i = 0; i < p.stages; ++i) {
             mbar_init(&ctrl->full_w[i], 1);
-            mbar_init(&ctrl->full_x[i], 1);
             mbar_init(&ctrl->full_b[i], 1);
             mbar_init(&ctrl->empty[i], 1);
             mbar_init(&ctrl->empty_b[i], cc ? 4 : 1);
@@ -156,102 +169,124 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
     const uint32_t acc0 = tmem_base, acc1 = tmem_base + (uint32_t)tn;
 
     if (warp == 0) {
-        // =========================================================== W / B-tile producer
+        // =========================================================== TMA producer: W tiles + their x_q tiles, B tiles
         if (lane == 0) {
             const uint64_t pol = l2_policy_evict_first();
-            int it = 0;
-            for (; it < n_base; ++it) {
-                const int st = it % p.stages, use = it / p.stages;
+            const CUtensorMap* tmb = (s == 0) ? &tm_b0 : (s == 1) ? &tm_b1 : (s == 2) ? &tm_b2 : &tm_b3;
+            const uint32_t b_bytes = (uint32_t)kTileN * p.rc * 2;
+            const uint32_t wx_bytes = (uint32_t)kWTileBytes + (uint32_t)tn * kBlockK;
+            SlotWalk w;
+            uint32_t par_w = 0, par_b = 0, last_b = 0;   // per slot: parity of the next release to await (W / B tenant), last tenant
+            int n_steps = 0;
+            bool have_list = false, k1_done = false;
+            for (;;) {
                 if (ctrl->abort_flag) break;
-                if (use > 0) OB_WAIT(&ctrl->empty[st], (uint32_t)((use - 1) & 1), 1, it)
-                mbar_arrive_expect_tx(&ctrl->full_w[st], kWTileBytes);
-                tma_load_2d_hint(ring + (size_t)st * stage_bytes, &tm_w, &ctrl->full_w[st], (kb0 + it) * kBlockK,
-                                 slice_off + n0_local, pol);
-            }
-            OB_TRACE(2)
-            if (it == n_base && !ctrl->abort_flag) {
-                bool ok = mbar_wait(&ctrl->list_ready, 0, limit_ns);
-                if (!ok) record_timeout(p, ctrl, 2, 0);
-                const int n_steps = ok ? ctrl->n_steps : 0;
-                const CUtensorMap* tmb = (s == 0) ? &tm_b0 : (s == 1) ? &tm_b1 : (s == 2) ? &tm_b2 : &tm_b3;
-                const uint32_t b_bytes = (uint32_t)kTileN * p.rc * 2;
-                for (int li = 0; li < n_steps; ++li, ++it) {
-                    const int st = it % p.stages, prev = it - p.stages;
-                    if (ctrl->abort_flag) break;
-                    if (prev >= n_base) {          // the slot last held a B tile
-                        OB_WAIT(&ctrl->empty_b[st], (uint32_t)((li / p.stages - 1) & 1), 3, it)
-                    } else if (prev >= 0) {        // the slot last held a W tile
-                        OB_WAIT(&ctrl->empty[st], (uint32_t)((prev / p.stages) & 1), 3, it)
-                    }
-                    const LoraStep e = ctrl->steps[li];
-                    mbar_arrive_expect_tx(&ctrl->full_b[st], b_bytes);
-                    tma_load_2d(ring + (size_t)st * stage_bytes, tmb, &ctrl->full_b[st], e.chunk * p.rc,
-                                e.lora * n_s + n0_local);
+                if (!have_list && w.needs_list(n_base)) {
+                    if (!mbar_wait(&ctrl->list_ready, 0, limit_ns)) { record_timeout(p, ctrl, 2, w.it); break; }
+                    n_steps = ctrl->n_steps;
+                    have_list = true;
                 }
-                OB_TRACE(3)
+                const bool finished = w.done(n_base, n_steps);
+                if (!k1_done && (finished || w.it >= p.stages)) {
+                    // The ring is full (or everything is requested): from here on progress needs K1's x_q.  Wait for K1 and
+                    // request the x_q tile of every W slot issued so far.
+                    griddep_wait();
+                    OB_TRACE(4)
+                    k1_done = true;
+                    SlotWalk r;
+                    while (r.it < w.it) {
+                        const bool rb = r.is_b(n_base, n_steps);
+                        if (!rb) {
+                            const int st = r.it % p.stages;
+                            tma_load_2d(ring + (size_t)st * stage_bytes + kWTileBytes, &tm_x, &ctrl->full_w[st],
+                                        (kb0 + r.k) * kBlockK, t0);
+                        }
+                        r.advance(rb);
+                    }
+                }
+                if (finished) break;
+                const int st = w.it % p.stages;
+                const uint32_t bit = 1u << st;
+                if (w.it >= p.stages) {                 // wait until the slot's previous tenant was consumed
+                    if (last_b & bit) {
+                        OB_WAIT(&ctrl->empty_b[st], (par_b >> st) & 1u, 3, w.it)
+                        par_b ^= bit;
+                    } else {
+                        OB_WAIT(&ctrl->empty[st], (par_w >> st) & 1u, 1, w.it)
+                        par_w ^= bit;
+                    }
+                }
+                const bool isb = w.is_b(n_base, n_steps);
+                if (isb) {
+                    const LoraStep e = ctrl->steps[w.li];
+                    mbar_arrive_expect_tx(&ctrl->full_b[st], b_bytes);
+                    tma_load_2d(ring + (size_t)st * stage_bytes, tmb, &ctrl->full_b[st], e.chunk * p.rc, e.lora * n_s + n0_local);
+                    last_b |= bit;
+                } else {
+                    mbar_arrive_expect_tx(&ctrl->full_w[st], wx_bytes);
+                    tma_load_2d_hint(ring + (size_t)st * stage_bytes, &tm_w, &ctrl->full_w[st], (kb0 + w.k) * kBlockK,
+                                     slice_off + n0_local, pol);
+                    if (k1_done)
+                        tma_load_2d(ring + (size_t)st * stage_bytes + kWTileBytes, &tm_x, &ctrl->full_w[st],
+                                    (kb0 + w.k) * kBlockK, t0);
+                    last_b &= ~bit;
+                }
+                w.advance(isb);
             }
-        }
-    } else if (warp == 2) {
-        // =========================================================== x_q producer (depends on K1)
-        if (lane == 0) {
-            griddep_wait();
-            OB_TRACE(4)
-            for (int it = 0; it < n_base; ++it) {
-                const int st = it % p.stages, use = it / p.stages;
-                if (ctrl->abort_flag) break;
-                if (use > 0) OB_WAIT(&ctrl->empty[st], (uint32_t)((use - 1) & 1), 4, it)
-                mbar_arrive_expect_tx(&ctrl->full_x[st], (uint32_t)tn * kBlockK);
-                tma_load_2d(ring + (size_t)st * stage_bytes + kWTileBytes, &tm_x, &ctrl->full_x[st], (kb0 + it) * kBlockK, t0);
-            }
+            OB_TRACE(3)
         }
     } else if (warp == 1) {
         // =========================================================== MMA issuer
         if (lane == 0) {
             const uint32_t idesc8 = umma_idesc(0, 0, kTileN, (uint32_t)tn);
             const uint32_t idesc16 = umma_idesc(1, 1, kTileN, (uint32_t)tn);
-            int it = 0;
-            for (; it < n_base; ++it) {
-                const int st = it % p.stages, use = it / p.stages;
-                if (ctrl->abort_flag) break;
-                OB_WAIT(&ctrl->full_w[st], (uint32_t)(use & 1), 5, it)
-                OB_WAIT(&ctrl->full_x[st], (uint32_t)(use & 1), 6, it)
-                if (it == 0) { OB_TRACE(5) }
-                tc_fence_after();
-                const uint32_t wa = smem_u32(ring + (size_t)st * stage_bytes);
-                const uint64_t dw = umma_smem_desc(wa, 1024, 2);
-                const uint64_t dx = umma_smem_desc(wa + kWTileBytes, 1024, 2);
+            const uint32_t row_bytes = (uint32_t)p.rc * 2;                 // 32, 64 or 128
+            const uint32_t lt = row_bytes == 128 ? 2u : row_bytes == 64 ? 4u : 6u;
+            const uint32_t sbo = row_bytes * 8;
+            SlotWalk w;
+            uint32_t par_w = 0, par_b = 0;
+            int n_steps = 0;
+            bool have_list = false, ok = true;
+            for (;;) {
+                if (ctrl->abort_flag) { ok = false; break; }
+                if (!have_list && w.needs_list(n_base)) {
+                    if (!mbar_wait(&ctrl->list_ready, 0, limit_ns)) { record_timeout(p, ctrl, 7, w.it); ok = false; break; }
+                    n_steps = ctrl->n_steps;
+                    have_list = true;
+                }
+                if (w.done(n_base, n_steps)) break;
+                const int st = w.it % p.stages;
+                const uint32_t bit = 1u << st;
+                const bool isb = w.is_b(n_base, n_steps);
+                if (!isb) {
+                    if (!mbar_wait(&ctrl->full_w[st], (par_w >> st) & 1u, limit_ns)) { record_timeout(p, ctrl, 5, w.it); ok = false; break; }
+                    par_w ^= bit;
+                    if (w.k == 0) { OB_TRACE(5) }
+                    tc_fence_after();
+                    const uint32_t wa = smem_u32(ring + (size_t)st * stage_bytes);
+                    const uint64_t dw = umma_smem_desc(wa, 1024, 2);
+                    const uint64_t dx = umma_smem_desc(wa + kWTileBytes, 1024, 2);
 #pragma unroll
-                for (int k = 0; k < kBlockK / 32; ++k)
-                    umma_f8f6f4(acc0, dw + (uint64_t)(k * 2), dx + (uint64_t)(k * 2), idesc8, (it > 0 || k > 0) ? 1u : 0u);
-                umma_commit(&ctrl->empty[st]);
-            }
-            OB_TRACE(6)
-            if (cc) {
-                if (it == n_base && !ctrl->abort_flag) umma_commit(&ctrl->acc_full);
-            } else if (it == n_base && !ctrl->abort_flag) {
-                bool ok = mbar_wait(&ctrl->list_ready, 0, limit_ns);
-                if (!ok) record_timeout(p, ctrl, 7, 0);
-                const int n_steps = ok ? ctrl->n_steps : 0;
-                const uint32_t row_bytes = (uint32_t)p.rc * 2;                 // 32, 64 or 128
-                const uint32_t lt = row_bytes == 128 ? 2u : row_bytes == 64 ? 4u : 6u;
-                const uint32_t sbo = row_bytes * 8;
-                int li = 0;
-                for (; li < n_steps; ++li, ++it) {
-                    const int st = it % p.stages;
-                    const int hb = li & 1, hu = li >> 1;
-                    if (ctrl->abort_flag) break;
-                    OB_WAIT(&ctrl->full_b[st], (uint32_t)((li / p.stages) & 1), 8, it)
-                    OB_WAIT(&ctrl->h_full[hb], (uint32_t)(hu & 1), 9, it)
+                    for (int k = 0; k < kBlockK / 32; ++k)
+                        umma_f8f6f4(acc0, dw + (uint64_t)(k * 2), dx + (uint64_t)(k * 2), idesc8, (w.k > 0 || k > 0) ? 1u : 0u);
+                    umma_commit(&ctrl->empty[st]);
+                    if (w.k == n_base - 1) { OB_TRACE(6) }
+                } else if (!cc) {
+                    const int hb = w.li & 1, hu = w.li >> 1;
+                    if (!mbar_wait(&ctrl->full_b[st], (par_b >> st) & 1u, limit_ns)) { record_timeout(p, ctrl, 8, w.it); ok = false; break; }
+                    par_b ^= bit;
+                    if (!mbar_wait(&ctrl->h_full[hb], (uint32_t)(hu & 1), limit_ns)) { record_timeout(p, ctrl, 9, w.it); ok = false; break; }
                     tc_fence_after();
                     const uint64_t db = umma_smem_desc(smem_u32(ring + (size_t)st * stage_bytes), sbo, lt);
                     const uint64_t dh = umma_smem_desc(smem_u32(hbuf + (size_t)hb * h_bytes), sbo, lt);
                     for (int k = 0; k < p.rc / 16; ++k)
-                        umma_f16(acc1, db + (uint64_t)(k * 2), dh + (uint64_t)(k * 2), idesc16, (li > 0 || k > 0) ? 1u : 0u);
+                        umma_f16(acc1, db + (uint64_t)(k * 2), dh + (uint64_t)(k * 2), idesc16, (w.li > 0 || k > 0) ? 1u : 0u);
                     umma_commit(&ctrl->empty_b[st]);
                     umma_commit(&ctrl->h_empty[hb]);
                 }
-                if (li == n_steps && !ctrl->abort_flag) umma_commit(&ctrl->acc_full);
+                w.advance(isb);
             }
+            if (ok) umma_commit(&ctrl->acc_full);
         }
     } else if (warp >= 4) {
         // =========================================================== segment index, H tiles, epilogue
@@ -340,14 +375,22 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
             if (te == 0) { OB_TRACE(9) }
             // ---- expand steps: B tiles arrive in the ring behind the W tiles.  Each warp follows the barriers on its own
             //      (no CTA-wide sync per step) and frees the slot with one arrival per warp.
-            for (int li = 0; li < n_steps; ++li) {
-                const int it = n_base + li;
-                const int st = it % p.stages;
+            SlotWalk w;
+            uint32_t par_b = 0;
+            while (w.li < n_steps) {
+                const bool isb = w.is_b(n_base, n_steps);
+                if (!isb) {
+                    w.advance(false);
+                    continue;
+                }
+                const int li = w.li;
+                const int st = w.it % p.stages;
                 if (ctrl->abort_flag) break;
-                if (!mbar_wait(&ctrl->full_b[st], (uint32_t)((li / p.stages) & 1), limit_ns)) {
-                    if (lane == 0) record_timeout(p, ctrl, 12, it);
+                if (!mbar_wait(&ctrl->full_b[st], (par_b >> st) & 1u, limit_ns)) {
+                    if (lane == 0) record_timeout(p, ctrl, 12, w.it);
                     break;
                 }
+                par_b ^= 1u << st;
                 const LoraStep e = ctrl->steps[li];
                 const uint8_t* btile = ring + (size_t)st * stage_bytes;
                 const uint32_t row_off = (uint32_t)n_local * (uint32_t)row_bytes;
@@ -374,6 +417,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                 }
                 __syncwarp();                                     // every lane has read its B row
                 if (lane == 0) mbar_arrive(&ctrl->empty_b[st]);
+                w.advance(true);
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
         } else {
@@ -487,17 +531,16 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
             }
             if (te == 0) { OB_TRACE(12) }
             if (p.split2 > 1) {
-                __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, 128;" ::: "memory");    // all 128 threads' partials precede the arrival below
                 if (te == 0) {
-                    const int old = atomicAdd(p.counters + tile_lin, 1);
+                    int old;                                      // release our partials, acquire the other splits'
+                    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + tile_lin) : "memory");
                     ctrl->last_flag = (old == p.split2 - 1) ? 1 : 0;
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (ctrl->last_flag) {
                     // The last CTA of the tile adds the partials in split order.  Thread = 4 output features x every 4th
                     // token; 8 tokens' loads are in flight per split so the sum is not a chain of dependent L2 round trips.
-                    __threadfence();
                     const float* pbase = p.part + (size_t)tile_lin * p.split2 * (size_t)tn * kTileN;
                     const int tg = te >> 5, n4 = (te & 31) * 4;
                     for (int cb = 0; cb < tn; cb += 32) {
