@@ -45,8 +45,9 @@ struct K2Ctrl {
     uint64_t full_b[12];   // B tiles of the expand steps: own barriers, so their consumers need not follow the base phases
     uint64_t empty[12];
     uint64_t empty_b[12];  // release of a slot that held a B tile (4 arrivals: one per expanding warp; 1 from the MMA warp)
-    uint64_t h_full[2];
-    uint64_t h_empty[2];
+    uint64_t h_full[8];
+    uint64_t h_empty[8];
+    uint64_t htab_ready;
     uint64_t list_ready;
     uint64_t acc_full;
     uint32_t tmem_base;
@@ -104,11 +105,13 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tn = p.tn;
     const int stage_bytes = kWTileBytes + tn * kBlockK;
-    const bool cc = p.expand_cc != 0;                          // expand on the CUDA cores (token tiles of 16 / 32)
+    const bool small = tn <= 32;                               // decode tiles: h table in shared memory + a builder warp
+    const int nh = p.nh;                                       // masked H tiles in flight
     const int h_bytes = (int)align_up((size_t)tn * p.rc * 2, 1024);
     uint8_t* ring = smem;
-    uint8_t* hbuf = ring + (size_t)p.stages * stage_bytes;    // cc: the fp32 h table [tn][R]; else two masked H tiles
-    K2Ctrl* ctrl = reinterpret_cast<K2Ctrl*>(hbuf + (cc ? align_up((size_t)tn * p.R * 4, 1024) : 2 * (size_t)h_bytes));
+    uint8_t* hbuf = ring + (size_t)p.stages * stage_bytes;    // nh masked H tiles (UMMA layout)
+    uint8_t* htab = hbuf + (size_t)nh * h_bytes;              // small: bf16 h table [tn][R]
+    K2Ctrl* ctrl = reinterpret_cast<K2Ctrl*>(htab + (small ? align_up((size_t)tn * p.R * 2, 1024) : 0));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     griddep_launch_dependents();                               // the next kernel in the stream may start its own prologue
@@ -139,12 +142,13 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
             mbar_init(&ctrl->full_w[i], 1);
             mbar_init(&ctrl->full_b[i], 1);
             mbar_init(&ctrl->empty[i], 1);
-            mbar_init(&ctrl->empty_b[i], cc ? 4 : 1);
+            mbar_init(&ctrl->empty_b[i], 1);
         }
-        mbar_init(&ctrl->h_full[0], 1);
-        mbar_init(&ctrl->h_full[1], 1);
-        mbar_init(&ctrl->h_empty[0], 1);
-        mbar_init(&ctrl->h_empty[1], 1);
+        for (int i = 0; i < 8; ++i) {
+            mbar_init(&ctrl->h_full[i], 1);
+            mbar_init(&ctrl->h_empty[i], 1);
+        }
+        mbar_init(&ctrl->htab_ready, 1);
         mbar_init(&ctrl->list_ready, 1);
         mbar_init(&ctrl->acc_full, 1);
         ctrl->abort_flag = 0;
@@ -271,8 +275,8 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                         umma_f8f6f4(acc0, dw + (uint64_t)(k * 2), dx + (uint64_t)(k * 2), idesc8, (w.k > 0 || k > 0) ? 1u : 0u);
                     umma_commit(&ctrl->empty[st]);
                     if (w.k == n_base - 1) { OB_TRACE(6) }
-                } else if (!cc) {
-                    const int hb = w.li & 1, hu = w.li >> 1;
+                } else {
+                    const int hb = w.li % nh, hu = w.li / nh;
                     if (!mbar_wait(&ctrl->full_b[st], (par_b >> st) & 1u, limit_ns)) { record_timeout(p, ctrl, 8, w.it); ok = false; break; }
                     par_b ^= bit;
                     if (!mbar_wait(&ctrl->h_full[hb], (uint32_t)(hu & 1), limit_ns)) { record_timeout(p, ctrl, 9, w.it); ok = false; break; }
@@ -287,6 +291,49 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                 w.advance(isb);
             }
             if (ok) umma_commit(&ctrl->acc_full);
+        }
+    } else if (warp == 2) {
+        // =========================================================== masked-H builder (decode tiles)
+        // Step li multiplies B_l's tile with H = the h rows of tenant l's tokens, zero elsewhere.  The nh tiles start as
+        // zeros; per step the warp clears the rows the tile's previous step filled and copies this step's rows out of the h
+        // table -- one or two 128-byte rows in a mixed decode batch -- so it runs far ahead of the B tiles' arrival.
+        if (small) {
+            for (int i = lane; i < nh * h_bytes / 16; i += 32) reinterpret_cast<uint4*>(hbuf)[i] = make_uint4(0u, 0u, 0u, 0u);
+            bool ok = mbar_wait(&ctrl->list_ready, 0, limit_ns);
+            const int n_steps = ok ? ctrl->n_steps : 0;
+            if (ok && n_steps > 0) ok = mbar_wait(&ctrl->htab_ready, 0, limit_ns);
+            if (!ok && lane == 0) record_timeout(p, ctrl, 13, 0);
+            const int row_bytes = p.rc * 2, cpr = row_bytes / 16;
+            const uint32_t swz = (uint32_t)cpr - 1u;
+            for (int li = 0; ok && li < n_steps; ++li) {
+                const int hb = li % nh, hu = li / nh;
+                if (ctrl->abort_flag) break;
+                uint8_t* tile = hbuf + (size_t)hb * h_bytes;
+                if (hu > 0) {
+                    if (!mbar_wait(&ctrl->h_empty[hb], (uint32_t)((hu - 1) & 1), limit_ns)) {
+                        if (lane == 0) record_timeout(p, ctrl, 10, li);
+                        break;
+                    }
+                    const LoraStep o = ctrl->steps[li - nh];
+                    for (int c = lane; c < ((int)o.hi - (int)o.lo) * cpr; c += 32) {
+                        uint32_t off = (uint32_t)((int)o.lo + c / cpr) * (uint32_t)row_bytes + (uint32_t)(c % cpr) * 16u;
+                        off ^= ((off >> 7) & swz) << 4;
+                        *reinterpret_cast<uint4*>(tile + off) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    __syncwarp();
+                }
+                const LoraStep e = ctrl->steps[li];
+                for (int c = lane; c < ((int)e.hi - (int)e.lo) * cpr; c += 32) {
+                    const int row = (int)e.lo + c / cpr, c16 = c % cpr;
+                    const uint4 v = *reinterpret_cast<const uint4*>(htab + ((size_t)row * p.R + (size_t)e.chunk * p.rc) * 2 + (size_t)c16 * 16);
+                    uint32_t off = (uint32_t)row * (uint32_t)row_bytes + (uint32_t)c16 * 16u;
+                    off ^= ((off >> 7) & swz) << 4;
+                    *reinterpret_cast<uint4*>(tile + off) = v;
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctrl->h_full[hb]);
+            }
         }
     } else if (warp >= 4) {
         // =========================================================== segment index, H tiles, epilogue
@@ -345,84 +392,41 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
         const uint32_t swz = (uint32_t)cpr - 1u;
         const int q = warp & 3;
         const int n_local = q * 32 + lane;
-        float accl[32];                                       // cc mode: this thread's LoRA sums, one per token of the tile
-#pragma unroll
-        for (int c = 0; c < 32; ++c) accl[c] = 0.0f;
-
-        if (cc) {
-            // ---- h table: bf16( sum over K1's splits, in split order ), widened back to fp32, for every token of the tile
-            float* htab = reinterpret_cast<float*>(hbuf);
+        if (small) {
+            // ---- h table: bf16( sum over K1's splits, in split order ) for every token of the tile, once
             if (n_steps > 0) {
-                const int groups = p.R / 4;
+                const int groups = p.R / 8;
                 for (int idx = te; idx < tn * groups; idx += 128) {
-                    const int row = idx / groups, g4 = idx % groups;
-                    float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    const int row = idx / groups, g8 = idx % groups;
+                    float acc[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) acc[u] = 0.0f;
                     if (t0 + row < n_all) {
                         for (int j1 = 0; j1 < p.split1; ++j1) {
-                            const float4 u = __ldcg(reinterpret_cast<const float4*>(
-                                p.hp + (((size_t)j1 * p.S + s) * p.max_m + (size_t)(t0 + row)) * p.R + (size_t)g4 * 4));
-                            acc.x += u.x; acc.y += u.y; acc.z += u.z; acc.w += u.w;
+                            const float4* src = reinterpret_cast<const float4*>(
+                                p.hp + (((size_t)j1 * p.S + s) * p.max_m + (size_t)(t0 + row)) * p.R + (size_t)g8 * 8);
+                            const float4 u0 = __ldcg(src), u1 = __ldcg(src + 1);
+                            acc[0] += u0.x; acc[1] += u0.y; acc[2] += u0.z; acc[3] += u0.w;
+                            acc[4] += u1.x; acc[5] += u1.y; acc[6] += u1.z; acc[7] += u1.w;
                         }
                     }
-                    acc.x = __bfloat162float(__float2bfloat16_rn(acc.x));
-                    acc.y = __bfloat162float(__float2bfloat16_rn(acc.y));
-                    acc.z = __bfloat162float(__float2bfloat16_rn(acc.z));
-                    acc.w = __bfloat162float(__float2bfloat16_rn(acc.w));
-                    *reinterpret_cast<float4*>(htab + (size_t)row * p.R + (size_t)g4 * 4) = acc;
+                    __nv_bfloat162 b0 = __floats2bfloat162_rn(acc[0], acc[1]);
+                    __nv_bfloat162 b1 = __floats2bfloat162_rn(acc[2], acc[3]);
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(acc[4], acc[5]);
+                    __nv_bfloat162 b3 = __floats2bfloat162_rn(acc[6], acc[7]);
+                    uint4 out;
+                    out.x = *reinterpret_cast<uint32_t*>(&b0);
+                    out.y = *reinterpret_cast<uint32_t*>(&b1);
+                    out.z = *reinterpret_cast<uint32_t*>(&b2);
+                    out.w = *reinterpret_cast<uint32_t*>(&b3);
+                    *reinterpret_cast<uint4*>(htab + ((size_t)row * p.R + (size_t)g8 * 8) * 2) = out;
                 }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (te == 0) { OB_TRACE(9) }
-            // ---- expand steps: B tiles arrive in the ring behind the W tiles.  Each warp follows the barriers on its own
-            //      (no CTA-wide sync per step) and frees the slot with one arrival per warp.
-            SlotWalk w;
-            uint32_t par_b = 0;
-            while (w.li < n_steps) {
-                const bool isb = w.is_b(n_base, n_steps);
-                if (!isb) {
-                    w.advance(false);
-                    continue;
-                }
-                const int li = w.li;
-                const int st = w.it % p.stages;
-                if (ctrl->abort_flag) break;
-                if (!mbar_wait(&ctrl->full_b[st], (par_b >> st) & 1u, limit_ns)) {
-                    if (lane == 0) record_timeout(p, ctrl, 12, w.it);
-                    break;
-                }
-                par_b ^= 1u << st;
-                const LoraStep e = ctrl->steps[li];
-                const uint8_t* btile = ring + (size_t)st * stage_bytes;
-                const uint32_t row_off = (uint32_t)n_local * (uint32_t)row_bytes;
-                for (int t = e.lo; t < (int)e.hi; ++t) {      // the tenant's tokens in this tile (1-2 in a mixed decode batch)
-                    const float4* hrow = reinterpret_cast<const float4*>(htab + (size_t)t * p.R + (size_t)e.chunk * p.rc);
-                    float a0 = 0.0f, a1 = 0.0f;
-                    for (int g = 0; g < p.rc / 16; ++g) {
-                        const uint32_t off = row_off + (uint32_t)g * 32u;
-                        const uint4 bq0 = *reinterpret_cast<const uint4*>(btile + (off ^ (((off >> 7) & swz) << 4)));
-                        const uint4 bq1 = *reinterpret_cast<const uint4*>(btile + ((off + 16u) ^ ((((off + 16u) >> 7) & swz) << 4)));
-                        const float4 h0 = hrow[g * 4 + 0], h1 = hrow[g * 4 + 1], h2 = hrow[g * 4 + 2], h3 = hrow[g * 4 + 3];
-                        a0 = fmaf(bf16_lo(bq0.x), h0.x, a0); a1 = fmaf(bf16_hi(bq0.x), h0.y, a1);
-                        a0 = fmaf(bf16_lo(bq0.y), h0.z, a0); a1 = fmaf(bf16_hi(bq0.y), h0.w, a1);
-                        a0 = fmaf(bf16_lo(bq0.z), h1.x, a0); a1 = fmaf(bf16_hi(bq0.z), h1.y, a1);
-                        a0 = fmaf(bf16_lo(bq0.w), h1.z, a0); a1 = fmaf(bf16_hi(bq0.w), h1.w, a1);
-                        a0 = fmaf(bf16_lo(bq1.x), h2.x, a0); a1 = fmaf(bf16_hi(bq1.x), h2.y, a1);
-                        a0 = fmaf(bf16_lo(bq1.y), h2.z, a0); a1 = fmaf(bf16_hi(bq1.y), h2.w, a1);
-                        a0 = fmaf(bf16_lo(bq1.z), h3.x, a0); a1 = fmaf(bf16_hi(bq1.z), h3.y, a1);
-                        a0 = fmaf(bf16_lo(bq1.w), h3.z, a0); a1 = fmaf(bf16_hi(bq1.w), h3.w, a1);
-                    }
-                    const float a = a0 + a1;
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) accl[c] += (c == t) ? a : 0.0f;   // keeps the sums in registers
-                }
-                __syncwarp();                                     // every lane has read its B row
-                if (lane == 0) mbar_arrive(&ctrl->empty_b[st]);
-                w.advance(true);
-            }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (te == 0) { mbar_arrive(&ctrl->htab_ready); OB_TRACE(9) }
         } else {
             for (int li = 0; li < n_steps; ++li) {
-                const int hb = li & 1, hu = li >> 1;
+                const int hb = li % nh, hu = li / nh;
                 if (te == 0) {                                    // one thread decides, so that all 128 leave together
                     int go = ctrl->abort_flag ? 0 : 1;
                     if (go && hu > 0 && !mbar_wait(&ctrl->h_empty[hb], (uint32_t)((hu - 1) & 1), limit_ns)) {
@@ -491,26 +495,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
             const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
             const bool has_lora = n_steps > 0;
             float* part = p.part + ((size_t)tile_lin * p.split2 + j) * (size_t)tn * kTileN;
-            if (cc) {
-#pragma unroll
-                for (int c0 = 0; c0 < 32; c0 += 16) {
-                    if (c0 < tn) {
-                        uint32_t r0[16];
-                        tmem_ld16(acc0 + lane_addr + (uint32_t)c0, r0);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) {
-                            const int row = ctrl->rowmap[c0 + c];
-                            const float v = fmaf(__uint_as_float(r0[c]), ctrl->sx[c0 + c] * s_w, accl[c0 + c]);
-                            if (p.split2 == 1) {
-                                if (row >= 0 && n_ok) p.y[(int64_t)row * p.ldy + n_glob] = __float2bfloat16_rn(v);
-                            } else {
-                                part[(size_t)(c0 + c) * kTileN + n_local] = v;
-                            }
-                        }
-                    }
-                }
-            } else {
+            {
                 for (int c0 = 0; c0 < tn; c0 += 16) {
                     uint32_t r0[16], r1[16];
                     tmem_ld16(acc0 + lane_addr + (uint32_t)c0, r0);
@@ -589,8 +574,11 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
     if (tid == 0) { OB_TRACE(14) }
 }
 
+int k2_fp8_h_tiles(int tn) { return tn <= 16 ? 8 : tn <= 32 ? 4 : 2; }
+
 size_t k2_fp8_smem_bytes(int tn, int stages, int rc, int R) {
-    const size_t aux = tn <= 32 ? align_up((size_t)tn * R * 4, 1024) : 2 * align_up((size_t)tn * rc * 2, 1024);
+    const size_t aux = (size_t)k2_fp8_h_tiles(tn) * align_up((size_t)tn * rc * 2, 1024) +
+                       (tn <= 32 ? align_up((size_t)tn * R * 2, 1024) : 0);
     return 1024 + (size_t)stages * (kWTileBytes + (size_t)tn * kBlockK) + aux + kCtrlBytes;
 }
 

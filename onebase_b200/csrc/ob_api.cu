@@ -8,6 +8,7 @@
 
 namespace ob {
 size_t k2_fp8_smem_bytes(int tn, int stages, int rc, int R);
+int k2_fp8_h_tiles(int tn);
 cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream);
 cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                           dim3 grid, size_t smem, int pdl, cudaStream_t stream);
@@ -256,7 +257,7 @@ int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     p.kblocks = (d.K + kBlockK - 1) / kBlockK;
     p.stages = r.stages;
     p.rc = l->rc;
-    p.expand_cc = r.tn <= 32 ? 1 : 0;
+    p.nh = k2_fp8_h_tiles(r.tn);
     p.max_m = sh->max_m;
     p.wait_ms = r.wait_ms;
     p.s_w = d.s_w;

@@ -90,7 +90,7 @@ struct K2Params {
     int kblocks;           // ceil(K / 128)
     int stages;
     int rc;                // rank chunk per expand step: min(R, 64)
-    int expand_cc;         // 1: expand on the CUDA cores (token tiles of 16 / 32); 0: bf16 MMAs into accumulator 1
+    int nh;                // masked H tiles in flight (expand steps the builder may run ahead of the B tiles)
     int max_m;
     uint32_t wait_ms;
     const float* s_w;
