@@ -67,8 +67,11 @@ static_assert(sizeof(K2Ctrl) <= kCtrlBytes, "control block too large");
 // of after them.  The number of expand steps is only needed from the first slot that could be a B tile.
 struct SlotWalk {
     int it = 0, k = 0, li = 0;
-    __device__ bool needs_list(int n_base) const { return it % 3 == 2 || k >= n_base; }
-    __device__ bool is_b(int n_base, int n_steps) const { return li < n_steps && (k >= n_base || it % 3 == 2); }
+    int lead;   // slots at the start that are W tiles regardless: the first ring fill never waits for the segment index
+    __device__ explicit SlotWalk(int lead_slots) : lead(lead_slots) {}
+    __device__ bool b_slot() const { return it >= lead && (it - lead) % 3 == 2; }
+    __device__ bool needs_list(int n_base) const { return b_slot() || k >= n_base; }
+    __device__ bool is_b(int n_base, int n_steps) const { return li < n_steps && (k >= n_base || b_slot()); }
     __device__ bool done(int n_base, int n_steps) const { return k >= n_base && li >= n_steps; }
     __device__ void advance(bool was_b) {
         ++it;
@@ -179,7 +182,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
             const CUtensorMap* tmb = (s == 0) ? &tm_b0 : (s == 1) ? &tm_b1 : (s == 2) ? &tm_b2 : &tm_b3;
             const uint32_t b_bytes = (uint32_t)kTileN * p.rc * 2;
             const uint32_t wx_bytes = (uint32_t)kWTileBytes + (uint32_t)tn * kBlockK;
-            SlotWalk w;
+            SlotWalk w(p.stages);
             uint32_t par_w = 0, par_b = 0, last_b = 0;   // per slot: parity of the next release to await (W / B tenant), last tenant
             int n_steps = 0;
             bool have_list = false, k1_done = false;
@@ -197,7 +200,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                     griddep_wait();
                     OB_TRACE(4)
                     k1_done = true;
-                    SlotWalk r;
+                    SlotWalk r(p.stages);
                     while (r.it < w.it) {
                         const bool rb = r.is_b(n_base, n_steps);
                         if (!rb) {
@@ -247,7 +250,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
             const uint32_t row_bytes = (uint32_t)p.rc * 2;                 // 32, 64 or 128
             const uint32_t lt = row_bytes == 128 ? 2u : row_bytes == 64 ? 4u : 6u;
             const uint32_t sbo = row_bytes * 8;
-            SlotWalk w;
+            SlotWalk w(p.stages);
             uint32_t par_w = 0, par_b = 0;
             int n_steps = 0;
             bool have_list = false, ok = true;
