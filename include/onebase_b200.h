@@ -149,6 +149,25 @@ int ob_k1_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWor
 int ob_k2_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape,
               const ObTileCfg* cfg, int pdl, void* cuda_stream);
 
+/* K2 for callers that cannot allocate device memory for scratch: the same kernel and result as ob_k2_fp8, but its
+ * split-K scratch (fp32 partial tiles, per-tile arrival counters) lives in a fixed device array inside the library
+ * instead of the workspace's split-K region.  Meant for hosts that must not call cudaMalloc where this runs -- inside
+ * a stream capture, on a serving thread whose memory pool is frozen after warm-up, or from a runtime that hands the
+ * library nothing but its tensors -- and so cannot grow a workspace when a tile choice needs more split-K room.
+ * This entry point has no counterpart in the reference (its Triton host code allocates torch tensors freely).
+ *   - `workspace` must still hold what ob_k1_fp8 wrote for this batch (x_q, s_x, shrink partials) and receives the
+ *     status words; its own split-K region is neither needed nor touched (a shape with max_split2 = 1 is enough).
+ *   - limit: split2 * n_tiles * tn * 128 * 4 bytes of partials must fit OB_STATIC_SCRATCH_BYTES minus 16 KiB of
+ *     counters; larger requests return OB_ERR_TOO_LARGE before any launch.  Every GPU that loads the library holds
+ *     the array (OB_STATIC_SCRATCH_BYTES) until the process exits.
+ *   - the first call on each device resolves the array's device address and zeroes its counters on `cuda_stream`;
+ *     make that first call before any stream capture.  It calls no cudaMalloc / cudaFree or other allocating routine.
+ *   - all calls on a device share the one array: two calls that overlap on the GPU (different streams) race.  A call
+ *     leaves the counters at zero; the partial tiles keep the last call's contents and are overwritten before use. */
+#define OB_STATIC_SCRATCH_BYTES (8u << 20)
+int ob_k2_fp8_static(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape,
+                     const ObTileCfg* cfg, int pdl, void* cuda_stream);
+
 /* K1 then K2 linked by programmatic dependent launch: the decode chain `run_pdl` (lowbit_lora/hopper_pdl.py:104-175). */
 int ob_chain_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape,
                  const ObTileCfg* cfg, void* cuda_stream);

@@ -63,6 +63,8 @@ SYMBOLS = {
                             C.c_void_p]),
     "ob_k2_fp8": (C.c_int, [C.c_void_p, C.POINTER(ObBatch), C.c_void_p, C.POINTER(ObWorkspaceShape), C.POINTER(ObTileCfg),
                             C.c_int, C.c_void_p]),
+    "ob_k2_fp8_static": (C.c_int, [C.c_void_p, C.POINTER(ObBatch), C.c_void_p, C.POINTER(ObWorkspaceShape),
+                                   C.POINTER(ObTileCfg), C.c_int, C.c_void_p]),
     "ob_chain_fp8": (C.c_int, [C.c_void_p, C.POINTER(ObBatch), C.c_void_p, C.POINTER(ObWorkspaceShape),
                                C.POINTER(ObTileCfg), C.c_void_p]),
     "ob_segment_index": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,

@@ -291,9 +291,96 @@ int prepare_call(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape*
     return validate_workspace(l, ws, sh, r->split1, r->split2);
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// ob_k2_fp8_static: K2 for callers that cannot allocate device memory.  Its split-K scratch (fp32 partial tiles and
+// the per-tile arrival counters) lives in the file-scope device array below instead of the caller's workspace.  Every
+// GPU that loads this library holds the array until the process exits.
+constexpr size_t kStaticCounterBytes = sizeof(int32_t) * kCounterSlots;                      // 16 KiB of arrival counters
+constexpr size_t kStaticPartBytes = (size_t)OB_STATIC_SCRATCH_BYTES - kStaticCounterBytes;   // the rest: partial tiles
+static __device__ __align__(256) unsigned char g_k2_static_scratch[OB_STATIC_SCRATCH_BYTES];
+
+// Device address of the array on the current device, resolved once per device.  In host code the array's name is only a
+// stand-in symbol, not a device address, so the kernel must be given what cudaGetSymbolAddress returns.  The first call
+// on a device also zeroes the counters (a memset on the caller's stream; later launches return them to zero themselves).
+int static_scratch_for_current_device(cudaStream_t stream, unsigned char** out) {
+    static unsigned char* addr[64] = {nullptr};
+    static std::mutex mu;
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return OB_ERR_TOO_LARGE;
+    std::lock_guard<std::mutex> g(mu);
+    if (addr[dev] == nullptr) {
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_k2_static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaMemsetAsync(ptr, 0, kStaticCounterBytes, stream);
+        if (e != cudaSuccess) return (int)e;
+        addr[dev] = static_cast<unsigned char*>(ptr);
+    }
+    *out = addr[dev];
+    return OB_OK;
+}
+
 }  // namespace
 
 extern "C" {
+
+int ob_k2_fp8_static(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape,
+                     const ObTileCfg* cfg, int pdl, void* cuda_stream) {
+    Resolved r;
+    int st = validate_batch(layer, batch);
+    if (st != OB_OK) return st;
+    if (layer->d.base_fmt != OB_BASE_FP8 || layer->d.lora_fmt != OB_LORA_BF16) return OB_ERR_FORMAT;
+    st = resolve_cfg(layer, batch->M, cfg, &r);
+    if (st != OB_OK) return st;
+    // the workspace only has to hold what K1 wrote (and the status words): its own split-K region is not used
+    st = validate_workspace(layer, workspace, shape, r.split1, 1);
+    if (st != OB_OK) return st;
+    const size_t need = r.split2 > 1 ? (size_t)r.split2 * (size_t)layer->n_tiles * (size_t)r.tn * kTileN * sizeof(float) : 0;
+    if (need > kStaticPartBytes) return OB_ERR_TOO_LARGE;   // beyond the static scratch: use ob_k2_fp8 with a workspace
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    unsigned char* scratch = nullptr;
+    st = static_scratch_for_current_device(stream, &scratch);
+    if (st != OB_OK) return st;
+
+    const ObLayerDesc& d = layer->d;
+    const WorkspaceLayout lay = workspace_layout(*shape);
+    uint8_t* base = static_cast<uint8_t*>(workspace);
+    CUtensorMap tm_x;
+    st = get_xmap(layer, base + lay.xq, shape->max_m, r.tn, &tm_x);
+    if (st != OB_OK) return st;
+    K2Params p = {};
+    p.M = batch->M; p.N = d.N; p.K = d.K; p.S = d.S; p.R = d.R; p.L = d.L;
+    for (int s = 0; s < OB_MAX_SLICES; ++s) p.widths[s] = s < d.S ? d.widths[s] : 0;
+    p.lora_fmt = d.lora_fmt;
+    p.tn = r.tn;
+    p.split2 = r.split2;
+    p.split1 = r.split1;
+    p.kblocks = (d.K + kBlockK - 1) / kBlockK;
+    p.stages = r.stages;
+    p.rc = layer->rc;
+    p.nh = k2_fp8_h_tiles(r.tn);
+    p.max_m = shape->max_m;
+    p.wait_ms = r.wait_ms;
+    p.s_w = d.s_w;
+    p.sx = reinterpret_cast<const float*>(base + lay.sx);
+    p.hp = reinterpret_cast<const float*>(base + lay.hp);
+    p.meta = meta_of(batch);
+    p.y = static_cast<__nv_bfloat16*>(batch->y);
+    p.ldy = batch->ldy;
+    p.counters = reinterpret_cast<int32_t*>(scratch);                       // static scratch: arrival counters ...
+    p.part = reinterpret_cast<float*>(scratch + kStaticCounterBytes);       // ... and split-K partial tiles
+    p.status = reinterpret_cast<int32_t*>(base + lay.status);
+    for (int s = 0; s < d.S; ++s) { p.b[s] = d.b[s]; p.sb[s] = d.sb[s]; }
+    p.bg = d.bg;
+    p.trace = nullptr;
+    p.trace_ctas = 0;
+    dim3 grid((unsigned)layer->n_tiles, (unsigned)r.split2, (unsigned)r.m_tiles);
+    cudaError_t e = launch_k2_fp8(p, layer->tm_w, tm_x, layer->tm_b, grid, k2_fp8_smem_bytes(r.tn, r.stages, layer->rc, d.R),
+                                  pdl, stream);
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
 
 int ob_version(void) { return OB_ABI_VERSION; }
 
