@@ -1,25 +1,24 @@
 // K2 (FP8 base): y = bf16( s_x * s_w * (x_q W_q^T) + sum over tenants of h B^T ), one CTA per (128 output features,
-// token tile, K split), hand-written for sm_100a:
+// token tile, K split), two CTAs per SM, hand-written for sm_100a:
 //
 //   swap-AB orientation -- the 128 rows of the W tile sit on the MMA's M side, the tokens (16..256 per tile, adapter-
 //   sorted positions written by K1) on its N side, so a decode batch of 1..32 tokens wastes no tensor-core rows and the
-//   kernel is a pure stream of W from HBM.
+//   kernel is a pure stream of W (and the tenants' B) from HBM.
 //
-//   warp 0   TMA producer: W tiles [128 x 128 B] (128-byte swizzle) into a shared-memory ring, then -- through the same
-//            ring -- each expand step's B tile [128 x rank chunk] (bf16).  Independent of K1, so under programmatic
-//            dependent launch the whole ring fills while K1 is still running.
-//   warp 2   TMA producer of the x_q tiles [tokens x 128 B]; waits for K1 (griddepcontrol.wait) first.
+//   warp 0   the TMA producer.  One ring of shared-memory slots carries W tiles [128 x 128 B] (128-byte swizzle, L2
+//            evict-first) each with its x_q tile [tokens x 128 B], and the expand steps' B tiles [128 x rank chunk]
+//            (bf16), interleaved (SlotWalk) so that the tenants' B streams in between the W tiles instead of after them.
+//            W and B do not depend on K1: under programmatic dependent launch the ring fills while K1 still runs; the
+//            x_q tiles are requested after griddepcontrol.wait.
 //   warp 1   allocates TMEM and issues tcgen05.mma: kind::f8f6f4 (e4m3 x e4m3, fp32) into accumulator 0 for the base
-//            GEMM, kind::f16 (bf16) into accumulator 1 for the LoRA expand; tcgen05.commit releases ring slots.
-//   warps 4-7  read vLLM's segment index and list the (segment, rank chunk) expand steps of this tile.  After K1:
-//            * token tiles of 16 / 32 (decode): they sum K1's split-K partials once into a bf16 h table in shared memory and
-//              do the expand themselves on the CUDA cores, straight from the B tiles as these arrive in the ring -- thread
-//              n keeps its 32 token sums in registers, no per-step tile building, nothing on the tensor pipe's path;
-//            * larger token tiles (prefill): they build each step's masked H tile (the tenant's rows, zero elsewhere) in the
-//              UMMA layout and warp 1 issues the bf16 MMAs into accumulator 1.
-//            Finally the epilogue: tcgen05.ld, s_x*s_w*acc0 + LoRA, bf16 rows scattered back through the sort.  With
-//            split-K > 1 they write fp32 partials instead and the last CTA to arrive adds them in split order
-//            (deterministic) and resets the arrival counter.
+//            GEMM, kind::f16 (bf16) into accumulator 1 for each expand step; tcgen05.commit releases ring slots.
+//   warp 2   (decode tiles, <= 32 tokens) keeps masked H tiles ready: H of a step = the h rows of that tenant's tokens,
+//            zero elsewhere, in the UMMA layout; it only rewrites the one or two rows that change between steps.
+//   warps 4-7  read vLLM's segment index, list the (segment, rank chunk) expand steps of this tile; after K1 they sum
+//            its split-K partials once into a bf16 h table in shared memory (decode tiles) or build the masked H tiles
+//            themselves (larger tiles); finally the epilogue: tcgen05.ld both accumulators, s_x*s_w*acc0 + acc1, bf16
+//            rows scattered back through the sort.  With split-K > 1 they write fp32 partials instead and the last CTA
+//            to arrive adds them in split order (deterministic) and resets the arrival counter.
 //
 // What it computes is lowbit_lora/kernels/fp8_lora_vllm.py:123-284 (`_gemm_vllm`, BASE=True) and the decode-chain GEMM
 // lowbit_lora/kernels/fp8_lora_pdl.py:324-495; positions, padding and stale metadata follow fp8_lora_vllm.py:147-163.
