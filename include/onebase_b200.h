@@ -69,7 +69,8 @@ typedef struct ObLayerDesc {
     int32_t widths[OB_MAX_SLICES];   /* N_s, sum = N */
     int32_t max_m;                   /* largest token count of a call */
     const void* w_q;                 /* FP8: [N,K] e4m3.  NVFP4: [N,K/2] packed e2m1, element 2i in the low nibble */
-    const void* w_sf;                /* NVFP4: [N,K/16] ue4m3 block scales, linear (checkpoint) layout.  FP8: null */
+    const void* w_sf;                /* NVFP4: ue4m3 block scales PACKED by ob_nvfp4_pack_scales from the checkpoint's linear
+                                        [N,K/16] layout (ob_nvfp4_packed_scale_bytes bytes).  FP8: null */
     const float* s_w;                /* FP8: [1] per-tensor weight scale */
     const float* x_global;           /* NVFP4: [1] static activation global scale (1 / input_scale) */
     const float* alpha;              /* NVFP4: [1] 1 / (x_global * w_global) */
@@ -79,6 +80,8 @@ typedef struct ObLayerDesc {
     const void* sb[OB_MAX_SLICES];   /* FP8: fp32 [L,N_s].           NVFP4: ue4m3 [L,1,N_s,R/16] */
     const float* ag;                 /* NVFP4 adapters: fp32 [S,L] inverse global scales of A */
     const float* bg;                 /* NVFP4 adapters: fp32 [S,L] inverse global scales of B */
+    int32_t quant_rcp_approx;        /* NVFP4 base: 1 = reciprocals by rcp.approx.ftz (bit-identical to vLLM's CUDA quantizer,
+                                        nvfp4_lora_vllm.py:61-67), 0 = IEEE reciprocals (the torch recipe, :361-376) */
 } ObLayerDesc;
 
 /* One call's inputs and output: the arguments of `op(x, meta_args, out=...)`
@@ -171,6 +174,26 @@ int ob_k2_fp8_static(ObLayer* layer, const ObBatch* batch, void* workspace, cons
 /* K1 then K2 linked by programmatic dependent launch: the decode chain `run_pdl` (lowbit_lora/hopper_pdl.py:104-175). */
 int ob_chain_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape,
                  const ObTileCfg* cfg, void* cuda_stream);
+
+/* The NVFP4-base counterparts of ob_k1_fp8 / ob_k2_fp8 / ob_chain_fp8.  K1 quantizes x to e2m1 codes with one ue4m3
+ * scale per 16 elements against the static global scale (vLLM's scaled_fp4_quant recipe) and shrinks; K2 is the
+ * block-scaled tcgen05 GEMM (kind::mxf4nvf4, scale factors in TMEM) with the same expand.  Replace the launches of
+ * `_shrink_nvfp4` / `_gemm_nvfp4` (lowbit_lora/kernels/nvfp4_lora_vllm.py:591-630) and `run_pdl4`
+ * (lowbit_lora/blackwell_pdl.py:59-133). */
+int ob_k1_nvfp4(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape,
+                const ObTileCfg* cfg, void* cuda_stream);
+int ob_k2_nvfp4(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape,
+                const ObTileCfg* cfg, int pdl, void* cuda_stream);
+int ob_chain_nvfp4(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape,
+                   const ObTileCfg* cfg, void* cuda_stream);
+
+/* One-time re-layout of an NVFP4 weight's block scales from the checkpoint's linear [N, K/16] ue4m3 matrix (what the
+ * reference keeps before vLLM swizzles it, lowbit_lora/plugin.py:155-174) into the order K2 copies to TMEM: per
+ * (128-row output tile of a slice, 256-element K slot) four 512-byte atoms [row % 32][row / 32][4 scales], zero padded.
+ * `widths` are host integers.  The caller allocates `packed` (ob_nvfp4_packed_scale_bytes). */
+int ob_nvfp4_packed_scale_bytes(int32_t K, int32_t S, const int32_t* widths, size_t* bytes);
+int ob_nvfp4_pack_scales(const void* w_sf_linear, int32_t K, int32_t S, const int32_t* widths, void* packed,
+                         size_t packed_bytes, void* cuda_stream);
 
 /* Token sort + segment index on the device: vLLM's LoRAKernelMeta.prepare_tensors
  * (vllm/lora/ops/triton_ops/lora_kernel_metadata.py:110-168) incl. its stale-on-no-adapter behaviour.

@@ -30,7 +30,7 @@ class ObLayerDesc(C.Structure):
         ("L", C.c_int32), ("R", C.c_int32), ("widths", C.c_int32 * OB_MAX_SLICES), ("max_m", C.c_int32),
         ("w_q", C.c_void_p), ("w_sf", C.c_void_p), ("s_w", C.c_void_p), ("x_global", C.c_void_p), ("alpha", C.c_void_p),
         ("a", C.c_void_p * OB_MAX_SLICES), ("b", C.c_void_p * OB_MAX_SLICES), ("sa", C.c_void_p * OB_MAX_SLICES),
-        ("sb", C.c_void_p * OB_MAX_SLICES), ("ag", C.c_void_p), ("bg", C.c_void_p),
+        ("sb", C.c_void_p * OB_MAX_SLICES), ("ag", C.c_void_p), ("bg", C.c_void_p), ("quant_rcp_approx", C.c_int32),
     ]
 
 
@@ -67,6 +67,15 @@ SYMBOLS = {
                                    C.POINTER(ObTileCfg), C.c_int, C.c_void_p]),
     "ob_chain_fp8": (C.c_int, [C.c_void_p, C.POINTER(ObBatch), C.c_void_p, C.POINTER(ObWorkspaceShape),
                                C.POINTER(ObTileCfg), C.c_void_p]),
+    "ob_k1_nvfp4": (C.c_int, [C.c_void_p, C.POINTER(ObBatch), C.c_void_p, C.POINTER(ObWorkspaceShape), C.POINTER(ObTileCfg),
+                              C.c_void_p]),
+    "ob_k2_nvfp4": (C.c_int, [C.c_void_p, C.POINTER(ObBatch), C.c_void_p, C.POINTER(ObWorkspaceShape), C.POINTER(ObTileCfg),
+                              C.c_int, C.c_void_p]),
+    "ob_chain_nvfp4": (C.c_int, [C.c_void_p, C.POINTER(ObBatch), C.c_void_p, C.POINTER(ObWorkspaceShape),
+                                 C.POINTER(ObTileCfg), C.c_void_p]),
+    "ob_nvfp4_packed_scale_bytes": (C.c_int, [C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.POINTER(C.c_size_t)]),
+    "ob_nvfp4_pack_scales": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_int32), C.c_void_p, C.c_size_t,
+                                       C.c_void_p]),
     "ob_segment_index": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                    C.c_void_p, C.c_void_p]),
     "ob_trace_buffer": (C.c_int, [C.c_void_p, C.c_int64]),

@@ -1,5 +1,6 @@
-// K1 (FP8 base): per-token dynamic e4m3 quantization of the activations, fused in one launch with every tenant's LoRA
-// shrink h = x A^T.
+// K1: activation quantization -- per-token dynamic e4m3 for an FP8 base, or e2m1 codes with one ue4m3 scale per 16
+// elements against a static global scale for an NVFP4 base -- fused in one launch with every tenant's LoRA shrink
+// h = x A^T.
 //
 // One launch, two kinds of CTA (256 threads each):
 //   * CTAs [0, M): quantize one tile POSITION each.  Position p stands for row `position_row(p)` of x: the adapter-sorted
@@ -95,6 +96,77 @@ __device__ void quantize_position(const K1Params& p, int pos) {
     for (int i = tid + kQuantCache * kK1Threads; i < nvec; i += kK1Threads) out[i] = quant8(__ldg(xr + i), sx);
 }
 
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
+    f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
+}
+
+// e2m1 code of v (bit 3 = sign): round to nearest even on {0,.5,1,1.5,2,3,4,6}, saturating -- the threshold chain of
+// lowbit_lora/kernels/nvfp4_lora_vllm.py:70-76 (ties .25/1.25/2.5/5 go down, .75/1.75/3.5 go up).
+__device__ __forceinline__ uint32_t e2m1_code(float v) {
+    const float a = fabsf(v);
+    const uint32_t mag = (uint32_t)(a > 0.25f) + (uint32_t)(a >= 0.75f) + (uint32_t)(a > 1.25f) + (uint32_t)(a >= 1.75f) +
+                         (uint32_t)(a > 2.5f) + (uint32_t)(a >= 3.5f) + (uint32_t)(a > 5.0f);
+    return mag | (v < 0.0f ? 8u : 0u);
+}
+
+__device__ __forceinline__ float e4m3_to_float(uint32_t code) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)code));
+    return __half2float(__ushort_as_half((unsigned short)(h2 & 0xFFFFu)));
+}
+
+// NVFP4 activation quantization of one position (vLLM's scaled_fp4_quant recipe, lowbit_lora/kernels/nvfp4_lora_vllm.py:
+// 102-115 / 361-376): per 16-element block sf = e4m3_rn(min(gs * (blockmax * rcp(6)), 448)), out_scale = sf != 0 ?
+// rcp(sf * rcp(gs)) : 0, code = e2m1_rn(x * out_scale); codes packed two per byte (element 2i in the low nibble).  One
+// thread per block.  The scales go straight into K2's scale-factor atoms: [token tile][K slot][128-token block][MMA][r%32]
+// [r/32][4], r = position within the token tile.
+__device__ void quantize_position_nvfp4(const K1Params& p, int pos) {
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int sorted_row = p.meta.srt[pos];
+    int n_all, n_ad;
+    segment_totals(p.meta, p.L, lane, n_all, n_ad);
+    n_all = min(n_all, p.M);
+    const int row = (n_ad > 0 && pos < n_all) ? min(max(sorted_row, 0), p.M - 1) : pos;
+    const float gs = __ldg(p.x_global);
+    griddep_wait();
+    const uint4* xr = reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.ldx);
+    const float rcp6 = p.rcp_approx ? rcp_approx_ftz(6.0f) : __frcp_rn(6.0f);
+    const float rgs = p.rcp_approx ? rcp_approx_ftz(gs) : __frcp_rn(gs);
+    const int nblocks = p.K >> 4;
+    const int mt = pos / p.tn, r = pos % p.tn;
+    uint8_t* sf_tile = p.xsf + (size_t)mt * p.kslots * p.nblk * kSfSlotBytes;
+    const int sf_row = (r >> 7) * kSfSlotBytes + (r & 31) * 16 + ((r & 127) >> 5) * 4;
+    for (int b = tid; b < p.kslots * 16; b += kK1Threads) {
+        uint32_t sf_code = 0;
+        if (b < nblocks) {
+            float v[16];
+            unpack8(__ldg(xr + 2 * b), *reinterpret_cast<float(*)[8]>(&v[0]));
+            unpack8(__ldg(xr + 2 * b + 1), *reinterpret_cast<float(*)[8]>(&v[8]));
+            float vmax = 0.0f;
+#pragma unroll
+            for (int e = 0; e < 16; ++e) vmax = fmaxf(vmax, fabsf(v[e]));
+            const float sfv = fminf(__fmul_rn(gs, __fmul_rn(vmax, rcp6)), 448.0f);
+            sf_code = (uint32_t)cvt_e4m3x2(sfv, 0.0f) & 0xFFu;
+            const float sff = e4m3_to_float(sf_code);
+            float osc = 0.0f;
+            if (sff != 0.0f) {
+                const float den = __fmul_rn(sff, rgs);
+                osc = p.rcp_approx ? rcp_approx_ftz(den) : __frcp_rn(den);
+            }
+            uint32_t lo = 0, hi = 0;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                lo |= e2m1_code(__fmul_rn(v[e], osc)) << (4 * e);
+                hi |= e2m1_code(__fmul_rn(v[8 + e], osc)) << (4 * e);
+            }
+            *reinterpret_cast<uint2*>(p.xq + (size_t)pos * (size_t)(p.K >> 1) + (size_t)b * 8) = make_uint2(lo, hi);
+        }
+        // K slot b / 16, MMA (b % 16) / 4, scale b % 4; blocks past K are zero scales
+        sf_tile[(size_t)(b >> 4) * p.nblk * kSfSlotBytes + sf_row + ((b & 15) >> 2) * 512 + (b & 3)] = (uint8_t)sf_code;
+    }
+}
+
 // 32 lane-partial values per lane -> lane i holds the warp-wide sum of value i (31 shuffles).
 __device__ __forceinline__ float transpose_reduce32(float (&v)[32], int lane) {
 #pragma unroll
@@ -108,11 +180,6 @@ __device__ __forceinline__ float transpose_reduce32(float (&v)[32], int lane) {
         }
     }
     return v[0];
-}
-
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-    f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
-    f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
 }
 
 __device__ __forceinline__ void load_a8(uint4 (&av)[8], const __nv_bfloat16* a, int K, int k, bool act) {
@@ -293,7 +360,8 @@ __global__ void __launch_bounds__(kK1Threads) k1_fp8_kernel(const K1Params p) {
     griddep_launch_dependents();
     OB_TRACE1(0)
     if ((int)blockIdx.x < p.n_quant_ctas) {
-        quantize_position(p, blockIdx.x);
+        if (p.base_fmt == OB_BASE_NVFP4) quantize_position_nvfp4(p, blockIdx.x);
+        else quantize_position(p, blockIdx.x);
         OB_TRACE1(3)
         return;
     }

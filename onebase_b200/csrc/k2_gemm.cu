@@ -1,4 +1,5 @@
-// K2 (FP8 base): y = bf16( s_x * s_w * (x_q W_q^T) + sum over tenants of h B^T ), one CTA per (128 output features,
+// K2: y = bf16( scale * (x_q W_q^T) + sum over tenants of h B^T ) for an FP8 (e4m3, scale = s_x * s_w) or NVFP4 (e2m1 with
+// ue4m3 block scales, scale = alpha) base, one CTA per (128 output features,
 // token tile, K split), two CTAs per SM, hand-written for sm_100a:
 //
 //   swap-AB orientation -- the 128 rows of the W tile sit on the MMA's M side, the tokens (16..256 per tile, adapter-
@@ -11,7 +12,9 @@
 //            W and B do not depend on K1: under programmatic dependent launch the ring fills while K1 still runs; the
 //            x_q tiles are requested after griddepcontrol.wait.
 //   warp 1   allocates TMEM and issues tcgen05.mma: kind::f8f6f4 (e4m3 x e4m3, fp32) into accumulator 0 for the base
-//            GEMM, kind::f16 (bf16) into accumulator 1 for each expand step; tcgen05.commit releases ring slots.
+//            GEMM -- or, for an NVFP4 base, kind::mxf4nvf4.block_scale.scale_vec::4X with both operands' ue4m3 block
+//            scales copied from the slot into TMEM by tcgen05.cp -- and kind::f16 (bf16) into accumulator 1 for each
+//            expand step; tcgen05.commit releases ring slots.
 //   warp 2   (decode tiles, <= 32 tokens) keeps masked H tiles ready: H of a step = the h rows of that tenant's tokens,
 //            zero elsewhere, in the UMMA layout; it only rewrites the one or two rows that change between steps.
 //   warps 4-7  read vLLM's segment index, list the (segment, rank chunk) expand steps of this tile; after K1 they sum
@@ -99,14 +102,16 @@ __device__ __forceinline__ void record_timeout(const K2Params& p, K2Ctrl* c, int
         break;                                            \
     }
 
+template <bool FP4>
 __global__ void __launch_bounds__(kK2Threads, 2)
-k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
               const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
               const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_b3) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tn = p.tn;
-    const int stage_bytes = kWTileBytes + tn * kBlockK;
+    const int sf_bytes = FP4 ? kSfSlotBytes * (1 + p.nblk) : 0;   // W scales + activation scales of one K slot
+    const int stage_bytes = kWTileBytes + tn * kBlockK + sf_bytes;
     const bool small = tn <= 32;                               // decode tiles: h table in shared memory + a builder warp
     const int nh = p.nh;                                       // masked H tiles in flight
     const int h_bytes = (int)align_up((size_t)tn * p.rc * 2, 1024);
@@ -158,7 +163,11 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
         ctrl->last_flag = 0;
         fence_mbar_init();
     }
-    const uint32_t tmem_cols = (2 * tn <= 32) ? 32u : (uint32_t)(2 * tn);
+    // TMEM: two fp32 accumulators of tn columns; NVFP4 adds, per ring slot, 4 MMAs x (4 columns of W scales + 4 per
+    // 128-token block of activation scales)
+    const uint32_t sf_cols_per_slot = FP4 ? 16u * (1u + (uint32_t)p.nblk) : 0u;
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < 2u * (uint32_t)tn + sf_cols_per_slot * (uint32_t)p.stages) tmem_cols *= 2;
     if (warp == 1) {
         tmem_alloc(&ctrl->tmem_base, tmem_cols);
         tmem_relinquish();
@@ -180,7 +189,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
             const uint64_t pol = l2_policy_evict_first();
             const CUtensorMap* tmb = (s == 0) ? &tm_b0 : (s == 1) ? &tm_b1 : (s == 2) ? &tm_b2 : &tm_b3;
             const uint32_t b_bytes = (uint32_t)kTileN * p.rc * 2;
-            const uint32_t wx_bytes = (uint32_t)kWTileBytes + (uint32_t)tn * kBlockK;
+            const uint32_t wx_bytes = (uint32_t)kWTileBytes + (uint32_t)tn * kBlockK + (uint32_t)sf_bytes;
             SlotWalk w(p.stages);
             uint32_t par_w = 0, par_b = 0, last_b = 0;   // per slot: parity of the next release to await (W / B tenant), last tenant
             int n_steps = 0;
@@ -204,8 +213,12 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                         const bool rb = r.is_b(n_base, n_steps);
                         if (!rb) {
                             const int st = r.it % p.stages;
-                            tma_load_2d(ring + (size_t)st * stage_bytes + kWTileBytes, &tm_x, &ctrl->full_w[st],
-                                        (kb0 + r.k) * kBlockK, t0);
+                            uint8_t* slot = ring + (size_t)st * stage_bytes;
+                            tma_load_2d(slot + kWTileBytes, &tm_x, &ctrl->full_w[st], (kb0 + r.k) * kBlockK, t0);
+                            if (FP4)
+                                bulk_load(slot + kWTileBytes + tn * kBlockK + kSfSlotBytes,
+                                          p.xsf + ((size_t)blockIdx.z * p.kblocks + (kb0 + r.k)) * p.nblk * kSfSlotBytes,
+                                          (uint32_t)(kSfSlotBytes * p.nblk), &ctrl->full_w[st]);
                         }
                         r.advance(rb);
                     }
@@ -232,9 +245,17 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                     mbar_arrive_expect_tx(&ctrl->full_w[st], wx_bytes);
                     tma_load_2d_hint(ring + (size_t)st * stage_bytes, &tm_w, &ctrl->full_w[st], (kb0 + w.k) * kBlockK,
                                      slice_off + n0_local, pol);
-                    if (k1_done)
-                        tma_load_2d(ring + (size_t)st * stage_bytes + kWTileBytes, &tm_x, &ctrl->full_w[st],
-                                    (kb0 + w.k) * kBlockK, t0);
+                    uint8_t* slot = ring + (size_t)st * stage_bytes;
+                    if (FP4)
+                        bulk_load(slot + kWTileBytes + tn * kBlockK, p.wsf + ((size_t)blockIdx.x * p.kblocks + (kb0 + w.k)) * kSfSlotBytes,
+                                  kSfSlotBytes, &ctrl->full_w[st]);
+                    if (k1_done) {
+                        tma_load_2d(slot + kWTileBytes, &tm_x, &ctrl->full_w[st], (kb0 + w.k) * kBlockK, t0);
+                        if (FP4)
+                            bulk_load(slot + kWTileBytes + tn * kBlockK + kSfSlotBytes,
+                                      p.xsf + ((size_t)blockIdx.z * p.kblocks + (kb0 + w.k)) * p.nblk * kSfSlotBytes,
+                                      (uint32_t)(kSfSlotBytes * p.nblk), &ctrl->full_w[st]);
+                    }
                     last_b &= ~bit;
                 }
                 w.advance(isb);
@@ -246,6 +267,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
         if (lane == 0) {
             const uint32_t idesc8 = umma_idesc(0, 0, kTileN, (uint32_t)tn);
             const uint32_t idesc16 = umma_idesc(1, 1, kTileN, (uint32_t)tn);
+            const uint32_t idesc4 = umma_idesc_nvfp4(kTileN, (uint32_t)tn);
             const uint32_t row_bytes = (uint32_t)p.rc * 2;                 // 32, 64 or 128
             const uint32_t lt = row_bytes == 128 ? 2u : row_bytes == 64 ? 4u : 6u;
             const uint32_t sbo = row_bytes * 8;
@@ -272,9 +294,24 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
                     const uint32_t wa = smem_u32(ring + (size_t)st * stage_bytes);
                     const uint64_t dw = umma_smem_desc(wa, 1024, 2);
                     const uint64_t dx = umma_smem_desc(wa + kWTileBytes, 1024, 2);
+                    if (FP4) {
+                        // scale factors of this slot: shared memory -> this slot's TMEM columns, then the block-scaled MMAs
+                        const uint32_t sfs = wa + kWTileBytes + (uint32_t)tn * kBlockK;
+                        const uint32_t sft = tmem_base + 2u * (uint32_t)tn + (uint32_t)st * sf_cols_per_slot;
 #pragma unroll
-                    for (int k = 0; k < kBlockK / 32; ++k)
-                        umma_f8f6f4(acc0, dw + (uint64_t)(k * 2), dx + (uint64_t)(k * 2), idesc8, (w.k > 0 || k > 0) ? 1u : 0u);
+                        for (int k = 0; k < kBlockK / 32; ++k) {
+                            const uint32_t ta = sft + (uint32_t)k * 4u;
+                            const uint32_t tb = sft + 16u + (uint32_t)k * 4u * (uint32_t)p.nblk;
+                            tmem_cp_sf(ta, sf_smem_desc(sfs + (uint32_t)k * 512u));
+                            for (int b = 0; b < p.nblk; ++b)
+                                tmem_cp_sf(tb + 4u * (uint32_t)b, sf_smem_desc(sfs + kSfSlotBytes + ((uint32_t)b * 4u + (uint32_t)k) * 512u));
+                            umma_nvfp4(acc0, dw + (uint64_t)(k * 2), dx + (uint64_t)(k * 2), idesc4, ta, tb, (w.k > 0 || k > 0) ? 1u : 0u);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < kBlockK / 32; ++k)
+                            umma_f8f6f4(acc0, dw + (uint64_t)(k * 2), dx + (uint64_t)(k * 2), idesc8, (w.k > 0 || k > 0) ? 1u : 0u);
+                    }
                     umma_commit(&ctrl->empty[st]);
                     if (w.k == n_base - 1) { OB_TRACE(6) }
                 } else {
@@ -387,7 +424,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
 
         griddep_wait();                                       // K1's s_x and shrink partials from here on
         if (te == 0) { OB_TRACE(8) }
-        for (int c = te; c < tn; c += 128) ctrl->sx[c] = (t0 + c < p.M) ? p.sx[t0 + c] : 0.0f;
+        for (int c = te; c < tn; c += 128) ctrl->sx[c] = FP4 ? 1.0f : ((t0 + c < p.M) ? p.sx[t0 + c] : 0.0f);
 
         const int row_bytes = p.rc * 2;
         const int cpr = row_bytes / 16;                       // 16-byte chunks per tile row
@@ -493,7 +530,7 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
         if (done) {
             const bool n_ok = n0_local + n_local < n_s;
             const int n_glob = slice_off + n0_local + n_local;
-            const float s_w = __ldg(p.s_w);
+            const float s_w = FP4 ? __ldg(p.alpha) : __ldg(p.s_w);   // NVFP4: one scale 1 / (x_global * w_global)
             const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
             const bool has_lora = n_steps > 0;
             float* part = p.part + ((size_t)tile_lin * p.split2 + j) * (size_t)tn * kTileN;
@@ -578,20 +615,22 @@ k2_fp8_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const 
 
 int k2_fp8_h_tiles(int tn) { return tn <= 16 ? 8 : tn <= 32 ? 4 : 2; }
 
-size_t k2_fp8_smem_bytes(int tn, int stages, int rc, int R) {
+size_t k2_fp8_smem_bytes(int tn, int stages, int rc, int R, int fp4) {
+    const size_t sf = fp4 ? (size_t)kSfSlotBytes * (1 + (tn > 128 ? 2 : 1)) : 0;
     const size_t aux = (size_t)k2_fp8_h_tiles(tn) * align_up((size_t)tn * rc * 2, 1024) +
                        (tn <= 32 ? align_up((size_t)tn * R * 2, 1024) : 0);
-    return 1024 + (size_t)stages * (kWTileBytes + (size_t)tn * kBlockK) + aux + kCtrlBytes;
+    return 1024 + (size_t)stages * (kWTileBytes + (size_t)tn * kBlockK + sf) + aux + kCtrlBytes;
 }
 
-cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
-                          dim3 grid, size_t smem, int pdl, cudaStream_t stream) {
+template <bool FP4>
+static cudaError_t launch_k2_impl(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
+                                  dim3 grid, size_t smem, int pdl, cudaStream_t stream) {
     static int configured_for[64] = {0};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64 && !configured_for[dev]) {
-        e = cudaFuncSetAttribute(k2_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        e = cudaFuncSetAttribute(k2_kernel<FP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
         configured_for[dev] = 1;
     }
@@ -605,7 +644,17 @@ cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUte
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, k2_fp8_kernel, p, tm_w, tm_x, tm_b[0], tm_b[1], tm_b[2], tm_b[3]);
+    return cudaLaunchKernelEx(&cfg, k2_kernel<FP4>, p, tm_w, tm_x, tm_b[0], tm_b[1], tm_b[2], tm_b[3]);
+}
+
+cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
+                          dim3 grid, size_t smem, int pdl, cudaStream_t stream) {
+    return launch_k2_impl<false>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream);
+}
+
+cudaError_t launch_k2_nvfp4(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
+                            dim3 grid, size_t smem, int pdl, cudaStream_t stream) {
+    return launch_k2_impl<true>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream);
 }
 
 }  // namespace ob

@@ -7,11 +7,15 @@
 #include "ob_common.cuh"
 
 namespace ob {
-size_t k2_fp8_smem_bytes(int tn, int stages, int rc, int R);
+size_t k2_fp8_smem_bytes(int tn, int stages, int rc, int R, int fp4);
+cudaError_t launch_k2_nvfp4(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
+                            dim3 grid, size_t smem, int pdl, cudaStream_t stream);
 int k2_fp8_h_tiles(int tn);
 cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream);
 cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                           dim3 grid, size_t smem, int pdl, cudaStream_t stream);
+cudaError_t launch_pack_scales(const uint8_t* linear, int K, int S, const int32_t* widths, uint8_t* packed, size_t bytes,
+                               cudaStream_t stream);
 cudaError_t launch_segment_index(const int32_t* token_lora, int M, int L, int32_t* tok, int32_t* srt, int32_t* seg_n,
                                  int32_t* seg_start, int32_t* seg_ids, cudaStream_t stream);
 }  // namespace ob
@@ -105,6 +109,7 @@ int validate_desc(const ObLayerDesc* d) {
     if (!d->w_q) return OB_ERR_NULL;
     if (d->base_fmt == OB_BASE_FP8 && !d->s_w) return OB_ERR_NULL;
     if (d->base_fmt == OB_BASE_NVFP4 && (!d->w_sf || !d->x_global || !d->alpha)) return OB_ERR_NULL;
+    if (d->base_fmt == OB_BASE_NVFP4 && d->K % 32 != 0) return OB_ERR_SHAPE;
     if (!aligned16(d->w_q) || (d->w_sf && !aligned16(d->w_sf))) return OB_ERR_ALIGN;
     for (int s = 0; s < d->S; ++s) {
         if (!d->a[s] || !d->b[s]) return OB_ERR_NULL;
@@ -133,6 +138,8 @@ int validate_workspace(const ObLayer* l, const void* ws, const ObWorkspaceShape*
     return OB_OK;
 }
 
+int k_bytes(const ObLayerDesc& d) { return d.base_fmt == OB_BASE_NVFP4 ? d.K / 2 : d.K; }
+
 struct Resolved {
     int tn, split1, split2, stages, m_tiles, k_per_split, pb;
     uint32_t wait_ms;
@@ -146,8 +153,11 @@ int default_tn(int M) {
 
 int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     const ObLayerDesc& d = l->d;
-    const int kblocks = (d.K + kBlockK - 1) / kBlockK;
+    const bool fp4 = d.base_fmt == OB_BASE_NVFP4;
+    const int kblocks = (k_bytes(d) + kBlockK - 1) / kBlockK;
     r->tn = (cfg && cfg->tn) ? cfg->tn : default_tn(M);
+    if (fp4 && r->tn > 128 && !(cfg && cfg->tn)) r->tn = 128;   // NVFP4: scale factors share TMEM with the accumulators
+    if (fp4 && r->tn > 128) return OB_ERR_TILE;
     if (!(r->tn == 16 || r->tn == 32 || r->tn == 64 || r->tn == 128 || r->tn == 256)) return OB_ERR_TILE;
     r->m_tiles = (M + r->tn - 1) / r->tn;
     int split2 = (cfg && cfg->split2) ? cfg->split2 : 0;
@@ -174,12 +184,14 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     int stages = (cfg && cfg->stages) ? cfg->stages : 0;
     if (stages == 0) {   // prefer a footprint that lets two CTAs share an SM (3+ stages), else the deepest ring that fits
         stages = 12;
-        while (stages > 3 && k2_fp8_smem_bytes(r->tn, stages, rc, d.R) > kSmemTwoPerSm) --stages;
-        if (k2_fp8_smem_bytes(r->tn, stages, rc, d.R) > kSmemTwoPerSm) stages = 12;
+        while (stages > 3 && k2_fp8_smem_bytes(r->tn, stages, rc, d.R, d.base_fmt == OB_BASE_NVFP4) > kSmemTwoPerSm) --stages;
+        if (k2_fp8_smem_bytes(r->tn, stages, rc, d.R, d.base_fmt == OB_BASE_NVFP4) > kSmemTwoPerSm) stages = 12;
     }
     if (stages < 2 || stages > 12) return OB_ERR_TILE;
-    while (stages > 2 && k2_fp8_smem_bytes(r->tn, stages, rc, d.R) > kSmemLimit) --stages;
-    if (k2_fp8_smem_bytes(r->tn, stages, rc, d.R) > kSmemLimit) return OB_ERR_TILE;
+    while (stages > 2 && k2_fp8_smem_bytes(r->tn, stages, rc, d.R, d.base_fmt == OB_BASE_NVFP4) > kSmemLimit) --stages;
+    if (k2_fp8_smem_bytes(r->tn, stages, rc, d.R, d.base_fmt == OB_BASE_NVFP4) > kSmemLimit) return OB_ERR_TILE;
+    if (fp4)   // TMEM: 2 tn accumulator columns + 32 scale-factor columns per ring slot, 512 in all
+        while (stages > 2 && 2 * r->tn + 32 * stages > 512) --stages;
     r->stages = stages;
     if ((long long)(d.L < r->tn ? d.L : r->tn) * (d.R / rc) > kMaxLoraIters) return OB_ERR_TOO_LARGE;
     r->wait_ms = (cfg && cfg->wait_ms > 0) ? (uint32_t)cfg->wait_ms : 2000u;
@@ -199,7 +211,7 @@ int get_xmap(ObLayer* l, const void* xq, int rows, int tn, CUtensorMap* out) {
     m.base = xq;
     m.rows = rows;
     m.tn = tn;
-    int st = encode_2d(&m.tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, (uint64_t)l->d.K, (uint64_t)rows, (uint64_t)l->d.K,
+    int st = encode_2d(&m.tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, (uint64_t)k_bytes(l->d), (uint64_t)rows, (uint64_t)k_bytes(l->d),
                        kBlockK, (uint32_t)tn);
     if (st != OB_OK) return st;
     l->xmaps.push_back(m);
@@ -230,6 +242,13 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     p.sx = reinterpret_cast<float*>(base + lay.sx);
     p.hp = reinterpret_cast<float*>(base + lay.hp);
     p.max_m = sh->max_m;
+    p.base_fmt = d.base_fmt;
+    p.tn = r.tn;
+    p.nblk = r.tn > 128 ? 2 : 1;
+    p.kslots = (d.K + 255) / 256;
+    p.rcp_approx = d.quant_rcp_approx;
+    p.x_global = d.x_global;
+    p.xsf = base + lay.xsf;
     p.trace = g_trace ? g_trace + g_trace_ctas * OB_TRACE_EVENTS : nullptr;   // K1's stamps follow K2's
     p.trace_ctas = g_trace_ctas;
     const long long warps = (long long)p.n_pblocks * p.units_per_block;
@@ -254,10 +273,14 @@ int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     p.tn = r.tn;
     p.split2 = r.split2;
     p.split1 = r.split1;
-    p.kblocks = (d.K + kBlockK - 1) / kBlockK;
+    p.kblocks = (k_bytes(d) + kBlockK - 1) / kBlockK;
     p.stages = r.stages;
     p.rc = l->rc;
     p.nh = k2_fp8_h_tiles(r.tn);
+    p.wsf = static_cast<const uint8_t*>(d.w_sf);
+    p.xsf = base + lay.xsf;
+    p.alpha = d.alpha;
+    p.nblk = r.tn > 128 ? 2 : 1;
     p.max_m = sh->max_m;
     p.wait_ms = r.wait_ms;
     p.s_w = d.s_w;
@@ -278,14 +301,18 @@ int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
         if (lay.part + need > lay.total) return OB_ERR_WORKSPACE;
     }
     dim3 grid((unsigned)l->n_tiles, (unsigned)r.split2, (unsigned)r.m_tiles);
-    cudaError_t e = launch_k2_fp8(p, l->tm_w, tm_x, l->tm_b, grid, k2_fp8_smem_bytes(r.tn, r.stages, l->rc, d.R), pdl, stream);
+    const bool fp4 = d.base_fmt == OB_BASE_NVFP4;
+    const size_t smem = k2_fp8_smem_bytes(r.tn, r.stages, l->rc, d.R, fp4 ? 1 : 0);
+    cudaError_t e = fp4 ? launch_k2_nvfp4(p, l->tm_w, tm_x, l->tm_b, grid, smem, pdl, stream)
+                        : launch_k2_fp8(p, l->tm_w, tm_x, l->tm_b, grid, smem, pdl, stream);
     return e == cudaSuccess ? OB_OK : (int)e;
 }
 
-int prepare_call(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const ObTileCfg* cfg, Resolved* r) {
+int prepare_call(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const ObTileCfg* cfg, Resolved* r,
+                 int base_fmt = OB_BASE_FP8) {
     int st = validate_batch(l, b);
     if (st != OB_OK) return st;
-    if (l->d.base_fmt != OB_BASE_FP8 || l->d.lora_fmt != OB_LORA_BF16) return OB_ERR_FORMAT;
+    if (l->d.base_fmt != base_fmt || l->d.lora_fmt != OB_LORA_BF16) return OB_ERR_FORMAT;
     st = resolve_cfg(l, b->M, cfg, r);
     if (st != OB_OK) return st;
     return validate_workspace(l, ws, sh, r->split1, r->split2);
@@ -377,7 +404,7 @@ int ob_k2_fp8_static(ObLayer* layer, const ObBatch* batch, void* workspace, cons
     p.trace = nullptr;
     p.trace_ctas = 0;
     dim3 grid((unsigned)layer->n_tiles, (unsigned)r.split2, (unsigned)r.m_tiles);
-    cudaError_t e = launch_k2_fp8(p, layer->tm_w, tm_x, layer->tm_b, grid, k2_fp8_smem_bytes(r.tn, r.stages, layer->rc, d.R),
+    cudaError_t e = launch_k2_fp8(p, layer->tm_w, tm_x, layer->tm_b, grid, k2_fp8_smem_bytes(r.tn, r.stages, layer->rc, d.R, 0),
                                   pdl, stream);
     return e == cudaSuccess ? OB_OK : (int)e;
 }
@@ -433,9 +460,9 @@ int ob_layer_create(const ObLayerDesc* desc, ObLayer** out) {
     l->rc = desc->R < 64 ? desc->R : 64;
     l->n_tiles = 0;
     for (int s = 0; s < desc->S; ++s) l->n_tiles += (desc->widths[s] + kTileN - 1) / kTileN;
-    if (desc->base_fmt == OB_BASE_FP8) {
-        st = encode_2d(&l->tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, desc->w_q, (uint64_t)desc->K, (uint64_t)desc->N,
-                       (uint64_t)desc->K, kBlockK, kTileN);
+    {
+        const uint64_t kb = (uint64_t)k_bytes(*desc);   // bytes of one W row: K e4m3 codes or K/2 packed e2m1 pairs
+        st = encode_2d(&l->tm_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, desc->w_q, kb, (uint64_t)desc->N, kb, kBlockK, kTileN);
         if (st == OB_OK && desc->lora_fmt == OB_LORA_BF16) {
             for (int s = 0; s < OB_MAX_SLICES && st == OB_OK; ++s) {
                 const int ss = s < desc->S ? s : 0;   // unused slots repeat slice 0 so every kernel argument is a valid map
@@ -482,6 +509,57 @@ int ob_chain_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const Ob
     st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
     if (st != OB_OK) return st;
     return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
+}
+
+int ob_k1_nvfp4(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape, const ObTileCfg* cfg,
+                void* cuda_stream) {
+    Resolved r;
+    int st = prepare_call(layer, batch, workspace, shape, cfg, &r, OB_BASE_NVFP4);
+    if (st != OB_OK) return st;
+    return k1_fp8_impl(layer, batch, workspace, shape, r, 0, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int ob_k2_nvfp4(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape, const ObTileCfg* cfg,
+                int pdl, void* cuda_stream) {
+    Resolved r;
+    int st = prepare_call(layer, batch, workspace, shape, cfg, &r, OB_BASE_NVFP4);
+    if (st != OB_OK) return st;
+    return k2_fp8_impl(layer, batch, workspace, shape, r, pdl, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int ob_chain_nvfp4(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape, const ObTileCfg* cfg,
+                   void* cuda_stream) {
+    Resolved r;
+    int st = prepare_call(layer, batch, workspace, shape, cfg, &r, OB_BASE_NVFP4);
+    if (st != OB_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
+    if (st != OB_OK) return st;
+    return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
+}
+
+int ob_nvfp4_packed_scale_bytes(int32_t K, int32_t S, const int32_t* widths, size_t* bytes) {
+    if (!widths || !bytes) return OB_ERR_NULL;
+    if (K < 32 || K % 32 != 0 || S < 1 || S > OB_MAX_SLICES) return OB_ERR_SHAPE;
+    size_t tiles = 0;
+    for (int s = 0; s < S; ++s) {
+        if (widths[s] <= 0) return OB_ERR_SHAPE;
+        tiles += (size_t)(widths[s] + kTileN - 1) / kTileN;
+    }
+    *bytes = tiles * (size_t)((K + 255) / 256) * kSfSlotBytes;
+    return OB_OK;
+}
+
+int ob_nvfp4_pack_scales(const void* w_sf_linear, int32_t K, int32_t S, const int32_t* widths, void* packed,
+                         size_t packed_bytes, void* cuda_stream) {
+    size_t need = 0;
+    int st = ob_nvfp4_packed_scale_bytes(K, S, widths, &need);
+    if (st != OB_OK) return st;
+    if (!w_sf_linear || !packed) return OB_ERR_NULL;
+    if (packed_bytes < need) return OB_ERR_WORKSPACE;
+    cudaError_t e = launch_pack_scales(static_cast<const uint8_t*>(w_sf_linear), K, S, widths, static_cast<uint8_t*>(packed),
+                                       need, static_cast<cudaStream_t>(cuda_stream));
+    return e == cudaSuccess ? OB_OK : (int)e;
 }
 
 int ob_segment_index(const int32_t* token_lora, int32_t M, int32_t L, int32_t* tok, int32_t* srt, int32_t* seg_n,

@@ -14,6 +14,7 @@ constexpr int kTileN = 128;          // output features per GEMM tile (rows of W
 constexpr int kBlockK = 128;         // bytes of K per ring stage row (one 128-byte swizzle row)
 constexpr int kMaxLoraIters = 512;   // capacity of a CTA's list of (segment, rank chunk) expand steps
 constexpr int kCounterSlots = 4096;  // split-K arrival counters in the workspace
+constexpr int kSfSlotBytes = 2048;   // NVFP4: scale factors of 128 rows x one 256-element K slot (4 atoms of 512 bytes)
 
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -23,7 +24,7 @@ struct WorkspaceLayout {
     size_t counters;   // int32 [kCounterSlots]   zero between launches
     size_t sx;         // fp32  [max_m]           per-position activation scale
     size_t xq;         // bytes [max_m * max_k]   quantized activations, row pitch = the calling layer's K (FP8) or K/2
-    size_t xsf;        // bytes [max_m * max_k/16] NVFP4 activation block scales
+    size_t xsf;        // bytes NVFP4 activation block scales: [token tile][256-element K slot][128-token block][2048]
     size_t hp;         // fp32  [max_split1 * max_sr * max_m]  shrink partials [split][slice][position][rank]
     size_t part;       // fp32  [max_split2 * token tile * (max_n rounded to tiles)]  GEMM split-K partials
     size_t total;
@@ -36,7 +37,7 @@ __host__ __device__ inline WorkspaceLayout workspace_layout(const ObWorkspaceSha
     l.counters = off; off = align_up(off + sizeof(int32_t) * kCounterSlots, 1024);
     l.sx = off;       off = align_up(off + sizeof(float) * (size_t)s.max_m, 1024);
     l.xq = off;       off = align_up(off + (size_t)s.max_m * (size_t)s.max_k, 1024);
-    l.xsf = off;      off = align_up(off + (size_t)s.max_m * (size_t)(s.max_k / 16 + 16), 1024);
+    l.xsf = off;      off = align_up(off + ((size_t)s.max_m + 15) / 16 * (((size_t)s.max_k + 255) / 256) * kSfSlotBytes, 1024);
     l.hp = off;       off = align_up(off + sizeof(float) * (size_t)s.max_split1 * (size_t)s.max_sr * (size_t)s.max_m, 1024);
     const size_t n_pad = align_up((size_t)s.max_n, kTileN) + (size_t)OB_MAX_SLICES * kTileN;
     size_t m_pad = 16;                                        // split-K serves one token tile: min(max_m, 256) tokens
@@ -76,6 +77,11 @@ struct K1Params {
     float* sx;             // [M]
     float* hp;             // [split1][S][max_m][R]
     int max_m;
+    int base_fmt;          // OB_BASE_FP8: per-token e4m3 quantization; OB_BASE_NVFP4: e2m1 codes + ue4m3 scale per 16
+    int tn, nblk, kslots;  // NVFP4: K2's token tile, its 128-token scale blocks, 256-element K slots (scale layout)
+    int rcp_approx;        // NVFP4: 1 = rcp.approx.ftz reciprocals (vLLM's CUDA quantizer), 0 = IEEE (the torch recipe)
+    const float* x_global; // NVFP4: [1] static activation global scale
+    uint8_t* xsf;          // NVFP4: activation block scales, packed per (token tile, K slot) in scale-factor atoms
     unsigned long long* trace;   // optional timeline buffer (null: off); K1 stamps go after K2's region
     long long trace_ctas;
 };
@@ -105,6 +111,10 @@ struct K2Params {
     const void* b[OB_MAX_SLICES];
     const void* sb[OB_MAX_SLICES];
     const float* bg;
+    const uint8_t* wsf;    // NVFP4 base: W block scales, packed per (128-row tile, 256-element K slot) in scale-factor atoms
+    const uint8_t* xsf;    // NVFP4 base: K1's activation block scales, packed per (token tile, K slot)
+    const float* alpha;    // NVFP4 base: [1] 1 / (x_global * w_global)
+    int nblk;              // NVFP4 base: 128-token scale-factor blocks per token tile (1, or 2 for 256-token tiles)
     unsigned long long* trace;   // optional timeline buffer (null: off)
     long long trace_ctas;
 };

@@ -80,6 +80,12 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
     asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
     return p;
 }
+// 1-D bulk copy global -> this CTA's shared memory (16-byte aligned, size a multiple of 16); bytes counted on `bar`.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
 // Generic-proxy writes to shared memory -> visible to the async proxy (UMMA / TMA reads).
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -137,6 +143,33 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
         "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
+}
+// Instruction descriptor of the block-scaled kinds: e2m1 x e2m1 (format 1 of kind::mxf4nvf4), ue4m3 scales (one per 16
+// elements: scale_vec::4X, K = 64), fp32 accumulate, both operands K-major, scale-factor ids 0.
+__host__ __device__ constexpr uint32_t umma_idesc_nvfp4(uint32_t m, uint32_t n) {
+    return (1u << 7) | (1u << 10) | ((n >> 3) << 17) | (0u << 23) | ((m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_nvfp4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa_tmem,
+                                           uint32_t sfb_tmem, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %6, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n"
+        "}\n" ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+        : "memory");
+}
+// Shared memory -> TMEM copy of one 512-byte scale-factor atom (32 rows x 16 bytes), replicated to the four 32-lane
+// quarters: TMEM lane l, 4 columns from `taddr` <- shared row (l % 32).
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t smem_desc) {
+    asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+// Descriptor of an unswizzled K-major block whose rows are 16 bytes: 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t sf_smem_desc(uint32_t saddr) {
+    uint64_t d = static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4);
+    d |= static_cast<uint64_t>(128u >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    return d;
 }
 // TMEM -> registers: this warp's 32 lanes x 16 consecutive fp32 columns starting at taddr (lane field = 32 * (warp % 4)).
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {

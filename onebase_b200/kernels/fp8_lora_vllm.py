@@ -95,6 +95,8 @@ class VllmFusedFP8LoRA:
     per-slice buffers [L, 1, R, K] / [L, 1, N_s, R] (bf16, alpha/r folded into B); max_m = the engine's max tokens per
     forward.  Tokens are described by vLLM's LoRAKernelMeta tensors (tok, srt, seg_n, seg_start, seg_ids)."""
 
+    _K1, _K2, _CHAIN, _FMT = "ob_k1_fp8", "ob_k2_fp8", "ob_chain_fp8", "fp8"   # entry points and tile-table format key
+
     def __init__(self, w_q, s_w, a_stacked, b_stacked, max_m, *, split_k=None, lora_fp8=False, lora_fp4=False):
         if w_q.device.type != "cuda":
             raise RuntimeError("onebase_b200 runs on CUDA devices only (there is no CPU path)")
@@ -139,12 +141,15 @@ class VllmFusedFP8LoRA:
     def __del__(self):
         h = getattr(self, "_h", None)
         if h:
-            _lib.lib().ob_layer_destroy(h)
+            try:
+                _lib.lib().ob_layer_destroy(h)
+            except Exception:   # noqa: BLE001 - interpreter shutdown: the library may already be gone
+                pass
             self._h = None
 
     # ------------------------------------------------------------------------------------------------- tile choice
     def tile(self, M: int, cfg: dict | None = None) -> _lib.ObTileCfg:
-        c = dict(tile_for(_bucket(M), self.N, self.K, self.S, self.R, "fp8"))
+        c = dict(tile_for(_bucket(M), self.N, self.K, self.S, self.R, self._FMT))
         if self.split_k:
             c["split1"] = self.split_k
         if cfg:
@@ -174,12 +179,12 @@ class VllmFusedFP8LoRA:
         ws, sh = C.c_void_p(self.scratch.ptr), C.byref(self.scratch.shape)
         st = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
         if shrink and gemm and pdl:
-            _lib.call("ob_chain_fp8", self._h, C.byref(b), ws, sh, C.byref(t), st)
+            _lib.call(self._CHAIN, self._h, C.byref(b), ws, sh, C.byref(t), st)
         else:
             if shrink:
-                _lib.call("ob_k1_fp8", self._h, C.byref(b), ws, sh, C.byref(t), st)
+                _lib.call(self._K1, self._h, C.byref(b), ws, sh, C.byref(t), st)
             if gemm:
-                _lib.call("ob_k2_fp8", self._h, C.byref(b), ws, sh, C.byref(t), 0, st)
+                _lib.call(self._K2, self._h, C.byref(b), ws, sh, C.byref(t), 0, st)
         return y
 
     def warmup(self) -> None:

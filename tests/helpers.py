@@ -34,3 +34,16 @@ def oracle_y(d: dict, x: torch.Tensor, eff_ids: torch.Tensor) -> torch.Tensor:
 def max_err_ratio(y: torch.Tensor, ref: torch.Tensor) -> float:
     """max-abs-error / ||ref||_inf (the acceptance bound is 2e-2)."""
     return float((y.float().cpu() - ref).abs().max() / ref.abs().max().clamp_min(1e-30))
+
+
+def build_nvfp4_op(d: dict, max_m: int, device="cuda", **kw):
+    from onebase_b200.kernels.nvfp4_lora_vllm import VllmFusedNVFP4LoRA
+    a_st = tuple(t.to(device) for t in d["a_stacked"])
+    b_st = tuple(t.to(device) for t in d["b_stacked"])
+    return VllmFusedNVFP4LoRA(d["w_q4"].to(device), d["w_sf"].to(device), d["w_global"], d["x_global"], a_st, b_st, max_m, **kw)
+
+
+def oracle_y_nvfp4(d: dict, x: torch.Tensor, eff_ids: torch.Tensor) -> torch.Tensor:
+    from oracle import nvfp4 as on4
+    A, B = ofp8.stack_slices(d["a_stacked"], d["b_stacked"])
+    return on4.fused_projection(x, eff_ids, d["w_q4"], d["w_sf"], d["w_global"], d["x_global"], A, B, d["widths"])
