@@ -56,8 +56,9 @@ def test_quant_codes_and_scales_bit_exact_golden(golden, ci):
 
 def test_e2m1_ties_fixture(golden):
     g = golden("nvfp4")
-    x = t(g["ties_x"]).to(torch.bfloat16)                     # every tie point is exactly representable in bf16 ...
-    keep = (x.float() == t(g["ties_x"]))                      # ... except the "just above" probes, which are masked out
+    x16 = t(g["ties_x"]).to(torch.bfloat16)                   # every tie point is exactly representable in bf16 ...
+    keep = (x16.float() == t(g["ties_x"]))                    # ... except the "just above" probes, which are masked out
+    x = torch.cat([x16, torch.zeros_like(x16)], dim=1)        # K must be a multiple of 32: one more (all-zero) block per row
     M, K = x.shape
     d = _case(K, (128,), 16, 2, M)
     d["x_global"] = 1.0
@@ -68,9 +69,10 @@ def test_e2m1_ties_fixture(golden):
     xq, xsf = op.codes(M)
     q_ref, sf_ref = on4.quant(x, 1.0)
     assert torch.equal(xq.cpu(), q_ref) and torch.equal(u8(xsf).cpu(), u8(sf_ref))
+    assert int(u8(xsf).cpu()[:, 1].sum()) == 0                # the zero-scale guard: an all-zero block has scale 0, codes 0
     want = t(g["ties_q"])
-    both = keep.reshape(M, K // 2, 2).all(-1)
-    assert torch.equal(xq.cpu()[both], want[both])
+    both = keep.reshape(M, 8, 2).all(-1)
+    assert torch.equal(xq.cpu()[:, :8][both], want[both])
 
 
 @pytest.mark.parametrize("K,widths,R,L,M,kind", [
