@@ -1,0 +1,167 @@
+"""Tensor-parallel sharding of the fused projection, as vLLM shards LoRA linear layers.
+
+Column-parallel (qkv, gate_up): every slice's output rows are split across ranks -- W rows and B rows
+`[rank * w_s, (rank + 1) * w_s)` of each slice with `w_s = width_s / tp` (vllm/lora/layers/column_parallel_linear.py:
+251-262; for qkv the kv slices are replicated when there are fewer kv heads than ranks, :442-463); A is not sliced, so
+the whole shrink runs on every rank and there is NO collective.
+Row-parallel (o, down): K is split -- W columns and A columns `[rank * K/tp, (rank + 1) * K/tp)`, all of B
+(vllm/lora/layers/row_parallel_linear.py:32-40); each rank computes a partial base GEMM plus a partial LoRA term and the
+layer all-reduces `y [M, N]` (bf16, NCCL over NVLink) (:73-76).  This is the form the reference's plugin serves under
+LOWBIT_TP=1 (lowbit_lora/plugin.py:239-245).  The shard functions are plain tensor slicing and work on any device.
+"""
+from __future__ import annotations
+
+import json
+import os
+import statistics
+
+import torch
+
+
+def shard_column(w_q, a_stacked, b_stacked, tp: int, rank: int, replicate=()):
+    """Per-rank (w_q, a_stacked, b_stacked) of a column-parallel projection.  `replicate[s]` > 1 means slice s is
+    replicated over that many consecutive ranks (kv heads fewer than ranks)."""
+    widths = [t.shape[2] for t in b_stacked]
+    rows, b_out, off = [], [], 0
+    for s, w in enumerate(widths):
+        rep = replicate[s] if s < len(replicate) else 1
+        parts = max(1, tp // rep)
+        assert w % parts == 0, f"slice {s} of width {w} does not split into {parts} shards"
+        ws = w // parts
+        sid = rank // rep if rep > 1 else rank
+        lo = (sid % parts) * ws
+        rows.append(w_q[off + lo: off + lo + ws])
+        b_out.append(b_stacked[s][:, :, lo:lo + ws].contiguous())
+        off += w
+    return torch.cat(rows, 0).contiguous(), tuple(a_stacked), tuple(b_out)
+
+
+def shard_row(w_q, a_stacked, b_stacked, tp: int, rank: int):
+    """Per-rank (w_q, a_stacked, b_stacked) of a row-parallel projection (K split; B whole)."""
+    K = w_q.shape[1]
+    assert K % tp == 0
+    ks = K // tp
+    lo = rank * ks
+    return (w_q[:, lo:lo + ks].contiguous(), tuple(a[..., lo:lo + ks].contiguous() for a in a_stacked), tuple(b_stacked))
+
+
+def shard_input_row(x, tp: int, rank: int):
+    """A row-parallel layer's input is already split along K (the previous column-parallel layer's output shard)."""
+    ks = x.shape[1] // tp
+    return x[:, rank * ks:(rank + 1) * ks].contiguous()
+
+
+def all_reduce_output(y: torch.Tensor, group=None) -> torch.Tensor:
+    """The row-parallel layer's exchange step: sum of the ranks' partial outputs (vLLM's tensor_model_parallel_all_reduce)."""
+    import torch.distributed as dist
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
+    return y
+
+
+# ------------------------------------------------------------------------------------------------------ benchmark
+QWEN3_8B = {"qkv": (4096, (4096, 1024, 1024), "col"), "o": (4096, (4096,), "row"),
+            "gate_up": (4096, (12288, 12288), "col"), "down": (12288, (4096,), "row")}
+L_SLOTS, RANK = 32, 64
+
+
+def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
+    """One Qwen3-8B decoder layer at tensor-parallel size `world` (one process per GPU, NCCL): column-parallel qkv /
+    gate_up, row-parallel o / down each followed by an all-reduce of y.  Strong scaling: the same M tokens on every N.
+    Device time per step with CUDA events (max over ranks), L2 flushed before every step."""
+    import torch.distributed as dist
+    from onebase_b200.kernels.fp8_lora_vllm import VllmFusedFP8LoRA
+    from onebase_b200.metadata import KernelMeta
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", device_id=dev)
+    M = args.m
+    warmup = max(3, args.warmup)
+    g = torch.Generator(device=dev).manual_seed(0)            # same seed on every rank: identical full tensors, then sharded
+    ids = torch.randint(0, L_SLOTS, (M,), generator=torch.Generator().manual_seed(0), dtype=torch.int32).to(dev)
+    km = KernelMeta.make(L_SLOTS, M, dev)
+    km.prepare_tensors(ids)
+    meta = km.meta_args(M)
+    layer = {}
+    for name, (K, widths, kind) in QWEN3_8B.items():
+        N = sum(widths)
+        w = torch.randn(N, K, device=dev, generator=g) * 0.02
+        s_w = (w.abs().max() / 448.0).reshape(1).float()
+        w_q = (w / s_w).to(torch.float8_e4m3fn)
+        del w
+        a_st = tuple(((torch.rand(L_SLOTS, 1, RANK, K, device=dev, generator=g) * 2 - 1) / K ** 0.5).to(torch.bfloat16)
+                     for _ in widths)
+        b_st = tuple((torch.randn(L_SLOTS, 1, n, RANK, device=dev, generator=g) * 0.01).to(torch.bfloat16) for n in widths)
+        x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+        if kind == "col":
+            rep = (1, max(1, world // 8), max(1, world // 8)) if name == "qkv" else ()
+            w_r, a_r, b_r = shard_column(w_q.view(torch.uint8), a_st, b_st, world, rank, rep)
+            x_r = x
+        else:
+            w_r, a_r, b_r = shard_row(w_q.view(torch.uint8), a_st, b_st, world, rank)
+            x_r = shard_input_row(x, world, rank)
+        del w_q, a_st, b_st
+        op = VllmFusedFP8LoRA(w_r.view(torch.float8_e4m3fn), s_w, a_r, b_r, max_m=M)
+        layer[name] = (op, x_r, torch.empty(M, op.N, dtype=torch.bfloat16, device=dev), kind)
+    torch.cuda.empty_cache()
+
+    def step():
+        for name in ("qkv", "o", "gate_up", "down"):
+            op, x, y, kind = layer[name]
+            op(x, meta, out=y)
+            if kind == "row":
+                dist.all_reduce(y)
+
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    graphed = True
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step()
+        run = graph.replay
+    except Exception:   # noqa: BLE001 - a collective that cannot be captured: time eager launches instead
+        graphed = False
+        torch.cuda.synchronize()
+        run = step
+    for _ in range(warmup):
+        flush.fill_(1)
+        run()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(args.steps):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        run()
+        e1.record()
+        e1.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = torch.tensor([statistics.fmean(ts)], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    status = layer["qkv"][0].scratch.status()
+    ok = torch.tensor([1 if status[0] == 0 else 0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        ms_v = float(ms.item())
+        print(json.dumps({
+            "metric": metric, "value": M / (ms_v * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": ms_v, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "fp8_e4m3", "data": "synthetic",
+            "config": {"workload": f"Qwen3-8B decoder layer at tensor-parallel {world}: column-parallel qkv / gate_up, row-parallel "
+                                   f"o / down + NCCL all-reduce of y; FP8 base, decode M={M}, 32 bf16 tenants rank 64",
+                       "l2": "flushed by a 256 MB write before every timed step", "cuda_graph": graphed},
+            "layer_us": ms_v * 1e3, "gpu_launches": 8 * args.steps, "device_status_ok": bool(ok.item()),
+            "e2e": None, "roofline": None, "cpu_baseline": None}))
+    dist.destroy_process_group()
