@@ -74,7 +74,8 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
     from onebase_b200.metadata import KernelMeta
     dev = torch.device(f"cuda:{local}")
     torch.cuda.set_device(dev)
-    dist.init_process_group("nccl", device_id=dev)
+    import datetime
+    dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     M = args.m
     warmup = max(3, args.warmup)
     g = torch.Generator(device=dev).manual_seed(0)            # same seed on every rank: identical full tensors, then sharded
@@ -105,32 +106,47 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
         layer[name] = (op, x_r, torch.empty(M, op.N, dtype=torch.bfloat16, device=dev), kind)
     torch.cuda.empty_cache()
 
-    def step():
-        for name in ("qkv", "o", "gate_up", "down"):
-            op, x, y, kind = layer[name]
+    def half(names):
+        for name in names:
+            op, x, y, _ = layer[name]
             op(x, meta, out=y)
-            if kind == "row":
-                dist.all_reduce(y)
+
+    def log(msg):
+        if os.environ.get("LOWBIT_VERBOSE"):
+            print(f"[tp rank {rank}] {msg}", flush=True)
 
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
-    for _ in range(2):
-        step()
+    y_o, y_down = layer["o"][2], layer["down"][2]
+    for _ in range(2):                                        # eager warm-up: kernels, scratch, NCCL communicator
+        half(("qkv", "o"))
+        dist.all_reduce(y_o)
+        half(("gate_up", "down"))
+        dist.all_reduce(y_down)
     torch.cuda.synchronize()
-    graphed = True
-    try:
+    log("eager warm-up done")
+    # The kernels of each half are captured in a CUDA graph; the two all-reduces are issued between the replays (NCCL is
+    # not captured: the collective stays an ordinary stream-ordered launch).
+    graphs = []
+    for names in (("qkv", "o"), ("gate_up", "down")):
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            step()
+            half(names)
         torch.cuda.current_stream().wait_stream(side)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            step()
-        run = graph.replay
-    except Exception:   # noqa: BLE001 - a collective that cannot be captured: time eager launches instead
-        graphed = False
-        torch.cuda.synchronize()
-        run = step
+        gph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gph):
+            half(names)
+        graphs.append(gph)
+    torch.cuda.synchronize()
+    log("graphs captured")
+    graphed = True
+
+    def run():
+        graphs[0].replay()
+        dist.all_reduce(y_o)
+        graphs[1].replay()
+        dist.all_reduce(y_down)
+
     for _ in range(warmup):
         flush.fill_(1)
         run()
@@ -161,7 +177,8 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
             "dtype": "fp8_e4m3", "data": "synthetic",
             "config": {"workload": f"Qwen3-8B decoder layer at tensor-parallel {world}: column-parallel qkv / gate_up, row-parallel "
                                    f"o / down + NCCL all-reduce of y; FP8 base, decode M={M}, 32 bf16 tenants rank 64",
-                       "l2": "flushed by a 256 MB write before every timed step", "cuda_graph": graphed},
+                       "l2": "flushed by a 256 MB write before every timed step",
+                       "cuda_graph": "two graphs of 4 kernels each; the NCCL all-reduces are launched between them" if graphed else "no"},
             "layer_us": ms_v * 1e3, "gpu_launches": 8 * args.steps, "device_status_ok": bool(ok.item()),
             "e2e": None, "roofline": None, "cpu_baseline": None}))
     dist.destroy_process_group()
