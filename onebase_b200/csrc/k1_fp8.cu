@@ -182,19 +182,88 @@ __device__ __forceinline__ float transpose_reduce32(float (&v)[32], int lane) {
     return v[0];
 }
 
-__device__ __forceinline__ void load_a8(uint4 (&av)[8], const __nv_bfloat16* a, int K, int k, bool act) {
+// The 8 rank rows a warp owns, in the adapter's storage format: bf16, e4m3 codes (fp32 scale per row, applied after the
+// dot) or packed e2m1 codes with one ue4m3 scale per 16 elements (and one fp32 global per adapter and slice, applied
+// after the dot) -- lowbit_lora/kernels/fp8_lora_vllm.py:85-118.  A lane always covers 8 consecutive K elements of each
+// row: 16, 8 or 4 bytes of codes (+ 1 scale byte).
+template <int FMT>
+struct ARows {
+    const uint8_t* base;      // row 0 of the 8 rows, element 0
+    const uint8_t* sbase;     // NVFP4: block scales of row 0
+    size_t row_bytes, srow_bytes;
+    __device__ __forceinline__ ARows(const K1Params& p, int lora, int s, int rg) {
+        const size_t row = (size_t)lora * p.R + (size_t)rg * 8;
+        row_bytes = FMT == kLoraBf16 ? (size_t)p.K * 2 : FMT == kLoraFp8 ? (size_t)p.K : (size_t)p.K / 2;
+        srow_bytes = (size_t)p.K / 16;
+        base = static_cast<const uint8_t*>(p.a[s]) + row * row_bytes;
+        sbase = FMT == kLoraNvfp4 ? static_cast<const uint8_t*>(p.sa[s]) + row * srow_bytes : nullptr;
+    }
+    // raw codes of the lane's 8 elements at column k of each row (x: codes; y: the block's scale byte for NVFP4)
+    __device__ __forceinline__ void load(uint4 (&av)[8], int k, bool act) const {
 #pragma unroll
-    for (int r = 0; r < 8; ++r) av[r] = act ? __ldg(reinterpret_cast<const uint4*>(a + (size_t)r * K + k)) : make_uint4(0u, 0u, 0u, 0u);
+        for (int r = 0; r < 8; ++r) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (act) {
+                if (FMT == kLoraBf16) {
+                    v = __ldg(reinterpret_cast<const uint4*>(base + r * row_bytes + (size_t)k * 2));
+                } else if (FMT == kLoraFp8) {
+                    const uint2 c = __ldg(reinterpret_cast<const uint2*>(base + r * row_bytes + (size_t)k));
+                    v.x = c.x; v.y = c.y;
+                } else {
+                    v.x = __ldg(reinterpret_cast<const uint32_t*>(base + r * row_bytes + (size_t)k / 2));
+                    v.y = __ldg(sbase + r * srow_bytes + (size_t)k / 16);
+                }
+            }
+            av[r] = v;
+        }
+    }
+};
+
+__device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t two_codes) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)two_codes));
+    return __half22float2(*reinterpret_cast<__half2*>(&h2));
+}
+
+__device__ __forceinline__ float e2m1_value(uint32_t code) {
+    const uint32_t mag = code & 7u;
+    float v = __uint_as_float(0x3F000000u + (mag << 22));          // magnitudes 2..7: 1, 1.5, 2, 3, 4, 6
+    v = mag == 0 ? 0.0f : (mag == 1 ? 0.5f : v);
+    return (code & 8u) ? -v : v;
+}
+
+template <int FMT>
+__device__ __forceinline__ void unpack_a(const uint4& v, float (&f)[8]) {
+    if (FMT == kLoraBf16) {
+        unpack8(v, f);
+    } else if (FMT == kLoraFp8) {
+        const float2 a = e4m3x2_to_float2(v.x & 0xFFFFu), b = e4m3x2_to_float2(v.x >> 16);
+        const float2 c = e4m3x2_to_float2(v.y & 0xFFFFu), d = e4m3x2_to_float2(v.y >> 16);
+        f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+    } else {
+        const float sf = e4m3_to_float(v.y & 0xFFu);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] = e2m1_value((v.x >> (4 * e)) & 15u) * sf;    // exact in bf16, as the reference notes
+    }
+}
+
+// Scale applied to a finished dot product: the row's fp32 scale (FP8-stored) or the adapter's inverse global (NVFP4-stored).
+template <int FMT>
+__device__ __forceinline__ float post_scale(const K1Params& p, int lora, int s, int row_in_slice) {
+    if (FMT == kLoraFp8) return __ldg(static_cast<const float*>(p.sa[s]) + (size_t)lora * p.R + row_in_slice);
+    if (FMT == kLoraNvfp4) return __ldg(p.ag + (size_t)s * p.L + lora);
+    return 1.0f;
 }
 
 // One pass of a warp: 8 rank rows [k0, k1) of adapter `lora`, slice s, times the `nt` (<= 4) tokens whose x rows are
 // rows[0..nt); writes the split-K partial hp[j][s][pos0 + t][rg*8 .. +8].  bf16 adapters.  The first block of A is
 // requested before the wait on the preceding kernel (A is static); x is read and hp written only after it.
-__device__ __forceinline__ void shrink_pass_bf16(const K1Params& p, int lora, int s, int rg, int j, int k0, int k1, int pos0,
+template <int FMT>
+__device__ __forceinline__ void shrink_pass(const K1Params& p, int lora, int s, int rg, int j, int k0, int k1, int pos0,
                                                  const int* rows, int nt, int lane) {
-    const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(p.a[s]) + ((size_t)lora * p.R + (size_t)rg * 8) * p.K;
+    const ARows<FMT> a(p, lora, s, rg);
     uint4 av[8];
-    load_a8(av, a, p.K, k0 + lane * 8, k0 + lane * 8 < k1);
+    a.load(av, k0 + lane * 8, k0 + lane * 8 < k1);
     OB_TRACE1(1)
     griddep_wait();
     OB_TRACE1(2)
@@ -220,7 +289,7 @@ __device__ __forceinline__ void shrink_pass_bf16(const K1Params& p, int lora, in
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
             float af[8];
-            unpack8(av[r], af);
+            unpack_a<FMT>(av[r], af);
 #pragma unroll
             for (int t = 0; t < 4; ++t) {
                 float sacc = acc[r * 4 + t];
@@ -229,18 +298,19 @@ __device__ __forceinline__ void shrink_pass_bf16(const K1Params& p, int lora, in
                 acc[r * 4 + t] = sacc;
             }
         }
-        if (kk + 256 < k1) load_a8(av, a, p.K, k + 256, k + 256 < k1);
+        if (kk + 256 < k1) a.load(av, k + 256, k + 256 < k1);
     }
     const float total = transpose_reduce32(acc, lane);
     const int r = lane >> 2, t = lane & 3;
-    if (t < nt) p.hp[(((size_t)j * p.S + s) * p.max_m + (pos0 + t)) * p.R + rg * 8 + r] = total;
+    if (t < nt) p.hp[(((size_t)j * p.S + s) * p.max_m + (pos0 + t)) * p.R + rg * 8 + r] = total * post_scale<FMT>(p, lora, s, rg * 8 + r);
 }
 
+template <int FMT>
 __device__ __forceinline__ void fma8(float (&acc)[8], const uint4 (&av)[8], const float (&xf)[8]) {
 #pragma unroll
     for (int r = 0; r < 8; ++r) {
         float af[8];
-        unpack8(av[r], af);
+        unpack_a<FMT>(av[r], af);
         float sacc = acc[r];
 #pragma unroll
         for (int e = 0; e < 8; ++e) sacc = fmaf(af[e], xf[e], sacc);
@@ -250,13 +320,14 @@ __device__ __forceinline__ void fma8(float (&acc)[8], const uint4 (&av)[8], cons
 
 // Decode form of the pass (one token): two K steps of A in flight per lane (8 KB per warp), both requested before the wait
 // on the preceding kernel.  8 lane-partials -> lanes 0..7 hold the 8 rank rows' sums (2 butterfly + 3 transposing steps).
-__device__ __forceinline__ void shrink_pass1_bf16(const K1Params& p, int lora, int s, int rg, int j, int k0, int k1, int pos,
+template <int FMT>
+__device__ __forceinline__ void shrink_pass1(const K1Params& p, int lora, int s, int rg, int j, int k0, int k1, int pos,
                                                   int row, int lane) {
-    const __nv_bfloat16* a = reinterpret_cast<const __nv_bfloat16*>(p.a[s]) + ((size_t)lora * p.R + (size_t)rg * 8) * p.K;
+    const ARows<FMT> a(p, lora, s, rg);
     const int kl = k0 + lane * 8;
     uint4 a0[8], a1[8];
-    load_a8(a0, a, p.K, kl, kl < k1);
-    load_a8(a1, a, p.K, kl + 256, kl + 256 < k1);
+    a.load(a0, kl, kl < k1);
+    a.load(a1, kl + 256, kl + 256 < k1);
     OB_TRACE1(1)
     griddep_wait();
     OB_TRACE1(2)
@@ -273,10 +344,10 @@ __device__ __forceinline__ void shrink_pass1_bf16(const K1Params& p, int lora, i
 #pragma unroll
             for (int e = 0; e < 8; ++e) x1[e] = 0.0f;
         }
-        fma8(acc, a0, x0);
-        load_a8(a0, a, p.K, k + 512, k + 512 < k1);
-        fma8(acc, a1, x1);
-        load_a8(a1, a, p.K, k + 768, k + 768 < k1);
+        fma8<FMT>(acc, a0, x0);
+        a.load(a0, k + 512, k + 512 < k1);
+        fma8<FMT>(acc, a1, x1);
+        a.load(a1, k + 768, k + 768 < k1);
     }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -293,13 +364,14 @@ __device__ __forceinline__ void shrink_pass1_bf16(const K1Params& p, int lora, i
             acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
         }
     }
-    if (lane < 8) p.hp[(((size_t)j * p.S + s) * p.max_m + pos) * p.R + rg * 8 + lane] = acc[0];
+    if (lane < 8) p.hp[(((size_t)j * p.S + s) * p.max_m + pos) * p.R + rg * 8 + lane] = acc[0] * post_scale<FMT>(p, lora, s, rg * 8 + lane);
 }
 
 // One warp: block `pb` of p.pb consecutive sorted positions, unit `u` -> (slice, group of 8 rank rows, K split).
 // One warp-wide read of the segment index gives the batch totals and the segment (adapter) of each of the warp's
 // positions; the positions' token rows are requested at the same time.  Then one pass per run of positions that share
 // an adapter.
+template <int FMT>
 __device__ void shrink_unit(const K1Params& p, int pb, int u, int lane) {
     const int p0 = pb * p.pb;
     int rows[4];
@@ -343,7 +415,7 @@ __device__ void shrink_unit(const K1Params& p, int pb, int u, int lane) {
     const int k0 = j * p.k_per_split;
     const int k1 = min(p.K, k0 + p.k_per_split);
     if (p.pb == 1) {
-        if (lora_of[0] >= 0) shrink_pass1_bf16(p, lora_of[0], s, rg, j, k0, k1, p0, rows[0], lane);
+        if (lora_of[0] >= 0) shrink_pass1<FMT>(p, lora_of[0], s, rg, j, k0, k1, p0, rows[0], lane);
         return;
     }
     int q = 0;
@@ -351,7 +423,7 @@ __device__ void shrink_unit(const K1Params& p, int pb, int u, int lane) {
         const int lora = lora_of[q];
         int nt = 1;
         while (q + nt < np && lora_of[q + nt] == lora) ++nt;
-        if (lora >= 0) shrink_pass_bf16(p, lora, s, rg, j, k0, k1, p0 + q, rows + q, nt, lane);
+        if (lora >= 0) shrink_pass<FMT>(p, lora, s, rg, j, k0, k1, p0 + q, rows + q, nt, lane);
         q += nt;
     }
 }
@@ -369,7 +441,9 @@ __global__ void __launch_bounds__(kK1Threads) k1_fp8_kernel(const K1Params p) {
     const int w = ((int)blockIdx.x - p.n_quant_ctas) * (kK1Threads / 32) + (threadIdx.x >> 5);
     const int pb = w / p.units_per_block;
     if (pb >= p.n_pblocks) return;
-    shrink_unit(p, pb, w % p.units_per_block, lane);
+    if (p.lora_fmt == kLoraFp8) shrink_unit<kLoraFp8>(p, pb, w % p.units_per_block, lane);
+    else if (p.lora_fmt == kLoraNvfp4) shrink_unit<kLoraNvfp4>(p, pb, w % p.units_per_block, lane);
+    else shrink_unit<kLoraBf16>(p, pb, w % p.units_per_block, lane);
     OB_TRACE1(3)
 }
 

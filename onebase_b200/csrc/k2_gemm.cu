@@ -81,6 +81,31 @@ struct SlotWalk {
     }
 };
 
+// Per-slot bookkeeping of the ring, identical in every role that hands slots out: which barrier frees slot `st` for reuse
+// (the one of its previous tenant: `empty` after a W tile, `empty_b` after a B tile) and with which phase parity.  Every
+// role that calls acquire() for EVERY slot, in order, stays in step whether or not it actually waits.
+struct RingBook {
+    uint32_t par_w = 0, par_b = 0, last_b = 0;
+    // returns 0: slot never used; 1: wait `empty[st]`; 2: wait `empty_b[st]`; the parity to wait for goes to `parity`
+    __device__ int acquire(int it, int st, int stages, bool is_b, uint32_t& parity) {
+        const uint32_t bit = 1u << st;
+        int kind = 0;
+        if (it >= stages) {
+            if (last_b & bit) {
+                kind = 2;
+                parity = (par_b >> st) & 1u;
+                par_b ^= bit;
+            } else {
+                kind = 1;
+                parity = (par_w >> st) & 1u;
+                par_w ^= bit;
+            }
+        }
+        if (is_b) last_b |= bit; else last_b &= ~bit;
+        return kind;
+    }
+};
+
 __device__ __forceinline__ void record_timeout(const K2Params& p, K2Ctrl* c, int where, int it) {
     c->abort_flag = 1;
     if (atomicCAS(p.status, OB_DEV_OK, OB_DEV_WAIT_TIMEOUT) == OB_DEV_OK) {
@@ -101,6 +126,77 @@ __device__ __forceinline__ void record_timeout(const K2Params& p, K2Ctrl* c, int
         record_timeout(p, ctrl, (where), (it));           \
         break;                                            \
     }
+
+__device__ __forceinline__ float k2_e2m1_value(uint32_t code) {
+    const uint32_t mag = code & 7u;
+    float v = __uint_as_float(0x3F000000u + (mag << 22));
+    v = mag == 0 ? 0.0f : (mag == 1 ? 0.5f : v);
+    return (code & 8u) ? -v : v;
+}
+
+__device__ __forceinline__ float k2_e4m3_value(uint32_t code) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)code));
+    return __half2float(__ushort_as_half((unsigned short)(h2 & 0xFFFFu)));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+    __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&b);
+}
+
+// Expand step e's B tile [128 rows x rank chunk] from a stored-format adapter into a ring slot, dequantized in
+// registers to bf16 with the scales folded in (one rounding), in the UMMA layout: thread `te` owns output row
+// n0_local + te.  FP8-stored: bf16(code * sb[l, n]); NVFP4-stored: bf16(e2m1 * block scale * bg[s, l])
+// (lowbit_lora/kernels/fp8_lora_vllm.py:249-278).  Rows past the slice's width are zero.
+__device__ __forceinline__ void fill_b_tile(const K2Params& p, const LoraStep& e, int s, int n_s, int n0_local, uint8_t* tile,
+                                            int te, int row_bytes, uint32_t swz) {
+    const int n = n0_local + te;
+    const bool ok = n < n_s;
+    const size_t row = (size_t)e.lora * n_s + (size_t)(ok ? n : 0);
+    const uint32_t row_off = (uint32_t)te * (uint32_t)row_bytes;
+    if (p.lora_fmt == kLoraFp8) {
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.b[s]) + row * p.R + (size_t)e.chunk * p.rc);
+        const float sc = ok ? __ldg(static_cast<const float*>(p.sb[s]) + row) : 0.0f;
+        for (int g = 0; g < p.rc / 16; ++g) {                  // 16 codes -> two 16-byte chunks of bf16
+            const uint4 c = ok ? __ldg(src + g) : make_uint4(0u, 0u, 0u, 0u);
+            const uint32_t w[4] = {c.x, c.y, c.z, c.w};
+            uint32_t o[8];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                o[2 * q] = pack_bf16x2(k2_e4m3_value(w[q] & 0xFFu) * sc, k2_e4m3_value((w[q] >> 8) & 0xFFu) * sc);
+                o[2 * q + 1] = pack_bf16x2(k2_e4m3_value((w[q] >> 16) & 0xFFu) * sc, k2_e4m3_value(w[q] >> 24) * sc);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t off = row_off + (uint32_t)(2 * g + h) * 16u;
+                off ^= ((off >> 7) & swz) << 4;
+                *reinterpret_cast<uint4*>(tile + off) = make_uint4(o[4 * h], o[4 * h + 1], o[4 * h + 2], o[4 * h + 3]);
+            }
+        }
+    } else {
+        const uint2* src = reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(p.b[s]) + (row * p.R + (size_t)e.chunk * p.rc) / 2);
+        const uint8_t* sfp = static_cast<const uint8_t*>(p.sb[s]) + row * (p.R / 16) + (size_t)e.chunk * p.rc / 16;
+        const float bg = __ldg(p.bg + (size_t)s * p.L + e.lora);
+        for (int g = 0; g < p.rc / 16; ++g) {                  // one block of 16 codes (8 bytes) + its scale
+            const uint2 c = ok ? __ldg(src + g) : make_uint2(0u, 0u);
+            const float sf = ok ? k2_e4m3_value(__ldg(sfp + g)) : 0.0f;
+            const uint32_t w[2] = {c.x, c.y};
+            uint32_t o[8];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+                const uint32_t b8 = (w[q >> 2] >> (8 * (q & 3))) & 0xFFu;      // two codes: element 2q in the low nibble
+                o[q] = pack_bf16x2(k2_e2m1_value(b8 & 15u) * sf * bg, k2_e2m1_value(b8 >> 4) * sf * bg);
+            }
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                uint32_t off = row_off + (uint32_t)(2 * g + h) * 16u;
+                off ^= ((off >> 7) & swz) << 4;
+                *reinterpret_cast<uint4*>(tile + off) = make_uint4(o[4 * h], o[4 * h + 1], o[4 * h + 2], o[4 * h + 3]);
+            }
+        }
+    }
+}
 
 template <bool FP4>
 __global__ void __launch_bounds__(kK2Threads, 2)
@@ -191,7 +287,8 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
             const uint32_t b_bytes = (uint32_t)kTileN * p.rc * 2;
             const uint32_t wx_bytes = (uint32_t)kWTileBytes + (uint32_t)tn * kBlockK + (uint32_t)sf_bytes;
             SlotWalk w(p.stages);
-            uint32_t par_w = 0, par_b = 0, last_b = 0;   // per slot: parity of the next release to await (W / B tenant), last tenant
+            RingBook book;
+            const bool b_by_tma = p.lora_fmt == kLoraBf16;
             int n_steps = 0;
             bool have_list = false, k1_done = false;
             for (;;) {
@@ -225,22 +322,20 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                 }
                 if (finished) break;
                 const int st = w.it % p.stages;
-                const uint32_t bit = 1u << st;
-                if (w.it >= p.stages) {                 // wait until the slot's previous tenant was consumed
-                    if (last_b & bit) {
-                        OB_WAIT(&ctrl->empty_b[st], (par_b >> st) & 1u, 3, w.it)
-                        par_b ^= bit;
-                    } else {
-                        OB_WAIT(&ctrl->empty[st], (par_w >> st) & 1u, 1, w.it)
-                        par_w ^= bit;
-                    }
-                }
                 const bool isb = w.is_b(n_base, n_steps);
+                uint32_t parity = 0;
+                const int kind = book.acquire(w.it, st, p.stages, isb, parity);   // wait until the slot's previous tenant was consumed
+                if (kind == 2) {
+                    OB_WAIT(&ctrl->empty_b[st], parity, 3, w.it)
+                } else if (kind == 1) {
+                    OB_WAIT(&ctrl->empty[st], parity, 1, w.it)
+                }
                 if (isb) {
-                    const LoraStep e = ctrl->steps[w.li];
-                    mbar_arrive_expect_tx(&ctrl->full_b[st], b_bytes);
-                    tma_load_2d(ring + (size_t)st * stage_bytes, tmb, &ctrl->full_b[st], e.chunk * p.rc, e.lora * n_s + n0_local);
-                    last_b |= bit;
+                    if (b_by_tma) {       // bf16 adapters: the B tile comes by TMA; stored formats are dequantized by warps 4-7
+                        const LoraStep e = ctrl->steps[w.li];
+                        mbar_arrive_expect_tx(&ctrl->full_b[st], b_bytes);
+                        tma_load_2d(ring + (size_t)st * stage_bytes, tmb, &ctrl->full_b[st], e.chunk * p.rc, e.lora * n_s + n0_local);
+                    }
                 } else {
                     mbar_arrive_expect_tx(&ctrl->full_w[st], wx_bytes);
                     tma_load_2d_hint(ring + (size_t)st * stage_bytes, &tm_w, &ctrl->full_w[st], (kb0 + w.k) * kBlockK,
@@ -256,7 +351,6 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                                       p.xsf + ((size_t)blockIdx.z * p.kblocks + (kb0 + w.k)) * p.nblk * kSfSlotBytes,
                                       (uint32_t)(kSfSlotBytes * p.nblk), &ctrl->full_w[st]);
                     }
-                    last_b &= ~bit;
                 }
                 w.advance(isb);
             }
@@ -463,12 +557,28 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (te == 0) { mbar_arrive(&ctrl->htab_ready); OB_TRACE(9) }
-        } else {
+        }
+        const bool stored = p.lora_fmt != kLoraBf16;          // FP8- / NVFP4-stored adapters: these warps produce the B tiles
+        if (stored || !small) {
+            SlotWalk w(p.stages);
+            RingBook book;
             for (int li = 0; li < n_steps; ++li) {
+                uint32_t parity = 0;
+                while (!w.is_b(n_base, n_steps)) {            // W slots in between: bookkeeping only
+                    book.acquire(w.it, w.it % p.stages, p.stages, false, parity);
+                    w.advance(false);
+                }
+                const int st = w.it % p.stages;
+                const int kind = book.acquire(w.it, st, p.stages, true, parity);
                 const int hb = li % nh, hu = li / nh;
                 if (te == 0) {                                    // one thread decides, so that all 128 leave together
                     int go = ctrl->abort_flag ? 0 : 1;
-                    if (go && hu > 0 && !mbar_wait(&ctrl->h_empty[hb], (uint32_t)((hu - 1) & 1), limit_ns)) {
+                    if (go && stored && kind != 0 &&
+                        !mbar_wait(kind == 2 ? &ctrl->empty_b[st] : &ctrl->empty[st], parity, limit_ns)) {
+                        record_timeout(p, ctrl, 14, w.it);
+                        go = 0;
+                    }
+                    if (go && !small && hu > 0 && !mbar_wait(&ctrl->h_empty[hb], (uint32_t)((hu - 1) & 1), limit_ns)) {
                         record_timeout(p, ctrl, 10, li);
                         go = 0;
                     }
@@ -477,6 +587,8 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (!ctrl->go_flag) break;
                 const LoraStep e = ctrl->steps[li];
+                if (stored) fill_b_tile(p, e, s, n_s, n0_local, ring + (size_t)st * stage_bytes, te, row_bytes, swz);
+                if (!small) {
                 uint8_t* hdst = hbuf + (size_t)hb * h_bytes;
                 for (int ch = te; ch < tn * cpr; ch += 128) {
                     const int row = ch / cpr, c16 = ch % cpr;
@@ -506,12 +618,17 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                     off ^= ((off >> 7) & swz) << 4;
                     *reinterpret_cast<uint4*>(hdst + off) = out;
                 }
+                }
                 fence_proxy_async_smem();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (te == 0) mbar_arrive(&ctrl->h_full[hb]);
+                if (te == 0) {
+                    if (stored) mbar_arrive(&ctrl->full_b[st]);
+                    if (!small) mbar_arrive(&ctrl->h_full[hb]);
+                }
+                w.advance(true);
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");        // sx / rowmap visible to all epilogue threads
         }
+        asm volatile("bar.sync 1, 128;" ::: "memory");            // sx / rowmap visible to all epilogue threads
 
         // ---- epilogue
         if (te == 0) { OB_TRACE(10) }

@@ -312,7 +312,7 @@ int prepare_call(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape*
                  int base_fmt = OB_BASE_FP8) {
     int st = validate_batch(l, b);
     if (st != OB_OK) return st;
-    if (l->d.base_fmt != base_fmt || l->d.lora_fmt != OB_LORA_BF16) return OB_ERR_FORMAT;
+    if (l->d.base_fmt != base_fmt) return OB_ERR_FORMAT;
     st = resolve_cfg(l, b->M, cfg, r);
     if (st != OB_OK) return st;
     return validate_workspace(l, ws, sh, r->split1, r->split2);

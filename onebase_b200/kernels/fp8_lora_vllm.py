@@ -14,6 +14,7 @@ import ctypes as C
 import torch
 
 from onebase_b200 import _lib
+from onebase_b200.kernels.adapter_store import AdapterStore
 from onebase_b200.tile_table import tile_for
 
 FP8_MAX = 448.0
@@ -22,6 +23,20 @@ _BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024, 2048, 4096, 8192, 1 << 
 
 def _bucket(M: int) -> int:
     return next(b for b in _BUCKETS if M <= b)
+
+
+def fill_adapter_pointers(d: "_lib.ObLayerDesc", store: AdapterStore) -> None:
+    """The adapter pointer tables of a layer descriptor (reference: a_ptrs / b_ptrs / sa_ptrs / sb_ptrs, fp8_lora_vllm.py:
+    440-441,477-493)."""
+    d.lora_fmt = {"bf16": _lib.OB_LORA_BF16, "fp8": _lib.OB_LORA_FP8, "nvfp4": _lib.OB_LORA_NVFP4}[store.fmt]
+    for s in range(store.S):
+        d.a[s] = store.a_q[s].data_ptr()
+        d.b[s] = store.b_q[s].data_ptr()
+        if store.fmt != "bf16":
+            d.sa[s] = store.a_s[s].data_ptr()
+            d.sb[s] = store.b_s[s].data_ptr()
+    if store.fmt == "nvfp4":
+        d.ag, d.bg = store.ag.data_ptr(), store.bg.data_ptr()
 
 
 class Scratch:
@@ -117,20 +132,19 @@ class VllmFusedFP8LoRA:
         self.max_m = int(max_m)
         self.split_k = split_k                                           # shrink split-K override (None: tile table)
         self.lora_fp8, self.lora_fp4 = lora_fp8, lora_fp4
-        if lora_fp8 or lora_fp4:
-            raise NotImplementedError("FP8- / NVFP4-stored adapters are not served yet")
+        assert not (lora_fp8 and lora_fp4)
         self.device = w_q.device
+        self.store = AdapterStore(a_stacked, b_stacked, "nvfp4" if lora_fp4 else "fp8" if lora_fp8 else "bf16")
         self.scratch = shared_scratch(self.device)
         self.scratch.ensure(self.max_m, self.K, self.N, self.S * self.R, Scratch.MAX_SPLIT2)
         self.dispatch = {}                                               # kept for report compatibility: always fused
         self.wait_ms = 2000
         d = _lib.ObLayerDesc()
-        d.base_fmt, d.lora_fmt = _lib.OB_BASE_FP8, _lib.OB_LORA_BF16
+        d.base_fmt = _lib.OB_BASE_FP8
         d.N, d.K, d.S, d.L, d.R, d.max_m = self.N, self.K, self.S, self.L, self.R, self.max_m
         for s in range(self.S):
             d.widths[s] = widths[s]
-            d.a[s] = a_stacked[s].data_ptr()
-            d.b[s] = b_stacked[s].data_ptr()
+        fill_adapter_pointers(d, self.store)
         d.w_q, d.s_w = w_q.data_ptr(), self.s_w.data_ptr()
         self._desc = d
         h = C.c_void_p()
@@ -193,11 +207,28 @@ class VllmFusedFP8LoRA:
         self.scratch.ensure(self.max_m, self.K, self.N, self.S * self.R, Scratch.MAX_SPLIT2)
 
     def requantize(self, index: int | None = None) -> None:
-        """bf16 adapters are read in place: nothing to refresh (reference: fp8_lora_vllm.py:504-524)."""
-        return
+        """Refresh the low-precision copy of one slot (or all) from vLLM's bf16 slots after vLLM wrote or cleared it
+        (reference: fp8_lora_vllm.py:504-524).  bf16 adapters are read in place: nothing to do."""
+        self.store.requantize(index)
 
     def release(self, a_stage, b_stage) -> None:
-        raise NotImplementedError("release() applies to FP8- / NVFP4-stored adapters")
+        """Serve from the low-precision copies alone; vLLM then writes every adapter through one staging slot
+        (reference: fp8_lora_vllm.py:498-502)."""
+        assert self.lora_fp8 or self.lora_fp4
+        self.store.release(a_stage, b_stage)
+        self.a_stacked, self.b_stacked = a_stage, b_stage
+
+    # the reference exposes the copies under these names (tests read them)
+    a8 = property(lambda self: self.store.a_q)
+    b8 = property(lambda self: self.store.b_q)
+    sa = property(lambda self: self.store.a_s)
+    sb = property(lambda self: self.store.b_s)
+    a4 = property(lambda self: self.store.a_q)
+    b4 = property(lambda self: self.store.b_q)
+    a4s = property(lambda self: self.store.a_s)
+    b4s = property(lambda self: self.store.b_s)
+    ag = property(lambda self: self.store.ag)
+    bg = property(lambda self: self.store.bg)
 
 
 def run_pdl(op: VllmFusedFP8LoRA, x, meta_args, cfg: dict | None = None, out=None, pdl: bool = True, shrink: bool = True,

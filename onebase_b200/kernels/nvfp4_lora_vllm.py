@@ -15,7 +15,8 @@ import ctypes as C
 import torch
 
 from onebase_b200 import _lib
-from onebase_b200.kernels.fp8_lora_vllm import Scratch, VllmFusedFP8LoRA, shared_scratch
+from onebase_b200.kernels.adapter_store import AdapterStore
+from onebase_b200.kernels.fp8_lora_vllm import Scratch, VllmFusedFP8LoRA, fill_adapter_pointers, shared_scratch
 
 E2M1_MAX = 6.0
 
@@ -44,8 +45,6 @@ class VllmFusedNVFP4LoRA(VllmFusedFP8LoRA):
                  rcp_approx=False):
         if w_q.device.type != "cuda":
             raise RuntimeError("onebase_b200 runs on CUDA devices only (there is no CPU path)")
-        if lora_fmt != "bf16":
-            raise NotImplementedError("FP8- / NVFP4-stored adapters are not served yet")
         self.w_q, self.w_sf = w_q, w_sf
         self.N = w_q.shape[0]
         self.K = 2 * w_q.shape[1]
@@ -64,7 +63,9 @@ class VllmFusedNVFP4LoRA(VllmFusedFP8LoRA):
         self.max_m = int(max_m)
         self.split_k = split_k
         self.lora_fmt = lora_fmt
+        self.lora_fp8, self.lora_fp4 = lora_fmt == "fp8", lora_fmt == "nvfp4"
         self.device = w_q.device
+        self.store = AdapterStore(a_stacked, b_stacked, lora_fmt)
         self.w_global = float(w_global)
         self.x_global = torch.tensor([float(x_global)], dtype=torch.float32, device=self.device)
         self.alpha = torch.tensor([1.0 / (float(x_global) * float(w_global))], dtype=torch.float32, device=self.device)
@@ -74,12 +75,11 @@ class VllmFusedNVFP4LoRA(VllmFusedFP8LoRA):
         self.dispatch = {}
         self.wait_ms = 2000
         d = _lib.ObLayerDesc()
-        d.base_fmt, d.lora_fmt = _lib.OB_BASE_NVFP4, _lib.OB_LORA_BF16
+        d.base_fmt = _lib.OB_BASE_NVFP4
         d.N, d.K, d.S, d.L, d.R, d.max_m = self.N, self.K, self.S, self.L, self.R, self.max_m
         for s in range(self.S):
             d.widths[s] = widths[s]
-            d.a[s] = a_stacked[s].data_ptr()
-            d.b[s] = b_stacked[s].data_ptr()
+        fill_adapter_pointers(d, self.store)
         d.w_q, d.w_sf = w_q.data_ptr(), self.w_sf_packed.data_ptr()
         d.x_global, d.alpha = self.x_global.data_ptr(), self.alpha.data_ptr()
         d.quant_rcp_approx = 1 if rcp_approx else 0

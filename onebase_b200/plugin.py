@@ -19,7 +19,8 @@ Switches (environment, read at install / layer build; same names and meaning as 
   LOWBIT_VERBOSE=1        print what was installed
   LOWBIT_WARMUP=0         skip the load-time scratch growth
   LOWBIT_COMPILE_CACHE=0  disable vLLM's compile cache instead of keying it
-  LOWBIT_LORA_FP8 / LOWBIT_LORA_FP4 / LOWBIT_RELEASE_SLOTS   stored adapter formats: not served yet -> the layer falls back
+  LOWBIT_LORA_FP8=1 / LOWBIT_LORA_FP4=1   serve the adapters FP8-stored (e4m3, per-row scales) / NVFP4-stored from low-precision
+                          copies refreshed on every slot write; LOWBIT_RELEASE_SLOTS=0 keeps vLLM's bf16 slots as well
   LOWBIT_DISPATCH*, LOWBIT_HYBRIDQ, LOWBIT_LEAN_BASE, LOWBIT_TUNE_MAX_M   accepted and ignored: there is no timed
                           dispatch; tiles come from the table.
 """
@@ -112,6 +113,47 @@ def _is_fp8_per_tensor(base, qm) -> bool:
         return qm is not None
 
 
+def _hook_slot_writes(layer, op) -> None:
+    """Per instance: requantize a slot's low-precision copy after vLLM writes or clears it (reference: plugin.py:89-130).
+    By default (LOWBIT_RELEASE_SLOTS=0 keeps vLLM's buffers) the copies become the only per-slot storage: vLLM's bf16 slots
+    shrink to one staging slot that every write goes through."""
+    set_lora, reset_lora = layer.set_lora, layer.reset_lora
+    if _on("LOWBIT_RELEASE_SLOTS", "1"):
+        layer.lora_a_stacked = tuple(t[:1].clone() for t in layer.lora_a_stacked)
+        layer.lora_b_stacked = tuple(t[:1].clone() for t in layer.lora_b_stacked)
+        op.release(layer.lora_a_stacked, layer.lora_b_stacked)
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+        writing = [False]
+
+        def set_lora_s(index, *args, **kw):
+            writing[0] = True
+            try:
+                set_lora(0, *args, **kw)          # its reset_lora(0) lands in reset_lora_s
+            finally:
+                writing[0] = False
+            op.requantize(index)
+
+        def reset_lora_s(index):
+            reset_lora(0)
+            if not writing[0]:
+                op.requantize(index)              # a cleared slot: the copy of the zeroed staging slot
+
+        layer.set_lora, layer.reset_lora = set_lora_s, reset_lora_s
+        layer._lowbit_released = True
+        return
+
+    def set_lora_q(index, *args, **kw):
+        set_lora(index, *args, **kw)
+        op.requantize(index)
+
+    def reset_lora_q(index):
+        reset_lora(index)
+        op.requantize(index)
+
+    layer.set_lora, layer.reset_lora = set_lora_q, reset_lora_q
+
+
 def _build(layer) -> int:
     """Decide and construct once per layer (vLLM calls set_mapping right after wrapping a layer, after the base weights
     were quantized, before CUDA graphs are captured).  Returns the layer id or -1 (fallback to vLLM's own path)."""
@@ -122,12 +164,10 @@ def _build(layer) -> int:
     lid = -1
     kind = "fused"
     fp8_cls, nvfp4_cls = _op_classes()
-    stored = _on("LOWBIT_LORA_FP8") or _on("LOWBIT_LORA_FP4")
     st4 = getattr(base, "_lowbit_nvfp4", None)
     max_m = layer.punica_wrapper._token_lora_indices.numel()
-    if stored:
-        why = "stored adapter formats are not served yet"
-    elif not _adapters_ok(layer):
+    fmt = "nvfp4" if _on("LOWBIT_LORA_FP4") else "fp8" if _on("LOWBIT_LORA_FP8") else "bf16"
+    if not _adapters_ok(layer):
         why = "adapter buffers (dtype / slices / rank)"
     elif (getattr(layer, "tp_size", 1) != 1 or getattr(base, "bias", None) is not None) and not tp_ok:
         why = "tensor-parallel shard or bias without LOWBIT_TP=1"
@@ -136,7 +176,8 @@ def _build(layer) -> int:
         widths = [t.shape[2] for t in layer.lora_b_stacked]
         if w_q.shape[0] == sum(widths) and 2 * w_q.shape[1] == layer.lora_a_stacked[0].shape[3] and w_q.shape[1] % 16 == 0:
             op = nvfp4_cls(w_q, w_sf, 1.0 / st4["weight_scale_2"], 1.0 / st4["input_scale"], layer.lora_a_stacked,
-                           layer.lora_b_stacked, max_m, rcp_approx=os.environ.get("LOWBIT_NVFP4_RCP", "approx") != "exact")
+                           layer.lora_b_stacked, max_m, lora_fmt=fmt,
+                           rcp_approx=os.environ.get("LOWBIT_NVFP4_RCP", "approx") != "exact")
             kind = "fused-nvfp4"
             _REGISTRY.append(op)
             lid = len(_REGISTRY) - 1
@@ -147,13 +188,16 @@ def _build(layer) -> int:
         widths = [t.shape[2] for t in layer.lora_b_stacked]
         if w_q.is_contiguous() and w_q.shape[0] == sum(widths) and w_q.shape[1] == layer.lora_a_stacked[0].shape[3] \
                 and w_q.shape[1] % 16 == 0:
-            op = fp8_cls(w_q, base.weight_scale.reshape(1).float(), layer.lora_a_stacked, layer.lora_b_stacked, max_m)
+            op = fp8_cls(w_q, base.weight_scale.reshape(1).float(), layer.lora_a_stacked, layer.lora_b_stacked, max_m,
+                         lora_fp8=fmt == "fp8", lora_fp4=fmt == "nvfp4")
             _REGISTRY.append(op)
             lid = len(_REGISTRY) - 1
         else:
             why = "FP8 weight layout"
     else:
         why = "base is neither per-tensor FP8 nor ModelOpt NVFP4"
+    if lid >= 0 and fmt != "bf16":
+        _hook_slot_writes(layer, _REGISTRY[lid])
     if lid >= 0:
         if _on("LOWBIT_WARMUP", "1"):
             _REGISTRY[lid].warmup()

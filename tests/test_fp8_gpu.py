@@ -211,3 +211,75 @@ def test_rejects_bad_arguments_before_launch():
     assert e.value.status == -7
     torch.cuda.synchronize()
     _check_status(op)
+
+
+@pytest.mark.parametrize("fmt", ["fp8", "nvfp4"])
+def test_stored_adapter_formats_golden(golden, fmt):
+    """FP8- / NVFP4-stored adapters: the device copies are bit-identical to the ones the reference's AdapterStore made, and
+    the outputs match the reference run on the dequantized adapters (tests/golden/fp8_projection.npz)."""
+    g = golden("fp8_projection")
+    for ci in range(int(g["n_cases"])):
+        p = f"c{ci}_"
+        widths = tuple(int(v) for v in g[p + "widths"])
+        S = len(widths)
+        L = int(g[p + "L"])
+        d = {"w_q": e4m3(g[p + "w_q"]), "s_w": t(g[p + "s_w"]), "widths": widths,
+             "a_stacked": tuple(bf16(g[p + f"a{s}"]) for s in range(S)),
+             "b_stacked": tuple(bf16(g[p + f"b{s}"]) for s in range(S))}
+        x, tok = bf16(g[p + "x"]), t(g[p + "tok"])
+        M = x.shape[0]
+        op = build_fp8_op(d, max_m=64, lora_fp8=fmt == "fp8", lora_fp4=fmt == "nvfp4")
+        for s in range(S):
+            for have, name in ((op.store.a_q[s], "aq"), (op.store.a_s[s], "as"), (op.store.b_q[s], "bq"), (op.store.b_s[s], "bs")):
+                want = t(g[p + f"{fmt}_{name}{s}"])
+                assert torch.equal(have.cpu().view(want.dtype) if have.element_size() == want.element_size() else have.cpu(), want), (ci, fmt, name, s)
+        if fmt == "nvfp4":
+            assert torch.equal(op.store.ag.cpu(), t(g[p + "nvfp4_ag"])) and torch.equal(op.store.bg.cpu(), t(g[p + "nvfp4_bg"]))
+        idx = make_index(tok, L, 64)
+        y = op(x.cuda(), device_meta(idx, M))
+        torch.cuda.synchronize()
+        _check_status(op)
+        want_y = t(g[p + f"{fmt}_y"])
+        assert max_err_ratio(y, want_y) <= TOL, (ci, fmt, max_err_ratio(y, want_y))
+        assert float((y.float().cpu() - want_y).norm() / want_y.norm()) < 1e-2
+
+
+def test_released_slots_serve_from_the_copies_alone():
+    """After release(), vLLM writes every adapter through one staging slot and requantize(index) files it under its slot
+    (reference: tests/test_release_slots.py): the outputs equal those of the fully populated bf16 slots' copies."""
+    d = _case(512, (256, 128), 32, 4, 24, seed=9)
+    full = build_fp8_op(d, max_m=32, lora_fp8=True)
+    a_stage = tuple(torch.zeros_like(t_[:1]).cuda() for t_ in d["a_stacked"])
+    b_stage = tuple(torch.zeros_like(t_[:1]).cuda() for t_ in d["b_stacked"])
+    rel = build_fp8_op(d, max_m=32, lora_fp8=True)
+    rel.release(a_stage, b_stage)
+    for slot in (2, 0, 3, 1):                                   # slots written in any order through the staging slot
+        for s in range(2):
+            a_stage[s][0].copy_(d["a_stacked"][s][slot])
+            b_stage[s][0].copy_(d["b_stacked"][s][slot])
+        rel.requantize(slot)
+    for s in range(2):
+        assert torch.equal(rel.store.a_q[s].view(torch.uint8), full.store.a_q[s].view(torch.uint8))
+        assert torch.equal(rel.store.b_s[s], full.store.b_s[s])
+    idx = make_index(d["ids"], 4, 32)
+    meta = device_meta(idx, 24)
+    x = d["x"].cuda()
+    assert torch.equal(rel(x, meta), full(x, meta))
+
+
+def test_large_batch_three_token_tiles():
+    """M = 600: 256-token tiles (three of them), Zipf-distributed contiguous requests, the shrink's 4-position passes."""
+    d = _case(1024, (256, 128), 32, 8, 600, seed=21)
+    ids = configs.zipf_request_ids(600, 8, seed=4, mean_len=40)
+    ids[100:130] = -1
+    op = build_fp8_op(d, max_m=600)
+    idx = make_index(ids, 8, 600)
+    y = op(d["x"].cuda(), device_meta(idx, 600))
+    torch.cuda.synchronize()
+    _check_status(op)
+    rows, _ = oseg.resolve_positions(600, *idx.args(600))
+    q_ref, sx_ref = ofp8.quant_per_token(d["x"])
+    assert torch.equal(u8(op.scratch.xq(600, 1024)).cpu(), u8(q_ref)[rows])
+    A, B = ofp8.stack_slices(d["a_stacked"], d["b_stacked"])
+    ref = ofp8.fused_projection(d["x"], ids, d["w_q"], d["s_w"], A, B, d["widths"])
+    assert max_err_ratio(y, ref) <= TOL

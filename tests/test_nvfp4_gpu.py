@@ -162,3 +162,27 @@ def test_weight_scale_packing_round_trip():
             assert int(blk[n:].sum()) == 0
         row0 += w
         tile0 += (w + 127) // 128
+
+
+@pytest.mark.parametrize("fmt", ["fp8", "nvfp4"])
+def test_nvfp4_base_with_stored_adapters(fmt):
+    """NVFP4 base with FP8- or NVFP4-stored adapters (the benchmark's third configuration): outputs against the oracle run
+    on the dequantized adapters."""
+    from oracle import fp8 as ofp8
+    d = _case(1024, (256, 128), 64, 6, 29, seed=13)
+    op = build_nvfp4_op(d, max_m=64, lora_fmt=fmt)
+    As, Bs = [], []
+    for s in range(2):
+        for src, acc in ((d["a_stacked"][s], As), (d["b_stacked"][s], Bs)):
+            if fmt == "fp8":
+                codes, scale = ofp8.store_rows_fp8(src[:, 0])
+                acc.append(codes.float() * scale[..., None])
+            else:
+                acc.append(on4.dequant_stack(*on4.quant_stack(src[:, 0])))
+    idx = make_index(d["ids"], 6, 64)
+    y = op(d["x"].cuda(), device_meta(idx, 29))
+    torch.cuda.synchronize()
+    _status_ok(op)
+    ref = on4.fused_projection(d["x"], d["ids"], d["w_q4"], d["w_sf"], d["w_global"], d["x_global"], torch.cat(As, 1),
+                               torch.cat(Bs, 1), d["widths"])
+    assert max_err_ratio(y, ref) <= TOL

@@ -65,10 +65,20 @@ def test_build_decisions_and_report(plugin, monkeypatch):
     assert P._build(fake_layer(R=24)) == -1                              # unsupported rank
     monkeypatch.setenv("LOWBIT_TP", "1")
     assert P._build(fake_layer(tp=2)) == 1
-    monkeypatch.setenv("LOWBIT_LORA_FP8", "1")
-    assert P._build(fake_layer()) == -1                                  # stored formats: not served yet
+    monkeypatch.setenv("LOWBIT_LORA_FP8", "1")                           # FP8-stored adapters: slots released to one staging slot
+    lay = fake_layer()
+    writes = []
+    lay.set_lora = lambda index, *a, **k: (lay.reset_lora(index), writes.append(("set", index)))
+    lay.reset_lora = lambda index: writes.append(("reset", index))
+    FakeOp.requantize = lambda self, index=None: writes.append(("requant", index))
+    FakeOp.release = lambda self, a, b: writes.append(("release", a[0].shape[0]))
+    assert P._build(lay) == 2 and FakeOp.made[-1].kw["lora_fp8"] is True and lay._lowbit_released
+    assert lay.lora_a_stacked[0].shape[0] == 1                           # vLLM's L slots shrank to the staging slot
+    lay.set_lora(2, "A", "B")
+    lay.reset_lora(1)
+    assert writes == [("release", 1), ("reset", 0), ("set", 0), ("requant", 2), ("reset", 0), ("requant", 1)]
     lines = P._report_path.read_text().splitlines()
-    assert sum(" fused " in ln for ln in lines) == 2 and sum(" fallback " in ln for ln in lines) == 6
+    assert sum(" fused " in ln for ln in lines) == 3 and sum(" fallback " in ln for ln in lines) == 5
     assert all(ln.split()[0].isdigit() for ln in lines)                  # pid-tagged
 
 
