@@ -20,29 +20,37 @@ FP8_MAX = 448.0
 E2M1_MAX = 6.0
 
 
+def _c(value: float, like: torch.Tensor) -> torch.Tensor:
+    """A 0-dim fp32 tensor on `like`'s device.  Divisions are written tensor / tensor on purpose: on CUDA torch turns
+    `tensor / python_scalar` into a multiplication by the scalar's reciprocal, which is not the IEEE quotient and would
+    move a scale by one ulp (and with it some codes) against the CPU recipe."""
+    return torch.tensor(value, dtype=torch.float32, device=like.device)
+
+
 def store_rows_fp8(t: torch.Tensor):
     tf = t.float()
-    scale = (tf.abs().amax(-1) / FP8_MAX).clamp_min(1e-12)
-    return (tf / scale[..., None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), scale
+    scale = torch.div(tf.abs().amax(-1), _c(FP8_MAX, tf)).clamp_min(1e-12)
+    return torch.div(tf, scale[..., None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), scale
 
 
 def quant_stack_nvfp4(t: torch.Tensor):
     """t [l, rows, cols] -> (packed [l, rows, cols/2] uint8, block scales [l, rows, cols/16] e4m3, inverse globals [l])."""
     l, rows, cols = t.shape
     tf = t.float()
-    gs = (448.0 * E2M1_MAX / tf.abs().amax(dim=(1, 2)).clamp_min(1e-12)).float()
+    one = _c(1.0, tf)
+    gs = torch.div(_c(448.0 * E2M1_MAX, tf), tf.abs().amax(dim=(1, 2)).clamp_min(1e-12)).float()
     xb = tf.reshape(l, rows, cols // 16, 16)
     g = gs.view(l, 1, 1, 1)
     vmax = xb.abs().amax(-1, keepdim=True)
     sf = (g * (vmax * (1.0 / E2M1_MAX))).clamp(max=448.0).to(torch.float8_e4m3fn)
     sff = sf.float()
-    osc = torch.where(sff != 0, 1.0 / (sff * (1.0 / g)), torch.zeros_like(sff))
+    osc = torch.where(sff != 0, torch.div(one, sff * torch.div(one, g)), torch.zeros_like(sff))
     v = xb * osc
     a = v.abs()
     code = ((a > 0.25).int() + (a >= 0.75).int() + (a > 1.25).int() + (a >= 1.75).int() + (a > 2.5).int()
             + (a >= 3.5).int() + (a > 5.0).int() + 8 * (v < 0).int()).reshape(l, rows, cols // 2, 2)
     packed = (code[..., 0] | (code[..., 1] << 4)).to(torch.uint8)
-    return packed, sf.reshape(l, rows, cols // 16), (1.0 / gs).float()
+    return packed, sf.reshape(l, rows, cols // 16), torch.div(one, gs).float()
 
 
 class AdapterStore:
