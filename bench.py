@@ -92,7 +92,7 @@ def physical_index(local: int) -> int:
     return local
 
 
-def make_layer(M: int, device, seed: int = 0, tp: int = 1, rank: int = 0):
+def make_layer(M: int, device, seed: int = 0, base: str = "fp8", lora_fmt: str = "bf16"):
     """Random-init layer with the configuration's distributions, generated on the device (values do not matter for
     timing; the parity tests use CPU-drawn inputs).  Returns {proj: (op, x, meta)} plus the ids."""
     from onebase_b200.kernels.fp8_lora_vllm import VllmFusedFP8LoRA
@@ -106,14 +106,22 @@ def make_layer(M: int, device, seed: int = 0, tp: int = 1, rank: int = 0):
     for name, (K, widths) in PROJECTIONS.items():
         N = sum(widths)
         w = torch.randn(N, K, device=device, generator=g) * 0.02
-        s_w = (w.abs().max() / 448.0).reshape(1).float()
-        w_q = (w / s_w).to(torch.float8_e4m3fn)
+        if base == "fp8":
+            s_w = (w.abs().max() / 448.0).reshape(1).float()
+            w_q = (w / s_w).to(torch.float8_e4m3fn)
+        else:   # NVFP4: timing does not depend on the code values: random nibbles, block scales near 1
+            w_q = torch.randint(0, 256, (N, K // 2), device=device, generator=g, dtype=torch.uint8)
+            w_sf = torch.randint(0x30, 0x40, (N, K // 16), device=device, generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn)
         del w
         a_st = tuple(((torch.rand(L_SLOTS, 1, RANK, K, device=device, generator=g) * 2 - 1) / K ** 0.5).to(torch.bfloat16)
                      for _ in widths)
         b_st = tuple((torch.randn(L_SLOTS, 1, n, RANK, device=device, generator=g) * 0.01).to(torch.bfloat16) for n in widths)
         x = torch.randn(M, K, device=device, generator=g).to(torch.bfloat16)
-        op = VllmFusedFP8LoRA(w_q, s_w, a_st, b_st, max_m=M)
+        if base == "fp8":
+            op = VllmFusedFP8LoRA(w_q, s_w, a_st, b_st, max_m=M, lora_fp8=lora_fmt == "fp8", lora_fp4=lora_fmt == "nvfp4")
+        else:
+            from onebase_b200.kernels.nvfp4_lora_vllm import VllmFusedNVFP4LoRA
+            op = VllmFusedNVFP4LoRA(w_q, w_sf, 2688.0 / 0.1, 2688.0 / 4.0, a_st, b_st, max_m=M, lora_fmt=lora_fmt, rcp_approx=True)
         layer[name] = (op, x, torch.empty(M, N, dtype=torch.bfloat16, device=device))
     return layer, meta, ids
 
@@ -157,7 +165,7 @@ def profile_case(args, dev) -> None:
     keep = {args.profile: PROJECTIONS[args.profile]}
     saved, PROJECTIONS = PROJECTIONS, keep
     try:
-        layer, meta, ids = make_layer(args.m, dev)
+        layer, meta, ids = make_layer(args.m, dev, base=args.base, lora_fmt=args.lora_fmt)
     finally:
         PROJECTIONS = saved
     op, x, y = layer[args.profile]
@@ -168,7 +176,8 @@ def profile_case(args, dev) -> None:
     k2 = time_events(lambda: op(x, meta, out=y, shrink=False, pdl=False), args.steps, 2, flush)
     chain = time_events(graph_of(lambda: op(x, meta, out=y)).replay, args.steps, 2, flush)
     by = layer_bytes(args.m, int(torch.unique(ids).numel()))[args.profile]
-    print(json.dumps({"profile": args.profile, "M": args.m, "distinct": int(torch.unique(ids).numel()),
+    print(json.dumps({"profile": args.profile, "M": args.m, "base": args.base, "lora_fmt": args.lora_fmt,
+                      "distinct": int(torch.unique(ids).numel()),
                       "k1_us": statistics.fmean(k1) * 1e3, "k2_us": statistics.fmean(k2) * 1e3,
                       "chain_us": statistics.fmean(chain) * 1e3, "bytes": by}))
 
@@ -230,6 +239,8 @@ def main() -> None:
     ap.add_argument("--m", type=int, default=32, help="decode batch (tokens per step)")
     ap.add_argument("--impl", default="onebase_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--base", default="fp8", choices=["fp8", "nvfp4"], help="base format of the --profile case")
+    ap.add_argument("--lora-fmt", default="bf16", choices=["bf16", "fp8", "nvfp4"], help="adapter storage of the --profile case")
     ap.add_argument("--profile", default=None, metavar="PROJ",
                     help="small profiling case: build only this projection (qkv|o|gate_up|down) and launch K1 and K2 "
                          "separately --steps times each (for ncu captures); prints their mean times")

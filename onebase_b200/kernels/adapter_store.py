@@ -38,7 +38,8 @@ def quant_stack_nvfp4(t: torch.Tensor):
     l, rows, cols = t.shape
     tf = t.float()
     one = _c(1.0, tf)
-    gs = torch.div(_c(448.0 * E2M1_MAX, tf), tf.abs().amax(dim=(1, 2)).clamp_min(1e-12)).float()
+    # `scalar / tensor` in torch is reciprocal(tensor) * scalar (two roundings): the reference's global scale is that value
+    gs = (torch.reciprocal(tf.abs().amax(dim=(1, 2)).clamp_min(1e-12)) * (448.0 * E2M1_MAX)).float()
     xb = tf.reshape(l, rows, cols // 16, 16)
     g = gs.view(l, 1, 1, 1)
     vmax = xb.abs().amax(-1, keepdim=True)
