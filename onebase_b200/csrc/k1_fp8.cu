@@ -434,6 +434,10 @@ __global__ void __launch_bounds__(kK1Threads) k1_fp8_kernel(const K1Params p) {
     if ((int)blockIdx.x < p.n_quant_ctas) {
         if (p.base_fmt == OB_BASE_NVFP4) quantize_position_nvfp4(p, blockIdx.x);
         else quantize_position(p, blockIdx.x);
+        if (p.xq_ready != nullptr) {          // chain: tell K2 that this position's codes and scale are in memory
+            __syncthreads();
+            if (threadIdx.x == 0) red_release_add(p.xq_ready, 1);
+        }
         OB_TRACE1(3)
         return;
     }

@@ -302,7 +302,20 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                 if (!k1_done && (finished || w.it >= p.stages)) {
                     // The ring is full (or everything is requested): from here on progress needs K1's x_q.  Wait for K1 and
                     // request the x_q tile of every W slot issued so far.
-                    griddep_wait();
+                    if (p.xq_ready != nullptr) {
+                        // chain: K1's quantizing CTAs count the positions they finished; their codes are enough to start the
+                        // base GEMM, the rest of K1 (the shrink) keeps running beside it
+                        const uint64_t t_start = global_timer_ns();
+                        bool ready = false;
+                        for (uint32_t spin = 0;; ++spin) {
+                            if (ld_acquire(p.xq_ready) >= p.M) { ready = true; break; }
+                            if ((spin & 31u) == 31u && global_timer_ns() - t_start > limit_ns) break;
+                        }
+                        if (!ready) { record_timeout(p, ctrl, 15, w.it); break; }
+                        fence_proxy_async_all();
+                    } else {
+                        griddep_wait();
+                    }
                     OB_TRACE(4)
                     k1_done = true;
                     SlotWalk r(p.stages);
@@ -535,12 +548,27 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
 #pragma unroll
                     for (int u = 0; u < 8; ++u) acc[u] = 0.0f;
                     if (t0 + row < n_all) {
-                        for (int j1 = 0; j1 < p.split1; ++j1) {
-                            const float4* src = reinterpret_cast<const float4*>(
-                                p.hp + (((size_t)j1 * p.S + s) * p.max_m + (size_t)(t0 + row)) * p.R + (size_t)g8 * 8);
-                            const float4 u0 = __ldcg(src), u1 = __ldcg(src + 1);
-                            acc[0] += u0.x; acc[1] += u0.y; acc[2] += u0.z; acc[3] += u0.w;
-                            acc[4] += u1.x; acc[5] += u1.y; acc[6] += u1.z; acc[7] += u1.w;
+                        // four splits' loads in flight at a time (a plain loop would pay one L2 round trip per split),
+                        // added in split order
+                        const size_t jstride = (size_t)p.S * p.max_m * p.R;
+                        const float* src0 = p.hp + ((size_t)s * p.max_m + (size_t)(t0 + row)) * p.R + (size_t)g8 * 8;
+                        for (int j1 = 0; j1 < p.split1; j1 += 4) {
+                            float4 v[4][2];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                if (j1 + q < p.split1) {
+                                    const float4* src = reinterpret_cast<const float4*>(src0 + (size_t)(j1 + q) * jstride);
+                                    v[q][0] = __ldcg(src);
+                                    v[q][1] = __ldcg(src + 1);
+                                } else {
+                                    v[q][0] = v[q][1] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                                }
+                            }
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                acc[0] += v[q][0].x; acc[1] += v[q][0].y; acc[2] += v[q][0].z; acc[3] += v[q][0].w;
+                                acc[4] += v[q][1].x; acc[5] += v[q][1].y; acc[6] += v[q][1].z; acc[7] += v[q][1].w;
+                            }
                         }
                     }
                     __nv_bfloat162 b0 = __floats2bfloat162_rn(acc[0], acc[1]);
@@ -726,6 +754,13 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);
+    }
+    if (tid == 0 && p.chain_done != nullptr) {      // chain: the last CTA of the launch clears the flags for the next call
+        const int total = (int)(gridDim.x * gridDim.y * gridDim.z);
+        if (atomicAdd(p.chain_done, 1) == total - 1) {
+            *const_cast<volatile int32_t*>(p.xq_ready) = 0;
+            *const_cast<volatile int32_t*>(p.chain_done) = 0;
+        }
     }
     if (tid == 0) { OB_TRACE(14) }
 }

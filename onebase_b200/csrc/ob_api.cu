@@ -220,7 +220,7 @@ int get_xmap(ObLayer* l, const void* xq, int rows, int tn, CUtensorMap* out) {
 }
 
 int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, int pdl,
-                cudaStream_t stream) {
+                cudaStream_t stream, bool chain = false) {
     const ObLayerDesc& d = l->d;
     const WorkspaceLayout lay = workspace_layout(*sh);
     uint8_t* base = static_cast<uint8_t*>(ws);
@@ -249,6 +249,7 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     p.rcp_approx = d.quant_rcp_approx;
     p.x_global = d.x_global;
     p.xsf = base + lay.xsf;
+    p.xq_ready = chain ? reinterpret_cast<int32_t*>(base + lay.counters) + kCounterSlots : nullptr;
     p.trace = g_trace ? g_trace + g_trace_ctas * OB_TRACE_EVENTS : nullptr;   // K1's stamps follow K2's
     p.trace_ctas = g_trace_ctas;
     const long long warps = (long long)p.n_pblocks * p.units_per_block;
@@ -259,7 +260,7 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
 }
 
 int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, int pdl,
-                cudaStream_t stream) {
+                cudaStream_t stream, bool chain = false) {
     const ObLayerDesc& d = l->d;
     const WorkspaceLayout lay = workspace_layout(*sh);
     uint8_t* base = static_cast<uint8_t*>(ws);
@@ -292,6 +293,8 @@ int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     p.part = reinterpret_cast<float*>(base + lay.part);
     p.counters = reinterpret_cast<int32_t*>(base + lay.counters);
     p.status = reinterpret_cast<int32_t*>(base + lay.status);
+    p.xq_ready = chain ? p.counters + kCounterSlots : nullptr;
+    p.chain_done = chain ? p.counters + kCounterSlots + 1 : nullptr;
     for (int s = 0; s < d.S; ++s) { p.b[s] = d.b[s]; p.sb[s] = d.sb[s]; }
     p.bg = d.bg;
     p.trace = g_trace;
@@ -506,9 +509,9 @@ int ob_chain_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const Ob
     int st = prepare_call(layer, batch, workspace, shape, cfg, &r);
     if (st != OB_OK) return st;
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
+    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream, true);
     if (st != OB_OK) return st;
-    return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
+    return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream, true);
 }
 
 int ob_k1_nvfp4(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape, const ObTileCfg* cfg,
@@ -533,9 +536,9 @@ int ob_chain_nvfp4(ObLayer* layer, const ObBatch* batch, void* workspace, const 
     int st = prepare_call(layer, batch, workspace, shape, cfg, &r, OB_BASE_NVFP4);
     if (st != OB_OK) return st;
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
+    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream, true);
     if (st != OB_OK) return st;
-    return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
+    return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream, true);
 }
 
 int ob_nvfp4_packed_scale_bytes(int32_t K, int32_t S, const int32_t* widths, size_t* bytes) {

@@ -34,7 +34,7 @@ __host__ __device__ inline WorkspaceLayout workspace_layout(const ObWorkspaceSha
     WorkspaceLayout l;
     size_t off = 0;
     l.status = off;   off = align_up(off + sizeof(int32_t) * OB_STATUS_WORDS, 1024);
-    l.counters = off; off = align_up(off + sizeof(int32_t) * kCounterSlots, 1024);
+    l.counters = off; off = align_up(off + sizeof(int32_t) * (kCounterSlots + 16), 1024);   // + chain flags (x_q ready, CTAs done)
     l.sx = off;       off = align_up(off + sizeof(float) * (size_t)s.max_m, 1024);
     l.xq = off;       off = align_up(off + (size_t)s.max_m * (size_t)s.max_k, 1024);
     l.xsf = off;      off = align_up(off + ((size_t)s.max_m + 15) / 16 * (((size_t)s.max_k + 255) / 256) * kSfSlotBytes, 1024);
@@ -82,6 +82,7 @@ struct K1Params {
     int rcp_approx;        // NVFP4: 1 = rcp.approx.ftz reciprocals (vLLM's CUDA quantizer), 0 = IEEE (the torch recipe)
     const float* x_global; // NVFP4: [1] static activation global scale
     uint8_t* xsf;          // NVFP4: activation block scales, packed per (token tile, K slot) in scale-factor atoms
+    int32_t* xq_ready;     // chain: counts the positions whose codes and scale are written (null: no signal)
     unsigned long long* trace;   // optional timeline buffer (null: off); K1 stamps go after K2's region
     long long trace_ctas;
 };
@@ -115,6 +116,8 @@ struct K2Params {
     const uint8_t* xsf;    // NVFP4 base: K1's activation block scales, packed per (token tile, K slot)
     const float* alpha;    // NVFP4 base: [1] 1 / (x_global * w_global)
     int nblk;              // NVFP4 base: 128-token scale-factor blocks per token tile (1, or 2 for 256-token tiles)
+    int32_t* xq_ready;     // chain: K1's count of quantized positions; the producer polls it instead of waiting for all of K1
+    int32_t* chain_done;   // chain: CTAs of this launch that finished; the last one clears both words
     unsigned long long* trace;   // optional timeline buffer (null: off)
     long long trace_ctas;
 };

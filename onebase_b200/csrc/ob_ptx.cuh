@@ -89,6 +89,18 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint
 // Generic-proxy writes to shared memory -> visible to the async proxy (UMMA / TMA reads).
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// ------------------------------------------------------------------------------------------------- flags in global memory
+__device__ __forceinline__ void red_release_add(int32_t* addr, int32_t v) {
+    asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int32_t ld_acquire(const int32_t* addr) {
+    int32_t v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+    return v;
+}
+// Orders this thread's earlier generic-proxy observations before its later async-proxy (TMA) accesses.
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
 // ------------------------------------------------------------------------------------------------- PDL
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
