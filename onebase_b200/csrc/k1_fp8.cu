@@ -428,11 +428,13 @@ __device__ void shrink_unit(const K1Params& p, int pb, int u, int lane) {
     }
 }
 
-__global__ void __launch_bounds__(kK1Threads) k1_fp8_kernel(const K1Params p) {
+// One instantiation per (adapter storage, base format): each launch carries only the code of its own case.
+template <int LORA_FMT, bool FP4_BASE>
+__global__ void __launch_bounds__(kK1Threads) k1_kernel(const K1Params p) {
     griddep_launch_dependents();
     OB_TRACE1(0)
     if ((int)blockIdx.x < p.n_quant_ctas) {
-        if (p.base_fmt == OB_BASE_NVFP4) quantize_position_nvfp4(p, blockIdx.x);
+        if (FP4_BASE) quantize_position_nvfp4(p, blockIdx.x);
         else quantize_position(p, blockIdx.x);
         if (p.xq_ready != nullptr) {          // chain: tell K2 that this position's codes and scale are in memory
             __syncthreads();
@@ -445,13 +447,12 @@ __global__ void __launch_bounds__(kK1Threads) k1_fp8_kernel(const K1Params p) {
     const int w = ((int)blockIdx.x - p.n_quant_ctas) * (kK1Threads / 32) + (threadIdx.x >> 5);
     const int pb = w / p.units_per_block;
     if (pb >= p.n_pblocks) return;
-    if (p.lora_fmt == kLoraFp8) shrink_unit<kLoraFp8>(p, pb, w % p.units_per_block, lane);
-    else if (p.lora_fmt == kLoraNvfp4) shrink_unit<kLoraNvfp4>(p, pb, w % p.units_per_block, lane);
-    else shrink_unit<kLoraBf16>(p, pb, w % p.units_per_block, lane);
+    shrink_unit<LORA_FMT>(p, pb, w % p.units_per_block, lane);
     OB_TRACE1(3)
 }
 
-cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream) {
+template <int LORA_FMT, bool FP4_BASE>
+static cudaError_t launch_k1_impl(const K1Params& p, int grid, int pdl, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(kK1Threads);
@@ -462,7 +463,19 @@ cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t str
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, k1_fp8_kernel, p);
+    return cudaLaunchKernelEx(&cfg, k1_kernel<LORA_FMT, FP4_BASE>, p);
+}
+
+cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream) {
+    const bool fp4 = p.base_fmt == OB_BASE_NVFP4;
+    switch (p.lora_fmt) {
+        case kLoraFp8:
+            return fp4 ? launch_k1_impl<kLoraFp8, true>(p, grid, pdl, stream) : launch_k1_impl<kLoraFp8, false>(p, grid, pdl, stream);
+        case kLoraNvfp4:
+            return fp4 ? launch_k1_impl<kLoraNvfp4, true>(p, grid, pdl, stream) : launch_k1_impl<kLoraNvfp4, false>(p, grid, pdl, stream);
+        default:
+            return fp4 ? launch_k1_impl<kLoraBf16, true>(p, grid, pdl, stream) : launch_k1_impl<kLoraBf16, false>(p, grid, pdl, stream);
+    }
 }
 
 }  // namespace ob

@@ -198,7 +198,7 @@ __device__ __forceinline__ void fill_b_tile(const K2Params& p, const LoraStep& e
     }
 }
 
-template <bool FP4>
+template <bool FP4, bool STORED>
 __global__ void __launch_bounds__(kK2Threads, 2)
 k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
               const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
@@ -288,7 +288,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
             const uint32_t wx_bytes = (uint32_t)kWTileBytes + (uint32_t)tn * kBlockK + (uint32_t)sf_bytes;
             SlotWalk w(p.stages);
             RingBook book;
-            const bool b_by_tma = p.lora_fmt == kLoraBf16;
+            const bool b_by_tma = !STORED;
             int n_steps = 0;
             bool have_list = false, k1_done = false;
             for (;;) {
@@ -586,7 +586,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (te == 0) { mbar_arrive(&ctrl->htab_ready); OB_TRACE(9) }
         }
-        const bool stored = p.lora_fmt != kLoraBf16;          // FP8- / NVFP4-stored adapters: these warps produce the B tiles
+        constexpr bool stored = STORED;                       // FP8- / NVFP4-stored adapters: these warps produce the B tiles
         if (stored || !small) {
             SlotWalk w(p.stages);
             RingBook book;
@@ -615,7 +615,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (!ctrl->go_flag) break;
                 const LoraStep e = ctrl->steps[li];
-                if (stored) fill_b_tile(p, e, s, n_s, n0_local, ring + (size_t)st * stage_bytes, te, row_bytes, swz);
+                if constexpr (STORED) fill_b_tile(p, e, s, n_s, n0_local, ring + (size_t)st * stage_bytes, te, row_bytes, swz);
                 if (!small) {
                 uint8_t* hdst = hbuf + (size_t)hb * h_bytes;
                 for (int ch = te; ch < tn * cpr; ch += 128) {
@@ -774,7 +774,7 @@ size_t k2_fp8_smem_bytes(int tn, int stages, int rc, int R, int fp4) {
     return 1024 + (size_t)stages * (kWTileBytes + (size_t)tn * kBlockK + sf) + aux + kCtrlBytes;
 }
 
-template <bool FP4>
+template <bool FP4, bool STORED>
 static cudaError_t launch_k2_impl(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                                   dim3 grid, size_t smem, int pdl, cudaStream_t stream) {
     static int configured_for[64] = {0};
@@ -782,7 +782,7 @@ static cudaError_t launch_k2_impl(const K2Params& p, const CUtensorMap& tm_w, co
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64 && !configured_for[dev]) {
-        e = cudaFuncSetAttribute(k2_kernel<FP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        e = cudaFuncSetAttribute(k2_kernel<FP4, STORED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return e;
         configured_for[dev] = 1;
     }
@@ -796,17 +796,19 @@ static cudaError_t launch_k2_impl(const K2Params& p, const CUtensorMap& tm_w, co
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, k2_kernel<FP4>, p, tm_w, tm_x, tm_b[0], tm_b[1], tm_b[2], tm_b[3]);
+    return cudaLaunchKernelEx(&cfg, k2_kernel<FP4, STORED>, p, tm_w, tm_x, tm_b[0], tm_b[1], tm_b[2], tm_b[3]);
 }
 
 cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                           dim3 grid, size_t smem, int pdl, cudaStream_t stream) {
-    return launch_k2_impl<false>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream);
+    return p.lora_fmt == kLoraBf16 ? launch_k2_impl<false, false>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream)
+                                   : launch_k2_impl<false, true>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream);
 }
 
 cudaError_t launch_k2_nvfp4(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                             dim3 grid, size_t smem, int pdl, cudaStream_t stream) {
-    return launch_k2_impl<true>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream);
+    return p.lora_fmt == kLoraBf16 ? launch_k2_impl<true, false>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream)
+                                   : launch_k2_impl<true, true>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream);
 }
 
 }  // namespace ob
