@@ -64,18 +64,29 @@ struct K2Ctrl {
 static_assert(sizeof(K2Ctrl) <= kCtrlBytes, "control block too large");
 
 // The ring's slot sequence, identical in every role.  Slot `it` (ring position it % stages) holds either the next W
-// k-block together with its x_q tile, or the next expand step's B tile: every third slot is a B tile while expand steps
-// remain, and once one kind is exhausted the other takes every slot.  B tiles thus stream in between the W tiles instead
-// of after them.  The number of expand steps is only needed from the first slot that could be a B tile.
+// k-block together with its x_q tile, or the next expand step's B tile.  The first `lead` slots (one ring fill) are W
+// tiles whatever the batch, so the stream starts without waiting for the segment index; after them the n_steps B tiles
+// are spread evenly among the remaining W tiles (an error-accumulating line walk), so that the tenants' B streams in
+// between the W tiles and both kinds run out together.  The number of expand steps is needed from slot `lead` on.
 struct SlotWalk {
     int it = 0, k = 0, li = 0;
-    int lead;   // slots at the start that are W tiles regardless: the first ring fill never waits for the segment index
+    int lead;   // slots at the start that are W tiles regardless
+    int acc = 0;
     __device__ explicit SlotWalk(int lead_slots) : lead(lead_slots) {}
-    __device__ bool b_slot() const { return it >= lead && (it - lead) % 3 == 2; }
-    __device__ bool needs_list(int n_base) const { return b_slot() || k >= n_base; }
-    __device__ bool is_b(int n_base, int n_steps) const { return li < n_steps && (k >= n_base || b_slot()); }
+    __device__ bool needs_list(int n_base) const { return it >= lead || k >= n_base; }
+    __device__ bool is_b(int n_base, int n_steps) const {
+        if (li >= n_steps) return false;
+        if (k >= n_base) return true;
+        if (it < lead) return false;
+        const int total = (n_base > lead ? n_base - lead : 0) + n_steps;
+        return acc + n_steps >= total;
+    }
     __device__ bool done(int n_base, int n_steps) const { return k >= n_base && li >= n_steps; }
-    __device__ void advance(bool was_b) {
+    __device__ void advance(bool was_b, int n_base, int n_steps) {
+        if (it >= lead && k < n_base && li < n_steps) {      // the line walk only runs while both kinds remain
+            acc += n_steps;
+            if (was_b) acc -= (n_base > lead ? n_base - lead : 0) + n_steps;
+        }
         ++it;
         if (was_b) ++li; else ++k;
     }
@@ -330,7 +341,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                                           p.xsf + ((size_t)blockIdx.z * p.kblocks + (kb0 + r.k)) * p.nblk * kSfSlotBytes,
                                           (uint32_t)(kSfSlotBytes * p.nblk), &ctrl->full_w[st]);
                         }
-                        r.advance(rb);
+                        r.advance(rb, n_base, n_steps);
                     }
                 }
                 if (finished) break;
@@ -365,7 +376,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                                       (uint32_t)(kSfSlotBytes * p.nblk), &ctrl->full_w[st]);
                     }
                 }
-                w.advance(isb);
+                w.advance(isb, n_base, n_steps);
             }
             OB_TRACE(3)
         }
@@ -434,7 +445,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                     umma_commit(&ctrl->empty_b[st]);
                     umma_commit(&ctrl->h_empty[hb]);
                 }
-                w.advance(isb);
+                w.advance(isb, n_base, n_steps);
             }
             if (ok) umma_commit(&ctrl->acc_full);
         }
@@ -594,7 +605,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                 uint32_t parity = 0;
                 while (!w.is_b(n_base, n_steps)) {            // W slots in between: bookkeeping only
                     book.acquire(w.it, w.it % p.stages, p.stages, false, parity);
-                    w.advance(false);
+                    w.advance(false, n_base, n_steps);
                 }
                 const int st = w.it % p.stages;
                 const int kind = book.acquire(w.it, st, p.stages, true, parity);
@@ -653,7 +664,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                     if (stored) mbar_arrive(&ctrl->full_b[st]);
                     if (!small) mbar_arrive(&ctrl->h_full[hb]);
                 }
-                w.advance(true);
+                w.advance(true, n_base, n_steps);
             }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");            // sx / rowmap visible to all epilogue threads

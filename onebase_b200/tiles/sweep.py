@@ -74,11 +74,12 @@ def main() -> None:
             meta = km.meta_args(M)
             x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
             y = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
-            best = (float("inf"), None)
-            tried = 0
+            default_us = time_chain(op, x, meta, y, {}, flush, reps=25)
+            best = (default_us, {})
+            tried = 1
             for split2 in (1, 2, 3, 4, 6, 8):
-                for stages in (3, 4, 5, 8, 12):
-                    cfg = {"split2": split2, "stages": stages}
+                for stages in (0, 3, 4):
+                    cfg = {"split2": split2, **({"stages": stages} if stages else {})}
                     try:
                         us = time_chain(op, x, meta, y, cfg, flush)
                     except _lib.ObError:
@@ -95,7 +96,9 @@ def main() -> None:
                 tried += 1
                 if us < best[0]:
                     best = (us, cfg)
-            default_us = time_chain(op, x, meta, y, {}, flush)
+            if best[1]:   # confirm with more replays; a choice must beat the library's own rule by 3 % to enter the table
+                again = time_chain(op, x, meta, y, best[1], flush, reps=25)
+                best = (again, best[1]) if again < 0.97 * default_us else (default_us, {})
             status = op.scratch.status()
             assert status[0] == 0, status[:8]
             row = {"M": M, "N": N, "K": K, "S": len(widths), "R": RANK, "fmt": "fp8", **best[1], "us": round(best[0], 2),
