@@ -703,6 +703,8 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                         if (has_lora) v += __uint_as_float(r1[c]);
                         if (p.split2 == 1) {
                             if (row >= 0 && n_ok) p.y[(int64_t)row * p.ldy + n_glob] = __float2bfloat16_rn(v);
+                        } else if (p.cluster_reduce) {
+                            reinterpret_cast<float*>(ring)[(c0 + c) * kTileN + n_local] = v;   // the ring is idle by now
                         } else {
                             part[(size_t)(c0 + c) * kTileN + n_local] = v;
                         }
@@ -710,7 +712,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                 }
             }
             if (te == 0) { OB_TRACE(12) }
-            if (p.split2 > 1) {
+            if (p.split2 > 1 && !p.cluster_reduce) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");    // all 128 threads' partials precede the arrival below
                 if (te == 0) {
                     int old;                                      // release our partials, acquire the other splits'
@@ -757,6 +759,42 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
         }
     }
 
+    if (p.cluster_reduce) {
+        // The K splits of a tile are the CTAs of one cluster.  Each has left its fp32 partial tile at the start of its own
+        // shared memory; split j now sums tokens j, j + split2, ... over the cluster in split order and writes those rows.
+        // Every thread of every CTA takes part in both barriers, whatever happened to it before.
+        __syncthreads();
+        cluster_sync_all();
+        if (warp >= 4 && ctrl->go_flag) {
+            const int te = tid - 128, tg = te >> 5, n4 = (te & 31) * 4;
+            const uint32_t own = smem_u32(ring);
+            for (int c = j + p.split2 * tg; c < tn; c += p.split2 * 4) {
+                float4 v[8];
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj)
+                    if (jj < p.split2) v[jj] = ld_cluster_f4(cluster_peer_addr(own + (uint32_t)(c * kTileN + n4) * 4u, (uint32_t)jj));
+                float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                for (int jj = 0; jj < 8; ++jj)
+                    if (jj < p.split2) { acc.x += v[jj].x; acc.y += v[jj].y; acc.z += v[jj].z; acc.w += v[jj].w; }
+                const int row = ctrl->rowmap[c];
+                if (row >= 0) {
+                    __nv_bfloat16* yr = p.y + (int64_t)row * p.ldy + slice_off + n0_local + n4;
+                    const int left = n_s - (n0_local + n4);
+                    if (left >= 4 && (((uintptr_t)yr) & 7) == 0) {
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+                        *reinterpret_cast<uint2*>(yr) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                    } else {
+                        if (left > 0) yr[0] = __float2bfloat16_rn(acc.x);
+                        if (left > 1) yr[1] = __float2bfloat16_rn(acc.y);
+                        if (left > 2) yr[2] = __float2bfloat16_rn(acc.z);
+                        if (left > 3) yr[3] = __float2bfloat16_rn(acc.w);
+                    }
+                }
+            }
+        }
+        cluster_sync_all();
+    }
     if (tid == 128) { OB_TRACE(13) }
     // ---- teardown: nobody leaves while TMEM is in use or copies may still land in this CTA's shared memory
     if (ctrl->abort_flag) __nanosleep(200000);
@@ -802,12 +840,50 @@ static cudaError_t launch_k2_impl(const K2Params& p, const CUtensorMap& tm_w, co
     cfg.blockDim = dim3(kK2Threads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (pdl) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    if (p.cluster_reduce) {                      // the K splits of one tile (grid y) are one cluster
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 1;
+        attr[n_attr].val.clusterDim.y = (unsigned)p.split2;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = n_attr;
     return cudaLaunchKernelEx(&cfg, k2_kernel<FP4, STORED>, p, tm_w, tm_x, tm_b[0], tm_b[1], tm_b[2], tm_b[3]);
+}
+
+// How many clusters of `split2` CTAs (grid y) of this kernel the current device keeps resident at once; 0 on error.
+template <bool FP4, bool STORED>
+static int max_clusters_impl(int split2, size_t smem) {
+    cudaError_t e = cudaFuncSetAttribute(k2_kernel<FP4, STORED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return 0;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(64, (unsigned)split2, 1);
+    cfg.blockDim = dim3(kK2Threads);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = (unsigned)split2;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, k2_kernel<FP4, STORED>, &cfg);
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+    return n;
+}
+
+int k2_max_active_clusters(int fp4, int stored, int split2, size_t smem) {
+    return fp4 ? (stored ? max_clusters_impl<true, true>(split2, smem) : max_clusters_impl<true, false>(split2, smem))
+               : (stored ? max_clusters_impl<false, true>(split2, smem) : max_clusters_impl<false, false>(split2, smem));
 }
 
 cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,

@@ -1,5 +1,7 @@
 // The C ABI (include/onebase_b200.h): argument validation, launch geometry, TMA descriptor construction, launches.
 // Host code only allocates host memory; device memory always belongs to the caller.
+#include <cstdio>
+#include <cstdlib>
 #include <mutex>
 #include <new>
 #include <vector>
@@ -11,6 +13,7 @@ size_t k2_fp8_smem_bytes(int tn, int stages, int rc, int R, int fp4);
 cudaError_t launch_k2_nvfp4(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                             dim3 grid, size_t smem, int pdl, cudaStream_t stream);
 int k2_fp8_h_tiles(int tn);
+int k2_max_active_clusters(int fp4, int stored, int split2, size_t smem);
 cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream);
 cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                           dim3 grid, size_t smem, int pdl, cudaStream_t stream);
@@ -259,6 +262,33 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     return e == cudaSuccess ? OB_OK : (int)e;
 }
 
+// Split-K through a cluster: up to 8 splits, a partial tile that fits the operand ring, and all of the launch's clusters
+// resident at once (a cluster is placed whole inside one GPC, so fewer fit than single CTAs would).  Otherwise, and under
+// LOWBIT_SPLITK_GLOBAL=1, the partials go through the workspace and the arrival counters.
+bool cluster_reduce_fits(const ObLayer* l, const Resolved& r, size_t smem) {
+    static const bool force_global = [] { const char* v = std::getenv("LOWBIT_SPLITK_GLOBAL"); return v && v[0] == '1'; }();
+    if (force_global || r.split2 < 2 || r.split2 > 8) return false;
+    const size_t ring_bytes = (size_t)r.stages * ((size_t)kTileN * kBlockK + (size_t)r.tn * kBlockK);
+    if ((size_t)r.tn * kTileN * sizeof(float) > ring_bytes) return false;
+    static std::mutex mu;
+    static std::vector<std::pair<unsigned long long, int>> cache;   // (device, formats, split2, smem) -> resident clusters
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return false;
+    const int fp4 = l->d.base_fmt == OB_BASE_NVFP4 ? 1 : 0, stored = l->d.lora_fmt == kLoraBf16 ? 0 : 1;
+    const unsigned long long key = ((unsigned long long)dev << 48) | ((unsigned long long)(fp4 * 2 + stored) << 44) |
+                                   ((unsigned long long)r.split2 << 40) | (unsigned long long)smem;
+    std::lock_guard<std::mutex> g(mu);
+    int n = -1;
+    for (const auto& kv : cache) if (kv.first == key) n = kv.second;
+    if (n < 0) {
+        n = k2_max_active_clusters(fp4, stored, r.split2, smem);
+        cache.emplace_back(key, n);
+        if (std::getenv("LOWBIT_VERBOSE"))
+            std::fprintf(stderr, "[onebase_b200] split-K clusters of %d CTAs, %zu B shared memory: %d resident at once\n", r.split2, smem, n);
+    }
+    return l->n_tiles <= n;
+}
+
 int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, int pdl,
                 cudaStream_t stream, bool chain = false) {
     const ObLayerDesc& d = l->d;
@@ -306,6 +336,7 @@ int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     dim3 grid((unsigned)l->n_tiles, (unsigned)r.split2, (unsigned)r.m_tiles);
     const bool fp4 = d.base_fmt == OB_BASE_NVFP4;
     const size_t smem = k2_fp8_smem_bytes(r.tn, r.stages, l->rc, d.R, fp4 ? 1 : 0);
+    p.cluster_reduce = cluster_reduce_fits(l, r, smem) ? 1 : 0;
     cudaError_t e = fp4 ? launch_k2_nvfp4(p, l->tm_w, tm_x, l->tm_b, grid, smem, pdl, stream)
                         : launch_k2_fp8(p, l->tm_w, tm_x, l->tm_b, grid, smem, pdl, stream);
     return e == cudaSuccess ? OB_OK : (int)e;

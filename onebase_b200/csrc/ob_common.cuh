@@ -93,6 +93,7 @@ struct K2Params {
     int lora_fmt;
     int tn;                // tokens per tile (MMA N)
     int split2;            // GEMM split-K
+    int cluster_reduce;    // split2 > 1: the splits of a tile form one thread-block cluster and add their partials through shared memory
     int split1;            // shrink partials to sum
     int kblocks;           // ceil(K / 128)
     int stages;
