@@ -119,6 +119,9 @@ typedef struct ObTileCfg {
     int32_t split1;                  /* shrink split-K (1..32) */
     int32_t stages;                  /* shared-memory ring depth of the GEMM (2..12) */
     int32_t wait_ms;                 /* bound of every device-side wait in milliseconds (default 2000) */
+    int32_t fused;                   /* ob_chain_*: 1 = one kernel for the whole chain where that form applies (bf16
+                                      * adapters, at most 32 tokens): every GEMM CTA first takes a share of the
+                                      * quantization and of the shrink from work counters in the workspace */
 } ObTileCfg;
 
 typedef struct ObLayer ObLayer;      /* opaque: validated descriptor + TMA tensor maps (host memory only) */

@@ -17,416 +17,11 @@
 // The kernel starts with griddepcontrol.launch_dependents so that a dependent K2 may begin streaming W at once, and it
 // may itself be launched as a programmatic dependent of the preceding kernel: it reads the segment index and requests
 // its first block of A before griddepcontrol.wait, and touches x and the scratch only after it.
-#include "ob_common.cuh"
-#include "ob_ptx.cuh"
+#include "k1_device.cuh"
 
 namespace ob {
 
-#define OB_TRACE1(ev) \
-    if (p.trace != nullptr && (long long)blockIdx.x < p.trace_ctas && threadIdx.x == 0) \
-        p.trace[(long long)blockIdx.x * OB_TRACE_EVENTS + (ev)] = global_timer_ns();
-
 constexpr int kK1Threads = 256;
-constexpr int kQuantCache = 8;      // 16-byte vectors of the row a thread keeps in registers between the two passes
-constexpr float kFp8Max = 448.0f;
-constexpr float kMinTokenScale = 1.0f / (448.0f * 512.0f);
-
-__device__ __forceinline__ float amax8(const uint4& v) {
-    float m = fmaxf(fabsf(bf16_lo(v.x)), fabsf(bf16_hi(v.x)));
-    m = fmaxf(m, fmaxf(fabsf(bf16_lo(v.y)), fabsf(bf16_hi(v.y))));
-    m = fmaxf(m, fmaxf(fabsf(bf16_lo(v.z)), fabsf(bf16_hi(v.z))));
-    return fmaxf(m, fmaxf(fabsf(bf16_lo(v.w)), fabsf(bf16_hi(v.w))));
-}
-
-__device__ __forceinline__ float q1(float v, float sx) {
-    return fminf(fmaxf(__fdiv_rn(v, sx), -kFp8Max), kFp8Max);
-}
-
-__device__ __forceinline__ uint2 quant8(const uint4& v, float sx) {
-    uint2 o;
-    o.x = (uint32_t)cvt_e4m3x2(q1(bf16_lo(v.x), sx), q1(bf16_hi(v.x), sx)) |
-          ((uint32_t)cvt_e4m3x2(q1(bf16_lo(v.y), sx), q1(bf16_hi(v.y), sx)) << 16);
-    o.y = (uint32_t)cvt_e4m3x2(q1(bf16_lo(v.z), sx), q1(bf16_hi(v.z), sx)) |
-          ((uint32_t)cvt_e4m3x2(q1(bf16_lo(v.w), sx), q1(bf16_hi(v.w), sx)) << 16);
-    return o;
-}
-
-__device__ void quantize_position(const K1Params& p, int pos) {
-    __shared__ float s_part[kK1Threads / 32];
-    __shared__ float s_scale;
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int sorted_row = p.meta.srt[pos];            // requested together with the segment index (one latency, not two)
-    int n_all, n_ad;
-    segment_totals(p.meta, p.L, lane, n_all, n_ad);
-    n_all = min(n_all, p.M);
-    const int row = (n_ad > 0 && pos < n_all) ? min(max(sorted_row, 0), p.M - 1) : pos;
-    griddep_wait();                                   // x comes from the preceding kernel; the scratch may still be read by it
-    const uint4* xr = reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.ldx);
-    const int nvec = p.K >> 3;
-    uint4 cache[kQuantCache];
-    float amax = 0.0f;
-#pragma unroll
-    for (int c = 0; c < kQuantCache; ++c) {
-        const int i = tid + c * kK1Threads;
-        if (i < nvec) {
-            cache[c] = __ldg(xr + i);
-            amax = fmaxf(amax, amax8(cache[c]));
-        }
-    }
-    for (int i = tid + kQuantCache * kK1Threads; i < nvec; i += kK1Threads) amax = fmaxf(amax, amax8(__ldg(xr + i)));
-#pragma unroll
-    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    if (lane == 0) s_part[warp] = amax;
-    __syncthreads();
-    if (tid == 0) {
-        float m = s_part[0];
-        for (int w = 1; w < kK1Threads / 32; ++w) m = fmaxf(m, s_part[w]);
-        const float sx = fmaxf(__fdiv_rn(m, kFp8Max), kMinTokenScale);
-        s_scale = sx;
-        p.sx[pos] = sx;
-    }
-    __syncthreads();
-    const float sx = s_scale;
-    uint2* out = reinterpret_cast<uint2*>(p.xq + (size_t)pos * (size_t)p.K);
-#pragma unroll
-    for (int c = 0; c < kQuantCache; ++c) {
-        const int i = tid + c * kK1Threads;
-        if (i < nvec) out[i] = quant8(cache[c], sx);
-    }
-    for (int i = tid + kQuantCache * kK1Threads; i < nvec; i += kK1Threads) out[i] = quant8(__ldg(xr + i), sx);
-}
-
-__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
-    f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
-    f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
-}
-
-// e2m1 code of v (bit 3 = sign): round to nearest even on {0,.5,1,1.5,2,3,4,6}, saturating -- the threshold chain of
-// lowbit_lora/kernels/nvfp4_lora_vllm.py:70-76 (ties .25/1.25/2.5/5 go down, .75/1.75/3.5 go up).
-__device__ __forceinline__ uint32_t e2m1_code(float v) {
-    const float a = fabsf(v);
-    const uint32_t mag = (uint32_t)(a > 0.25f) + (uint32_t)(a >= 0.75f) + (uint32_t)(a > 1.25f) + (uint32_t)(a >= 1.75f) +
-                         (uint32_t)(a > 2.5f) + (uint32_t)(a >= 3.5f) + (uint32_t)(a > 5.0f);
-    return mag | (v < 0.0f ? 8u : 0u);
-}
-
-__device__ __forceinline__ float e4m3_to_float(uint32_t code) {
-    uint32_t h2;
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)code));
-    return __half2float(__ushort_as_half((unsigned short)(h2 & 0xFFFFu)));
-}
-
-// NVFP4 activation quantization of one position (vLLM's scaled_fp4_quant recipe, lowbit_lora/kernels/nvfp4_lora_vllm.py:
-// 102-115 / 361-376): per 16-element block sf = e4m3_rn(min(gs * (blockmax * rcp(6)), 448)), out_scale = sf != 0 ?
-// rcp(sf * rcp(gs)) : 0, code = e2m1_rn(x * out_scale); codes packed two per byte (element 2i in the low nibble).  One
-// thread per block.  The scales go straight into K2's scale-factor atoms: [token tile][K slot][128-token block][MMA][r%32]
-// [r/32][4], r = position within the token tile.
-__device__ void quantize_position_nvfp4(const K1Params& p, int pos) {
-    const int tid = threadIdx.x, lane = tid & 31;
-    const int sorted_row = p.meta.srt[pos];
-    int n_all, n_ad;
-    segment_totals(p.meta, p.L, lane, n_all, n_ad);
-    n_all = min(n_all, p.M);
-    const int row = (n_ad > 0 && pos < n_all) ? min(max(sorted_row, 0), p.M - 1) : pos;
-    const float gs = __ldg(p.x_global);
-    griddep_wait();
-    const uint4* xr = reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.ldx);
-    const float rcp6 = p.rcp_approx ? rcp_approx_ftz(6.0f) : __frcp_rn(6.0f);
-    const float rgs = p.rcp_approx ? rcp_approx_ftz(gs) : __frcp_rn(gs);
-    const int nblocks = p.K >> 4;
-    const int mt = pos / p.tn, r = pos % p.tn;
-    uint8_t* sf_tile = p.xsf + (size_t)mt * p.kslots * p.nblk * kSfSlotBytes;
-    const int sf_row = (r >> 7) * kSfSlotBytes + (r & 31) * 16 + ((r & 127) >> 5) * 4;
-    for (int b = tid; b < p.kslots * 16; b += kK1Threads) {
-        uint32_t sf_code = 0;
-        if (b < nblocks) {
-            float v[16];
-            unpack8(__ldg(xr + 2 * b), *reinterpret_cast<float(*)[8]>(&v[0]));
-            unpack8(__ldg(xr + 2 * b + 1), *reinterpret_cast<float(*)[8]>(&v[8]));
-            float vmax = 0.0f;
-#pragma unroll
-            for (int e = 0; e < 16; ++e) vmax = fmaxf(vmax, fabsf(v[e]));
-            const float sfv = fminf(__fmul_rn(gs, __fmul_rn(vmax, rcp6)), 448.0f);
-            sf_code = (uint32_t)cvt_e4m3x2(sfv, 0.0f) & 0xFFu;
-            const float sff = e4m3_to_float(sf_code);
-            float osc = 0.0f;
-            if (sff != 0.0f) {
-                const float den = __fmul_rn(sff, rgs);
-                osc = p.rcp_approx ? rcp_approx_ftz(den) : __frcp_rn(den);
-            }
-            uint32_t lo = 0, hi = 0;
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                lo |= e2m1_code(__fmul_rn(v[e], osc)) << (4 * e);
-                hi |= e2m1_code(__fmul_rn(v[8 + e], osc)) << (4 * e);
-            }
-            *reinterpret_cast<uint2*>(p.xq + (size_t)pos * (size_t)(p.K >> 1) + (size_t)b * 8) = make_uint2(lo, hi);
-        }
-        // K slot b / 16, MMA (b % 16) / 4, scale b % 4; blocks past K are zero scales
-        sf_tile[(size_t)(b >> 4) * p.nblk * kSfSlotBytes + sf_row + ((b & 15) >> 2) * 512 + (b & 3)] = (uint8_t)sf_code;
-    }
-}
-
-// 32 lane-partial values per lane -> lane i holds the warp-wide sum of value i (31 shuffles).
-__device__ __forceinline__ float transpose_reduce32(float (&v)[32], int lane) {
-#pragma unroll
-    for (int off = 16, n = 32; off >= 1; off >>= 1, n >>= 1) {
-        const bool upper = (lane & off) != 0;
-#pragma unroll
-        for (int i = 0; i < n / 2; ++i) {
-            const float send = upper ? v[i] : v[i + n / 2];
-            const float keep = upper ? v[i + n / 2] : v[i];
-            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-        }
-    }
-    return v[0];
-}
-
-// The 8 rank rows a warp owns, in the adapter's storage format: bf16, e4m3 codes (fp32 scale per row, applied after the
-// dot) or packed e2m1 codes with one ue4m3 scale per 16 elements (and one fp32 global per adapter and slice, applied
-// after the dot) -- lowbit_lora/kernels/fp8_lora_vllm.py:85-118.  A lane always covers 8 consecutive K elements of each
-// row: 16, 8 or 4 bytes of codes (+ 1 scale byte).
-template <int FMT>
-struct ARows {
-    const uint8_t* base;      // row 0 of the 8 rows, element 0
-    const uint8_t* sbase;     // NVFP4: block scales of row 0
-    size_t row_bytes, srow_bytes;
-    __device__ __forceinline__ ARows(const K1Params& p, int lora, int s, int rg) {
-        const size_t row = (size_t)lora * p.R + (size_t)rg * 8;
-        row_bytes = FMT == kLoraBf16 ? (size_t)p.K * 2 : FMT == kLoraFp8 ? (size_t)p.K : (size_t)p.K / 2;
-        srow_bytes = (size_t)p.K / 16;
-        base = static_cast<const uint8_t*>(p.a[s]) + row * row_bytes;
-        sbase = FMT == kLoraNvfp4 ? static_cast<const uint8_t*>(p.sa[s]) + row * srow_bytes : nullptr;
-    }
-    // raw codes of the lane's 8 elements at column k of each row (x: codes; y: the block's scale byte for NVFP4)
-    __device__ __forceinline__ void load(uint4 (&av)[8], int k, bool act) const {
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (act) {
-                if (FMT == kLoraBf16) {
-                    v = __ldg(reinterpret_cast<const uint4*>(base + r * row_bytes + (size_t)k * 2));
-                } else if (FMT == kLoraFp8) {
-                    const uint2 c = __ldg(reinterpret_cast<const uint2*>(base + r * row_bytes + (size_t)k));
-                    v.x = c.x; v.y = c.y;
-                } else {
-                    v.x = __ldg(reinterpret_cast<const uint32_t*>(base + r * row_bytes + (size_t)k / 2));
-                    v.y = __ldg(sbase + r * srow_bytes + (size_t)k / 16);
-                }
-            }
-            av[r] = v;
-        }
-    }
-};
-
-__device__ __forceinline__ float2 e4m3x2_to_float2(uint32_t two_codes) {
-    uint32_t h2;
-    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"((uint16_t)two_codes));
-    return __half22float2(*reinterpret_cast<__half2*>(&h2));
-}
-
-__device__ __forceinline__ float e2m1_value(uint32_t code) {
-    const uint32_t mag = code & 7u;
-    float v = __uint_as_float(0x3F000000u + (mag << 22));          // magnitudes 2..7: 1, 1.5, 2, 3, 4, 6
-    v = mag == 0 ? 0.0f : (mag == 1 ? 0.5f : v);
-    return (code & 8u) ? -v : v;
-}
-
-template <int FMT>
-__device__ __forceinline__ void unpack_a(const uint4& v, float (&f)[8]) {
-    if (FMT == kLoraBf16) {
-        unpack8(v, f);
-    } else if (FMT == kLoraFp8) {
-        const float2 a = e4m3x2_to_float2(v.x & 0xFFFFu), b = e4m3x2_to_float2(v.x >> 16);
-        const float2 c = e4m3x2_to_float2(v.y & 0xFFFFu), d = e4m3x2_to_float2(v.y >> 16);
-        f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
-    } else {
-        const float sf = e4m3_to_float(v.y & 0xFFu);
-#pragma unroll
-        for (int e = 0; e < 8; ++e) f[e] = e2m1_value((v.x >> (4 * e)) & 15u) * sf;    // exact in bf16, as the reference notes
-    }
-}
-
-// Scale applied to a finished dot product: the row's fp32 scale (FP8-stored) or the adapter's inverse global (NVFP4-stored).
-template <int FMT>
-__device__ __forceinline__ float post_scale(const K1Params& p, int lora, int s, int row_in_slice) {
-    if (FMT == kLoraFp8) return __ldg(static_cast<const float*>(p.sa[s]) + (size_t)lora * p.R + row_in_slice);
-    if (FMT == kLoraNvfp4) return __ldg(p.ag + (size_t)s * p.L + lora);
-    return 1.0f;
-}
-
-// One pass of a warp: 8 rank rows [k0, k1) of adapter `lora`, slice s, times the `nt` (<= 4) tokens whose x rows are
-// rows[0..nt); writes the split-K partial hp[j][s][pos0 + t][rg*8 .. +8].  bf16 adapters.  The first block of A is
-// requested before the wait on the preceding kernel (A is static); x is read and hp written only after it.
-template <int FMT>
-__device__ __forceinline__ void shrink_pass(const K1Params& p, int lora, int s, int rg, int j, int k0, int k1, int pos0,
-                                                 const int* rows, int nt, int lane) {
-    const ARows<FMT> a(p, lora, s, rg);
-    uint4 av[8];
-    a.load(av, k0 + lane * 8, k0 + lane * 8 < k1);
-    OB_TRACE1(1)
-    griddep_wait();
-    OB_TRACE1(2)
-    const __nv_bfloat16* xrow[4];
-#pragma unroll
-    for (int t = 0; t < 4; ++t) xrow[t] = p.x + (int64_t)rows[t < nt ? t : 0] * p.ldx;
-    float acc[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) acc[i] = 0.0f;
-    for (int kk = k0; kk < k1; kk += 256) {
-        const int k = kk + lane * 8;
-        const bool act = k < k1;
-        float xf[4][8];
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            if (t < nt && act) {
-                unpack8(__ldg(reinterpret_cast<const uint4*>(xrow[t] + k)), xf[t]);
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) xf[t][e] = 0.0f;
-            }
-        }
-#pragma unroll
-        for (int r = 0; r < 8; ++r) {
-            float af[8];
-            unpack_a<FMT>(av[r], af);
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                float sacc = acc[r * 4 + t];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) sacc = fmaf(af[e], xf[t][e], sacc);
-                acc[r * 4 + t] = sacc;
-            }
-        }
-        if (kk + 256 < k1) a.load(av, k + 256, k + 256 < k1);
-    }
-    const float total = transpose_reduce32(acc, lane);
-    const int r = lane >> 2, t = lane & 3;
-    if (t < nt) p.hp[(((size_t)j * p.S + s) * p.max_m + (pos0 + t)) * p.R + rg * 8 + r] = total * post_scale<FMT>(p, lora, s, rg * 8 + r);
-}
-
-template <int FMT>
-__device__ __forceinline__ void fma8(float (&acc)[8], const uint4 (&av)[8], const float (&xf)[8]) {
-#pragma unroll
-    for (int r = 0; r < 8; ++r) {
-        float af[8];
-        unpack_a<FMT>(av[r], af);
-        float sacc = acc[r];
-#pragma unroll
-        for (int e = 0; e < 8; ++e) sacc = fmaf(af[e], xf[e], sacc);
-        acc[r] = sacc;
-    }
-}
-
-// Decode form of the pass (one token): two K steps of A in flight per lane (8 KB per warp), both requested before the wait
-// on the preceding kernel.  8 lane-partials -> lanes 0..7 hold the 8 rank rows' sums (2 butterfly + 3 transposing steps).
-template <int FMT>
-__device__ __forceinline__ void shrink_pass1(const K1Params& p, int lora, int s, int rg, int j, int k0, int k1, int pos,
-                                                  int row, int lane) {
-    const ARows<FMT> a(p, lora, s, rg);
-    const int kl = k0 + lane * 8;
-    uint4 a0[8], a1[8];
-    a.load(a0, kl, kl < k1);
-    a.load(a1, kl + 256, kl + 256 < k1);
-    OB_TRACE1(1)
-    griddep_wait();
-    OB_TRACE1(2)
-    const __nv_bfloat16* xrow = p.x + (int64_t)row * p.ldx;
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-    for (int k = kl; k < k1; k += 512) {
-        float x0[8], x1[8];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(xrow + k)), x0);
-        if (k + 256 < k1) {
-            unpack8(__ldg(reinterpret_cast<const uint4*>(xrow + k + 256)), x1);
-        } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) x1[e] = 0.0f;
-        }
-        fma8<FMT>(acc, a0, x0);
-        a.load(a0, k + 512, k + 512 < k1);
-        fma8<FMT>(acc, a1, x1);
-        a.load(a1, k + 768, k + 768 < k1);
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 16);
-        acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], 8);
-    }
-#pragma unroll
-    for (int off = 4, n = 8; off >= 1; off >>= 1, n >>= 1) {
-        const bool upper = (lane & off) != 0;
-#pragma unroll
-        for (int i = 0; i < n / 2; ++i) {
-            const float send = upper ? acc[i] : acc[i + n / 2];
-            const float keep = upper ? acc[i + n / 2] : acc[i];
-            acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-        }
-    }
-    if (lane < 8) p.hp[(((size_t)j * p.S + s) * p.max_m + pos) * p.R + rg * 8 + lane] = acc[0] * post_scale<FMT>(p, lora, s, rg * 8 + lane);
-}
-
-// One warp: block `pb` of p.pb consecutive sorted positions, unit `u` -> (slice, group of 8 rank rows, K split).
-// One warp-wide read of the segment index gives the batch totals and the segment (adapter) of each of the warp's
-// positions; the positions' token rows are requested at the same time.  Then one pass per run of positions that share
-// an adapter.
-template <int FMT>
-__device__ void shrink_unit(const K1Params& p, int pb, int u, int lane) {
-    const int p0 = pb * p.pb;
-    int rows[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-        int r = (q < p.pb && p0 + q < p.M) ? p.meta.srt[p0 + q] : 0;
-        rows[q] = r < 0 ? 0 : (r > p.M - 1 ? p.M - 1 : r);
-    }
-    int lora_of[4] = {-1, -1, -1, -1};
-    int n_all = 0, n_ad = 0;
-    for (int base = 0; base <= p.L; base += 32) {
-        const int i = base + lane;
-        int id = -1, st = 0, cnt = 0;
-        if (i <= p.L) {
-            id = p.meta.seg_ids[i];
-            st = p.meta.seg_start[i];
-            cnt = p.meta.seg_n[i];
-        }
-        n_all += cnt;
-        n_ad += id >= 0 ? cnt : 0;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const bool hit = q < p.pb && id >= 0 && id < p.L && st <= p0 + q && p0 + q < st + cnt;
-            const uint32_t m = __ballot_sync(0xffffffffu, hit);
-            if (m) lora_of[q] = __shfl_sync(0xffffffffu, id, __ffs(m) - 1);
-        }
-    }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) {
-        n_all += __shfl_xor_sync(0xffffffffu, n_all, o);
-        n_ad += __shfl_xor_sync(0xffffffffu, n_ad, o);
-    }
-    n_all = min(n_all, p.M);
-    if (n_ad <= 0) return;
-    const int np = min(p.pb, n_all - p0);
-    if (np <= 0) return;
-    const int groups = p.R >> 3;
-    const int j = u % p.split1;
-    const int rg = (u / p.split1) % groups;
-    const int s = u / (p.split1 * groups);
-    const int k0 = j * p.k_per_split;
-    const int k1 = min(p.K, k0 + p.k_per_split);
-    if (p.pb == 1) {
-        if (lora_of[0] >= 0) shrink_pass1<FMT>(p, lora_of[0], s, rg, j, k0, k1, p0, rows[0], lane);
-        return;
-    }
-    int q = 0;
-    while (q < np) {
-        const int lora = lora_of[q];
-        int nt = 1;
-        while (q + nt < np && lora_of[q + nt] == lora) ++nt;
-        if (lora >= 0) shrink_pass<FMT>(p, lora, s, rg, j, k0, k1, p0 + q, rows + q, nt, lane);
-        q += nt;
-    }
-}
 
 // One instantiation per (adapter storage, base format): each launch carries only the code of its own case.
 template <int LORA_FMT, bool FP4_BASE>
@@ -434,8 +29,10 @@ __global__ void __launch_bounds__(kK1Threads) k1_kernel(const K1Params p) {
     griddep_launch_dependents();
     OB_TRACE1(0)
     if ((int)blockIdx.x < p.n_quant_ctas) {
-        if (FP4_BASE) quantize_position_nvfp4(p, blockIdx.x);
-        else quantize_position(p, blockIdx.x);
+        const int row = row_of_position(p, blockIdx.x, threadIdx.x & 31);
+        griddep_wait();                               // x comes from the preceding kernel; the scratch may still be read by it
+        if (FP4_BASE) quantize_row_nvfp4<kK1Threads>(p, blockIdx.x, row, threadIdx.x);
+        else quantize_row<kK1Threads, 0>(p, blockIdx.x, row, threadIdx.x);
         if (p.xq_ready != nullptr) {          // chain: tell K2 that this position's codes and scale are in memory
             __syncthreads();
             if (threadIdx.x == 0) red_release_add(p.xq_ready, 1);

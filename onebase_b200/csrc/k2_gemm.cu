@@ -27,8 +27,7 @@
 // lowbit_lora/kernels/fp8_lora_pdl.py:324-495; positions, padding and stale metadata follow fp8_lora_vllm.py:147-163.
 // Every wait is bounded (wait_ms); a wait that runs out records where in the workspace status words and the CTA leaves
 // without storing.
-#include "ob_common.cuh"
-#include "ob_ptx.cuh"
+#include "k1_device.cuh"
 
 namespace ob {
 
@@ -57,6 +56,8 @@ struct K2Ctrl {
     int n_steps;          // expand steps of this CTA
     int last_flag;
     int go_flag;          // the epilogue warps' shared continue / stop decision
+    int claim;            // fused: the position the four epilogue warps claimed together
+    int lora_pos[32];     // fused: adapter slot of each of the tile's positions (-1: none)
     float sx[256];
     int rowmap[256];
     LoraStep steps[kMaxLoraIters];
@@ -209,11 +210,36 @@ __device__ __forceinline__ void fill_b_tile(const K2Params& p, const LoraStep& e
     }
 }
 
-template <bool FP4, bool STORED>
+// Fused decode form: the warps of every CTA except the producer and the MMA issuer claim the shrink kernel's work
+// (positions to quantize, then shrink units) from two counters before they take up their GEMM roles.  A claimed piece of
+// work never waits for another CTA, so the launch cannot deadlock however its CTAs are scheduled.
+template <int FMT>
+__device__ __forceinline__ void fused_shrink_units(const K2Params& p, const K1Params& k1, const K2Ctrl* ctrl, int lane) {
+    const int groups = k1.R >> 3;
+    for (;;) {
+        int u = 0;
+        if (lane == 0) u = atomicAdd(p.work_shrink, 1);
+        u = __shfl_sync(0xffffffffu, u, 0);
+        if (u >= p.shrink_units) break;
+        // unit -> (position, slice, group of 8 rank rows, K split); the position's row and adapter were worked out once
+        // per CTA together with the expand steps
+        const int pos = u / k1.units_per_block, uu = u % k1.units_per_block;
+        const int lora = ctrl->lora_pos[pos], row = ctrl->rowmap[pos];
+        if (lora >= 0 && row >= 0) {
+            const int j = uu % k1.split1, rg = (uu / k1.split1) % groups, sl = uu / (k1.split1 * groups);
+            const int k0 = j * k1.k_per_split;
+            shrink_pass1<FMT>(k1, lora, sl, rg, j, k0, min(k1.K, k0 + k1.k_per_split), pos, row, lane);
+        }
+        __syncwarp();
+        if (lane == 0) red_release_add(p.hp_ready, 1);      // the unit's partial sums are in memory
+    }
+}
+
+template <bool FP4, bool STORED, bool FUSED>
 __global__ void __launch_bounds__(kK2Threads, 2)
 k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
               const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
-              const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_b3) {
+              const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_b3, const K1Params k1) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int tn = p.tn;
@@ -247,6 +273,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
     const int n_base = kb1 - kb0;
     const int n_chunks = p.R / p.rc;
     const int tile_lin = blockIdx.z * gridDim.x + blockIdx.x;
+    const int lead = FUSED ? max(p.stages, n_base) : p.stages;   // fused: every W tile first -- the shrink runs beside them
     const long long trace_cta = blockIdx.x + (long long)gridDim.x * (blockIdx.y + (long long)gridDim.y * blockIdx.z);
     if (tid == 0) { OB_TRACE(0) }
 
@@ -297,7 +324,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
             const CUtensorMap* tmb = (s == 0) ? &tm_b0 : (s == 1) ? &tm_b1 : (s == 2) ? &tm_b2 : &tm_b3;
             const uint32_t b_bytes = (uint32_t)kTileN * p.rc * 2;
             const uint32_t wx_bytes = (uint32_t)kWTileBytes + (uint32_t)tn * kBlockK + (uint32_t)sf_bytes;
-            SlotWalk w(p.stages);
+            SlotWalk w(lead);
             RingBook book;
             const bool b_by_tma = !STORED;
             int n_steps = 0;
@@ -313,9 +340,10 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                 if (!k1_done && (finished || w.it >= p.stages)) {
                     // The ring is full (or everything is requested): from here on progress needs K1's x_q.  Wait for K1 and
                     // request the x_q tile of every W slot issued so far.
-                    if (p.xq_ready != nullptr) {
-                        // chain: K1's quantizing CTAs count the positions they finished; their codes are enough to start the
-                        // base GEMM, the rest of K1 (the shrink) keeps running beside it
+                    griddep_wait();     // the preceding kernel is complete: K1's outputs, or (fused) x and the cleared counters
+                    if constexpr (FUSED) {
+                        // The CTAs' epilogue warps count the positions they quantized; those codes are enough to start the
+                        // base GEMM while the shrink units keep running beside it.
                         const uint64_t t_start = global_timer_ns();
                         bool ready = false;
                         for (uint32_t spin = 0;; ++spin) {
@@ -324,12 +352,10 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                         }
                         if (!ready) { record_timeout(p, ctrl, 15, w.it); break; }
                         fence_proxy_async_all();
-                    } else {
-                        griddep_wait();
                     }
                     OB_TRACE(4)
                     k1_done = true;
-                    SlotWalk r(p.stages);
+                    SlotWalk r(lead);
                     while (r.it < w.it) {
                         const bool rb = r.is_b(n_base, n_steps);
                         if (!rb) {
@@ -389,7 +415,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
             const uint32_t row_bytes = (uint32_t)p.rc * 2;                 // 32, 64 or 128
             const uint32_t lt = row_bytes == 128 ? 2u : row_bytes == 64 ? 4u : 6u;
             const uint32_t sbo = row_bytes * 8;
-            SlotWalk w(p.stages);
+            SlotWalk w(lead);
             uint32_t par_w = 0, par_b = 0;
             int n_steps = 0;
             bool have_list = false, ok = true;
@@ -457,6 +483,10 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
         if (small) {
             for (int i = lane; i < nh * h_bytes / 16; i += 32) reinterpret_cast<uint4*>(hbuf)[i] = make_uint4(0u, 0u, 0u, 0u);
             bool ok = mbar_wait(&ctrl->list_ready, 0, limit_ns);
+            if constexpr (FUSED) {
+                griddep_wait();
+                if (ok) fused_shrink_units<kLoraBf16>(p, k1, ctrl, lane);
+            }
             const int n_steps = ok ? ctrl->n_steps : 0;
             if (ok && n_steps > 0) ok = mbar_wait(&ctrl->htab_ready, 0, limit_ns);
             if (!ok && lane == 0) record_timeout(p, ctrl, 13, 0);
@@ -492,6 +522,12 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                 if (lane == 0) mbar_arrive(&ctrl->h_full[hb]);
             }
         }
+    } else if (warp == 3) {
+        if constexpr (FUSED) {
+            const bool ok = mbar_wait(&ctrl->list_ready, 0, limit_ns);
+            griddep_wait();
+            if (ok) fused_shrink_units<kLoraBf16>(p, k1, ctrl, lane);
+        }
     } else if (warp >= 4) {
         // =========================================================== segment index, H tiles, epilogue
         const int te = tid - 128;
@@ -501,6 +537,10 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
         for (int c = te; c < tn; c += 128) {
             const int pos = t0 + c;
             ctrl->rowmap[c] = pos < p.M ? position_row(p.meta, pos, p.M, n_all, n_ad) : -1;
+        }
+        if (FUSED) {
+            for (int c = te; c < 32; c += 128) ctrl->lora_pos[c] = -1;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
         }
         if (warp == 4) {
             int total = 0;                                   // (segment, chunk) steps of this tile so far, all splits
@@ -517,6 +557,8 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                     }
                     const bool ok = lora >= 0 && lora < p.L && lo < hi;
                     const uint32_t mask = __ballot_sync(0xffffffffu, ok);
+                    if (FUSED && ok)
+                        for (int pos = lo; pos < hi; ++pos) ctrl->lora_pos[pos - t0] = lora;
                     if (ok) {
                         const int idx = total / n_chunks + __popc(mask & ((1u << lane) - 1u));
                         for (int c = 0; c < n_chunks; ++c) {
@@ -541,8 +583,34 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
         const int n_steps = ctrl->n_steps;
 
         griddep_wait();                                       // K1's s_x and shrink partials from here on
+        if constexpr (FUSED) {
+            // x is final now.  Quantize positions, one per claim of the four warps together; then shrink units, one per
+            // claim of a warp; then wait until every position and every unit of the launch is done.
+            for (;;) {
+                if (te == 0) ctrl->claim = atomicAdd(p.work_quant, 1);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int qpos = ctrl->claim;
+                if (qpos >= p.M) break;
+                const int qrow = ctrl->rowmap[qpos];          // t0 = 0: the fused form serves one token tile
+                if (FP4) quantize_row_nvfp4<128>(k1, qpos, qrow, te);
+                else quantize_row<128, 1>(k1, qpos, qrow, te);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (te == 0) red_release_add(p.xq_ready, 1);
+            }
+            fused_shrink_units<kLoraBf16>(p, k1, ctrl, lane);
+            if (te == 0) {
+                const uint64_t t_start = global_timer_ns();
+                bool ready = false;
+                for (uint32_t spin = 0;; ++spin) {
+                    if (ld_acquire(p.xq_ready) >= p.M && ld_acquire(p.hp_ready) >= p.shrink_units) { ready = true; break; }
+                    if ((spin & 31u) == 31u && global_timer_ns() - t_start > limit_ns) break;
+                }
+                if (!ready) record_timeout(p, ctrl, 16, 0);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         if (te == 0) { OB_TRACE(8) }
-        for (int c = te; c < tn; c += 128) ctrl->sx[c] = FP4 ? 1.0f : ((t0 + c < p.M) ? p.sx[t0 + c] : 0.0f);
+        for (int c = te; c < tn; c += 128) ctrl->sx[c] = FP4 ? 1.0f : ((t0 + c < p.M) ? __ldcg(p.sx + t0 + c) : 0.0f);
 
         const int row_bytes = p.rc * 2;
         const int cpr = row_bytes / 16;                       // 16-byte chunks per tile row
@@ -595,11 +663,11 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                 }
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (te == 0) { mbar_arrive(&ctrl->htab_ready); OB_TRACE(9) }
+            if (te == 0) { mbar_arrive(&ctrl->htab_ready); }
         }
         constexpr bool stored = STORED;                       // FP8- / NVFP4-stored adapters: these warps produce the B tiles
         if (stored || !small) {
-            SlotWalk w(p.stages);
+            SlotWalk w(lead);
             RingBook book;
             for (int li = 0; li < n_steps; ++li) {
                 uint32_t parity = 0;
@@ -670,7 +738,6 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
         asm volatile("bar.sync 1, 128;" ::: "memory");            // sx / rowmap visible to all epilogue threads
 
         // ---- epilogue
-        if (te == 0) { OB_TRACE(10) }
         if (te == 0) {
             int go = ctrl->abort_flag ? 0 : 1;
             if (go && !mbar_wait(&ctrl->acc_full, 0u, limit_ns)) {
@@ -711,7 +778,6 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                     }
                 }
             }
-            if (te == 0) { OB_TRACE(12) }
             if (p.split2 > 1 && !p.cluster_reduce) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");    // all 128 threads' partials precede the arrival below
                 if (te == 0) {
@@ -795,7 +861,6 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
         }
         cluster_sync_all();
     }
-    if (tid == 128) { OB_TRACE(13) }
     // ---- teardown: nobody leaves while TMEM is in use or copies may still land in this CTA's shared memory
     if (ctrl->abort_flag) __nanosleep(200000);
     tc_fence_before();
@@ -804,10 +869,15 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);
     }
-    if (tid == 0 && p.chain_done != nullptr) {      // chain: the last CTA of the launch clears the flags for the next call
+    if (FUSED && tid == 0) {                        // the last CTA of the launch clears the work counters for the next call
         const int total = (int)(gridDim.x * gridDim.y * gridDim.z);
         if (atomicAdd(p.chain_done, 1) == total - 1) {
             *const_cast<volatile int32_t*>(p.xq_ready) = 0;
+            if constexpr (FUSED) {
+                *const_cast<volatile int32_t*>(p.work_quant) = 0;
+                *const_cast<volatile int32_t*>(p.work_shrink) = 0;
+                *const_cast<volatile int32_t*>(p.hp_ready) = 0;
+            }
             *const_cast<volatile int32_t*>(p.chain_done) = 0;
         }
     }
@@ -823,15 +893,19 @@ size_t k2_fp8_smem_bytes(int tn, int stages, int rc, int R, int fp4) {
     return 1024 + (size_t)stages * (kWTileBytes + (size_t)tn * kBlockK + sf) + aux + kCtrlBytes;
 }
 
-template <bool FP4, bool STORED>
+template <bool FP4, bool STORED, bool FUSED>
 static cudaError_t launch_k2_impl(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
-                                  dim3 grid, size_t smem, int pdl, cudaStream_t stream) {
+                                  dim3 grid, size_t smem, int pdl, cudaStream_t stream, const K1Params& k1) {
     static int configured_for[64] = {0};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64 && !configured_for[dev]) {
-        e = cudaFuncSetAttribute(k2_kernel<FP4, STORED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncAttributes fa;                    // the opt-in limit covers static + dynamic shared memory
+        e = cudaFuncGetAttributes(&fa, k2_kernel<FP4, STORED, FUSED>);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(k2_kernel<FP4, STORED, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 227 * 1024 - (int)fa.sharedSizeBytes);
         if (e != cudaSuccess) return e;
         configured_for[dev] = 1;
     }
@@ -856,13 +930,13 @@ static cudaError_t launch_k2_impl(const K2Params& p, const CUtensorMap& tm_w, co
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    return cudaLaunchKernelEx(&cfg, k2_kernel<FP4, STORED>, p, tm_w, tm_x, tm_b[0], tm_b[1], tm_b[2], tm_b[3]);
+    return cudaLaunchKernelEx(&cfg, k2_kernel<FP4, STORED, FUSED>, p, tm_w, tm_x, tm_b[0], tm_b[1], tm_b[2], tm_b[3], k1);
 }
 
 // How many clusters of `split2` CTAs (grid y) of this kernel the current device keeps resident at once; 0 on error.
 template <bool FP4, bool STORED>
 static int max_clusters_impl(int split2, size_t smem) {
-    cudaError_t e = cudaFuncSetAttribute(k2_kernel<FP4, STORED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(k2_kernel<FP4, STORED, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(64, (unsigned)split2, 1);
@@ -876,7 +950,7 @@ static int max_clusters_impl(int split2, size_t smem) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    e = cudaOccupancyMaxActiveClusters(&n, k2_kernel<FP4, STORED>, &cfg);
+    e = cudaOccupancyMaxActiveClusters(&n, k2_kernel<FP4, STORED, false>, &cfg);
     if (e != cudaSuccess) { (void)cudaGetLastError(); return 0; }
     return n;
 }
@@ -888,14 +962,23 @@ int k2_max_active_clusters(int fp4, int stored, int split2, size_t smem) {
 
 cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                           dim3 grid, size_t smem, int pdl, cudaStream_t stream) {
-    return p.lora_fmt == kLoraBf16 ? launch_k2_impl<false, false>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream)
-                                   : launch_k2_impl<false, true>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream);
+    const K1Params none = {};
+    return p.lora_fmt == kLoraBf16 ? launch_k2_impl<false, false, false>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream, none)
+                                   : launch_k2_impl<false, true, false>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream, none);
 }
 
 cudaError_t launch_k2_nvfp4(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                             dim3 grid, size_t smem, int pdl, cudaStream_t stream) {
-    return p.lora_fmt == kLoraBf16 ? launch_k2_impl<true, false>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream)
-                                   : launch_k2_impl<true, true>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream);
+    const K1Params none = {};
+    return p.lora_fmt == kLoraBf16 ? launch_k2_impl<true, false, false>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream, none)
+                                   : launch_k2_impl<true, true, false>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream, none);
+}
+
+// The fused decode kernel (bf16 adapters, one token tile of at most 32 tokens): quantization, shrink and GEMM in one launch.
+cudaError_t launch_fused(const K2Params& p, const K1Params& k1, const CUtensorMap& tm_w, const CUtensorMap& tm_x,
+                         const CUtensorMap* tm_b, dim3 grid, size_t smem, cudaStream_t stream) {
+    return k1.base_fmt == OB_BASE_NVFP4 ? launch_k2_impl<true, false, true>(p, tm_w, tm_x, tm_b, grid, smem, 1, stream, k1)
+                                        : launch_k2_impl<false, false, true>(p, tm_w, tm_x, tm_b, grid, smem, 1, stream, k1);
 }
 
 }  // namespace ob

@@ -14,6 +14,8 @@ cudaError_t launch_k2_nvfp4(const K2Params& p, const CUtensorMap& tm_w, const CU
                             dim3 grid, size_t smem, int pdl, cudaStream_t stream);
 int k2_fp8_h_tiles(int tn);
 int k2_max_active_clusters(int fp4, int stored, int split2, size_t smem);
+cudaError_t launch_fused(const K2Params& p, const K1Params& k1, const CUtensorMap& tm_w, const CUtensorMap& tm_x,
+                         const CUtensorMap* tm_b, dim3 grid, size_t smem, cudaStream_t stream);
 cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream);
 cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                           dim3 grid, size_t smem, int pdl, cudaStream_t stream);
@@ -27,7 +29,7 @@ using namespace ob;
 
 namespace {
 
-constexpr size_t kSmemLimit = 227 * 1024;
+constexpr size_t kSmemLimit = 226 * 1024;    // dynamic part; the kernels keep a few static words besides
 constexpr size_t kSmemTwoPerSm = 112 * 1024;   // two CTAs of this size (+1 KB reserved each) fit one SM's 228 KB
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -144,7 +146,7 @@ int validate_workspace(const ObLayer* l, const void* ws, const ObWorkspaceShape*
 int k_bytes(const ObLayerDesc& d) { return d.base_fmt == OB_BASE_NVFP4 ? d.K / 2 : d.K; }
 
 struct Resolved {
-    int tn, split1, split2, stages, m_tiles, k_per_split, pb;
+    int tn, split1, split2, stages, m_tiles, k_per_split, pb, fused;
     uint32_t wait_ms;
 };
 
@@ -198,6 +200,7 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     r->stages = stages;
     if ((long long)(d.L < r->tn ? d.L : r->tn) * (d.R / rc) > kMaxLoraIters) return OB_ERR_TOO_LARGE;
     r->wait_ms = (cfg && cfg->wait_ms > 0) ? (uint32_t)cfg->wait_ms : 2000u;
+    r->fused = (cfg && cfg->fused) ? 1 : 0;
     return OB_OK;
 }
 
@@ -222,8 +225,7 @@ int get_xmap(ObLayer* l, const void* xq, int rows, int tn, CUtensorMap* out) {
     return OB_OK;
 }
 
-int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, int pdl,
-                cudaStream_t stream, bool chain = false) {
+K1Params k1_params(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, bool chain) {
     const ObLayerDesc& d = l->d;
     const WorkspaceLayout lay = workspace_layout(*sh);
     uint8_t* base = static_cast<uint8_t*>(ws);
@@ -255,6 +257,12 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     p.xq_ready = chain ? reinterpret_cast<int32_t*>(base + lay.counters) + kCounterSlots : nullptr;
     p.trace = g_trace ? g_trace + g_trace_ctas * OB_TRACE_EVENTS : nullptr;   // K1's stamps follow K2's
     p.trace_ctas = g_trace_ctas;
+    return p;
+}
+
+int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, int pdl,
+                cudaStream_t stream, bool chain = false) {
+    const K1Params p = k1_params(l, b, ws, sh, r, chain);
     const long long warps = (long long)p.n_pblocks * p.units_per_block;
     const long long grid = p.n_quant_ctas + (warps + 7) / 8;
     if (grid > 0x7fffffffLL) return OB_ERR_TOO_LARGE;
@@ -289,15 +297,23 @@ bool cluster_reduce_fits(const ObLayer* l, const Resolved& r, size_t smem) {
     return l->n_tiles <= n;
 }
 
-int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, int pdl,
-                cudaStream_t stream, bool chain = false) {
+// K2's launch: parameters, tensor map of the quantized activations, grid and shared memory.
+struct K2Launch {
+    K2Params p;
+    CUtensorMap tm_x;
+    dim3 grid;
+    size_t smem;
+    bool fp4;
+};
+
+int k2_prepare(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, bool chain, K2Launch* out) {
     const ObLayerDesc& d = l->d;
     const WorkspaceLayout lay = workspace_layout(*sh);
     uint8_t* base = static_cast<uint8_t*>(ws);
-    CUtensorMap tm_x;
-    int st = get_xmap(l, base + lay.xq, sh->max_m, r.tn, &tm_x);
+    int st = get_xmap(l, base + lay.xq, sh->max_m, r.tn, &out->tm_x);
     if (st != OB_OK) return st;
-    K2Params p = {};
+    out->p = K2Params{};
+    K2Params& p = out->p;
     p.M = b->M; p.N = d.N; p.K = d.K; p.S = d.S; p.R = d.R; p.L = d.L;
     for (int s = 0; s < OB_MAX_SLICES; ++s) p.widths[s] = s < d.S ? d.widths[s] : 0;
     p.lora_fmt = d.lora_fmt;
@@ -333,12 +349,44 @@ int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
         const size_t need = (size_t)r.split2 * (size_t)l->n_tiles * (size_t)r.tn * kTileN * sizeof(float);
         if (lay.part + need > lay.total) return OB_ERR_WORKSPACE;
     }
-    dim3 grid((unsigned)l->n_tiles, (unsigned)r.split2, (unsigned)r.m_tiles);
-    const bool fp4 = d.base_fmt == OB_BASE_NVFP4;
-    const size_t smem = k2_fp8_smem_bytes(r.tn, r.stages, l->rc, d.R, fp4 ? 1 : 0);
-    p.cluster_reduce = cluster_reduce_fits(l, r, smem) ? 1 : 0;
-    cudaError_t e = fp4 ? launch_k2_nvfp4(p, l->tm_w, tm_x, l->tm_b, grid, smem, pdl, stream)
-                        : launch_k2_fp8(p, l->tm_w, tm_x, l->tm_b, grid, smem, pdl, stream);
+    out->grid = dim3((unsigned)l->n_tiles, (unsigned)r.split2, (unsigned)r.m_tiles);
+    out->fp4 = d.base_fmt == OB_BASE_NVFP4;
+    out->smem = k2_fp8_smem_bytes(r.tn, r.stages, l->rc, d.R, out->fp4 ? 1 : 0);
+    p.cluster_reduce = cluster_reduce_fits(l, r, out->smem) ? 1 : 0;
+    return OB_OK;
+}
+
+int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, int pdl,
+                cudaStream_t stream, bool chain = false) {
+    K2Launch k;
+    const int st = k2_prepare(l, b, ws, sh, r, chain, &k);
+    if (st != OB_OK) return st;
+    cudaError_t e = k.fp4 ? launch_k2_nvfp4(k.p, l->tm_w, k.tm_x, l->tm_b, k.grid, k.smem, pdl, stream)
+                          : launch_k2_fp8(k.p, l->tm_w, k.tm_x, l->tm_b, k.grid, k.smem, pdl, stream);
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
+
+// ObTileCfg.fused: a decode chain of bf16 adapters as ONE kernel.  Every CTA of the GEMM first takes a share of the
+// quantization and of the shrink from two work counters, so the weight stream starts with the launch and no second launch
+// sits in between; in exchange the shrink's dependent loads queue behind the CTA's own weight stream.  Which form wins
+// depends on the shape, so the tile table decides.
+bool fused_applies(const ObLayer* l, const Resolved& r) {
+    return r.fused && l->d.lora_fmt == kLoraBf16 && r.pb == 1 && r.m_tiles == 1 && r.tn <= 32;
+}
+
+int fused_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, cudaStream_t stream) {
+    K2Launch k;
+    const int st = k2_prepare(l, b, ws, sh, r, true, &k);
+    if (st != OB_OK) return st;
+    K1Params k1 = k1_params(l, b, ws, sh, r, true);
+    k1.trace = g_trace ? g_trace + g_trace_ctas * OB_TRACE_EVENTS : nullptr;
+    k.p.work_quant = k.p.counters + kCounterSlots + 2;
+    k.p.work_shrink = k.p.counters + kCounterSlots + 3;
+    k.p.hp_ready = k.p.counters + kCounterSlots + 4;
+    const long long units = (long long)k1.n_pblocks * k1.units_per_block;
+    if (units > 0x3fffffffLL) return OB_ERR_TOO_LARGE;
+    k.p.shrink_units = (int)units;
+    cudaError_t e = launch_fused(k.p, k1, l->tm_w, k.tm_x, l->tm_b, k.grid, k.smem, stream);
     return e == cudaSuccess ? OB_OK : (int)e;
 }
 
@@ -540,9 +588,10 @@ int ob_chain_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const Ob
     int st = prepare_call(layer, batch, workspace, shape, cfg, &r);
     if (st != OB_OK) return st;
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream, true);
+    if (fused_applies(layer, r)) return fused_impl(layer, batch, workspace, shape, r, stream);
+    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
     if (st != OB_OK) return st;
-    return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream, true);
+    return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
 }
 
 int ob_k1_nvfp4(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape, const ObTileCfg* cfg,
@@ -567,9 +616,10 @@ int ob_chain_nvfp4(ObLayer* layer, const ObBatch* batch, void* workspace, const 
     int st = prepare_call(layer, batch, workspace, shape, cfg, &r, OB_BASE_NVFP4);
     if (st != OB_OK) return st;
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
-    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream, true);
+    if (fused_applies(layer, r)) return fused_impl(layer, batch, workspace, shape, r, stream);
+    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
     if (st != OB_OK) return st;
-    return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream, true);
+    return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
 }
 
 int ob_nvfp4_packed_scale_bytes(int32_t K, int32_t S, const int32_t* widths, size_t* bytes) {

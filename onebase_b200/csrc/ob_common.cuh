@@ -118,7 +118,11 @@ struct K2Params {
     const float* alpha;    // NVFP4 base: [1] 1 / (x_global * w_global)
     int nblk;              // NVFP4 base: 128-token scale-factor blocks per token tile (1, or 2 for 256-token tiles)
     int32_t* xq_ready;     // chain: K1's count of quantized positions; the producer polls it instead of waiting for all of K1
-    int32_t* chain_done;   // chain: CTAs of this launch that finished; the last one clears both words
+    int32_t* chain_done;   // chain: CTAs of this launch that finished; the last one clears the chain's words
+    int32_t* work_quant;   // fused: next position to quantize (claimed by a CTA's four epilogue warps together)
+    int32_t* work_shrink;  // fused: next shrink unit (claimed by one warp)
+    int32_t* hp_ready;     // fused: shrink units finished
+    int shrink_units;      // fused: position blocks x units per block
     unsigned long long* trace;   // optional timeline buffer (null: off)
     long long trace_ctas;
 };

@@ -169,7 +169,7 @@ class VllmFusedFP8LoRA:
         if cfg:
             c.update(cfg)
         return _lib.ObTileCfg(c.get("tn", 0), c.get("split2", 0), c.get("split1", 0), c.get("stages", 0),
-                              c.get("wait_ms", self.wait_ms))
+                              c.get("wait_ms", self.wait_ms), c.get("fused", 0))
 
     # ------------------------------------------------------------------------------------------------- the call
     def _batch(self, x, meta_args, out):

@@ -157,7 +157,15 @@ def test_fused_projection_matches_oracle(K, widths, R, L, M, kind):
     y3 = op(x.cuda(), meta)
     torch.cuda.synchronize()
     assert torch.equal(y, y2) and torch.equal(y, y3)
-    counters = op.scratch.region("counters", 4 * 4096).view(torch.int32)
+    if M <= 32:
+        # the one-kernel form of the chain: same codes, same output bits, twice in a row (its work counters clear themselves)
+        op.scratch.xq(M, K).zero_()
+        y4 = op(x.cuda(), meta, cfg={"fused": 1})
+        y5 = op(x.cuda(), meta, cfg={"fused": 1})
+        torch.cuda.synchronize()
+        assert torch.equal(y, y4) and torch.equal(y, y5)
+        assert torch.equal(u8(op.scratch.xq(M, K)).cpu(), u8(q_ref)[rows])
+    counters = op.scratch.region("counters", 4 * (4096 + 16)).view(torch.int32)
     assert int(counters.abs().sum()) == 0
     _check_status(op)
 

@@ -129,6 +129,13 @@ def test_fused_projection_matches_oracle(K, widths, R, L, M, kind):
     y2 = op(x.cuda(), meta, pdl=False)
     torch.cuda.synchronize()
     assert torch.equal(y, y2)
+    if M <= 32:                                                # the one-kernel form of the chain, twice in a row
+        y4 = op(x.cuda(), meta, cfg={"fused": 1})
+        y5 = op(x.cuda(), meta, cfg={"fused": 1})
+        torch.cuda.synchronize()
+        assert torch.equal(y, y4) and torch.equal(y, y5)
+        xq2, xsf2 = op.codes(M)
+        assert torch.equal(xq2.cpu(), q_ref[rows]) and torch.equal(u8(xsf2).cpu(), u8(sf_ref)[rows])
     _status_ok(op)
 
 
