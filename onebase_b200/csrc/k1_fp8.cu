@@ -33,6 +33,11 @@ __global__ void __launch_bounds__(kK1Threads) k1_kernel(const K1Params p) {
         griddep_wait();                               // x comes from the preceding kernel; the scratch may still be read by it
         if (FP4_BASE) quantize_row_nvfp4<kK1Threads>(p, blockIdx.x, row, threadIdx.x);
         else quantize_row<kK1Threads, 0>(p, blockIdx.x, row, threadIdx.x);
+        if (p.xs != nullptr) {                        // the tensor-core shrink reads x in position order by TMA
+            const uint4* xr = reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.ldx);
+            uint4* xo = reinterpret_cast<uint4*>(p.xs + (size_t)blockIdx.x * (size_t)p.K);
+            for (int i = threadIdx.x; i < (p.K >> 3); i += kK1Threads) xo[i] = __ldg(xr + i);
+        }
         if (p.xq_ready != nullptr) {          // chain: tell K2 that this position's codes and scale are in memory
             __syncthreads();
             if (threadIdx.x == 0) red_release_add(p.xq_ready, 1);

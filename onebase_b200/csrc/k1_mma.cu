@@ -1,0 +1,269 @@
+// K1b: the LoRA shrink h = x A^T of a prefill batch on the tensor cores (bf16 adapters, more than 32 tokens).
+//
+// The CUDA-core shrink of k1_fp8.cu re-reads an adapter's A once per four tokens; with hundreds of tokens per tenant that
+// is hundreds of megabytes of L2 traffic.  Here a CTA owns (128 adapter-sorted positions, slice, K split) and multiplies
+// its 128 x K tile of x with the A of EVERY tenant that has a position in the tile, one fp32 accumulator of R columns in
+// tensor memory per tenant (tcgen05.mma kind::f16, M = 128 positions, N = R).  Rows of a tenant's accumulator that belong
+// to other tenants' positions are computed and thrown away -- a tile of a sorted batch holds two or three tenants, and the
+// shrink is a small share of the layer's flops.  Operands arrive by TMA through a shared-memory ring: the x tile comes
+// from the adapter-sorted bf16 copy of x that K1's quantizing CTAs leave in the workspace, the A tiles straight from the
+// stacked adapters.  Output: the split-K partials hp[split][slice][position][rank] (fp32) that K2 adds in split order,
+// the same array the CUDA-core shrink writes.  Computes what lowbit_lora/kernels/fp8_lora_vllm.py:72-120 computes.
+//
+// Warp roles: 0 = TMA producer, 1 = MMA issuer (and the owner of the tensor-memory allocation), 2..5 = epilogue (warp w
+// reads the 32 accumulator lanes w % 4 may touch).  Every wait is bounded; a wait that runs out records where in the
+// workspace's status words and the CTA leaves without storing.
+#include "ob_common.cuh"
+#include "ob_ptx.cuh"
+
+namespace ob {
+
+constexpr int kMmaThreads = 192;
+constexpr int kMmaTile = 128;          // positions per CTA (the MMA's M)
+constexpr int kMmaKStep = 64;          // bf16 elements per ring slot: one 128-byte swizzle atom
+constexpr int kMmaXBytes = kMmaTile * kMmaKStep * 2;       // 16 KB
+constexpr int kMmaMaxCols = 512;       // tensor-memory columns: R per tenant in flight
+constexpr int kMmaMaxStages = 8;
+constexpr int kMmaMaxList = 128;       // tenants with a position in one tile
+
+struct K1mCtrl {
+    uint64_t full[kMmaMaxStages];
+    uint64_t empty[kMmaMaxStages];
+    uint64_t acc_full;
+    uint64_t acc_empty;
+    uint32_t tmem_base;
+    volatile int abort_flag;
+    int n_list;
+    int lora[kMmaMaxList];             // the tile's tenants in segment order
+    short gidx[kMmaTile];              // list entry of each position (-1: no adapter)
+};
+
+__device__ __forceinline__ void k1m_timeout(const K1mParams& p, K1mCtrl* c, int where, int it) {
+    c->abort_flag = 1;
+    if (atomicCAS(p.status, OB_DEV_OK, OB_DEV_WAIT_TIMEOUT) == OB_DEV_OK) {
+        p.status[1] = 100 + where;
+        p.status[2] = blockIdx.x;
+        p.status[3] = blockIdx.y;
+        p.status[4] = blockIdx.z;
+        p.status[5] = it;
+    }
+}
+
+__global__ void __launch_bounds__(kMmaThreads, 1)
+k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, const __grid_constant__ CUtensorMap tm_a0,
+              const __grid_constant__ CUtensorMap tm_a1, const __grid_constant__ CUtensorMap tm_a2,
+              const __grid_constant__ CUtensorMap tm_a3) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* ring = smem;
+    K1mCtrl* ctrl = reinterpret_cast<K1mCtrl*>(smem + p.ring_bytes);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    griddep_launch_dependents();
+    const uint64_t limit_ns = (uint64_t)p.wait_ms * 1000000ull;
+    const int t0 = blockIdx.x * kMmaTile, s = blockIdx.y, j = blockIdx.z;
+    const int k0 = j * p.k_per_split, k1 = min(p.K, k0 + p.k_per_split);
+    const int n_ksteps = k1 > k0 ? (k1 - k0 + kMmaKStep - 1) / kMmaKStep : 0;
+    const int a_bytes = p.R * kMmaKStep * 2;                  // one tenant's A tile of a ring slot
+    const int group = kMmaMaxCols / p.R;                      // tenants whose accumulators fit tensor memory at once
+
+    if (tid == 0) {
+        for (int i = 0; i < kMmaMaxStages; ++i) {
+            mbar_init(&ctrl->full[i], 1);
+            mbar_init(&ctrl->empty[i], 1);
+        }
+        mbar_init(&ctrl->acc_full, 1);
+        mbar_init(&ctrl->acc_empty, 4);
+        ctrl->abort_flag = 0;
+        ctrl->n_list = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tm_xs);
+        tma_prefetch_desc(s == 0 ? &tm_a0 : s == 1 ? &tm_a1 : s == 2 ? &tm_a2 : &tm_a3);
+    }
+    for (int c = tid; c < kMmaTile; c += kMmaThreads) ctrl->gidx[c] = -1;
+    __syncthreads();
+    // ---- the tile's tenants, from the segment index (static during the preceding kernels)
+    if (warp == 2) {
+        int n_all, n_ad;
+        segment_totals(p.meta, p.L, lane, n_all, n_ad);
+        n_all = min(n_all, p.M);
+        int total = 0;
+        if (n_ad > 0) {
+            for (int base = 0; base <= p.L; base += 32) {
+                const int i = base + lane;
+                int lora = -1, lo = 0, hi = 0;
+                if (i <= p.L) {
+                    lora = p.meta.seg_ids[i];
+                    const int cnt = p.meta.seg_n[i], sst = p.meta.seg_start[i];
+                    lo = max(sst, t0);
+                    hi = min(min(sst + cnt, t0 + kMmaTile), n_all);
+                    if (cnt <= 0 || sst < 0) lora = -1;
+                }
+                const bool ok = lora >= 0 && lora < p.L && lo < hi;
+                const uint32_t mask = __ballot_sync(0xffffffffu, ok);
+                if (ok) {
+                    const int idx = total + __popc(mask & ((1u << lane) - 1u));
+                    if (idx < kMmaMaxList) {
+                        ctrl->lora[idx] = lora;
+                        for (int pos = lo; pos < hi; ++pos) ctrl->gidx[pos - t0] = (short)idx;
+                    }
+                }
+                total += __popc(mask);
+            }
+        }
+        if (lane == 0) ctrl->n_list = min(total, kMmaMaxList);
+    }
+    __syncthreads();
+    const int n_list = ctrl->n_list;
+    if (n_list == 0 || n_ksteps == 0) return;                 // no tenant in this tile (uniform: nothing was allocated)
+    const int n_pass = (n_list + group - 1) / group;
+    const int first_group = min(n_list, group);
+    uint32_t tmem_cols = 32;
+    while (tmem_cols < (uint32_t)(first_group * p.R)) tmem_cols *= 2;
+    const int stage_bytes = kMmaXBytes + first_group * a_bytes;           // slot size of the widest pass
+    int stages = p.ring_bytes / stage_bytes;
+    stages = stages > kMmaMaxStages ? kMmaMaxStages : stages;
+    if (warp == 1) {
+        tmem_alloc(&ctrl->tmem_base, tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = ctrl->tmem_base;
+
+    if (warp == 0) {
+        // =========================================================== TMA producer
+        if (lane == 0) {
+            const CUtensorMap* tma = s == 0 ? &tm_a0 : s == 1 ? &tm_a1 : s == 2 ? &tm_a2 : &tm_a3;
+            griddep_wait();                                   // the sorted copy of x comes from the preceding kernel
+            int it = 0;
+            for (int pass = 0; pass < n_pass && !ctrl->abort_flag; ++pass) {
+                const int g0 = pass * group, ng = min(group, n_list - g0);
+                for (int ks = 0; ks < n_ksteps; ++ks, ++it) {
+                    const int st = it % stages;
+                    if (it >= stages && !mbar_wait(&ctrl->empty[st], (uint32_t)((it / stages - 1) & 1), limit_ns)) {
+                        k1m_timeout(p, ctrl, 1, it);
+                        break;
+                    }
+                    uint8_t* slot = ring + (size_t)st * stage_bytes;
+                    mbar_arrive_expect_tx(&ctrl->full[st], (uint32_t)(kMmaXBytes + ng * a_bytes));
+                    tma_load_2d(slot, &tm_xs, &ctrl->full[st], k0 + ks * kMmaKStep, t0);
+                    for (int g = 0; g < ng; ++g)
+                        tma_load_2d(slot + kMmaXBytes + (size_t)g * a_bytes, tma, &ctrl->full[st], k0 + ks * kMmaKStep,
+                                    ctrl->lora[g0 + g] * p.R);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // =========================================================== MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(1, 1, kMmaTile, (uint32_t)p.R);
+            int it = 0;
+            bool ok = true;
+            for (int pass = 0; pass < n_pass && ok; ++pass) {
+                const int g0 = pass * group, ng = min(group, n_list - g0);
+                if (pass > 0) {                               // the epilogue has read the previous pass's accumulators
+                    if (!mbar_wait(&ctrl->acc_empty, (uint32_t)((pass - 1) & 1), limit_ns)) { k1m_timeout(p, ctrl, 2, pass); break; }
+                    tc_fence_after();
+                }
+                for (int ks = 0; ks < n_ksteps; ++ks, ++it) {
+                    const int st = it % stages;
+                    if (ctrl->abort_flag || !mbar_wait(&ctrl->full[st], (uint32_t)((it / stages) & 1), limit_ns)) {
+                        if (!ctrl->abort_flag) k1m_timeout(p, ctrl, 3, it);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t xa = smem_u32(ring + (size_t)st * stage_bytes);
+                    const uint64_t dx = umma_smem_desc(xa, 1024, 2);
+                    for (int g = 0; g < ng; ++g) {
+                        const uint64_t da = umma_smem_desc(xa + kMmaXBytes + (uint32_t)(g * a_bytes), 1024, 2);
+#pragma unroll
+                        for (int kk = 0; kk < kMmaKStep / 16; ++kk)
+                            umma_f16(tmem_base + (uint32_t)(g * p.R), dx + (uint64_t)(kk * 2), da + (uint64_t)(kk * 2), idesc,
+                                     (ks > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&ctrl->empty[st]);
+                }
+                if (ok) umma_commit(&ctrl->acc_full);
+            }
+        }
+    } else {
+        // =========================================================== epilogue: accumulator rows -> hp partials
+        const int q = warp & 3;                               // the 32 tensor-memory lanes this warp may read
+        const int row = q * 32 + lane, pos = t0 + row;
+        const int mine = ctrl->gidx[row];
+        float* dst = p.hp + (((size_t)j * p.S + s) * p.max_m + (size_t)pos) * p.R;
+        for (int pass = 0; pass < n_pass; ++pass) {
+            const int g0 = pass * group, ng = min(group, n_list - g0);
+            int go = 1;
+            if (lane == 0) {
+                go = ctrl->abort_flag ? 0 : 1;
+                if (go && !mbar_wait(&ctrl->acc_full, (uint32_t)(pass & 1), limit_ns)) {
+                    k1m_timeout(p, ctrl, 4, pass);
+                    go = 0;
+                }
+            }
+            go = __shfl_sync(0xffffffffu, go, 0);
+            if (!go) break;
+            tc_fence_after();
+            for (int g = 0; g < ng; ++g) {
+                const bool own = mine == g0 + g && pos < p.M;
+                if (!__any_sync(0xffffffffu, own)) continue;  // none of this warp's positions belongs to the tenant
+                for (int c0 = 0; c0 < p.R; c0 += 16) {
+                    uint32_t r[16];
+                    tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(g * p.R + c0), r);
+                    tmem_ld_wait();
+                    if (own) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v)
+                            reinterpret_cast<float4*>(dst + c0)[v] =
+                                make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                            __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctrl->acc_empty);
+        }
+    }
+    // ---- teardown: nobody leaves while tensor memory is in use or copies may still land in this CTA's shared memory
+    if (ctrl->abort_flag) __nanosleep(200000);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+size_t k1_mma_smem_bytes(int ring_bytes) { return 1024 + (size_t)ring_bytes + sizeof(K1mCtrl) + 64; }
+
+cudaError_t launch_k1_mma(const K1mParams& p, const CUtensorMap& tm_xs, const CUtensorMap* tm_a, dim3 grid, cudaStream_t stream) {
+    static int configured_for[64] = {0};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    const size_t smem = k1_mma_smem_bytes(p.ring_bytes);
+    if (dev >= 0 && dev < 64 && !configured_for[dev]) {
+        e = cudaFuncSetAttribute(k1_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+        if (e != cudaSuccess) return e;
+        configured_for[dev] = 1;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kMmaThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // always a programmatic dependent of K1
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, k1_mma_kernel, p, tm_xs, tm_a[0], tm_a[1], tm_a[2], tm_a[3]);
+}
+
+}  // namespace ob

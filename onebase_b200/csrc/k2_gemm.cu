@@ -257,8 +257,12 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
     griddep_launch_dependents();                               // the next kernel in the stream may start its own prologue
     const uint64_t limit_ns = (uint64_t)p.wait_ms * 1000000ull;
 
-    // ---- tile coordinates: blockIdx.x walks the slices' 128-wide tiles, .y the K splits, .z the token tiles
-    int s = 0, n_tile = blockIdx.x, slice_off = 0;
+    // ---- tile coordinates: blockIdx.x walks the slices' 128-wide tiles, .y the K splits, .z the token tiles.  With more
+    // than one token tile the two swap: consecutive CTAs then share a W tile, which comes from HBM once and from L2 after.
+    const int n_idx = p.m_fast ? (int)blockIdx.z : (int)blockIdx.x;
+    const int m_idx = p.m_fast ? (int)blockIdx.x : (int)blockIdx.z;
+    const int n_count = p.m_fast ? (int)gridDim.z : (int)gridDim.x;
+    int s = 0, n_tile = n_idx, slice_off = 0;
     while (s < p.S - 1 && n_tile >= (p.widths[s] + kTileN - 1) / kTileN) {
         n_tile -= (p.widths[s] + kTileN - 1) / kTileN;
         slice_off += p.widths[s];
@@ -267,12 +271,12 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
     const int n_s = p.widths[s];
     const int n0_local = n_tile * kTileN;
     const int j = blockIdx.y;
-    const int t0 = blockIdx.z * tn;
+    const int t0 = m_idx * tn;
     const int kb0 = (int)(((int64_t)p.kblocks * j) / p.split2);
     const int kb1 = (int)(((int64_t)p.kblocks * (j + 1)) / p.split2);
     const int n_base = kb1 - kb0;
     const int n_chunks = p.R / p.rc;
-    const int tile_lin = blockIdx.z * gridDim.x + blockIdx.x;
+    const int tile_lin = m_idx * n_count + n_idx;
     const int lead = FUSED ? max(p.stages, n_base) : p.stages;   // fused: every W tile first -- the shrink runs beside them
     const long long trace_cta = blockIdx.x + (long long)gridDim.x * (blockIdx.y + (long long)gridDim.y * blockIdx.z);
     if (tid == 0) { OB_TRACE(0) }
@@ -320,7 +324,8 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
     if (warp == 0) {
         // =========================================================== TMA producer: W tiles + their x_q tiles, B tiles
         if (lane == 0) {
-            const uint64_t pol = l2_policy_evict_first();
+            // one token tile: W streams through once, so it should not displace the adapters; several token tiles re-read it
+            const uint64_t pol = p.m_fast ? l2_policy_evict_last() : l2_policy_evict_first();
             const CUtensorMap* tmb = (s == 0) ? &tm_b0 : (s == 1) ? &tm_b1 : (s == 2) ? &tm_b2 : &tm_b3;
             const uint32_t b_bytes = (uint32_t)kTileN * p.rc * 2;
             const uint32_t wx_bytes = (uint32_t)kWTileBytes + (uint32_t)tn * kBlockK + (uint32_t)sf_bytes;
@@ -364,7 +369,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                             tma_load_2d(slot + kWTileBytes, &tm_x, &ctrl->full_w[st], (kb0 + r.k) * kBlockK, t0);
                             if (FP4)
                                 bulk_load(slot + kWTileBytes + tn * kBlockK + kSfSlotBytes,
-                                          p.xsf + ((size_t)blockIdx.z * p.kblocks + (kb0 + r.k)) * p.nblk * kSfSlotBytes,
+                                          p.xsf + ((size_t)m_idx * p.kblocks + (kb0 + r.k)) * p.nblk * kSfSlotBytes,
                                           (uint32_t)(kSfSlotBytes * p.nblk), &ctrl->full_w[st]);
                         }
                         r.advance(rb, n_base, n_steps);
@@ -392,13 +397,13 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                                      slice_off + n0_local, pol);
                     uint8_t* slot = ring + (size_t)st * stage_bytes;
                     if (FP4)
-                        bulk_load(slot + kWTileBytes + tn * kBlockK, p.wsf + ((size_t)blockIdx.x * p.kblocks + (kb0 + w.k)) * kSfSlotBytes,
+                        bulk_load(slot + kWTileBytes + tn * kBlockK, p.wsf + ((size_t)n_idx * p.kblocks + (kb0 + w.k)) * kSfSlotBytes,
                                   kSfSlotBytes, &ctrl->full_w[st]);
                     if (k1_done) {
                         tma_load_2d(slot + kWTileBytes, &tm_x, &ctrl->full_w[st], (kb0 + w.k) * kBlockK, t0);
                         if (FP4)
                             bulk_load(slot + kWTileBytes + tn * kBlockK + kSfSlotBytes,
-                                      p.xsf + ((size_t)blockIdx.z * p.kblocks + (kb0 + w.k)) * p.nblk * kSfSlotBytes,
+                                      p.xsf + ((size_t)m_idx * p.kblocks + (kb0 + w.k)) * p.nblk * kSfSlotBytes,
                                       (uint32_t)(kSfSlotBytes * p.nblk), &ctrl->full_w[st]);
                     }
                 }

@@ -14,6 +14,7 @@ cudaError_t launch_k2_nvfp4(const K2Params& p, const CUtensorMap& tm_w, const CU
                             dim3 grid, size_t smem, int pdl, cudaStream_t stream);
 int k2_fp8_h_tiles(int tn);
 int k2_max_active_clusters(int fp4, int stored, int split2, size_t smem);
+cudaError_t launch_k1_mma(const K1mParams& p, const CUtensorMap& tm_xs, const CUtensorMap* tm_a, dim3 grid, cudaStream_t stream);
 cudaError_t launch_fused(const K2Params& p, const K1Params& k1, const CUtensorMap& tm_w, const CUtensorMap& tm_x,
                          const CUtensorMap* tm_b, dim3 grid, size_t smem, cudaStream_t stream);
 cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream);
@@ -91,6 +92,7 @@ struct ObLayer {
     int n_tiles;                  // 128-wide output tiles over all slices
     CUtensorMap tm_w;
     CUtensorMap tm_b[OB_MAX_SLICES];
+    CUtensorMap tm_a[OB_MAX_SLICES];   // bf16 adapters: A of each slice as [L * R, K], for the tensor-core shrink
     std::mutex mu;
     std::vector<XMap> xmaps;      // x_q maps by (workspace region, rows, token tile)
 };
@@ -146,13 +148,16 @@ int validate_workspace(const ObLayer* l, const void* ws, const ObWorkspaceShape*
 int k_bytes(const ObLayerDesc& d) { return d.base_fmt == OB_BASE_NVFP4 ? d.K / 2 : d.K; }
 
 struct Resolved {
-    int tn, split1, split2, stages, m_tiles, k_per_split, pb, fused;
+    int tn, split1, split2, stages, m_tiles, k_per_split, pb, fused, mma_shrink;
     uint32_t wait_ms;
 };
 
+// Token tile by default: the smallest of 16..128 that covers the batch.  Prefill batches stay at 128-token tiles: two
+// such CTAs share an SM (256 TMEM columns and a two-slot ring each), so one's epilogue runs under the other's main loop,
+// which measured faster than one 256-token CTA per SM.
 int default_tn(int M) {
     int tn = 16;
-    while (tn < M && tn < 256) tn *= 2;
+    while (tn < M && tn < 128) tn *= 2;
     return tn;
 }
 
@@ -172,10 +177,18 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
             while (split2 < 8 && l->n_tiles * (split2 + 1) <= 296 && kblocks / (split2 + 1) >= 4) ++split2;
     }
     if (split2 < 1 || split2 > 16 || split2 > kblocks || (split2 > 1 && r->m_tiles > 1)) return OB_ERR_TILE;
-    if ((long long)l->n_tiles * r->m_tiles > kCounterSlots) return OB_ERR_TOO_LARGE;
+    if (split2 > 1 && (long long)l->n_tiles * r->m_tiles > kCounterSlots) return OB_ERR_TOO_LARGE;   // one arrival counter per split tile
     r->split2 = split2;
     int split1 = (cfg && cfg->split1) ? cfg->split1 : 0;
-    const int pb = M <= 32 ? 1 : 4;
+    const int pb = M <= kDecodeTokens ? 1 : 4;
+    // Prefill batches of bf16 adapters shrink on the tensor cores (LOWBIT_SHRINK_CUDA_CORES=1 keeps the warp-level form).
+    static const bool no_mma = [] { const char* v = std::getenv("LOWBIT_SHRINK_CUDA_CORES"); return v && v[0] == '1'; }();
+    r->mma_shrink = (!no_mma && M > kDecodeTokens && d.lora_fmt == kLoraBf16) ? 1 : 0;
+    if (split1 == 0 && r->mma_shrink) {   // one wave of (128-position tile, slice, K split) CTAs, at least 256 elements each
+        const int tiles = ((M + 127) / 128) * d.S;
+        split1 = 1;
+        while (split1 < 16 && tiles * (split1 * 2) <= 148 && d.K / (split1 * 2) >= 256) split1 *= 2;
+    }
     if (split1 == 0) {   // as many K splits as keep the whole shrink in one wave of the GPU's 2 x 148 CTA slots (8 warps each)
         const long long units = (long long)((M + pb - 1) / pb) * d.S * (d.R / 8);
         split1 = 1;
@@ -187,9 +200,10 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     r->pb = pb;
     const int rc = l->rc;
     int stages = (cfg && cfg->stages) ? cfg->stages : 0;
-    if (stages == 0) {   // prefer a footprint that lets two CTAs share an SM (3+ stages), else the deepest ring that fits
+    if (stages == 0) {   // prefer a footprint that lets two CTAs share an SM (3+ stages; 2+ for 128-token tiles), else the deepest ring that fits
         stages = 12;
-        while (stages > 3 && k2_fp8_smem_bytes(r->tn, stages, rc, d.R, d.base_fmt == OB_BASE_NVFP4) > kSmemTwoPerSm) --stages;
+        const int floor_stages = r->tn >= 128 ? 2 : 3;
+        while (stages > floor_stages && k2_fp8_smem_bytes(r->tn, stages, rc, d.R, d.base_fmt == OB_BASE_NVFP4) > kSmemTwoPerSm) --stages;
         if (k2_fp8_smem_bytes(r->tn, stages, rc, d.R, d.base_fmt == OB_BASE_NVFP4) > kSmemTwoPerSm) stages = 12;
     }
     if (stages < 2 || stages > 12) return OB_ERR_TILE;
@@ -217,8 +231,10 @@ int get_xmap(ObLayer* l, const void* xq, int rows, int tn, CUtensorMap* out) {
     m.base = xq;
     m.rows = rows;
     m.tn = tn;
-    int st = encode_2d(&m.tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, (uint64_t)k_bytes(l->d), (uint64_t)rows, (uint64_t)k_bytes(l->d),
-                       kBlockK, (uint32_t)tn);
+    int st = tn < 0   // the adapter-sorted bf16 copy of x: 64-element x 128-row boxes for the tensor-core shrink
+                 ? encode_2d(&m.tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xq, (uint64_t)l->d.K, (uint64_t)rows, (uint64_t)l->d.K * 2, 64, 128)
+                 : encode_2d(&m.tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, (uint64_t)k_bytes(l->d), (uint64_t)rows,
+                             (uint64_t)k_bytes(l->d), kBlockK, (uint32_t)tn);
     if (st != OB_OK) return st;
     l->xmaps.push_back(m);
     *out = m.tm;
@@ -255,6 +271,7 @@ K1Params k1_params(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShap
     p.x_global = d.x_global;
     p.xsf = base + lay.xsf;
     p.xq_ready = chain ? reinterpret_cast<int32_t*>(base + lay.counters) + kCounterSlots : nullptr;
+    p.xs = r.mma_shrink ? reinterpret_cast<__nv_bfloat16*>(base + lay.xs) : nullptr;
     p.trace = g_trace ? g_trace + g_trace_ctas * OB_TRACE_EVENTS : nullptr;   // K1's stamps follow K2's
     p.trace_ctas = g_trace_ctas;
     return p;
@@ -263,10 +280,30 @@ K1Params k1_params(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShap
 int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, int pdl,
                 cudaStream_t stream, bool chain = false) {
     const K1Params p = k1_params(l, b, ws, sh, r, chain);
-    const long long warps = (long long)p.n_pblocks * p.units_per_block;
+    const long long warps = r.mma_shrink ? 0 : (long long)p.n_pblocks * p.units_per_block;
     const long long grid = p.n_quant_ctas + (warps + 7) / 8;
     if (grid > 0x7fffffffLL) return OB_ERR_TOO_LARGE;
     cudaError_t e = launch_k1_fp8(p, (int)grid, pdl, stream);
+    if (e != cudaSuccess) return (int)e;
+    if (!r.mma_shrink) return OB_OK;
+    // the shrink itself: one CTA per (128 positions, slice, K split), a programmatic dependent of the launch above
+    const ObLayerDesc& d = l->d;
+    const WorkspaceLayout lay = workspace_layout(*sh);
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    CUtensorMap tm_xs;
+    int st = get_xmap(l, base + lay.xs, sh->max_m, -1, &tm_xs);
+    if (st != OB_OK) return st;
+    K1mParams m = {};
+    m.M = b->M; m.K = d.K; m.S = d.S; m.R = d.R; m.L = d.L; m.max_m = sh->max_m;
+    m.split1 = r.split1;
+    m.k_per_split = r.k_per_split;
+    m.ring_bytes = 192 * 1024;
+    m.wait_ms = r.wait_ms;
+    m.meta = meta_of(b);
+    m.hp = reinterpret_cast<float*>(base + lay.hp);
+    m.status = reinterpret_cast<int32_t*>(base + lay.status);
+    dim3 mgrid((unsigned)((b->M + 127) / 128), (unsigned)d.S, (unsigned)r.split1);
+    e = launch_k1_mma(m, tm_xs, l->tm_a, mgrid, stream);
     return e == cudaSuccess ? OB_OK : (int)e;
 }
 
@@ -349,7 +386,10 @@ int k2_prepare(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* s
         const size_t need = (size_t)r.split2 * (size_t)l->n_tiles * (size_t)r.tn * kTileN * sizeof(float);
         if (lay.part + need > lay.total) return OB_ERR_WORKSPACE;
     }
-    out->grid = dim3((unsigned)l->n_tiles, (unsigned)r.split2, (unsigned)r.m_tiles);
+    p.m_fast = r.m_tiles > 1 ? 1 : 0;
+    if (p.m_fast && l->n_tiles > 65535) return OB_ERR_TOO_LARGE;
+    out->grid = p.m_fast ? dim3((unsigned)r.m_tiles, 1u, (unsigned)l->n_tiles)
+                         : dim3((unsigned)l->n_tiles, (unsigned)r.split2, (unsigned)r.m_tiles);
     out->fp4 = d.base_fmt == OB_BASE_NVFP4;
     out->smem = k2_fp8_smem_bytes(r.tn, r.stages, l->rc, d.R, out->fp4 ? 1 : 0);
     p.cluster_reduce = cluster_reduce_fits(l, r, out->smem) ? 1 : 0;
@@ -550,6 +590,9 @@ int ob_layer_create(const ObLayerDesc* desc, ObLayer** out) {
                 const int ss = s < desc->S ? s : 0;   // unused slots repeat slice 0 so every kernel argument is a valid map
                 st = encode_2d(&l->tm_b[s], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, desc->b[ss], (uint64_t)desc->R,
                                (uint64_t)desc->L * (uint64_t)desc->widths[ss], (uint64_t)desc->R * 2, (uint32_t)l->rc, kTileN);
+                if (st == OB_OK)
+                    st = encode_2d(&l->tm_a[s], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, desc->a[ss], (uint64_t)desc->K,
+                                   (uint64_t)desc->L * (uint64_t)desc->R, (uint64_t)desc->K * 2, 64, (uint32_t)desc->R);
             }
         }
     }

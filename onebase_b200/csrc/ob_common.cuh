@@ -13,6 +13,7 @@ namespace ob {
 constexpr int kTileN = 128;          // output features per GEMM tile (rows of W; the MMA's M)
 constexpr int kBlockK = 128;         // bytes of K per ring stage row (one 128-byte swizzle row)
 constexpr int kMaxLoraIters = 512;   // capacity of a CTA's list of (segment, rank chunk) expand steps
+constexpr int kDecodeTokens = 32;     // batches up to this size take the decode forms (one position per shrink warp)
 constexpr int kCounterSlots = 4096;  // split-K arrival counters in the workspace
 constexpr int kSfSlotBytes = 2048;   // NVFP4: scale factors of 128 rows x one 256-element K slot (4 atoms of 512 bytes)
 
@@ -27,6 +28,7 @@ struct WorkspaceLayout {
     size_t xsf;        // bytes NVFP4 activation block scales: [token tile][256-element K slot][128-token block][2048]
     size_t hp;         // fp32  [max_split1 * max_sr * max_m]  shrink partials [split][slice][position][rank]
     size_t part;       // fp32  [max_split2 * token tile * (max_n rounded to tiles)]  GEMM split-K partials
+    size_t xs;         // bf16  [max_m * max_k]   adapter-sorted copy of x for the tensor-core shrink (max_m > 32 only)
     size_t total;
 };
 
@@ -43,6 +45,7 @@ __host__ __device__ inline WorkspaceLayout workspace_layout(const ObWorkspaceSha
     size_t m_pad = 16;                                        // split-K serves one token tile: min(max_m, 256) tokens
     while (m_pad < (size_t)s.max_m && m_pad < 256) m_pad *= 2;
     l.part = off;     off = align_up(off + sizeof(float) * (s.max_split2 > 1 ? (size_t)s.max_split2 * m_pad * n_pad : 0), 1024);
+    l.xs = off;       off = align_up(off + (s.max_m > kDecodeTokens ? (size_t)s.max_m * (size_t)s.max_k * 2 : 0), 1024);
     l.total = off;
     return l;
 }
@@ -82,9 +85,22 @@ struct K1Params {
     int rcp_approx;        // NVFP4: 1 = rcp.approx.ftz reciprocals (vLLM's CUDA quantizer), 0 = IEEE (the torch recipe)
     const float* x_global; // NVFP4: [1] static activation global scale
     uint8_t* xsf;          // NVFP4: activation block scales, packed per (token tile, K slot) in scale-factor atoms
+    __nv_bfloat16* xs;     // prefill with a tensor-core shrink: the quantizing CTAs also copy their row here (null: no copy)
     int32_t* xq_ready;     // chain: counts the positions whose codes and scale are written (null: no signal)
     unsigned long long* trace;   // optional timeline buffer (null: off); K1 stamps go after K2's region
     long long trace_ctas;
+};
+
+// The tensor-core shrink of a prefill batch (k1_mma.cu).
+struct K1mParams {
+    int M, K, S, R, L, max_m;
+    int split1;            // K splits (grid z); K2 adds the partials in split order
+    int k_per_split;       // elements of K per split, a multiple of 64
+    int ring_bytes;        // shared memory of the operand ring
+    uint32_t wait_ms;
+    Meta meta;
+    float* hp;             // [split1][S][max_m][R]
+    int32_t* status;
 };
 
 struct K2Params {
@@ -93,6 +109,7 @@ struct K2Params {
     int lora_fmt;
     int tn;                // tokens per tile (MMA N)
     int split2;            // GEMM split-K
+    int m_fast;            // several token tiles: grid x walks the token tiles and grid z the output tiles
     int cluster_reduce;    // split2 > 1: the splits of a tile form one thread-block cluster and add their partials through shared memory
     int split1;            // shrink partials to sum
     int kblocks;           // ceil(K / 128)
