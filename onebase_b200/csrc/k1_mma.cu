@@ -34,6 +34,7 @@ struct K1mCtrl {
     uint32_t tmem_base;
     volatile int abort_flag;
     int n_list;
+    int last_flag;
     int lora[kMmaMaxList];             // the tile's tenants in segment order
     short gidx[kMmaTile];              // list entry of each position (-1: no adapter)
 };
@@ -196,6 +197,8 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
         const int row = q * 32 + lane, pos = t0 + row;
         const int mine = ctrl->gidx[row];
         float* dst = p.hp + (((size_t)j * p.S + s) * p.max_m + (size_t)pos) * p.R;
+        __nv_bfloat16* hdst = p.hb + ((size_t)s * p.max_m + (size_t)pos) * p.R;
+        const bool direct = p.split1 == 1;                     // no partials: the accumulator row is the finished h
         for (int pass = 0; pass < n_pass; ++pass) {
             const int g0 = pass * group, ng = min(group, n_list - g0);
             int go = 1;
@@ -216,7 +219,16 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
                     uint32_t r[16];
                     tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(g * p.R + c0), r);
                     tmem_ld_wait();
-                    if (own) {
+                    if (own && direct) {
+                        uint32_t o[8];
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[2 * v]), __uint_as_float(r[2 * v + 1]));
+                            o[v] = *reinterpret_cast<uint32_t*>(&b);
+                        }
+                        reinterpret_cast<uint4*>(hdst + c0)[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                        reinterpret_cast<uint4*>(hdst + c0)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                    } else if (own) {
 #pragma unroll
                         for (int v = 0; v < 4; ++v)
                             reinterpret_cast<float4*>(dst + c0)[v] =
@@ -228,6 +240,50 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctrl->acc_empty);
+        }
+        if (!direct) {
+            // The K splits of a (tile, slice) count their arrivals; the last one adds the partials in split order and writes
+            // the finished h once, so that K2's CTAs -- one per output tile -- need not each add them again.
+            const int te = tid - 64;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (te == 0) {
+                int old;
+                asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + blockIdx.x * p.S + s) : "memory");
+                ctrl->last_flag = (old == p.split1 - 1) ? 1 : 0;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (ctrl->last_flag && !ctrl->abort_flag) {
+                if (mine >= 0 && pos < p.M) {
+                    const size_t jstride = (size_t)p.S * p.max_m * p.R;
+                    const float* src = p.hp + ((size_t)s * p.max_m + (size_t)pos) * p.R;
+                    for (int c0 = 0; c0 < p.R; c0 += 8) {
+                        float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+                        for (int j1 = 0; j1 < p.split1; j1 += 4) {
+                            float4 v[4][2];
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                if (j1 + u < p.split1) {
+                                    const float4* q4 = reinterpret_cast<const float4*>(src + (size_t)(j1 + u) * jstride + c0);
+                                    v[u][0] = __ldcg(q4);
+                                    v[u][1] = __ldcg(q4 + 1);
+                                } else {
+                                    v[u][0] = v[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                                }
+                            }
+#pragma unroll
+                            for (int u = 0; u < 4; ++u) {
+                                a0.x += v[u][0].x; a0.y += v[u][0].y; a0.z += v[u][0].z; a0.w += v[u][0].w;
+                                a1.x += v[u][1].x; a1.y += v[u][1].y; a1.z += v[u][1].z; a1.w += v[u][1].w;
+                            }
+                        }
+                        __nv_bfloat162 b0 = __floats2bfloat162_rn(a0.x, a0.y), b1 = __floats2bfloat162_rn(a0.z, a0.w);
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(a1.x, a1.y), b3 = __floats2bfloat162_rn(a1.z, a1.w);
+                        *reinterpret_cast<uint4*>(hdst + c0) = make_uint4(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1),
+                                                                          *reinterpret_cast<uint32_t*>(&b2), *reinterpret_cast<uint32_t*>(&b3));
+                    }
+                }
+                if (te == 0) p.counters[blockIdx.x * p.S + s] = 0;
+            }
         }
     }
     // ---- teardown: nobody leaves while tensor memory is in use or copies may still land in this CTA's shared memory

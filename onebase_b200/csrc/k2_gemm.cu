@@ -674,17 +674,26 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
         if (stored || !small) {
             SlotWalk w(lead);
             RingBook book;
+            bool in_step = true;                              // te == 0: no wait on the way has run out
             for (int li = 0; li < n_steps; ++li) {
                 uint32_t parity = 0;
-                while (!w.is_b(n_base, n_steps)) {            // W slots in between: bookkeeping only
-                    book.acquire(w.it, w.it % p.stages, p.stages, false, parity);
+                while (!w.is_b(n_base, n_steps)) {
+                    // W slots in between.  When these warps fill the B slots themselves, one thread follows EVERY slot's
+                    // release like the producer does: a waiter that skipped phases of a slot's barrier could take a
+                    // phase two ahead of the barrier for complete and overwrite a tile that is still in use.
+                    const int kw = book.acquire(w.it, w.it % p.stages, p.stages, false, parity);
+                    if (stored && te == 0 && kw != 0 && in_step && !ctrl->abort_flag &&
+                        !mbar_wait(kw == 2 ? &ctrl->empty_b[w.it % p.stages] : &ctrl->empty[w.it % p.stages], parity, limit_ns)) {
+                        record_timeout(p, ctrl, 14, w.it);
+                        in_step = false;
+                    }
                     w.advance(false, n_base, n_steps);
                 }
                 const int st = w.it % p.stages;
                 const int kind = book.acquire(w.it, st, p.stages, true, parity);
                 const int hb = li % nh, hu = li / nh;
                 if (te == 0) {                                    // one thread decides, so that all 128 leave together
-                    int go = ctrl->abort_flag ? 0 : 1;
+                    int go = (ctrl->abort_flag || !in_step) ? 0 : 1;
                     if (go && stored && kind != 0 &&
                         !mbar_wait(kind == 2 ? &ctrl->empty_b[st] : &ctrl->empty[st], parity, limit_ns)) {
                         record_timeout(p, ctrl, 14, w.it);
@@ -705,7 +714,11 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                 for (int ch = te; ch < tn * cpr; ch += 128) {
                     const int row = ch / cpr, c16 = ch % cpr;
                     uint4 out = make_uint4(0u, 0u, 0u, 0u);
-                    if (row >= (int)e.lo && row < (int)e.hi) {
+                    if (p.hb != nullptr) {                 // the tensor-core shrink left the finished h
+                        if (row >= (int)e.lo && row < (int)e.hi)
+                            out = __ldcg(reinterpret_cast<const uint4*>(
+                                p.hb + ((size_t)s * p.max_m + (size_t)(t0 + row)) * p.R + (size_t)e.chunk * p.rc + (size_t)c16 * 8));
+                    } else if (row >= (int)e.lo && row < (int)e.hi) {
                         float acc[8];
 #pragma unroll
                         for (int u = 0; u < 8; ++u) acc[u] = 0.0f;

@@ -166,7 +166,8 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     const bool fp4 = d.base_fmt == OB_BASE_NVFP4;
     const int kblocks = (k_bytes(d) + kBlockK - 1) / kBlockK;
     r->tn = (cfg && cfg->tn) ? cfg->tn : default_tn(M);
-    if (fp4 && r->tn > 128 && !(cfg && cfg->tn)) r->tn = 128;   // NVFP4: scale factors share TMEM with the accumulators
+    // NVFP4: the scale factors share tensor memory with the accumulators; 64-token tiles leave room for two CTAs per SM
+    if (fp4 && r->tn > 64 && !(cfg && cfg->tn)) r->tn = 64;
     if (fp4 && r->tn > 128) return OB_ERR_TILE;
     if (!(r->tn == 16 || r->tn == 32 || r->tn == 64 || r->tn == 128 || r->tn == 256)) return OB_ERR_TILE;
     r->m_tiles = (M + r->tn - 1) / r->tn;
@@ -197,6 +198,8 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     if (split1 < 1 || split1 > 32) return OB_ERR_TILE;
     r->split1 = split1;
     r->k_per_split = (int)align_up((size_t)(d.K + split1 - 1) / split1, 256);
+    if (r->mma_shrink)   // every split must hold part of K: the splits of a tile count their arrivals
+        while (r->split1 > 1 && (long long)(r->split1 - 1) * r->k_per_split >= d.K) --r->split1;
     r->pb = pb;
     const int rc = l->rc;
     int stages = (cfg && cfg->stages) ? cfg->stages : 0;
@@ -301,7 +304,10 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     m.wait_ms = r.wait_ms;
     m.meta = meta_of(b);
     m.hp = reinterpret_cast<float*>(base + lay.hp);
+    m.hb = reinterpret_cast<__nv_bfloat16*>(base + lay.hb);
+    m.counters = reinterpret_cast<int32_t*>(base + lay.counters);
     m.status = reinterpret_cast<int32_t*>(base + lay.status);
+    if ((long long)((b->M + 127) / 128) * d.S > kCounterSlots) return OB_ERR_TOO_LARGE;
     dim3 mgrid((unsigned)((b->M + 127) / 128), (unsigned)d.S, (unsigned)r.split1);
     e = launch_k1_mma(m, tm_xs, l->tm_a, mgrid, stream);
     return e == cudaSuccess ? OB_OK : (int)e;
@@ -370,6 +376,7 @@ int k2_prepare(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* s
     p.s_w = d.s_w;
     p.sx = reinterpret_cast<const float*>(base + lay.sx);
     p.hp = reinterpret_cast<const float*>(base + lay.hp);
+    p.hb = r.mma_shrink ? reinterpret_cast<const __nv_bfloat16*>(base + lay.hb) : nullptr;
     p.meta = meta_of(b);
     p.y = static_cast<__nv_bfloat16*>(b->y);
     p.ldy = b->ldy;

@@ -29,6 +29,7 @@ struct WorkspaceLayout {
     size_t hp;         // fp32  [max_split1 * max_sr * max_m]  shrink partials [split][slice][position][rank]
     size_t part;       // fp32  [max_split2 * token tile * (max_n rounded to tiles)]  GEMM split-K partials
     size_t xs;         // bf16  [max_m * max_k]   adapter-sorted copy of x for the tensor-core shrink (max_m > 32 only)
+    size_t hb;         // bf16  [max_sr * max_m]  the tensor-core shrink's finished h [slice][position][rank] (max_m > 32 only)
     size_t total;
 };
 
@@ -46,6 +47,7 @@ __host__ __device__ inline WorkspaceLayout workspace_layout(const ObWorkspaceSha
     while (m_pad < (size_t)s.max_m && m_pad < 256) m_pad *= 2;
     l.part = off;     off = align_up(off + sizeof(float) * (s.max_split2 > 1 ? (size_t)s.max_split2 * m_pad * n_pad : 0), 1024);
     l.xs = off;       off = align_up(off + (s.max_m > kDecodeTokens ? (size_t)s.max_m * (size_t)s.max_k * 2 : 0), 1024);
+    l.hb = off;       off = align_up(off + (s.max_m > kDecodeTokens ? (size_t)s.max_sr * (size_t)s.max_m * 2 : 0), 1024);
     l.total = off;
     return l;
 }
@@ -99,7 +101,9 @@ struct K1mParams {
     int ring_bytes;        // shared memory of the operand ring
     uint32_t wait_ms;
     Meta meta;
-    float* hp;             // [split1][S][max_m][R]
+    float* hp;             // [split1][S][max_m][R] partials (split1 > 1)
+    __nv_bfloat16* hb;     // [S][max_m][R] the finished h: bf16 of the partials' sum in split order
+    int32_t* counters;     // one arrival counter per (position tile, slice); zero between launches
     int32_t* status;
 };
 
@@ -121,6 +125,7 @@ struct K2Params {
     const float* s_w;
     const float* sx;
     const float* hp;
+    const __nv_bfloat16* hb;   // prefill after the tensor-core shrink: finished h [S][max_m][R] (null: sum hp's partials)
     Meta meta;
     __nv_bfloat16* y;
     int64_t ldy;

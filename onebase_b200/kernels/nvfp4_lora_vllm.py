@@ -100,7 +100,7 @@ class VllmFusedNVFP4LoRA(VllmFusedFP8LoRA):
         K = self.K
         xq = self.scratch.region("xq", M * (K // 2)).view(M, K // 2)
         t = self.tile(M)
-        tn = tn or t.tn or min(128, max(16, 1 << (M - 1).bit_length()))
+        tn = tn or t.tn or min(64, max(16, 1 << (M - 1).bit_length()))   # the library's default token tile for an NVFP4 base
         nblk = 2 if tn > 128 else 1
         kslots = (K + 255) // 256
         m_tiles = (M + tn - 1) // tn
