@@ -109,6 +109,8 @@ typedef struct ObWorkspaceShape {
     int32_t max_sr;                  /* largest S*R */
     int32_t max_split1;              /* largest split-K of the shrink */
     int32_t max_split2;              /* largest split-K of the GEMM */
+    int32_t max_l;                   /* most adapter slots L of any layer sharing the workspace; 0 = no room for the
+                                      * per-tenant h blocks of the large-tile prefill GEMM, which is then not used */
 } ObWorkspaceShape;
 
 /* Per-call tile choice (what the reference's pick_cfg / plugin_cfg return,

@@ -43,7 +43,7 @@ class ObBatch(C.Structure):
 
 class ObWorkspaceShape(C.Structure):
     _fields_ = [("max_m", C.c_int32), ("max_k", C.c_int32), ("max_n", C.c_int32), ("max_sr", C.c_int32),
-                ("max_split1", C.c_int32), ("max_split2", C.c_int32)]
+                ("max_split1", C.c_int32), ("max_split2", C.c_int32), ("max_l", C.c_int32)]
 
 
 class ObTileCfg(C.Structure):

@@ -199,6 +199,9 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
         float* dst = p.hp + (((size_t)j * p.S + s) * p.max_m + (size_t)pos) * p.R;
         __nv_bfloat16* hdst = p.hb + ((size_t)s * p.max_m + (size_t)pos) * p.R;
         const bool direct = p.split1 == 1;                     // no partials: the accumulator row is the finished h
+        const bool cat = p.hcat != nullptr;                    // per-tenant blocks, pre-divided by the output scale
+        __nv_bfloat16* cdst = cat ? p.hcat + ((size_t)s * p.max_m + (size_t)pos) * ((size_t)p.lc * p.R) : nullptr;
+        const float inv = (cat && pos < p.M) ? 1.0f / (__ldcg(p.sx + pos) * __ldg(p.s_w)) : 0.0f;
         for (int pass = 0; pass < n_pass; ++pass) {
             const int g0 = pass * group, ng = min(group, n_list - g0);
             int go = 1;
@@ -214,12 +217,32 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
             tc_fence_after();
             for (int g = 0; g < ng; ++g) {
                 const bool own = mine == g0 + g && pos < p.M;
+                if (cat && direct) {                          // every row of the block: the tenant's rows scaled, zeros elsewhere
+                    for (int c0 = 0; c0 < p.R; c0 += 16) {
+                        uint32_t r[16];
+                        tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(g * p.R + c0), r);
+                        tmem_ld_wait();
+                        uint32_t o[8];
+#pragma unroll
+                        for (int v = 0; v < 8; ++v) {
+                            __nv_bfloat162 b = __floats2bfloat162_rn(own ? __uint_as_float(r[2 * v]) * inv : 0.0f,
+                                                                     own ? __uint_as_float(r[2 * v + 1]) * inv : 0.0f);
+                            o[v] = *reinterpret_cast<uint32_t*>(&b);
+                        }
+                        if (pos < p.max_m) {
+                            uint4* d4 = reinterpret_cast<uint4*>(cdst + (size_t)(g0 + g) * p.R + c0);
+                            d4[0] = make_uint4(o[0], o[1], o[2], o[3]);
+                            d4[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                        }
+                    }
+                    continue;
+                }
                 if (!__any_sync(0xffffffffu, own)) continue;  // none of this warp's positions belongs to the tenant
                 for (int c0 = 0; c0 < p.R; c0 += 16) {
                     uint32_t r[16];
                     tmem_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(g * p.R + c0), r);
                     tmem_ld_wait();
-                    if (own && direct) {
+                    if (own && direct) {                  // (not cat)
                         uint32_t o[8];
 #pragma unroll
                         for (int v = 0; v < 8; ++v) {
@@ -252,8 +275,18 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
                 ctrl->last_flag = (old == p.split1 - 1) ? 1 : 0;
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (ctrl->last_flag && !ctrl->abort_flag && cat && pos < p.max_m) {
+                // zeros for the block's other entries first; the position's own entry is written below
+                for (int li = 0; li < n_list; ++li) {
+                    if (li == mine && pos < p.M) continue;
+                    uint4* d4 = reinterpret_cast<uint4*>(cdst + (size_t)li * p.R);
+                    for (int c = 0; c < p.R / 8; ++c) d4[c] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
             if (ctrl->last_flag && !ctrl->abort_flag) {
                 if (mine >= 0 && pos < p.M) {
+                    __nv_bfloat16* odst = cat ? cdst + (size_t)mine * p.R : hdst;
+                    const float osc = cat ? inv : 1.0f;
                     const size_t jstride = (size_t)p.S * p.max_m * p.R;
                     const float* src = p.hp + ((size_t)s * p.max_m + (size_t)pos) * p.R;
                     for (int c0 = 0; c0 < p.R; c0 += 8) {
@@ -276,9 +309,9 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
                                 a1.x += v[u][1].x; a1.y += v[u][1].y; a1.z += v[u][1].z; a1.w += v[u][1].w;
                             }
                         }
-                        __nv_bfloat162 b0 = __floats2bfloat162_rn(a0.x, a0.y), b1 = __floats2bfloat162_rn(a0.z, a0.w);
-                        __nv_bfloat162 b2 = __floats2bfloat162_rn(a1.x, a1.y), b3 = __floats2bfloat162_rn(a1.z, a1.w);
-                        *reinterpret_cast<uint4*>(hdst + c0) = make_uint4(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1),
+                        __nv_bfloat162 b0 = __floats2bfloat162_rn(a0.x * osc, a0.y * osc), b1 = __floats2bfloat162_rn(a0.z * osc, a0.w * osc);
+                        __nv_bfloat162 b2 = __floats2bfloat162_rn(a1.x * osc, a1.y * osc), b3 = __floats2bfloat162_rn(a1.z * osc, a1.w * osc);
+                        *reinterpret_cast<uint4*>(odst + c0) = make_uint4(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1),
                                                                           *reinterpret_cast<uint32_t*>(&b2), *reinterpret_cast<uint32_t*>(&b3));
                     }
                 }

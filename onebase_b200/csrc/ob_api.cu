@@ -15,6 +15,8 @@ cudaError_t launch_k2_nvfp4(const K2Params& p, const CUtensorMap& tm_w, const CU
 int k2_fp8_h_tiles(int tn);
 int k2_max_active_clusters(int fp4, int stored, int split2, size_t smem);
 cudaError_t launch_k1_mma(const K1mParams& p, const CUtensorMap& tm_xs, const CUtensorMap* tm_a, dim3 grid, cudaStream_t stream);
+cudaError_t launch_k2_prefill(const K2pParams& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap& tm_h,
+                              const CUtensorMap* tm_b, dim3 grid, int pdl, cudaStream_t stream);
 cudaError_t launch_fused(const K2Params& p, const K1Params& k1, const CUtensorMap& tm_w, const CUtensorMap& tm_x,
                          const CUtensorMap* tm_b, dim3 grid, size_t smem, cudaStream_t stream);
 cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream);
@@ -93,6 +95,9 @@ struct ObLayer {
     CUtensorMap tm_w;
     CUtensorMap tm_b[OB_MAX_SLICES];
     CUtensorMap tm_a[OB_MAX_SLICES];   // bf16 adapters: A of each slice as [L * R, K], for the tensor-core shrink
+    bool big_ok;                       // FP8 base, bf16 adapters of rank >= 64, slice widths in multiples of 256:
+    CUtensorMap tm_w2;                 //   the 256 x 256 prefill GEMM applies; W and B in 256-row boxes
+    CUtensorMap tm_b2[OB_MAX_SLICES];
     std::mutex mu;
     std::vector<XMap> xmaps;      // x_q maps by (workspace region, rows, token tile)
 };
@@ -148,7 +153,7 @@ int validate_workspace(const ObLayer* l, const void* ws, const ObWorkspaceShape*
 int k_bytes(const ObLayerDesc& d) { return d.base_fmt == OB_BASE_NVFP4 ? d.K / 2 : d.K; }
 
 struct Resolved {
-    int tn, split1, split2, stages, m_tiles, k_per_split, pb, fused, mma_shrink;
+    int tn, split1, split2, stages, m_tiles, k_per_split, pb, fused, mma_shrink, big;
     uint32_t wait_ms;
 };
 
@@ -185,6 +190,10 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     // Prefill batches of bf16 adapters shrink on the tensor cores (LOWBIT_SHRINK_CUDA_CORES=1 keeps the warp-level form).
     static const bool no_mma = [] { const char* v = std::getenv("LOWBIT_SHRINK_CUDA_CORES"); return v && v[0] == '1'; }();
     r->mma_shrink = (!no_mma && M > kDecodeTokens && d.lora_fmt == kLoraBf16) ? 1 : 0;
+    // Larger batches go to the 256 x 256 prefill GEMM unless the caller names a token tile (LOWBIT_PREFILL_SMALL_TILES=1
+    // keeps k2_gemm.cu's tiles); prepare_call() drops the choice again when the workspace has no room for its h blocks.
+    static const bool no_big = [] { const char* v = std::getenv("LOWBIT_PREFILL_SMALL_TILES"); return v && v[0] == '1'; }();
+    r->big = (!no_big && r->mma_shrink && l->big_ok && M > kBigTileMinTokens && !(cfg && cfg->tn)) ? 1 : 0;
     if (split1 == 0 && r->mma_shrink) {   // one wave of (128-position tile, slice, K split) CTAs, at least 256 elements each
         const int tiles = ((M + 127) / 128) * d.S;
         split1 = 1;
@@ -234,7 +243,11 @@ int get_xmap(ObLayer* l, const void* xq, int rows, int tn, CUtensorMap* out) {
     m.base = xq;
     m.rows = rows;
     m.tn = tn;
-    int st = tn < 0   // the adapter-sorted bf16 copy of x: 64-element x 128-row boxes for the tensor-core shrink
+    const uint64_t lc = (uint64_t)(l->d.L < kMaxTileTenants ? l->d.L : kMaxTileTenants);
+    int st = tn == -2   // the shrink's per-tenant h blocks [S * rows, lc * R] bf16: 64-element x 128-row boxes
+                 ? encode_2d(&m.tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xq, lc * (uint64_t)l->d.R, (uint64_t)l->d.S * (uint64_t)rows,
+                             lc * (uint64_t)l->d.R * 2, 64, 128)
+             : tn < 0   // the adapter-sorted bf16 copy of x: 64-element x 128-row boxes for the tensor-core shrink
                  ? encode_2d(&m.tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xq, (uint64_t)l->d.K, (uint64_t)rows, (uint64_t)l->d.K * 2, 64, 128)
                  : encode_2d(&m.tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, (uint64_t)k_bytes(l->d), (uint64_t)rows,
                              (uint64_t)k_bytes(l->d), kBlockK, (uint32_t)tn);
@@ -307,6 +320,12 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     m.hb = reinterpret_cast<__nv_bfloat16*>(base + lay.hb);
     m.counters = reinterpret_cast<int32_t*>(base + lay.counters);
     m.status = reinterpret_cast<int32_t*>(base + lay.status);
+    if (r.big) {
+        m.hcat = reinterpret_cast<__nv_bfloat16*>(base + lay.hcat);
+        m.lc = d.L < kMaxTileTenants ? d.L : kMaxTileTenants;
+        m.sx = reinterpret_cast<const float*>(base + lay.sx);
+        m.s_w = d.s_w;
+    }
     if ((long long)((b->M + 127) / 128) * d.S > kCounterSlots) return OB_ERR_TOO_LARGE;
     dim3 mgrid((unsigned)((b->M + 127) / 128), (unsigned)d.S, (unsigned)r.split1);
     e = launch_k1_mma(m, tm_xs, l->tm_a, mgrid, stream);
@@ -403,8 +422,38 @@ int k2_prepare(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* s
     return OB_OK;
 }
 
+int k2_prefill_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, int pdl,
+                    cudaStream_t stream) {
+    const ObLayerDesc& d = l->d;
+    const WorkspaceLayout lay = workspace_layout(*sh);
+    uint8_t* base = static_cast<uint8_t*>(ws);
+    CUtensorMap tm_x, tm_h;
+    int st = get_xmap(l, base + lay.xq, sh->max_m, 256, &tm_x);
+    if (st == OB_OK) st = get_xmap(l, base + lay.hcat, sh->max_m, -2, &tm_h);
+    if (st != OB_OK) return st;
+    K2pParams p = {};
+    p.M = b->M; p.N = d.N; p.K = d.K; p.S = d.S; p.R = d.R; p.L = d.L;
+    for (int s = 0; s < OB_MAX_SLICES; ++s) p.widths[s] = s < d.S ? d.widths[s] : 0;
+    p.kblocks = (d.K + kBlockK - 1) / kBlockK;
+    p.stages = 3;
+    p.lc = d.L < kMaxTileTenants ? d.L : kMaxTileTenants;
+    p.max_m = sh->max_m;
+    p.wait_ms = r.wait_ms;
+    p.s_w = d.s_w;
+    p.sx = reinterpret_cast<const float*>(base + lay.sx);
+    p.meta = meta_of(b);
+    p.y = static_cast<__nv_bfloat16*>(b->y);
+    p.ldy = b->ldy;
+    p.status = reinterpret_cast<int32_t*>(base + lay.status);
+    if (d.N / 256 > 65535) return OB_ERR_TOO_LARGE;
+    dim3 grid((unsigned)((b->M + 255) / 256), 1u, (unsigned)(d.N / 256));
+    cudaError_t e = launch_k2_prefill(p, l->tm_w2, tm_x, tm_h, l->tm_b2, grid, pdl, stream);
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
+
 int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, int pdl,
                 cudaStream_t stream, bool chain = false) {
+    if (r.big) return k2_prefill_impl(l, b, ws, sh, r, pdl, stream);
     K2Launch k;
     const int st = k2_prepare(l, b, ws, sh, r, chain, &k);
     if (st != OB_OK) return st;
@@ -444,6 +493,7 @@ int prepare_call(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape*
     if (l->d.base_fmt != base_fmt) return OB_ERR_FORMAT;
     st = resolve_cfg(l, b->M, cfg, r);
     if (st != OB_OK) return st;
+    if (r->big && (!sh || sh->max_l < l->d.L)) r->big = 0;
     return validate_workspace(l, ws, sh, r->split1, r->split2);
 }
 
@@ -493,6 +543,9 @@ int ob_k2_fp8_static(ObLayer* layer, const ObBatch* batch, void* workspace, cons
     // the workspace only has to hold what K1 wrote (and the status words): its own split-K region is not used
     st = validate_workspace(layer, workspace, shape, r.split1, 1);
     if (st != OB_OK) return st;
+    if (r.big && shape->max_l < layer->d.L) r.big = 0;
+    // a prefill batch on the 256 x 256 GEMM needs no split-K scratch at all: the same launch as ob_k2_fp8
+    if (r.big) return k2_prefill_impl(layer, batch, workspace, shape, r, pdl, static_cast<cudaStream_t>(cuda_stream));
     const size_t need = r.split2 > 1 ? (size_t)r.split2 * (size_t)layer->n_tiles * (size_t)r.tn * kTileN * sizeof(float) : 0;
     if (need > kStaticPartBytes) return OB_ERR_TOO_LARGE;   // beyond the static scratch: use ob_k2_fp8 with a workspace
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
@@ -522,6 +575,7 @@ int ob_k2_fp8_static(ObLayer* layer, const ObBatch* batch, void* workspace, cons
     p.s_w = d.s_w;
     p.sx = reinterpret_cast<const float*>(base + lay.sx);
     p.hp = reinterpret_cast<const float*>(base + lay.hp);
+    p.hb = r.mma_shrink ? reinterpret_cast<const __nv_bfloat16*>(base + lay.hb) : nullptr;
     p.meta = meta_of(batch);
     p.y = static_cast<__nv_bfloat16*>(batch->y);
     p.ldy = batch->ldy;
@@ -601,6 +655,17 @@ int ob_layer_create(const ObLayerDesc* desc, ObLayer** out) {
                     st = encode_2d(&l->tm_a[s], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, desc->a[ss], (uint64_t)desc->K,
                                    (uint64_t)desc->L * (uint64_t)desc->R, (uint64_t)desc->K * 2, 64, (uint32_t)desc->R);
             }
+        }
+    }
+    l->big_ok = desc->base_fmt == OB_BASE_FP8 && desc->lora_fmt == OB_LORA_BF16 && desc->R >= 64;
+    for (int s = 0; s < desc->S; ++s) l->big_ok = l->big_ok && desc->widths[s] % 256 == 0;
+    if (st == OB_OK && l->big_ok) {
+        st = encode_2d(&l->tm_w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, desc->w_q, (uint64_t)desc->K, (uint64_t)desc->N, (uint64_t)desc->K,
+                       kBlockK, 256);
+        for (int s = 0; s < OB_MAX_SLICES && st == OB_OK; ++s) {
+            const int ss = s < desc->S ? s : 0;
+            st = encode_2d(&l->tm_b2[s], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, desc->b[ss], (uint64_t)desc->R,
+                           (uint64_t)desc->L * (uint64_t)desc->widths[ss], (uint64_t)desc->R * 2, 64, 256);
         }
     }
     if (st != OB_OK) {

@@ -13,6 +13,8 @@ namespace ob {
 constexpr int kTileN = 128;          // output features per GEMM tile (rows of W; the MMA's M)
 constexpr int kBlockK = 128;         // bytes of K per ring stage row (one 128-byte swizzle row)
 constexpr int kMaxLoraIters = 512;   // capacity of a CTA's list of (segment, rank chunk) expand steps
+constexpr int kMaxTileTenants = 128;  // tenants with a position in one 128-position block
+constexpr int kBigTileMinTokens = 128; // larger FP8 batches of bf16 adapters take the 256 x 256 prefill GEMM
 constexpr int kDecodeTokens = 32;     // batches up to this size take the decode forms (one position per shrink warp)
 constexpr int kCounterSlots = 4096;  // split-K arrival counters in the workspace
 constexpr int kSfSlotBytes = 2048;   // NVFP4: scale factors of 128 rows x one 256-element K slot (4 atoms of 512 bytes)
@@ -30,6 +32,7 @@ struct WorkspaceLayout {
     size_t part;       // fp32  [max_split2 * token tile * (max_n rounded to tiles)]  GEMM split-K partials
     size_t xs;         // bf16  [max_m * max_k]   adapter-sorted copy of x for the tensor-core shrink (max_m > 32 only)
     size_t hb;         // bf16  [max_sr * max_m]  the tensor-core shrink's finished h [slice][position][rank] (max_m > 32 only)
+    size_t hcat;       // bf16  [max_sr * max_m * min(max_l, 128)]  per-tenant h blocks of the large-tile prefill GEMM
     size_t total;
 };
 
@@ -48,6 +51,8 @@ __host__ __device__ inline WorkspaceLayout workspace_layout(const ObWorkspaceSha
     l.part = off;     off = align_up(off + sizeof(float) * (s.max_split2 > 1 ? (size_t)s.max_split2 * m_pad * n_pad : 0), 1024);
     l.xs = off;       off = align_up(off + (s.max_m > kDecodeTokens ? (size_t)s.max_m * (size_t)s.max_k * 2 : 0), 1024);
     l.hb = off;       off = align_up(off + (s.max_m > kDecodeTokens ? (size_t)s.max_sr * (size_t)s.max_m * 2 : 0), 1024);
+    const size_t lc = s.max_l < kMaxTileTenants ? (s.max_l > 0 ? s.max_l : 0) : kMaxTileTenants;
+    l.hcat = off;     off = align_up(off + (s.max_m > kBigTileMinTokens ? (size_t)s.max_sr * (size_t)s.max_m * lc * 2 : 0), 1024);
     l.total = off;
     return l;
 }
@@ -103,7 +108,31 @@ struct K1mParams {
     Meta meta;
     float* hp;             // [split1][S][max_m][R] partials (split1 > 1)
     __nv_bfloat16* hb;     // [S][max_m][R] the finished h: bf16 of the partials' sum in split order
+    // Large-tile prefill GEMM: instead of hb, block (position, list entry) of hcat [S][max_m][lc * R] receives
+    // h / (s_x[position] * s_w) for the entry that is the position's tenant and zeros for the block's other entries, so
+    // that the GEMM can add the expand into the base accumulator with plain TMA tiles (no masking, one final scale).
+    __nv_bfloat16* hcat;   // null: write hb
+    int lc;                // list entries per position in hcat: min(L, 128)
+    const float* sx;       // [max_m] per-position activation scales (K1's)
+    const float* s_w;      // [1]
     int32_t* counters;     // one arrival counter per (position tile, slice); zero between launches
+    int32_t* status;
+};
+
+// The 256 x 256 prefill GEMM (k2_prefill.cu): FP8 base, bf16 adapters.
+struct K2pParams {
+    int M, N, K, S, R, L;
+    int widths[OB_MAX_SLICES];
+    int kblocks;           // ceil(K / 128)
+    int stages;
+    int lc;                // list entries per position in hcat
+    int max_m;
+    uint32_t wait_ms;
+    const float* s_w;
+    const float* sx;
+    Meta meta;
+    __nv_bfloat16* y;
+    int64_t ldy;
     int32_t* status;
 };
 

@@ -53,12 +53,13 @@ class Scratch:
         self.buf = None
         self.offsets = None
 
-    def ensure(self, max_m: int, K: int, N: int, SR: int, split2: int = 1) -> None:
+    def ensure(self, max_m: int, K: int, N: int, SR: int, split2: int = 1, L: int = 0) -> None:
         s = self.shape
-        want = (max(s.max_m, max_m), max(s.max_k, K), max(s.max_n, N), max(s.max_sr, SR), max(s.max_split2, split2))
-        if self.buf is not None and want == (s.max_m, s.max_k, s.max_n, s.max_sr, s.max_split2):
+        want = (max(s.max_m, max_m), max(s.max_k, K), max(s.max_n, N), max(s.max_sr, SR), max(s.max_split2, split2),
+                max(s.max_l, L))
+        if self.buf is not None and want == (s.max_m, s.max_k, s.max_n, s.max_sr, s.max_split2, s.max_l):
             return
-        s.max_m, s.max_k, s.max_n, s.max_sr, s.max_split2 = want
+        s.max_m, s.max_k, s.max_n, s.max_sr, s.max_split2, s.max_l = want
         nbytes = C.c_size_t()
         _lib.call("ob_workspace_bytes", C.byref(s), C.byref(nbytes))
         offs = (C.c_size_t * 7)()
@@ -136,7 +137,7 @@ class VllmFusedFP8LoRA:
         self.device = w_q.device
         self.store = AdapterStore(a_stacked, b_stacked, "nvfp4" if lora_fp4 else "fp8" if lora_fp8 else "bf16")
         self.scratch = shared_scratch(self.device)
-        self.scratch.ensure(self.max_m, self.K, self.N, self.S * self.R, Scratch.MAX_SPLIT2)
+        self.scratch.ensure(self.max_m, self.K, self.N, self.S * self.R, Scratch.MAX_SPLIT2, self.L)
         self.dispatch = {}                                               # kept for report compatibility: always fused
         self.wait_ms = 2000
         d = _lib.ObLayerDesc()
@@ -204,7 +205,7 @@ class VllmFusedFP8LoRA:
     def warmup(self) -> None:
         """Nothing to compile or time at load: kernels are prebuilt and tiles come from the table.  Grows the scratch to
         its final size (before CUDA-graph capture), as the reference's warm-up does (fp8_lora_vllm.py:598-617)."""
-        self.scratch.ensure(self.max_m, self.K, self.N, self.S * self.R, Scratch.MAX_SPLIT2)
+        self.scratch.ensure(self.max_m, self.K, self.N, self.S * self.R, Scratch.MAX_SPLIT2, self.L)
 
     def requantize(self, index: int | None = None) -> None:
         """Refresh the low-precision copy of one slot (or all) from vLLM's bf16 slots after vLLM wrote or cleared it

@@ -71,7 +71,7 @@ class VllmFusedNVFP4LoRA(VllmFusedFP8LoRA):
         self.alpha = torch.tensor([1.0 / (float(x_global) * float(w_global))], dtype=torch.float32, device=self.device)
         self.w_sf_packed = pack_weight_scales(w_sf.contiguous().view(torch.uint8), self.K, widths)
         self.scratch = shared_scratch(self.device)
-        self.scratch.ensure(self.max_m, self.K, self.N, self.S * self.R, Scratch.MAX_SPLIT2)
+        self.scratch.ensure(self.max_m, self.K, self.N, self.S * self.R, Scratch.MAX_SPLIT2, self.L)
         self.dispatch = {}
         self.wait_ms = 2000
         d = _lib.ObLayerDesc()

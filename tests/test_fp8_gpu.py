@@ -104,11 +104,14 @@ def test_quant_codes_and_scales_bit_exact_golden(golden):
     (512, (256, 128), 64, 32, 32, "all32"),
     (1024, (384,), 64, 6, 77, "mixed"),                        # M > 64: 128-token tile, partial N tile
     (256, (128,), 256, 3, 9, "mixed"),                         # rank 256: four rank chunks
+    (512, (256, 512), 64, 8, 300, "mixed"),                    # > 128 tokens, widths in 256s: the 256 x 256 prefill GEMM
+    (1024, (768,), 128, 3, 200, "padded"),                     # ... with two rank chunks and padded metadata
+    (384, (512, 256, 256), 64, 40, 517, "all32"),              # ... three token tiles, more tenants than a block's width
 ])
 def test_fused_projection_matches_oracle(K, widths, R, L, M, kind):
     torch.manual_seed(1)
     d = _case(K, widths, R, L, M, seed=K + M)
-    max_m = 96
+    max_m = max(96, M + 3)
     op = build_fp8_op(d, max_m=max_m)
     idx = oseg.SegmentIndex(L, max_m)
     g = torch.Generator().manual_seed(7)
