@@ -14,7 +14,8 @@
 // Computes what lowbit_lora/kernels/fp8_lora_vllm.py:123-284 (`_gemm_vllm`) computes for a prefill batch.
 //
 // Warps: 0 = TMA producer (one thread), 1 = MMA issuer (one thread; owns the tensor-memory allocation), 2..5 = the tile's
-// expand steps from the segment index, then the epilogue (tcgen05.ld, scale, bf16 rows scattered back through the sort).
+// expand steps from the segment index, then the epilogue (tcgen05.ld, scale, the bf16 tile staged in shared memory, whole
+// token rows scattered back through the sort).
 // Ring slots of 64 KB: a W k-block [256 x 128 B] with its x_q tile [256 tokens x 128 B], or an expand step's B and h
 // tiles.  All W k-blocks come first, the expand steps last.  Every wait is bounded.
 #include "ob_common.cuh"
@@ -270,25 +271,32 @@ k2_prefill_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm_w, c
         asm volatile("bar.sync 1, 128;" ::: "memory");
         tc_fence_after();
         if (ctrl->go_flag) {
+            // The ring is idle now (every tile was consumed): it stages the output tile as [token][256 features] bf16, so
+            // that each token's 512 bytes leave in one coalesced store instead of 2-byte stores per feature.
             const int q = warp & 3;
             const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
+            const int n_tok = min(kPfTokens, p.M - t0);
 #pragma unroll 1
             for (int half = 0; half < 2; ++half) {
-                const int n_local = n0_local + half * 128 + q * 32 + lane;
-                const bool n_ok = n_local < n_s;
-                __nv_bfloat16* ycol = p.y + slice_off + n_local;
+                uint8_t* col = ring + (size_t)(half * 128 + q * 32 + lane) * 2;
 #pragma unroll 1
-                for (int c0 = 0; c0 < kPfTokens; c0 += 16) {
-                    if (t0 + c0 >= p.M) break;
-                    uint32_t r[16];
-                    tmem_ld16(tmem_base + lane_addr + (uint32_t)(half * kPfTokens + c0), r);
+                for (int c0 = 0; c0 < n_tok; c0 += 32) {
+                    uint32_t r[32];
+                    tmem_ld32(tmem_base + lane_addr + (uint32_t)(half * kPfTokens + c0), r);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        const int row = ctrl->rowmap[c0 + c];
-                        if (row >= 0 && n_ok) ycol[(int64_t)row * p.ldy] = __float2bfloat16_rn(__uint_as_float(r[c]) * ctrl->scale[c0 + c]);
-                    }
+                    for (int c = 0; c < 32; ++c)
+                        *reinterpret_cast<__nv_bfloat16*>(col + (size_t)(c0 + c) * (kPfRows * 2)) =
+                            __float2bfloat16_rn(__uint_as_float(r[c]) * ctrl->scale[c0 + c]);
                 }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            __nv_bfloat16* ybase = p.y + slice_off + n0_local + lane * 8;
+            for (int c = warp - 2; c < n_tok; c += 4) {
+                const int row = ctrl->rowmap[c];
+                if (row >= 0)
+                    *reinterpret_cast<uint4*>(ybase + (int64_t)row * p.ldy) =
+                        *reinterpret_cast<const uint4*>(ring + (size_t)c * (kPfRows * 2) + lane * 16);
             }
         }
     }

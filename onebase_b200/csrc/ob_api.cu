@@ -494,6 +494,7 @@ int prepare_call(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape*
     st = resolve_cfg(l, b->M, cfg, r);
     if (st != OB_OK) return st;
     if (r->big && (!sh || sh->max_l < l->d.L)) r->big = 0;
+    if (r->big && (b->ldy % 8 != 0 || !aligned16(b->y))) r->big = 0;   // its epilogue stores 16 bytes at a time
     return validate_workspace(l, ws, sh, r->split1, r->split2);
 }
 
@@ -543,7 +544,7 @@ int ob_k2_fp8_static(ObLayer* layer, const ObBatch* batch, void* workspace, cons
     // the workspace only has to hold what K1 wrote (and the status words): its own split-K region is not used
     st = validate_workspace(layer, workspace, shape, r.split1, 1);
     if (st != OB_OK) return st;
-    if (r.big && shape->max_l < layer->d.L) r.big = 0;
+    if (r.big && (shape->max_l < layer->d.L || batch->ldy % 8 != 0 || !aligned16(batch->y))) r.big = 0;
     // a prefill batch on the 256 x 256 GEMM needs no split-K scratch at all: the same launch as ob_k2_fp8
     if (r.big) return k2_prefill_impl(layer, batch, workspace, shape, r, pdl, static_cast<cudaStream_t>(cuda_stream));
     const size_t need = r.split2 > 1 ? (size_t)r.split2 * (size_t)layer->n_tiles * (size_t)r.tn * kTileN * sizeof(float) : 0;
