@@ -53,6 +53,22 @@ __global__ void __launch_bounds__(kK1Threads) k1_kernel(const K1Params p) {
     OB_TRACE1(3)
 }
 
+// Quantization alone, for batches whose shrink runs on the tensor cores: without the shrink's registers four of these
+// CTAs share an SM instead of two, which is what a launch of thousands of one-row CTAs needs.
+template <bool FP4_BASE>
+__global__ void __launch_bounds__(kK1Threads, 4) k1_quant_kernel(const K1Params p) {
+    griddep_launch_dependents();
+    const int row = row_of_position(p, blockIdx.x, threadIdx.x & 31);
+    griddep_wait();
+    if (FP4_BASE) quantize_row_nvfp4<kK1Threads>(p, blockIdx.x, row, threadIdx.x);
+    else quantize_row<kK1Threads, 0>(p, blockIdx.x, row, threadIdx.x);
+    if (p.xs != nullptr) {
+        const uint4* xr = reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.ldx);
+        uint4* xo = reinterpret_cast<uint4*>(p.xs + (size_t)blockIdx.x * (size_t)p.K);
+        for (int i = threadIdx.x; i < (p.K >> 3); i += kK1Threads) xo[i] = __ldg(xr + i);
+    }
+}
+
 template <int LORA_FMT, bool FP4_BASE>
 static cudaError_t launch_k1_impl(const K1Params& p, int grid, int pdl, cudaStream_t stream) {
     cudaLaunchConfig_t cfg = {};
@@ -65,6 +81,8 @@ static cudaError_t launch_k1_impl(const K1Params& p, int grid, int pdl, cudaStre
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
+    if (grid == p.n_quant_ctas && p.xq_ready == nullptr && p.trace == nullptr)   // no shrink warps in this launch
+        return cudaLaunchKernelEx(&cfg, k1_quant_kernel<FP4_BASE>, p);
     return cudaLaunchKernelEx(&cfg, k1_kernel<LORA_FMT, FP4_BASE>, p);
 }
 

@@ -3,7 +3,7 @@
 Replaces the reference's load-time timed dispatch (`tune_dispatch`, lowbit_lora/kernels/fp8_lora_vllm.py:554-596) with a
 lookup, keyed like the reference's swept tables (lowbit_lora/hopper_pdl.py:268-298): (M bucket, N, K, S, R, format).
 Rows live in `tiles/*.jsonl` next to this file (one JSON object per line: the key fields plus tn / split2 / split1 /
-stages).  A shape without a row falls back to the nearest M bucket of the same (N, K, S, R, format), then to the
+stages).  A shape without a row falls back to the M bucket next to it of the same (N, K, S, R, format), then to the
 library's own rule (an empty dict: every field 0 = default).  LOWBIT_PDL_CFG=<file> adds rows from another file, which
 win over the shipped ones.
 """
@@ -42,7 +42,10 @@ def tile_for(m_bucket: int, N: int, K: int, S: int, R: int, fmt: str) -> dict:
     hit = _TABLE.get((m_bucket, N, K, S, R, fmt))
     if hit is not None:
         return hit
+    # A neighbouring bucket's choice carries over only within one doubling: the swept rows are decode sizes, and their
+    # split-K choices are not even valid for a prefill batch (several token tiles cannot be split along K).
     near = [(abs(k[0].bit_length() - m_bucket.bit_length()), k) for k in _TABLE if k[1:] == (N, K, S, R, fmt)]
+    near = [n for n in near if n[0] <= 1]
     if near:
         cfg = dict(_TABLE[min(near)[1]])
         cfg.pop("tn", None)                      # the token tile follows the batch, not the neighbouring bucket

@@ -132,8 +132,9 @@ def test_tile_table_lookup_and_fallback(tmp_path, monkeypatch):
     monkeypatch.setenv("LOWBIT_PDL_CFG", str(f))
     tile_table.reload()
     assert tile_table.tile_for(32, 1000, 512, 1, 16, "fp8") == {"tn": 32, "split2": 3, "split1": 2, "stages": 4}
-    near = tile_table.tile_for(8, 1000, 512, 1, 16, "fp8")      # nearest bucket of the same shape, token tile not inherited
+    near = tile_table.tile_for(16, 1000, 512, 1, 16, "fp8")     # the bucket next to it of the same shape, token tile not inherited
     assert near == {"split2": 3, "split1": 2, "stages": 4}
+    assert tile_table.tile_for(2048, 1000, 512, 1, 16, "fp8") == {}   # a decode row says nothing about a prefill batch
     assert tile_table.tile_for(32, 999, 512, 1, 16, "fp8") == {}
     monkeypatch.delenv("LOWBIT_PDL_CFG")
     tile_table.reload()

@@ -107,6 +107,7 @@ def test_quant_codes_and_scales_bit_exact_golden(golden):
     (512, (256, 512), 64, 8, 300, "mixed"),                    # > 128 tokens, widths in 256s: the 256 x 256 prefill GEMM
     (1024, (768,), 128, 3, 200, "padded"),                     # ... with two rank chunks and padded metadata
     (384, (512, 256, 256), 64, 40, 517, "all32"),              # ... three token tiles, more tenants than a block's width
+    (4096, (4096,), 64, 32, 160, "mixed"),                     # a shape with swept decode rows in the tile table, at a prefill size
 ])
 def test_fused_projection_matches_oracle(K, widths, R, L, M, kind):
     torch.manual_seed(1)
