@@ -37,9 +37,9 @@ if str(ROOT) not in sys.path:
 PROJECTIONS = {"qkv": (4096, (4096, 1024, 1024)), "o": (4096, (4096,)), "gate_up": (4096, (12288, 12288)),
                "down": (12288, (4096,))}
 L_SLOTS, RANK = 32, 64
-# dram__bytes_read.sum + dram__bytes_write.sum of one k2_fp8_kernel launch on gate_up at M = 32 (23 distinct tenants), from the
-# ncu capture summarised in profiles/k2_fp8_kernel_gate_up_m32.md; other batch sizes were not captured
-K2_GATE_UP_TRAFFIC = {32: 177.3e6}
+# dram__bytes_read.sum + dram__bytes_write.sum of one k2_kernel launch on gate_up at M = 32 (23 distinct tenants), from the
+# ncu capture summarised in profiles/k2_kernel_gate_up_m32.md; other batch sizes were not captured
+K2_GATE_UP_TRAFFIC = {32: 178.5e6}
 METRIC = "decode tok/s at 32 tenants through one fused FP8+LoRA decoder layer (layer us and HBM roofline % alongside)"
 
 
@@ -331,7 +331,7 @@ def main() -> None:
         "layer_us": ms * 1e3, "layer_us_median": statistics.median(ts) * 1e3, "projection_us": per_proj,
         "layer_bytes": total_bytes, "layer_gbs": total_bytes / (ms * 1e-3) / 1e9,
         "layer_frac_of_peak": total_bytes / (ms * 1e-3) / 1e9 / peak,
-        "roofline": {"kernel": "k2_fp8_kernel (gate_up, launched alone)", "bound": "hbm", "achieved": k2_gbs, "peak": peak,
+        "roofline": {"kernel": "k2_kernel<FP8 base, bf16 adapters> (gate_up, launched alone)", "bound": "hbm", "achieved": k2_gbs, "peak": peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": k2_gbs / peak, "traffic": K2_GATE_UP_TRAFFIC.get(M) if distinct == 23 else None, "bytes": k2_bytes,
                      "us": k2_ms * 1e3, "k1_us_alone": k1_ms * 1e3},
         "e2e": {"value": M / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
