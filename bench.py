@@ -241,6 +241,9 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--base", default="fp8", choices=["fp8", "nvfp4"], help="base format of the --profile case")
     ap.add_argument("--lora-fmt", default="bf16", choices=["bf16", "fp8", "nvfp4"], help="adapter storage of the --profile case")
+    ap.add_argument("--tp-form", default="partial", choices=["partial", "sharded"],
+                    help="N > 1: row-parallel layers add partial LoRA terms (vLLM's default) or shard the adapters too and "
+                         "all-reduce the shrink partials first")
     ap.add_argument("--profile", default=None, metavar="PROJ",
                     help="small profiling case: build only this projection (qkv|o|gate_up|down) and launch K1 and K2 "
                          "separately --steps times each (for ncu captures); prints their mean times")

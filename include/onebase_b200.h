@@ -82,6 +82,13 @@ typedef struct ObLayerDesc {
     const float* bg;                 /* NVFP4 adapters: fp32 [S,L] inverse global scales of B */
     int32_t quant_rcp_approx;        /* NVFP4 base: 1 = reciprocals by rcp.approx.ftz (bit-identical to vLLM's CUDA quantizer,
                                         nvfp4_lora_vllm.py:61-67), 0 = IEEE reciprocals (the torch recipe, :361-376) */
+    /* Row-parallel layers with sharded adapters (vLLM's RowParallelLinearWithShardedLoRA,
+     * vllm/lora/layers/row_parallel_linear.py:118-160): this rank holds W and A for its K slice but only rows
+     * [b_row0[s], b_row0[s] + b_rows[s]) of each slice's B (`b[s]` is then [L,1,b_rows[s],R]); the expand is added to those
+     * output features only, after the caller has all-reduced the shrink partials in the workspace.  Both zero: the whole
+     * slice.  bf16 adapters only; b_row0 must be a multiple of 128, b_rows too unless the range ends with the slice. */
+    int32_t b_row0[OB_MAX_SLICES];
+    int32_t b_rows[OB_MAX_SLICES];
 } ObLayerDesc;
 
 /* One call's inputs and output: the arguments of `op(x, meta_args, out=...)`
@@ -144,6 +151,12 @@ int ob_workspace_offsets(const ObWorkspaceShape* shape, size_t out[7]);
  * (fp8_lora_vllm.py:425-496, nvfp4_lora_vllm.py:446-502): pointer tables, slice ends, format flags. */
 int ob_layer_create(const ObLayerDesc* desc, ObLayer** out);
 int ob_layer_destroy(ObLayer* layer);
+
+/* The tile choice a call of M tokens would run with: `cfg`'s non-zero fields, the rest filled in by the library's rule
+ * (tn, split2, split1, stages, wait_ms; fused as given).  For callers that need the shrink's split count -- e.g. to
+ * all-reduce exactly the partials [split1][S][max_m][R] that were written.  No counterpart in the reference, whose
+ * Python host code holds these numbers itself (`pick_cfg`, lowbit_lora/kernels/fp8_lora_vllm.py:287-312). */
+int ob_resolve_tile(ObLayer* layer, int32_t M, const ObTileCfg* cfg, ObTileCfg* out);
 
 /* K1, FP8 base: per-token dynamic e4m3 quantization of x (codes + scales into the workspace, at each token's
  * adapter-sorted position) fused with every tenant's shrink h = x A^T (split-K partials into the workspace).

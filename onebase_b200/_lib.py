@@ -31,6 +31,7 @@ class ObLayerDesc(C.Structure):
         ("w_q", C.c_void_p), ("w_sf", C.c_void_p), ("s_w", C.c_void_p), ("x_global", C.c_void_p), ("alpha", C.c_void_p),
         ("a", C.c_void_p * OB_MAX_SLICES), ("b", C.c_void_p * OB_MAX_SLICES), ("sa", C.c_void_p * OB_MAX_SLICES),
         ("sb", C.c_void_p * OB_MAX_SLICES), ("ag", C.c_void_p), ("bg", C.c_void_p), ("quant_rcp_approx", C.c_int32),
+        ("b_row0", C.c_int32 * OB_MAX_SLICES), ("b_rows", C.c_int32 * OB_MAX_SLICES),
     ]
 
 
@@ -59,6 +60,7 @@ SYMBOLS = {
     "ob_workspace_offsets": (C.c_int, [C.POINTER(ObWorkspaceShape), C.POINTER(C.c_size_t)]),
     "ob_layer_create": (C.c_int, [C.POINTER(ObLayerDesc), C.POINTER(C.c_void_p)]),
     "ob_layer_destroy": (C.c_int, [C.c_void_p]),
+    "ob_resolve_tile": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(ObTileCfg), C.POINTER(ObTileCfg)]),
     "ob_k1_fp8": (C.c_int, [C.c_void_p, C.POINTER(ObBatch), C.c_void_p, C.POINTER(ObWorkspaceShape), C.POINTER(ObTileCfg),
                             C.c_void_p]),
     "ob_k2_fp8": (C.c_int, [C.c_void_p, C.POINTER(ObBatch), C.c_void_p, C.POINTER(ObWorkspaceShape), C.POINTER(ObTileCfg),

@@ -389,7 +389,8 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                     if (b_by_tma) {       // bf16 adapters: the B tile comes by TMA; stored formats are dequantized by warps 4-7
                         const LoraStep e = ctrl->steps[w.li];
                         mbar_arrive_expect_tx(&ctrl->full_b[st], b_bytes);
-                        tma_load_2d(ring + (size_t)st * stage_bytes, tmb, &ctrl->full_b[st], e.chunk * p.rc, e.lora * n_s + n0_local);
+                        tma_load_2d(ring + (size_t)st * stage_bytes, tmb, &ctrl->full_b[st], e.chunk * p.rc,
+                                    e.lora * p.b_rows[s] + (n0_local - p.b_row0[s]));
                     }
                 } else {
                     mbar_arrive_expect_tx(&ctrl->full_w[st], wx_bytes);
@@ -549,6 +550,8 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
         }
         if (warp == 4) {
             int total = 0;                                   // (segment, chunk) steps of this tile so far, all splits
+            // sharded B: only the tiles whose rows this rank holds carry an expand
+            const bool has_b = n0_local >= p.b_row0[s] && n0_local < p.b_row0[s] + p.b_rows[s];
             if (n_ad > 0) {
                 for (int base = 0; base <= p.L; base += 32) {
                     const int i = base + lane;
@@ -560,10 +563,11 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                         hi = min(min(sst + cnt, t0 + tn), n_all);
                         if (cnt <= 0 || sst < 0) lora = -1;
                     }
-                    const bool ok = lora >= 0 && lora < p.L && lo < hi;
-                    const uint32_t mask = __ballot_sync(0xffffffffu, ok);
-                    if (FUSED && ok)
+                    const bool seg = lora >= 0 && lora < p.L && lo < hi;
+                    if (FUSED && seg)                        // (the shrink covers every position, with or without an expand here)
                         for (int pos = lo; pos < hi; ++pos) ctrl->lora_pos[pos - t0] = lora;
+                    const bool ok = seg && has_b;
+                    const uint32_t mask = __ballot_sync(0xffffffffu, ok);
                     if (ok) {
                         const int idx = total / n_chunks + __popc(mask & ((1u << lane) - 1u));
                         for (int c = 0; c < n_chunks; ++c) {

@@ -129,7 +129,20 @@ int validate_desc(const ObLayerDesc* d) {
         if (d->lora_fmt != OB_LORA_BF16 && (!d->sa[s] || !d->sb[s])) return OB_ERR_NULL;
     }
     if (d->lora_fmt == OB_LORA_NVFP4 && (!d->ag || !d->bg)) return OB_ERR_NULL;
+    for (int s = 0; s < d->S; ++s) {   // sharded B rows: whole 128-row tiles of the slice, bf16 adapters
+        if (d->b_rows[s] == 0 && d->b_row0[s] == 0) continue;
+        if (d->lora_fmt != OB_LORA_BF16) return OB_ERR_FORMAT;
+        if (d->b_row0[s] < 0 || d->b_rows[s] <= 0 || d->b_row0[s] % kTileN != 0 || d->b_row0[s] + d->b_rows[s] > d->widths[s] ||
+            (d->b_rows[s] % kTileN != 0 && d->b_row0[s] + d->b_rows[s] != d->widths[s]))
+            return OB_ERR_SHAPE;
+    }
     return OB_OK;
+}
+
+bool b_sharded(const ObLayerDesc& d) {
+    for (int s = 0; s < d.S; ++s)
+        if (d.b_rows[s] != 0) return true;
+    return false;
 }
 
 int validate_batch(const ObLayer* l, const ObBatch* b) {
@@ -189,7 +202,8 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     const int pb = M <= kDecodeTokens ? 1 : 4;
     // Prefill batches of bf16 adapters shrink on the tensor cores (LOWBIT_SHRINK_CUDA_CORES=1 keeps the warp-level form).
     static const bool no_mma = [] { const char* v = std::getenv("LOWBIT_SHRINK_CUDA_CORES"); return v && v[0] == '1'; }();
-    r->mma_shrink = (!no_mma && M > kDecodeTokens && d.lora_fmt == kLoraBf16) ? 1 : 0;
+    // (not for sharded adapters: their shrink partials are all-reduced between K1 and K2, so they must stay partials)
+    r->mma_shrink = (!no_mma && M > kDecodeTokens && d.lora_fmt == kLoraBf16 && !b_sharded(d)) ? 1 : 0;
     // Larger batches go to the 256 x 256 prefill GEMM unless the caller names a token tile (LOWBIT_PREFILL_SMALL_TILES=1
     // keeps k2_gemm.cu's tiles); prepare_call() drops the choice again when the workspace has no room for its h blocks.
     static const bool no_big = [] { const char* v = std::getenv("LOWBIT_PREFILL_SMALL_TILES"); return v && v[0] == '1'; }();
@@ -405,6 +419,10 @@ int k2_prepare(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* s
     p.xq_ready = chain ? p.counters + kCounterSlots : nullptr;
     p.chain_done = chain ? p.counters + kCounterSlots + 1 : nullptr;
     for (int s = 0; s < d.S; ++s) { p.b[s] = d.b[s]; p.sb[s] = d.sb[s]; }
+    for (int s = 0; s < OB_MAX_SLICES; ++s) {
+        p.b_row0[s] = s < d.S ? d.b_row0[s] : 0;
+        p.b_rows[s] = s < d.S ? (d.b_rows[s] ? d.b_rows[s] : d.widths[s]) : 0;
+    }
     p.bg = d.bg;
     p.trace = g_trace;
     p.trace_ctas = g_trace_ctas;
@@ -584,6 +602,10 @@ int ob_k2_fp8_static(ObLayer* layer, const ObBatch* batch, void* workspace, cons
     p.part = reinterpret_cast<float*>(scratch + kStaticCounterBytes);       // ... and split-K partial tiles
     p.status = reinterpret_cast<int32_t*>(base + lay.status);
     for (int s = 0; s < d.S; ++s) { p.b[s] = d.b[s]; p.sb[s] = d.sb[s]; }
+    for (int s = 0; s < OB_MAX_SLICES; ++s) {
+        p.b_row0[s] = s < d.S ? d.b_row0[s] : 0;
+        p.b_rows[s] = s < d.S ? (d.b_rows[s] ? d.b_rows[s] : d.widths[s]) : 0;
+    }
     p.bg = d.bg;
     p.trace = nullptr;
     p.trace_ctas = 0;
@@ -650,15 +672,16 @@ int ob_layer_create(const ObLayerDesc* desc, ObLayer** out) {
         if (st == OB_OK && desc->lora_fmt == OB_LORA_BF16) {
             for (int s = 0; s < OB_MAX_SLICES && st == OB_OK; ++s) {
                 const int ss = s < desc->S ? s : 0;   // unused slots repeat slice 0 so every kernel argument is a valid map
+                const int b_rows = desc->b_rows[ss] ? desc->b_rows[ss] : desc->widths[ss];   // rows of B this rank holds
                 st = encode_2d(&l->tm_b[s], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, desc->b[ss], (uint64_t)desc->R,
-                               (uint64_t)desc->L * (uint64_t)desc->widths[ss], (uint64_t)desc->R * 2, (uint32_t)l->rc, kTileN);
+                               (uint64_t)desc->L * (uint64_t)b_rows, (uint64_t)desc->R * 2, (uint32_t)l->rc, kTileN);
                 if (st == OB_OK)
                     st = encode_2d(&l->tm_a[s], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, desc->a[ss], (uint64_t)desc->K,
                                    (uint64_t)desc->L * (uint64_t)desc->R, (uint64_t)desc->K * 2, 64, (uint32_t)desc->R);
             }
         }
     }
-    l->big_ok = desc->base_fmt == OB_BASE_FP8 && desc->lora_fmt == OB_LORA_BF16 && desc->R >= 64;
+    l->big_ok = desc->base_fmt == OB_BASE_FP8 && desc->lora_fmt == OB_LORA_BF16 && desc->R >= 64 && !b_sharded(*desc);
     for (int s = 0; s < desc->S; ++s) l->big_ok = l->big_ok && desc->widths[s] % 256 == 0;
     if (st == OB_OK && l->big_ok) {
         st = encode_2d(&l->tm_w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, desc->w_q, (uint64_t)desc->K, (uint64_t)desc->N, (uint64_t)desc->K,
@@ -679,6 +702,21 @@ int ob_layer_create(const ObLayerDesc* desc, ObLayer** out) {
 
 int ob_layer_destroy(ObLayer* layer) {
     delete layer;
+    return OB_OK;
+}
+
+int ob_resolve_tile(ObLayer* layer, int32_t M, const ObTileCfg* cfg, ObTileCfg* out) {
+    if (!layer || !out) return OB_ERR_NULL;
+    if (M < 1 || M > layer->d.max_m) return OB_ERR_BATCH;
+    Resolved r;
+    const int st = resolve_cfg(layer, M, cfg, &r);
+    if (st != OB_OK) return st;
+    out->tn = r.tn;
+    out->split2 = r.split2;
+    out->split1 = r.split1;
+    out->stages = r.stages;
+    out->wait_ms = (int32_t)r.wait_ms;
+    out->fused = r.fused;
     return OB_OK;
 }
 

@@ -163,6 +163,8 @@ struct K2Params {
     int32_t* status;
     const void* b[OB_MAX_SLICES];
     const void* sb[OB_MAX_SLICES];
+    int b_row0[OB_MAX_SLICES];   // first output feature of each slice whose B rows this rank holds (0 unless B is sharded)
+    int b_rows[OB_MAX_SLICES];   // number of those rows (the slice's width unless B is sharded)
     const float* bg;
     const uint8_t* wsf;    // NVFP4 base: W block scales, packed per (128-row tile, 256-element K slot) in scale-factor atoms
     const uint8_t* xsf;    // NVFP4 base: K1's activation block scales, packed per (token tile, K slot)

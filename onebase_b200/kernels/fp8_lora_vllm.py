@@ -113,7 +113,8 @@ class VllmFusedFP8LoRA:
 
     _K1, _K2, _CHAIN, _FMT = "ob_k1_fp8", "ob_k2_fp8", "ob_chain_fp8", "fp8"   # entry points and tile-table format key
 
-    def __init__(self, w_q, s_w, a_stacked, b_stacked, max_m, *, split_k=None, lora_fp8=False, lora_fp4=False):
+    def __init__(self, w_q, s_w, a_stacked, b_stacked, max_m, *, split_k=None, lora_fp8=False, lora_fp4=False,
+                 b_shard=None):
         if w_q.device.type != "cuda":
             raise RuntimeError("onebase_b200 runs on CUDA devices only (there is no CPU path)")
         self.w_q, self.s_w = w_q, s_w.reshape(1).to(torch.float32)
@@ -122,8 +123,13 @@ class VllmFusedFP8LoRA:
         self.L, _, self.R, k_a = a_stacked[0].shape
         assert w_q.dtype == torch.float8_e4m3fn and w_q.is_contiguous()
         assert k_a == self.K and all(t.dtype == torch.bfloat16 and t.is_contiguous() for t in (*a_stacked, *b_stacked))
-        widths = [t.shape[2] for t in b_stacked]
+        # b_shard = [(first row, rows, slice width), ...] per slice: this rank holds only those rows of each slice's B
+        # (vLLM's row-parallel layers with sharded adapters); the expand then covers those output features only
+        self.b_shard = b_shard
+        widths = [t.shape[2] for t in b_stacked] if b_shard is None else [int(w) for _, _, w in b_shard]
         assert sum(widths) == self.N and self.S <= 4
+        assert b_shard is None or (not lora_fp8 and not lora_fp4 and
+                                   all(t.shape[2] == rows for t, (_, rows, _) in zip(b_stacked, b_shard)))
         ends = [sum(widths[:i + 1]) for i in range(self.S)]
         self.end0 = ends[0] if self.S >= 2 else self.N
         self.end1 = ends[1] if self.S >= 3 else self.N
@@ -146,6 +152,9 @@ class VllmFusedFP8LoRA:
         for s in range(self.S):
             d.widths[s] = widths[s]
         fill_adapter_pointers(d, self.store)
+        if b_shard is not None:
+            for s, (row0, rows, _) in enumerate(b_shard):
+                d.b_row0[s], d.b_rows[s] = int(row0), int(rows)
         d.w_q, d.s_w = w_q.data_ptr(), self.s_w.data_ptr()
         self._desc = d
         h = C.c_void_p()
@@ -171,6 +180,20 @@ class VllmFusedFP8LoRA:
             c.update(cfg)
         return _lib.ObTileCfg(c.get("tn", 0), c.get("split2", 0), c.get("split1", 0), c.get("stages", 0),
                               c.get("wait_ms", self.wait_ms), c.get("fused", 0))
+
+    def resolved_tile(self, M: int, cfg: dict | None = None) -> dict:
+        """The tile choice a call of M tokens runs with, the library's own rule filled in (ob_resolve_tile)."""
+        out = _lib.ObTileCfg()
+        _lib.call("ob_resolve_tile", self._h, int(M), C.byref(self.tile(M, cfg)), C.byref(out))
+        return {k: getattr(out, k) for k in ("tn", "split2", "split1", "stages", "fused")}
+
+    def shrink_partials(self, M: int, cfg: dict | None = None) -> torch.Tensor:
+        """The fp32 shrink partials the last K1 call of M tokens wrote, [split1, S, max_m, R], as a view of the workspace:
+        what a row-parallel layer with sharded adapters all-reduces between K1 and K2."""
+        split1 = self.resolved_tile(M, cfg)["split1"]
+        max_m = self.scratch.shape.max_m
+        n = split1 * self.S * max_m * self.R
+        return self.scratch.region("hp", 4 * n).view(torch.float32).view(split1, self.S, max_m, self.R)
 
     # ------------------------------------------------------------------------------------------------- the call
     def _batch(self, x, meta_args, out):

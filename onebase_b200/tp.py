@@ -7,7 +7,9 @@ the whole shrink runs on every rank and there is NO collective.
 Row-parallel (o, down): K is split -- W columns and A columns `[rank * K/tp, (rank + 1) * K/tp)`, all of B
 (vllm/lora/layers/row_parallel_linear.py:32-40); each rank computes a partial base GEMM plus a partial LoRA term and the
 layer all-reduces `y [M, N]` (bf16, NCCL over NVLink) (:73-76).  This is the form the reference's plugin serves under
-LOWBIT_TP=1 (lowbit_lora/plugin.py:239-245).  The shard functions are plain tensor slicing and work on any device.
+LOWBIT_TP=1 (lowbit_lora/plugin.py:239-245).  With sharded adapters (:118-160) B is split by output rows as well: the
+ranks first all-reduce the fp32 shrink partials, then each adds the expand to its own output features before the
+all-reduce of y.  The shard functions are plain tensor slicing and work on any device.
 """
 from __future__ import annotations
 
@@ -45,6 +47,38 @@ def shard_row(w_q, a_stacked, b_stacked, tp: int, rank: int):
     return (w_q[:, lo:lo + ks].contiguous(), tuple(a[..., lo:lo + ks].contiguous() for a in a_stacked), tuple(b_stacked))
 
 
+def shard_row_sharded_lora(w_q, a_stacked, b_stacked, tp: int, rank: int):
+    """Per-rank (w_q, a_stacked, b_stacked, b_shard) of a row-parallel projection whose adapters are sharded too (vLLM's
+    RowParallelLinearWithShardedLoRA, vllm/lora/layers/row_parallel_linear.py:118-160): W and A by K as in shard_row, and
+    of each slice's B only rows [rank * N_s / tp, (rank + 1) * N_s / tp).  `b_shard` = [(first row, rows, slice width)]
+    is what the op's constructor takes.  The shard boundaries must fall on 128-row tiles."""
+    w_r, a_r, _ = shard_row(w_q, a_stacked, b_stacked, tp, rank)
+    b_r, b_shard = [], []
+    for b in b_stacked:
+        n_s = b.shape[2]
+        assert n_s % tp == 0 and (n_s // tp) % 128 == 0, f"slice of width {n_s} does not split into {tp} shards of whole tiles"
+        rows = n_s // tp
+        b_r.append(b[:, :, rank * rows:(rank + 1) * rows].contiguous())
+        b_shard.append((rank * rows, rows, n_s))
+    return w_r, a_r, tuple(b_r), b_shard
+
+
+def run_row_parallel_sharded(op, x_r, meta_args, out=None, cfg=None, group=None):
+    """One row-parallel projection with sharded adapters on this rank: K1 on the rank's K slice, all-reduce of the fp32
+    shrink partials (a few hundred KB at most), K2 with the expand on the rank's output features only, all-reduce of y.
+    The two collectives are the exchange steps of this form (row_parallel_linear.py:135-160 and :73-76)."""
+    import torch.distributed as dist
+    M = x_r.shape[0]
+    y = op(x_r, meta_args, out=out, cfg=cfg, gemm=False)
+    multi = dist.is_initialized() and dist.get_world_size(group) > 1
+    if multi:
+        dist.all_reduce(op.shrink_partials(M, cfg), op=dist.ReduceOp.SUM, group=group)
+    y = op(x_r, meta_args, out=y, cfg=cfg, shrink=False)
+    if multi:
+        dist.all_reduce(y, op=dist.ReduceOp.SUM, group=group)
+    return y
+
+
 def shard_input_row(x, tp: int, rank: int):
     """A row-parallel layer's input is already split along K (the previous column-parallel layer's output shard)."""
     ks = x.shape[1] // tp
@@ -77,6 +111,7 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
     import datetime
     dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     M = args.m
+    sharded = getattr(args, "tp_form", "partial") == "sharded"   # row-parallel layers with sharded adapters
     warmup = max(3, args.warmup)
     g = torch.Generator(device=dev).manual_seed(0)            # same seed on every rank: identical full tensors, then sharded
     ids = torch.randint(0, L_SLOTS, (M,), generator=torch.Generator().manual_seed(0), dtype=torch.int32).to(dev)
@@ -94,15 +129,19 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
                      for _ in widths)
         b_st = tuple((torch.randn(L_SLOTS, 1, n, RANK, device=dev, generator=g) * 0.01).to(torch.bfloat16) for n in widths)
         x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+        b_shard = None
         if kind == "col":
             rep = (1, max(1, world // 8), max(1, world // 8)) if name == "qkv" else ()
             w_r, a_r, b_r = shard_column(w_q.view(torch.uint8), a_st, b_st, world, rank, rep)
             x_r = x
+        elif sharded:
+            w_r, a_r, b_r, b_shard = shard_row_sharded_lora(w_q.view(torch.uint8), a_st, b_st, world, rank)
+            x_r = shard_input_row(x, world, rank)
         else:
             w_r, a_r, b_r = shard_row(w_q.view(torch.uint8), a_st, b_st, world, rank)
             x_r = shard_input_row(x, world, rank)
         del w_q, a_st, b_st
-        op = VllmFusedFP8LoRA(w_r.view(torch.float8_e4m3fn), s_w, a_r, b_r, max_m=M)
+        op = VllmFusedFP8LoRA(w_r.view(torch.float8_e4m3fn), s_w, a_r, b_r, max_m=M, b_shard=b_shard)
         layer[name] = (op, x_r, torch.empty(M, op.N, dtype=torch.bfloat16, device=dev), kind)
     torch.cuda.empty_cache()
 
@@ -111,41 +150,79 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
             op, x, y, _ = layer[name]
             op(x, meta, out=y)
 
+    def col_then_k1(col, row):       # sharded adapters: the column-parallel chain, then the row-parallel layer's K1
+        op, x, y, _ = layer[col]
+        op(x, meta, out=y)
+        op, x, y, _ = layer[row]
+        op(x, meta, out=y, gemm=False)
+
+    def k2_only(row):
+        op, x, y, _ = layer[row]
+        op(x, meta, out=y, shrink=False)
+
+    hp_o = layer["o"][0].shrink_partials(M) if sharded else None
+    hp_down = layer["down"][0].shrink_partials(M) if sharded else None
+
     def log(msg):
         if os.environ.get("LOWBIT_VERBOSE"):
             print(f"[tp rank {rank}] {msg}", flush=True)
 
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     y_o, y_down = layer["o"][2], layer["down"][2]
+    def eager_step():
+        if sharded:
+            col_then_k1("qkv", "o")
+            dist.all_reduce(hp_o)
+            k2_only("o")
+            dist.all_reduce(y_o)
+            col_then_k1("gate_up", "down")
+            dist.all_reduce(hp_down)
+            k2_only("down")
+            dist.all_reduce(y_down)
+        else:
+            half(("qkv", "o"))
+            dist.all_reduce(y_o)
+            half(("gate_up", "down"))
+            dist.all_reduce(y_down)
+
     for _ in range(2):                                        # eager warm-up: kernels, scratch, NCCL communicator
-        half(("qkv", "o"))
-        dist.all_reduce(y_o)
-        half(("gate_up", "down"))
-        dist.all_reduce(y_down)
+        eager_step()
     torch.cuda.synchronize()
     log("eager warm-up done")
     # The kernels of each half are captured in a CUDA graph; the two all-reduces are issued between the replays (NCCL is
     # not captured: the collective stays an ordinary stream-ordered launch).
     graphs = []
-    for names in (("qkv", "o"), ("gate_up", "down")):
+    pieces = ([lambda: col_then_k1("qkv", "o"), lambda: k2_only("o"), lambda: col_then_k1("gate_up", "down"),
+               lambda: k2_only("down")] if sharded else [lambda: half(("qkv", "o")), lambda: half(("gate_up", "down"))])
+    for piece in pieces:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            half(names)
+            piece()
         torch.cuda.current_stream().wait_stream(side)
         gph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(gph):
-            half(names)
+            piece()
         graphs.append(gph)
     torch.cuda.synchronize()
     log("graphs captured")
     graphed = True
 
     def run():
-        graphs[0].replay()
-        dist.all_reduce(y_o)
-        graphs[1].replay()
-        dist.all_reduce(y_down)
+        if sharded:
+            graphs[0].replay()
+            dist.all_reduce(hp_o)
+            graphs[1].replay()
+            dist.all_reduce(y_o)
+            graphs[2].replay()
+            dist.all_reduce(hp_down)
+            graphs[3].replay()
+            dist.all_reduce(y_down)
+        else:
+            graphs[0].replay()
+            dist.all_reduce(y_o)
+            graphs[1].replay()
+            dist.all_reduce(y_down)
 
     for _ in range(warmup):
         flush.fill_(1)
@@ -176,9 +253,11 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
             "warmup": warmup, "ms_per_step": ms_v, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp8_e4m3", "data": "synthetic",
             "config": {"workload": f"Qwen3-8B decoder layer at tensor-parallel {world}: column-parallel qkv / gate_up, row-parallel "
-                                   f"o / down + NCCL all-reduce of y; FP8 base, decode M={M}, 32 bf16 tenants rank 64",
+                                   f"o / down + NCCL all-reduce of y"
+                                   f"{' (adapters sharded too: all-reduce of the shrink partials before the expand)' if sharded else ''}"
+                                   f"; FP8 base, decode M={M}, 32 bf16 tenants rank 64",
                        "l2": "flushed by a 256 MB write before every timed step",
-                       "cuda_graph": "two graphs of 4 kernels each; the NCCL all-reduces are launched between them" if graphed else "no"},
-            "layer_us": ms_v * 1e3, "gpu_launches": 8 * args.steps, "device_status_ok": bool(ok.item()),
+                       "cuda_graph": f"{len(graphs)} graphs; the NCCL all-reduces are launched between them" if graphed else "no"},
+            "layer_us": ms_v * 1e3, "gpu_launches": 8 * args.steps,   # our kernels: four K1 + four K2 per step "device_status_ok": bool(ok.item()),
             "e2e": None, "roofline": None, "cpu_baseline": None}))
     dist.destroy_process_group()

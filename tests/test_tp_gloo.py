@@ -62,8 +62,38 @@ def _worker(rank: int, world: int, port: int, out):
         row_err = float((y2 - expect).abs().max() / expect.abs().max())
         # and the sharded result stays close to the unsharded one (two different quantizations of x: twice the noise)
         assert float((y2 - full2).norm() / full2.norm()) < 6e-2
+        # row-parallel with sharded adapters: all-reduce of the fp32 shrink partials, then each rank expands its own rows of B
+        d3 = configs.with_fp8_base(configs.draw(256, (256, 256), 16, 3, 7, seed=8, w_std=0.05, b_std=0.05))
+        A3, B3 = ofp8.stack_slices(d3["a_stacked"], d3["b_stacked"])
+        w3, a3, b3, b_shard = tp.shard_row_sharded_lora(d3["w_q"].view(torch.uint8), d3["a_stacked"], d3["b_stacked"], world, rank)
+        x3 = tp.shard_input_row(d3["x"], world, rank)
+        A3r = torch.cat([t[:, 0] for t in a3], dim=1).float()                     # [L, S*R, K/tp]
+        ids3 = d3["ids"].to(torch.int64)
+        h = torch.zeros(x3.shape[0], A3r.shape[1])
+        for m in range(x3.shape[0]):
+            if ids3[m] >= 0:
+                h[m] = x3[m].float() @ A3r[ids3[m]].t()                           # this rank's partial of the shrink
+        dist.all_reduce(h)                                                        # exchange 1
+        hb = h.to(torch.bfloat16).float()
+        xq3, sx3 = ofp8.quant_per_token(x3)
+        y3 = (xq3.float() * sx3[:, None]) @ (w3.view(torch.float8_e4m3fn).float() * d3["s_w"]).t()
+        R3, off = 16, 0
+        for s_i, (row0, rows, width) in enumerate(b_shard):
+            for m in range(x3.shape[0]):
+                if ids3[m] >= 0:
+                    y3[m, off + row0: off + row0 + rows] += b3[s_i][ids3[m], 0].float() @ hb[m, s_i * R3:(s_i + 1) * R3]
+            off += width
+        dist.all_reduce(y3)                                                       # exchange 2
+        expect3 = ofp8.lora_term(d3["x"], d3["ids"], A3, B3, d3["widths"])        # the LoRA term is now the unsharded one
+        ks3 = 256 // world
+        for r in range(world):
+            xs = d3["x"][:, r * ks3:(r + 1) * ks3]
+            xq, sx = ofp8.quant_per_token(xs)
+            expect3 += (xq.float() * sx[:, None]) @ (d3["w_q"].float()[:, r * ks3:(r + 1) * ks3] * d3["s_w"]).t()
+        sharded_err = float((y3 - expect3).abs().max() / expect3.abs().max())
+        assert [tuple(t.shape) for t in b3] == [(3, 1, 256 // world, 16)] * 2 and b_shard[0] == (rank * 128, 128, 256)
         if rank == 0:
-            out.put((col_err, row_err, tuple(w_r.shape), tuple(w2.shape), tuple(a2[0].shape)))
+            out.put((col_err, row_err, tuple(w_r.shape), tuple(w2.shape), tuple(a2[0].shape), sharded_err))
     finally:
         dist.destroy_process_group()
 
@@ -78,9 +108,10 @@ def test_tensor_parallel_shards_two_ranks():
     for p in procs:
         p.join(timeout=240)
         assert p.exitcode == 0
-    col_err, row_err, w_shape, w2_shape, a2_shape = out.get()
+    col_err, row_err, w_shape, w2_shape, a2_shape, sharded_err = out.get()
     assert col_err == 0.0                                        # column shards are exact slices of the unsharded result
     assert row_err <= 1e-5
+    assert sharded_err <= 2e-3                                   # h is summed over the ranks in another order than one long dot
     assert w_shape == (128, 256) and w2_shape == (192, 256) and a2_shape == (3, 1, 32, 256)
 
 
