@@ -213,6 +213,17 @@ int ob_nvfp4_packed_scale_bytes(int32_t K, int32_t S, const int32_t* widths, siz
 int ob_nvfp4_pack_scales(const void* w_sf_linear, int32_t K, int32_t S, const int32_t* widths, void* packed,
                          size_t packed_bytes, void* cuda_stream);
 
+/* Adapter slot (re)quantization on the device, bit-identical to the reference's torch recipes; used when vLLM writes or
+ * clears an adapter slot (lowbit_lora/kernels/adapter_store.py:63-80, VllmFusedFP8LoRA.requantize
+ * lowbit_lora/kernels/fp8_lora_vllm.py:504-524).  `src` is bf16, rows contiguous, cols a multiple of 8 (16 for NVFP4).
+ *   FP8:   per row scale = max(amax / 448, 1e-12), codes = e4m3(x / scale)            -> codes [rows, cols], scales [rows]
+ *   NVFP4: per matrix m of `l` matrices [rows, cols]: global = 2688 / amax (the reference's two roundings), ue4m3 scale per
+ *          16 elements, packed e2m1 codes  -> packed [l, rows, cols/2], sf [l, rows, cols/16], inv_global [l] = 1 / global
+ *          (lowbit_lora/kernels/nvfp4_lora_vllm.py:379-397).  `amax_scratch` = l * 4 bytes of device memory. */
+int ob_requant_fp8_rows(const void* src, int64_t rows, int32_t cols, void* codes, float* scales, void* cuda_stream);
+int ob_requant_nvfp4(const void* src, int32_t l, int32_t rows, int32_t cols, void* packed, void* sf, float* inv_global,
+                     void* amax_scratch, void* cuda_stream);
+
 /* Token sort + segment index on the device: vLLM's LoRAKernelMeta.prepare_tensors
  * (vllm/lora/ops/triton_ops/lora_kernel_metadata.py:110-168) incl. its stale-on-no-adapter behaviour.
  * token_lora [M] int32 in; the five metadata tensors out (tok/srt of capacity >= M, seg_* of L+1 / L+2 / L+1). */

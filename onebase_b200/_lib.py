@@ -60,6 +60,9 @@ SYMBOLS = {
     "ob_workspace_offsets": (C.c_int, [C.POINTER(ObWorkspaceShape), C.POINTER(C.c_size_t)]),
     "ob_layer_create": (C.c_int, [C.POINTER(ObLayerDesc), C.POINTER(C.c_void_p)]),
     "ob_layer_destroy": (C.c_int, [C.c_void_p]),
+    "ob_requant_fp8_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "ob_requant_nvfp4": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                   C.c_void_p]),
     "ob_resolve_tile": (C.c_int, [C.c_void_p, C.c_int32, C.POINTER(ObTileCfg), C.POINTER(ObTileCfg)]),
     "ob_k1_fp8": (C.c_int, [C.c_void_p, C.POINTER(ObBatch), C.c_void_p, C.POINTER(ObWorkspaceShape), C.POINTER(ObTileCfg),
                             C.c_void_p]),

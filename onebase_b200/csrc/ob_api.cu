@@ -17,6 +17,9 @@ int k2_max_active_clusters(int fp4, int stored, int split2, size_t smem);
 cudaError_t launch_k1_mma(const K1mParams& p, const CUtensorMap& tm_xs, const CUtensorMap* tm_a, dim3 grid, cudaStream_t stream);
 cudaError_t launch_k2_prefill(const K2pParams& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap& tm_h,
                               const CUtensorMap* tm_b, dim3 grid, int pdl, cudaStream_t stream);
+cudaError_t launch_requant_fp8(const void* src, long long rows, int cols, void* codes, float* scales, cudaStream_t stream);
+cudaError_t launch_requant_nvfp4(const void* src, int l, int rows, int cols, void* packed, void* sf, float* inv_global,
+                                 unsigned int* amax_bits, cudaStream_t stream);
 cudaError_t launch_fused(const K2Params& p, const K1Params& k1, const CUtensorMap& tm_w, const CUtensorMap& tm_x,
                          const CUtensorMap* tm_b, dim3 grid, size_t smem, cudaStream_t stream);
 cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream);
@@ -797,6 +800,25 @@ int ob_nvfp4_pack_scales(const void* w_sf_linear, int32_t K, int32_t S, const in
     if (packed_bytes < need) return OB_ERR_WORKSPACE;
     cudaError_t e = launch_pack_scales(static_cast<const uint8_t*>(w_sf_linear), K, S, widths, static_cast<uint8_t*>(packed),
                                        need, static_cast<cudaStream_t>(cuda_stream));
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
+
+int ob_requant_fp8_rows(const void* src, int64_t rows, int32_t cols, void* codes, float* scales, void* cuda_stream) {
+    if (!src || !codes || !scales) return OB_ERR_NULL;
+    if (rows < 1 || rows > 0x7fffffffLL || cols < 8 || cols % 8 != 0) return OB_ERR_SHAPE;
+    if (!aligned16(src) || (reinterpret_cast<uintptr_t>(codes) & 7u)) return OB_ERR_ALIGN;
+    cudaError_t e = launch_requant_fp8(src, rows, cols, codes, scales, static_cast<cudaStream_t>(cuda_stream));
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
+
+int ob_requant_nvfp4(const void* src, int32_t l, int32_t rows, int32_t cols, void* packed, void* sf, float* inv_global,
+                     void* amax_scratch, void* cuda_stream) {
+    if (!src || !packed || !sf || !inv_global || !amax_scratch) return OB_ERR_NULL;
+    if (l < 1 || l > 65535 || rows < 1 || cols < 16 || cols % 16 != 0) return OB_ERR_SHAPE;
+    if (!aligned16(src) || (reinterpret_cast<uintptr_t>(packed) & 7u) || (reinterpret_cast<uintptr_t>(amax_scratch) & 3u))
+        return OB_ERR_ALIGN;
+    cudaError_t e = launch_requant_nvfp4(src, l, rows, cols, packed, sf, inv_global, static_cast<unsigned int*>(amax_scratch),
+                                         static_cast<cudaStream_t>(cuda_stream));
     return e == cudaSuccess ? OB_OK : (int)e;
 }
 

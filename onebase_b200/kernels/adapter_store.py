@@ -9,8 +9,8 @@ lora_a_stacked[s] [L,1,R,K] and lora_b_stacked[s] [L,1,N_s,R] (bf16); the store 
          lowbit_lora/kernels/nvfp4_lora_vllm.py:379-397, exact reciprocals).
 The kernels dequantize these in registers (K1: A; K2: B).  `requantize(index)` refreshes one slot (or all) after vLLM
 writes or clears it; after `release()`, vLLM writes every slot through one staging slot and the copies are the only
-per-slot storage.  The arithmetic is plain torch on the tensors' device (as in the reference: slot writes happen outside
-CUDA graphs).
+per-slot storage.  On the device the copies are made by the library's requantization kernels (one launch per buffer;
+the reference does it with torch ops: slot writes happen outside CUDA graphs); host tensors take the torch recipe.
 """
 from __future__ import annotations
 
@@ -27,7 +27,26 @@ def _c(value: float, like: torch.Tensor) -> torch.Tensor:
     return torch.tensor(value, dtype=torch.float32, device=like.device)
 
 
+def _stream(t: torch.Tensor):
+    import ctypes as C
+    return C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
 def store_rows_fp8(t: torch.Tensor):
+    """t [..., cols] bf16 -> (e4m3 codes of the same shape, fp32 scale per row).  On a CUDA tensor this is one launch of
+    the library's requantization kernel (ob_requant_fp8_rows); the torch lines below are the same arithmetic for host
+    tensors (the CPU tests compare the two through the golden fixtures)."""
+    if t.is_cuda and t.dtype == torch.bfloat16 and t.shape[-1] % 8 == 0:
+        import ctypes as C
+        from onebase_b200 import _lib
+        src = t.contiguous()
+        rows = src.numel() // src.shape[-1]
+        codes = torch.empty(src.shape, dtype=torch.float8_e4m3fn, device=t.device)
+        scale = torch.empty(src.shape[:-1], dtype=torch.float32, device=t.device)
+        with torch.cuda.device(t.device):
+            _lib.call("ob_requant_fp8_rows", C.c_void_p(src.data_ptr()), rows, src.shape[-1], C.c_void_p(codes.data_ptr()),
+                      C.c_void_p(scale.data_ptr()), _stream(t))
+        return codes, scale
     tf = t.float()
     scale = torch.div(tf.abs().amax(-1), _c(FP8_MAX, tf)).clamp_min(1e-12)
     return torch.div(tf, scale[..., None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn), scale
@@ -36,6 +55,18 @@ def store_rows_fp8(t: torch.Tensor):
 def quant_stack_nvfp4(t: torch.Tensor):
     """t [l, rows, cols] -> (packed [l, rows, cols/2] uint8, block scales [l, rows, cols/16] e4m3, inverse globals [l])."""
     l, rows, cols = t.shape
+    if t.is_cuda and t.dtype == torch.bfloat16 and cols % 16 == 0:   # one amax pass + one quantizing pass on the device
+        import ctypes as C
+        from onebase_b200 import _lib
+        src = t.contiguous()
+        packed = torch.empty(l, rows, cols // 2, dtype=torch.uint8, device=t.device)
+        sf = torch.empty(l, rows, cols // 16, dtype=torch.float8_e4m3fn, device=t.device)
+        inv_g = torch.empty(l, dtype=torch.float32, device=t.device)
+        amax = torch.empty(l, dtype=torch.int32, device=t.device)
+        with torch.cuda.device(t.device):
+            _lib.call("ob_requant_nvfp4", C.c_void_p(src.data_ptr()), l, rows, cols, C.c_void_p(packed.data_ptr()),
+                      C.c_void_p(sf.data_ptr()), C.c_void_p(inv_g.data_ptr()), C.c_void_p(amax.data_ptr()), _stream(t))
+        return packed, sf, inv_g
     tf = t.float()
     one = _c(1.0, tf)
     # `scalar / tensor` in torch is reciprocal(tensor) * scalar (two roundings): the reference's global scale is that value
