@@ -258,6 +258,7 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
                                    f"; FP8 base, decode M={M}, 32 bf16 tenants rank 64",
                        "l2": "flushed by a 256 MB write before every timed step",
                        "cuda_graph": f"{len(graphs)} graphs; the NCCL all-reduces are launched between them" if graphed else "no"},
-            "layer_us": ms_v * 1e3, "gpu_launches": 8 * args.steps,   # our kernels: four K1 + four K2 per step "device_status_ok": bool(ok.item()),
+            "layer_us": ms_v * 1e3, "gpu_launches": 8 * args.steps,   # our kernels: four K1 + four K2 per step
+            "device_status_ok": bool(ok.item()),
             "e2e": None, "roofline": None, "cpu_baseline": None}))
     dist.destroy_process_group()
