@@ -101,16 +101,17 @@ def _adapters_ok(layer) -> bool:
 
 
 def _is_fp8_per_tensor(base, qm) -> bool:
-    """The online per-tensor FP8 method (reference: isinstance checks on vLLM's classes, plugin.py:243-248); duck-typed
-    on the quantized tensors so that a vLLM that moved those classes is still recognised."""
+    """A linear layer whose weight vLLM holds as per-tensor e4m3 codes with one fp32 scale and whose activations are
+    quantized dynamically (reference: isinstance checks on vLLM's classes, plugin.py:243-248).  Recognised by the
+    quantized tensors plus the method's class NAME -- vLLM has moved and renamed these classes between releases
+    (`Fp8PerTensorOnlineLinearMethod` under quantization/online, `Fp8OnlineLinearMethod` / `Fp8LinearMethod` in
+    quantization/fp8.py) -- and never for block-quantized weights or a static activation scale."""
     w, ws = getattr(base, "weight", None), getattr(base, "weight_scale", None)
     if w is None or ws is None or w.dtype != torch.float8_e4m3fn or ws.numel() != 1:
         return False
-    try:
-        from vllm.model_executor.layers.quantization.online.fp8 import Fp8PerTensorOnlineLinearMethod
-        return isinstance(qm, Fp8PerTensorOnlineLinearMethod)
-    except Exception:   # noqa: BLE001
-        return qm is not None
+    if qm is None or getattr(qm, "block_quant", False) or getattr(base, "input_scale", None) is not None:
+        return False
+    return type(qm).__name__ in ("Fp8PerTensorOnlineLinearMethod", "Fp8OnlineLinearMethod", "Fp8LinearMethod")
 
 
 def _hook_slot_writes(layer, op) -> None:
