@@ -236,7 +236,7 @@ k2_prefill_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm_w, c
                         const bool ok = lora >= 0 && lora < p.L && lo < hi;
                         const uint32_t mask = __ballot_sync(0xffffffffu, ok);
                         if (ok) {
-                            const int rank = __popc(mask & ((1u << lane) - 1u));   // hits of lower lanes in this round
+                            const int rank = __popc(mask & ((1u << lane) - 1u));   // hits of lower lanes in this ballot
                             const int entry = entries + rank;
                             if (entry < kMaxTileTenants)
                                 for (int c = 0; c < n_chunks; ++c) {
