@@ -11,7 +11,9 @@ the timed events), W >= 3 warm-up replays, max over ranks.  Prints ONE JSON line
 
 `value`   tokens/s through the layer with inputs resident in HBM (M / mean replay time).
 `e2e`     the same through the public op call with HOST buffers: every step copies the four projections' activations from
-          pinned host memory, runs the layer, and copies the four outputs back (copies inside the timed region).
+          pinned host memory, runs the layer, and copies the four outputs back (copies inside the timed region).  The
+          step is one CUDA graph over three streams, so that a projection waits only for its own input and its output
+          goes down while the next projection runs.
 `roofline` for the dominant kernel (K2 of gate_up): algorithmic bytes (W + x + the distinct tenants' B + y) / its
           CUDA-event time when launched alone, against the measured HBM copy bandwidth.
 `cpu_baseline` the CPU oracle (a torch port of the reference's dequantize-and-matmul path) on this host's cores.
@@ -305,13 +307,51 @@ def main() -> None:
     h2d = sum(t.numel() * 2 for t in host_x.values())
     d2h = sum(t.numel() * 2 for t in host_y.values())
 
-    def e2e_step():
+    def e2e_serial():
         for n in PROJECTIONS:
             layer[n][1].copy_(host_x[n], non_blocking=True)
         graph.replay()
         for n in PROJECTIONS:
             host_y[n].copy_(layer[n][2], non_blocking=True)
 
+    def e2e_pipelined_graph():
+        """The same step as one CUDA graph over three streams: the inputs go up on a copy stream, each projection's chain
+        waits only for its own input, and each output goes down on another copy stream while the next chain runs."""
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2):
+            cap = torch.cuda.current_stream()
+            s_in.wait_stream(cap)
+            s_out.wait_stream(cap)
+            arrived = {}
+            with torch.cuda.stream(s_in):
+                for n in PROJECTIONS:
+                    layer[n][1].copy_(host_x[n], non_blocking=True)
+                    arrived[n] = torch.cuda.Event()
+                    arrived[n].record(s_in)
+            for n in PROJECTIONS:
+                op_n, x_n, y_n = layer[n]
+                cap.wait_event(arrived[n])
+                op_n(x_n, meta, out=y_n)
+                done = torch.cuda.Event()
+                done.record(cap)
+                s_out.wait_event(done)
+                with torch.cuda.stream(s_out):
+                    host_y[n].copy_(y_n, non_blocking=True)
+            cap.wait_stream(s_in)
+            cap.wait_stream(s_out)
+        return g2
+
+    e2e_kind = "one CUDA graph over three streams: uploads, the four chains and downloads overlap"
+    try:
+        e2e_step = e2e_pipelined_graph().replay
+        e2e_step()
+        torch.cuda.synchronize()
+        for n in PROJECTIONS:                                  # the pipelined step must deliver the same bytes
+            assert torch.equal(host_y[n], layer[n][2].cpu())
+    except Exception as exc:   # noqa: BLE001 - a driver that cannot capture the multi-stream step: run it serially
+        print(f"[bench] pipelined end-to-end step unavailable ({type(exc).__name__}: {exc}); timing the serial form", file=sys.stderr)
+        e2e_step, e2e_kind = e2e_serial, "serial: uploads, one graph replay, downloads"
     e2e_ms = statistics.fmean(time_events(e2e_step, args.steps, warmup, flush))
     sampler.stop_flag = True
     sampler.join(timeout=2)
@@ -338,7 +378,7 @@ def main() -> None:
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": k2_gbs / peak, "traffic": K2_GATE_UP_TRAFFIC.get(M) if distinct == 23 else None, "bytes": k2_bytes,
                      "us": k2_ms * 1e3, "k1_us_alone": k1_ms * 1e3},
         "e2e": {"value": M / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms},
+                "ms_per_step": e2e_ms, "how": e2e_kind},
         "gpu_launches": 8 * args.steps,
         "clocks": sampler.result(),
     }
