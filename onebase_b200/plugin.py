@@ -283,12 +283,23 @@ def install() -> None:
             y = y + bias
         return y if x.ndim == 2 else y.reshape(*shape[:-1], -1)
 
+    def _stock_allowed(layer) -> None:
+        """vLLM's own path indexes the per-slot bf16 buffers; once a layer serves from the low-precision copies alone those
+        buffers are a single staging slot, and a call the fused path cannot take must fail loudly instead of reading past it."""
+        if layer.__dict__.get("_lowbit_released"):
+            raise RuntimeError("onebase_b200: this layer's bf16 adapter slots were released (LOWBIT_RELEASE_SLOTS) and the call "
+                               "cannot be served by the fused path (input dtype or bias); set LOWBIT_RELEASE_SLOTS=0")
+
     def _apply_sync(self, x, bias=None):
         y = fused_or_none(self, x, bias)
+        if y is None:
+            _stock_allowed(self)
         return y if y is not None else orig_sync(self, x, bias)
 
     def apply(self, x, bias=None):
         y = fused_or_none(self, x, bias)
+        if y is None:
+            _stock_allowed(self)
         return y if y is not None else orig_apply(self, x, bias)
 
     BaseLinearLayerWithLoRA.set_mapping = set_mapping
@@ -302,6 +313,8 @@ def install() -> None:
         def make(orig):
             def apply_override(self, x, bias=None):
                 y = fused_or_none(self, x, bias)
+                if y is None:
+                    _stock_allowed(self)
                 return y if y is not None else orig(self, x, bias)
             return apply_override
 
