@@ -144,7 +144,9 @@ int ob_workspace_bytes(const ObWorkspaceShape* shape, size_t* bytes);
 /* Byte offsets of the workspace regions, for inspection (the reference exposes them as Scratch.xq / .sx / .hp,
  * fp8_lora_vllm.py:321-327): out[0..6] = status words, split-K counters, s_x [max_m] fp32, x_q codes (row pitch = the
  * calling layer's K; rows are adapter-sorted POSITIONS), NVFP4 activation block scales, shrink partials
- * [split1][S][max_m][R] fp32, GEMM split-K partials. */
+ * [split1][S][max_m][R] fp32, GEMM split-K partials.  Behind them the workspace holds regions only the kernels use (for
+ * max_m > 32: an adapter-sorted bf16 copy of x and the tensor-core shrink's finished h; for max_m > 128 and max_l > 0: the
+ * per-tenant h blocks of the large-tile prefill GEMM); ob_workspace_bytes counts them. */
 int ob_workspace_offsets(const ObWorkspaceShape* shape, size_t out[7]);
 
 /* Validate a layer and build its TMA descriptors.  Replaces VllmFusedFP8LoRA.__init__ / VllmFusedNVFP4LoRA.__init__

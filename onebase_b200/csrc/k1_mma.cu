@@ -289,30 +289,42 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
                     const float osc = cat ? inv : 1.0f;
                     const size_t jstride = (size_t)p.S * p.max_m * p.R;
                     const float* src = p.hp + ((size_t)s * p.max_m + (size_t)pos) * p.R;
-                    for (int c0 = 0; c0 < p.R; c0 += 8) {
-                        float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+                    // 32 columns at a time, four splits' loads of all of them in flight together: a plain loop would pay
+                    // one L2 round trip per 8 columns and split
+                    for (int cb = 0; cb < p.R; cb += 32) {
+                        float4 acc[8];
+#pragma unroll
+                        for (int q4 = 0; q4 < 8; ++q4) acc[q4] = make_float4(0.f, 0.f, 0.f, 0.f);
                         for (int j1 = 0; j1 < p.split1; j1 += 4) {
-                            float4 v[4][2];
+                            float4 v[4][8];
 #pragma unroll
                             for (int u = 0; u < 4; ++u) {
-                                if (j1 + u < p.split1) {
-                                    const float4* q4 = reinterpret_cast<const float4*>(src + (size_t)(j1 + u) * jstride + c0);
-                                    v[u][0] = __ldcg(q4);
-                                    v[u][1] = __ldcg(q4 + 1);
-                                } else {
-                                    v[u][0] = v[u][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                                for (int q4 = 0; q4 < 8; ++q4) {
+                                    v[u][q4] = (j1 + u < p.split1 && cb + q4 * 4 < p.R)
+                                                   ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(j1 + u) * jstride + cb) + q4)
+                                                   : make_float4(0.f, 0.f, 0.f, 0.f);
                                 }
                             }
 #pragma unroll
                             for (int u = 0; u < 4; ++u) {
-                                a0.x += v[u][0].x; a0.y += v[u][0].y; a0.z += v[u][0].z; a0.w += v[u][0].w;
-                                a1.x += v[u][1].x; a1.y += v[u][1].y; a1.z += v[u][1].z; a1.w += v[u][1].w;
+#pragma unroll
+                                for (int q4 = 0; q4 < 8; ++q4) {
+                                    acc[q4].x += v[u][q4].x; acc[q4].y += v[u][q4].y; acc[q4].z += v[u][q4].z; acc[q4].w += v[u][q4].w;
+                                }
                             }
                         }
-                        __nv_bfloat162 b0 = __floats2bfloat162_rn(a0.x * osc, a0.y * osc), b1 = __floats2bfloat162_rn(a0.z * osc, a0.w * osc);
-                        __nv_bfloat162 b2 = __floats2bfloat162_rn(a1.x * osc, a1.y * osc), b3 = __floats2bfloat162_rn(a1.z * osc, a1.w * osc);
-                        *reinterpret_cast<uint4*>(odst + c0) = make_uint4(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1),
-                                                                          *reinterpret_cast<uint32_t*>(&b2), *reinterpret_cast<uint32_t*>(&b3));
+#pragma unroll
+                        for (int q8 = 0; q8 < 4; ++q8) {
+                            if (cb + q8 * 8 < p.R) {
+                                const float4 a0 = acc[2 * q8], a1 = acc[2 * q8 + 1];
+                                __nv_bfloat162 b0 = __floats2bfloat162_rn(a0.x * osc, a0.y * osc), b1 = __floats2bfloat162_rn(a0.z * osc, a0.w * osc);
+                                __nv_bfloat162 b2 = __floats2bfloat162_rn(a1.x * osc, a1.y * osc), b3 = __floats2bfloat162_rn(a1.z * osc, a1.w * osc);
+                                *reinterpret_cast<uint4*>(odst + cb + q8 * 8) =
+                                    make_uint4(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1),
+                                               *reinterpret_cast<uint32_t*>(&b2), *reinterpret_cast<uint32_t*>(&b3));
+                            }
+                        }
                     }
                 }
                 if (te == 0) p.counters[blockIdx.x * p.S + s] = 0;
