@@ -1,6 +1,6 @@
 """Sweep the tile choices of the FP8 decode chain on this GPU and write the rows of a tile table.
 
-    python -m onebase_b200.tiles.sweep [--out onebase_b200/tiles/qwen3_8b_fp8.jsonl] [--ms 1,2,4,8,16,32]
+    python -m onebase_b200.tiles.sweep [--base fp8|nvfp4] [--out onebase_b200/tiles/qwen3_8b_<base>.jsonl] [--ms 1,2,4,8,16,32]
 
 For every decode batch size it times one Qwen3-8B decoder layer -- the four projection chains in one CUDA graph, L2
 flushed before each replay, median of the replays -- and walks each projection's choices in turn (GEMM split-K x ring
@@ -70,9 +70,10 @@ def main() -> None:
     tile_table._TABLE = {}                                    # start from the library's own rule, not from the shipped table
     from onebase_b200.metadata import KernelMeta
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default=str(Path(__file__).resolve().parent / "qwen3_8b_fp8.jsonl"))
+    ap.add_argument("--out", default=None, help="default: qwen3_8b_<base>.jsonl next to this file")
     ap.add_argument("--ms", default="1,2,4,8,16,32")
     ap.add_argument("--margin", type=float, default=0.02, help="a choice must shorten the layer by this fraction to be kept")
+    ap.add_argument("--base", default="fp8", choices=["fp8", "nvfp4"], help="base format of the swept layer (the rows' fmt key)")
     args = ap.parse_args()
     dev = torch.device("cuda:0")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -80,11 +81,16 @@ def main() -> None:
     ops = {}
     for name, (K, widths) in PROJECTIONS.items():
         N = sum(widths)
-        w_q = (torch.randn(N, K, device=dev, generator=g) * 0.5).to(torch.float8_e4m3fn)
-        s_w = torch.full((1,), 0.01, device=dev)
         a_st = tuple((torch.randn(L_SLOTS, 1, RANK, K, device=dev, generator=g) / K ** 0.5).to(torch.bfloat16) for _ in widths)
         b_st = tuple((torch.randn(L_SLOTS, 1, n, RANK, device=dev, generator=g) * 0.01).to(torch.bfloat16) for n in widths)
-        ops[name] = VllmFusedFP8LoRA(w_q, s_w, a_st, b_st, max_m=32)
+        if args.base == "fp8":
+            w_q = (torch.randn(N, K, device=dev, generator=g) * 0.5).to(torch.float8_e4m3fn)
+            ops[name] = VllmFusedFP8LoRA(w_q, torch.full((1,), 0.01, device=dev), a_st, b_st, max_m=32)
+        else:   # timing does not depend on the code values: random nibbles, block scales near 1
+            from onebase_b200.kernels.nvfp4_lora_vllm import VllmFusedNVFP4LoRA
+            w_q = torch.randint(0, 256, (N, K // 2), device=dev, generator=g, dtype=torch.uint8)
+            w_sf = torch.randint(0x30, 0x40, (N, K // 16), device=dev, generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn)
+            ops[name] = VllmFusedNVFP4LoRA(w_q, w_sf, 2688.0 / 0.1, 2688.0 / 4.0, a_st, b_st, max_m=32, rcp_approx=True)
     rows = []
     for M in (int(v) for v in args.ms.split(",")):
         ids = torch.randint(0, L_SLOTS, (M,), generator=torch.Generator().manual_seed(M), dtype=torch.int32).to(dev)
@@ -115,12 +121,12 @@ def main() -> None:
                             cfgs, best_us = trial, again
         for name, (K, widths) in PROJECTIONS.items():
             assert ops[name].scratch.status()[0] == 0, ops[name].scratch.status()[:8]
-            row = {"M": M, "N": sum(widths), "K": K, "S": len(widths), "R": RANK, "fmt": "fp8", **cfgs[name],
+            row = {"M": M, "N": sum(widths), "K": K, "S": len(widths), "R": RANK, "fmt": args.base, **cfgs[name],
                    "layer_us": round(best_us, 2), "default_layer_us": round(default_us, 2), "proj": name, "tried": tried,
                    "gpu": torch.cuda.get_device_name(0)}
             rows.append(row)
             print(json.dumps(row), flush=True)
-    Path(args.out).write_text("".join(json.dumps(r) + "\n" for r in rows))
+    Path(args.out or Path(__file__).resolve().parent / f"qwen3_8b_{args.base}.jsonl").write_text("".join(json.dumps(r) + "\n" for r in rows))
 
 
 if __name__ == "__main__":
