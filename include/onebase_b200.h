@@ -131,6 +131,10 @@ typedef struct ObTileCfg {
     int32_t fused;                   /* ob_chain_*: 1 = one kernel for the whole chain where that form applies (bf16
                                       * adapters, at most 32 tokens): every GEMM CTA first takes a share of the
                                       * quantization and of the shrink from work counters in the workspace */
+    int32_t prefill;                 /* batches of more than 32 tokens, bf16 adapters: 0 = library rule (tensor-core shrink
+                                      * from 512 tokens; 256 x 256 GEMM tiles when they fill the GPU), 1 = tensor-core
+                                      * shrink and, where the layer allows, 256 x 256 tiles whatever the size, 2 = the
+                                      * warp-level shrink and 64..128-token tiles */
 } ObTileCfg;
 
 typedef struct ObLayer ObLayer;      /* opaque: validated descriptor + TMA tensor maps (host memory only) */

@@ -49,7 +49,7 @@ class ObWorkspaceShape(C.Structure):
 
 class ObTileCfg(C.Structure):
     _fields_ = [("tn", C.c_int32), ("split2", C.c_int32), ("split1", C.c_int32), ("stages", C.c_int32),
-                ("wait_ms", C.c_int32), ("fused", C.c_int32)]
+                ("wait_ms", C.c_int32), ("fused", C.c_int32), ("prefill", C.c_int32)]
 
 
 # every symbol include/onebase_b200.h declares: name -> (restype, argtypes)

@@ -5,7 +5,8 @@ serving numbers, bench/overhead.py:126-138: random token ids, fixed output lengt
 
 Builds, under a temporary directory, the config of a Qwen3-8B-shaped model (hidden 4096, GQA 32/8, head_dim 128,
 intermediate 12288, vocab 151936; `--layers` of its 36 layers) and ONE random rank-64 adapter file that is registered under
-`--requests` different adapter ids (vLLM gives each id its own slot, so the kernels see that many tenants).  The base
+`--tenants` different adapter ids (default: one per request; vLLM gives each id its own slot, so the kernels see that
+many tenants).  The base
 weights are vLLM's dummy initialisation quantized online to per-tensor FP8 -- throughput does not depend on the values,
 and no checkpoint exists offline.  Prints one JSON line: tokens/s over a timed `generate` (prefill + decode) after a
 warm-up call, and the per-output-token time of the decode phase estimated from two output lengths.
@@ -27,6 +28,7 @@ def main() -> None:
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--out-tokens", type=int, default=128)
     ap.add_argument("--rank", type=int, default=64)
+    ap.add_argument("--tenants", type=int, default=0, help="adapter ids the requests cycle over (default: one per request)")
     ap.add_argument("--eager", action="store_true")
     args = ap.parse_args()
     os.environ.setdefault("VLLM_ENABLE_V1_MULTIPROCESSING", "0")
@@ -64,14 +66,15 @@ def main() -> None:
     from vllm import LLM, SamplingParams
     from vllm.lora.request import LoRARequest
     t0 = time.time()
+    tenants = args.tenants or args.requests
     llm = LLM(model=model_dir, load_format="dummy", quantization="fp8", dtype="bfloat16", enable_lora=True,
-              max_loras=args.requests, max_lora_rank=args.rank, skip_tokenizer_init=True, enforce_eager=args.eager,
+              max_loras=tenants, max_lora_rank=args.rank, skip_tokenizer_init=True, enforce_eager=args.eager,
               gpu_memory_utilization=0.6, max_model_len=args.prompt + args.out_tokens + 16, max_num_seqs=max(args.requests, 8),
               max_num_batched_tokens=8192, seed=0)
     up = time.time() - t0
     gp = torch.Generator().manual_seed(1)
     prompts = [{"prompt_token_ids": torch.randint(3, VOCAB, (args.prompt,), generator=gp).tolist()} for _ in range(args.requests)]
-    reqs = [LoRARequest(f"a{i}", i + 1, lora_dir) for i in range(args.requests)]
+    reqs = [LoRARequest(f"a{i % tenants}", i % tenants + 1, lora_dir) for i in range(args.requests)]
 
     def run(n_out: int) -> float:
         sp = SamplingParams(temperature=0.0, max_tokens=n_out, min_tokens=n_out, ignore_eos=True, detokenize=False)
@@ -86,7 +89,7 @@ def main() -> None:
     short, full = run(args.out_tokens // 4), run(args.out_tokens)
     decode_s = (full - short) / (args.out_tokens - args.out_tokens // 4)     # seconds per decode step of the whole batch
     rep = open(os.environ["LOWBIT_REPORT"]).read().splitlines() if os.path.exists(os.environ["LOWBIT_REPORT"]) else []
-    print(json.dumps({"mode": args.mode, "layers": args.layers, "requests": args.requests, "prompt": args.prompt,
+    print(json.dumps({"mode": args.mode, "layers": args.layers, "requests": args.requests, "tenants": tenants, "prompt": args.prompt,
                       "out_tokens": args.out_tokens, "engine_up_s": round(up, 1), "generate_s": round(full, 3),
                       "tokens_per_s": round(args.requests * args.out_tokens / full, 1),
                       "decode_step_ms": round(decode_s * 1e3, 3), "decode_tokens_per_s": round(args.requests / decode_s, 1),

@@ -205,21 +205,35 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     const int pb = M <= kDecodeTokens ? 1 : 4;
     // Prefill batches of bf16 adapters shrink on the tensor cores (LOWBIT_SHRINK_CUDA_CORES=1 keeps the warp-level form).
     static const bool no_mma = [] { const char* v = std::getenv("LOWBIT_SHRINK_CUDA_CORES"); return v && v[0] == '1'; }();
-    // (not for sharded adapters: their shrink partials are all-reduced between K1 and K2, so they must stay partials)
-    r->mma_shrink = (!no_mma && M > kDecodeTokens && d.lora_fmt == kLoraBf16 && !b_sharded(d)) ? 1 : 0;
+    // (not for sharded adapters: their shrink partials are all-reduced between K1 and K2, so they must stay partials).
+    // From kMmaShrinkTokens on: below it a 128-position tile of a many-tenant batch holds too many tenants for one
+    // accumulator pass (measured at 32 tenants: 60-120 us for the tensor-core form at 64-256 tokens, 35-50 us warp-level).
+    const int pf = cfg ? cfg->prefill : 0;             // 1 / 2 force the tensor-core / warp-level forms
+    r->mma_shrink = (!no_mma && pf != 2 && M > kDecodeTokens && (pf == 1 || M >= kMmaShrinkTokens) &&
+                     d.lora_fmt == kLoraBf16 && !b_sharded(d)) ? 1 : 0;
     // Larger batches go to the 256 x 256 prefill GEMM unless the caller names a token tile (LOWBIT_PREFILL_SMALL_TILES=1
     // keeps k2_gemm.cu's tiles); prepare_call() drops the choice again when the workspace has no room for its h blocks.
     static const bool no_big = [] { const char* v = std::getenv("LOWBIT_PREFILL_SMALL_TILES"); return v && v[0] == '1'; }();
-    r->big = (!no_big && r->mma_shrink && l->big_ok && M > kBigTileMinTokens && !(cfg && cfg->tn)) ? 1 : 0;
+    // ... and unless its 256 x 256 tiles would leave most of the 148 SMs idle (one CTA per SM): then k2_gemm.cu's 128 x 128
+    // tiles, four times as many, are the better fit.
+    const long long big_tiles = (long long)((M + 255) / 256) * (d.N / 256);
+    r->big = (!no_big && r->mma_shrink && l->big_ok && M > kBigTileMinTokens && !(cfg && cfg->tn) &&
+              (pf == 1 || big_tiles >= 120)) ? 1 : 0;
     if (split1 == 0 && r->mma_shrink) {   // one wave of (128-position tile, slice, K split) CTAs, at least 256 elements each
         const int tiles = ((M + 127) / 128) * d.S;
         split1 = 1;
         while (split1 < 16 && tiles * (split1 * 2) <= 148 && d.K / (split1 * 2) >= 256) split1 *= 2;
     }
-    if (split1 == 0) {   // as many K splits as keep the whole shrink in one wave of the GPU's 2 x 148 CTA slots (8 warps each)
+    if (split1 == 0) {
         const long long units = (long long)((M + pb - 1) / pb) * d.S * (d.R / 8);
         split1 = 1;
-        while (split1 < 16 && d.K / (split1 * 2) >= 512 && (units * split1 * 2 + 7) / 8 + M <= 296) split1 *= 2;
+        if (pb == 1)   // decode: as many K splits as keep the whole shrink in one wave of the GPU's 2 x 148 CTA slots (8 warps each)
+            while (split1 < 16 && d.K / (split1 * 2) >= 512 && (units * split1 * 2 + 7) / 8 + M <= 296) split1 *= 2;
+        else {         // four positions per warp: two to three waves of warps measured best (each re-reads A through L2);
+                       // every CTA of K2 adds the partials again, so a projection with many output tiles wants fewer of them
+            const int cap = l->n_tiles > 100 ? 4 : 16;
+            while (split1 < cap && d.K / (split1 * 2) >= 512 && units * split1 * 2 <= 6144) split1 *= 2;
+        }
     }
     if (split1 < 1 || split1 > 32) return OB_ERR_TILE;
     r->split1 = split1;
@@ -720,6 +734,7 @@ int ob_resolve_tile(ObLayer* layer, int32_t M, const ObTileCfg* cfg, ObTileCfg* 
     out->stages = r.stages;
     out->wait_ms = (int32_t)r.wait_ms;
     out->fused = r.fused;
+    out->prefill = r.big ? 1 : r.mma_shrink ? 0 : 2;       // what will run (the workspace may still veto the large tiles)
     return OB_OK;
 }
 

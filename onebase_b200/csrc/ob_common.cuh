@@ -15,6 +15,7 @@ constexpr int kBlockK = 128;         // bytes of K per ring stage row (one 128-b
 constexpr int kMaxLoraIters = 512;   // capacity of a CTA's list of (segment, rank chunk) expand steps
 constexpr int kMaxTileTenants = 128;  // tenants with a position in one 128-position block
 constexpr int kBigTileMinTokens = 128; // larger FP8 batches of bf16 adapters take the 256 x 256 prefill GEMM
+constexpr int kMmaShrinkTokens = 512;   // batches from this size on shrink on the tensor cores (bf16 adapters)
 constexpr int kDecodeTokens = 32;     // batches up to this size take the decode forms (one position per shrink warp)
 constexpr int kCounterSlots = 4096;  // split-K arrival counters in the workspace
 constexpr int kSfSlotBytes = 2048;   // NVFP4: scale factors of 128 rows x one 256-element K slot (4 atoms of 512 bytes)

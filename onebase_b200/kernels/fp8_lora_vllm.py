@@ -179,7 +179,7 @@ class VllmFusedFP8LoRA:
         if cfg:
             c.update(cfg)
         return _lib.ObTileCfg(c.get("tn", 0), c.get("split2", 0), c.get("split1", 0), c.get("stages", 0),
-                              c.get("wait_ms", self.wait_ms), c.get("fused", 0))
+                              c.get("wait_ms", self.wait_ms), c.get("fused", 0), c.get("prefill", 0))
 
     def resolved_tile(self, M: int, cfg: dict | None = None) -> dict:
         """The tile choice a call of M tokens runs with, the library's own rule filled in (ob_resolve_tile)."""

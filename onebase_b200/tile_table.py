@@ -31,7 +31,7 @@ def _load() -> dict:
                 continue
             row = json.loads(line)
             key = (int(row["M"]), int(row["N"]), int(row["K"]), int(row["S"]), int(row["R"]), str(row.get("fmt", "fp8")))
-            table[key] = {k: int(row[k]) for k in ("tn", "split2", "split1", "stages", "fused") if k in row}
+            table[key] = {k: int(row[k]) for k in ("tn", "split2", "split1", "stages", "fused", "prefill") if k in row}
     return table
 
 

@@ -145,6 +145,15 @@ def test_fused_projection_matches_oracle(K, widths, R, L, M, kind):
     y = op(x.cuda(), meta)
     torch.cuda.synchronize()
     _check_status(op)
+    if M > 128:   # also through the tensor-core shrink and the 256 x 256 GEMM tiles, whatever the library's size rule says
+        y_big = op(x.cuda(), meta, cfg={"prefill": 1})
+        y_small = op(x.cuda(), meta, cfg={"prefill": 2})
+        torch.cuda.synchronize()
+        _check_status(op)
+        for other in (y_big, y_small):
+            assert max_err_ratio(other, oracle_y(d, x, eff)) <= TOL
+        y = op(x.cuda(), meta)
+        torch.cuda.synchronize()
     # codes / scales bit-exact (kernel rows are sorted positions)
     rows, _ = oseg.resolve_positions(M, *meta_cpu)
     q_ref, sx_ref = ofp8.quant_per_token(x)
