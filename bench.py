@@ -94,12 +94,26 @@ def physical_index(local: int) -> int:
     return local
 
 
-def make_layer(M: int, device, seed: int = 0, base: str = "fp8", lora_fmt: str = "bf16"):
+def zipf_ids(M: int, seed: int = 0, exponent: float = 1.1) -> torch.Tensor:
+    """Prefill batch of the NVFP4 configuration: the M tokens are split across the 32 tenants in contiguous runs whose
+    sizes follow Zipf(1.1) (tenant of rank i gets a share proportional to 1 / i^1.1), tenants in a seeded random order."""
+    g = torch.Generator().manual_seed(seed)
+    share = 1.0 / torch.arange(1, L_SLOTS + 1, dtype=torch.float64) ** exponent
+    exact = share / share.sum() * M
+    counts = exact.floor().long()
+    order = torch.argsort(exact - counts, descending=True)
+    counts[order[: M - int(counts.sum())]] += 1              # largest remainders take the tokens the floors left over
+    tenants = torch.randperm(L_SLOTS, generator=g)
+    return torch.repeat_interleave(tenants.to(torch.int32), counts)
+
+
+def make_layer(M: int, device, seed: int = 0, base: str = "fp8", lora_fmt: str = "bf16", ids=None):
     """Random-init layer with the configuration's distributions, generated on the device (values do not matter for
     timing; the parity tests use CPU-drawn inputs).  Returns {proj: (op, x, meta)} plus the ids."""
     from onebase_b200.kernels.fp8_lora_vllm import VllmFusedFP8LoRA
     g = torch.Generator(device=device).manual_seed(seed)
-    ids = torch.randint(0, L_SLOTS, (M,), generator=torch.Generator().manual_seed(seed), dtype=torch.int32)
+    if ids is None:
+        ids = torch.randint(0, L_SLOTS, (M,), generator=torch.Generator().manual_seed(seed), dtype=torch.int32)
     from onebase_b200.metadata import KernelMeta
     km = KernelMeta.make(L_SLOTS, M, device)
     km.prepare_tensors(ids.to(device))
@@ -184,6 +198,58 @@ def profile_case(args, dev) -> None:
                       "chain_us": statistics.fmean(chain) * 1e3, "bytes": by}))
 
 
+def format_bytes(M: int, distinct: int, base: str, lora_fmt: str) -> int:
+    """Algorithmic bytes of one layer pass for a base / adapter storage format: W (+ its block scales), x, y and the distinct
+    tenants' A and B with their scales; intermediates excluded."""
+    w_b = 1.0 if base == "fp8" else 0.5625                  # NVFP4: half a byte per code + one scale byte per 16
+    total = 0.0
+    for K, widths in PROJECTIONS.values():
+        N, S = sum(widths), len(widths)
+        n_ab = S * RANK * K + N * RANK                      # adapter elements per tenant
+        if lora_fmt == "bf16":
+            ad = 2.0 * n_ab
+        elif lora_fmt == "fp8":
+            ad = 1.0 * n_ab + 4.0 * (S * RANK + N)          # codes + one fp32 scale per row of A and of B
+        else:
+            ad = 0.5625 * n_ab + 8.0 * S                    # codes + block scales + the two matrices' global scales
+        total += N * K * w_b + M * K * 2 + M * N * 2 + distinct * ad
+    return int(total)
+
+
+def matrix_case(args, dev) -> None:
+    """The configurations' grid, one JSON line per cell: base format x adapter storage x batch size; decode batches draw a
+    tenant per token, prefill batches (more than 64 tokens) split the tokens across the tenants by Zipf(1.1).  Each cell
+    is the four-projection layer as one CUDA graph, L2 flushed before every replay, CUDA events."""
+    peak, kind = measured_peaks()
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    cells = [("fp8", "bf16"), ("nvfp4", "bf16"), ("fp8", "fp8"), ("nvfp4", "fp8"), ("nvfp4", "nvfp4")]
+    sizes = [int(v) for v in args.matrix.split(",")] if args.matrix != "all" else [1, 2, 4, 8, 16, 32, 512, 2048, 8192]
+    for base, lora_fmt in cells:
+        for M in sizes:
+            ids = zipf_ids(M) if M > 64 else None
+            layer, meta, ids = make_layer(M, dev, base=base, lora_fmt=lora_fmt, ids=ids)
+            run_layer(layer, meta)
+            torch.cuda.synchronize()
+            status = [int(layer[n][0].scratch.status()[0]) for n in PROJECTIONS]
+            g = graph_of(lambda: run_layer(layer, meta))
+            steps = 30 if M <= 64 else 10
+            us = statistics.fmean(time_events(g.replay, steps, 3, flush)) * 1e3
+            distinct = int(torch.unique(ids).numel())
+            nbytes = format_bytes(M, distinct, base, lora_fmt)
+            flops = sum(2.0 * M * sum(w) * K for K, w in PROJECTIONS.values())
+            line = {"matrix": True, "base": base, "adapters": lora_fmt, "M": M, "distinct": distinct, "layer_us": round(us, 1),
+                    "tokens_per_s": round(M / us * 1e6), "device_status": status}
+            if M <= 64:
+                line.update({"bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1), "hbm_frac": round(nbytes / us / 1e3 / peak, 3),
+                             "peak_gbs": peak, "peak_kind": kind})
+            else:
+                line.update({"base_gemm_gflop": round(flops / 1e9, 1), "pflops": round(flops / us / 1e9, 3),
+                             "frac_of_nominal": round(flops / us / 1e9 / (4.5 if base == "fp8" else 9.0), 3)})
+            print(json.dumps(line), flush=True)
+            del layer, g
+            torch.cuda.empty_cache()
+
+
 def graph_of(fn) -> "torch.cuda.CUDAGraph":
     """Capture fn's launches in a CUDA graph (replays carry no host launch latency)."""
     side = torch.cuda.Stream()
@@ -246,6 +312,9 @@ def main() -> None:
     ap.add_argument("--tp-form", default="partial", choices=["partial", "sharded"],
                     help="N > 1: row-parallel layers add partial LoRA terms (vLLM's default) or shard the adapters too and "
                          "all-reduce the shrink partials first")
+    ap.add_argument("--matrix", default=None, metavar="SIZES",
+                    help="measure the grid of base formats x adapter storage formats at these batch sizes (comma-separated, "
+                         "or 'all' for 1,2,4,8,16,32,512,2048,8192); one JSON line per cell")
     ap.add_argument("--profile", default=None, metavar="PROJ",
                     help="small profiling case: build only this projection (qkv|o|gate_up|down) and launch K1 and K2 "
                          "separately --steps times each (for ncu captures); prints their mean times")
@@ -267,6 +336,9 @@ def main() -> None:
     torch.cuda.set_device(dev)
     if args.profile:
         profile_case(args, dev)
+        return
+    if args.matrix:
+        matrix_case(args, dev)
         return
     layer, meta, ids = make_layer(M, dev)
     distinct = int(torch.unique(ids).numel())

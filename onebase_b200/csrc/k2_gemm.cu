@@ -53,6 +53,7 @@ struct K2Ctrl {
     uint64_t acc_full;
     uint32_t tmem_base;
     volatile int abort_flag;
+    volatile int b_grant; // stored adapters: expand steps whose ring slot the producer has acquired for warps 4-7 to fill
     int n_steps;          // expand steps of this CTA
     int last_flag;
     int go_flag;          // the epilogue warps' shared continue / stop decision
@@ -297,6 +298,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
         mbar_init(&ctrl->list_ready, 1);
         mbar_init(&ctrl->acc_full, 1);
         ctrl->abort_flag = 0;
+        ctrl->b_grant = 0;
         ctrl->n_steps = 0;
         ctrl->last_flag = 0;
         fence_mbar_init();
@@ -334,47 +336,53 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
             const bool b_by_tma = !STORED;
             int n_steps = 0;
             bool have_list = false, k1_done = false;
+            // Progress beyond the slots issued so far needs K1's x_q: wait for K1, then request the x_q tile of every W slot
+            // issued so far.  (All of those slots are W tiles: the walk hands out no B tile before the list is known.)
+            auto wait_k1 = [&]() -> bool {
+                OB_TRACE(15)
+                griddep_wait();     // the preceding kernel is complete: K1's outputs, or (fused) x and the cleared counters
+                if constexpr (FUSED) {
+                    // The CTAs' epilogue warps count the positions they quantized; those codes are enough to start the
+                    // base GEMM while the shrink units keep running beside it.
+                    const uint64_t t_start = global_timer_ns();
+                    bool ready = false;
+                    for (uint32_t spin = 0;; ++spin) {
+                        if (ld_acquire(p.xq_ready) >= p.M) { ready = true; break; }
+                        if ((spin & 31u) == 31u && global_timer_ns() - t_start > limit_ns) break;
+                    }
+                    if (!ready) { record_timeout(p, ctrl, 15, w.it); return false; }
+                    fence_proxy_async_all();
+                }
+                OB_TRACE(4)
+                k1_done = true;
+                SlotWalk r(lead);
+                while (r.it < w.it) {
+                    const bool rb = r.is_b(n_base, n_steps);
+                    if (!rb) {
+                        const int st = r.it % p.stages;
+                        uint8_t* slot = ring + (size_t)st * stage_bytes;
+                        tma_load_2d(slot + kWTileBytes, &tm_x, &ctrl->full_w[st], (kb0 + r.k) * kBlockK, t0);
+                        if (FP4)
+                            bulk_load(slot + kWTileBytes + tn * kBlockK + kSfSlotBytes,
+                                      p.xsf + ((size_t)m_idx * p.kblocks + (kb0 + r.k)) * p.nblk * kSfSlotBytes,
+                                      (uint32_t)(kSfSlotBytes * p.nblk), &ctrl->full_w[st]);
+                    }
+                    r.advance(rb, n_base, n_steps);
+                }
+                return true;
+            };
             for (;;) {
                 if (ctrl->abort_flag) break;
+                // A full ring of W tiles needs no list: K1's codes first, so that the MMAs start while warps 4-7 still list
+                // the tile's expand steps.
+                if (!k1_done && w.it >= p.stages && w.it <= lead && w.k < n_base && !wait_k1()) break;
                 if (!have_list && w.needs_list(n_base)) {
                     if (!mbar_wait(&ctrl->list_ready, 0, limit_ns)) { record_timeout(p, ctrl, 2, w.it); break; }
                     n_steps = ctrl->n_steps;
                     have_list = true;
                 }
                 const bool finished = w.done(n_base, n_steps);
-                if (!k1_done && (finished || w.it >= p.stages)) {
-                    // The ring is full (or everything is requested): from here on progress needs K1's x_q.  Wait for K1 and
-                    // request the x_q tile of every W slot issued so far.
-                    griddep_wait();     // the preceding kernel is complete: K1's outputs, or (fused) x and the cleared counters
-                    if constexpr (FUSED) {
-                        // The CTAs' epilogue warps count the positions they quantized; those codes are enough to start the
-                        // base GEMM while the shrink units keep running beside it.
-                        const uint64_t t_start = global_timer_ns();
-                        bool ready = false;
-                        for (uint32_t spin = 0;; ++spin) {
-                            if (ld_acquire(p.xq_ready) >= p.M) { ready = true; break; }
-                            if ((spin & 31u) == 31u && global_timer_ns() - t_start > limit_ns) break;
-                        }
-                        if (!ready) { record_timeout(p, ctrl, 15, w.it); break; }
-                        fence_proxy_async_all();
-                    }
-                    OB_TRACE(4)
-                    k1_done = true;
-                    SlotWalk r(lead);
-                    while (r.it < w.it) {
-                        const bool rb = r.is_b(n_base, n_steps);
-                        if (!rb) {
-                            const int st = r.it % p.stages;
-                            uint8_t* slot = ring + (size_t)st * stage_bytes;
-                            tma_load_2d(slot + kWTileBytes, &tm_x, &ctrl->full_w[st], (kb0 + r.k) * kBlockK, t0);
-                            if (FP4)
-                                bulk_load(slot + kWTileBytes + tn * kBlockK + kSfSlotBytes,
-                                          p.xsf + ((size_t)m_idx * p.kblocks + (kb0 + r.k)) * p.nblk * kSfSlotBytes,
-                                          (uint32_t)(kSfSlotBytes * p.nblk), &ctrl->full_w[st]);
-                        }
-                        r.advance(rb, n_base, n_steps);
-                    }
-                }
+                if (!k1_done && (finished || w.it >= p.stages) && !wait_k1()) break;
                 if (finished) break;
                 const int st = w.it % p.stages;
                 const bool isb = w.is_b(n_base, n_steps);
@@ -391,11 +399,17 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                         mbar_arrive_expect_tx(&ctrl->full_b[st], b_bytes);
                         tma_load_2d(ring + (size_t)st * stage_bytes, tmb, &ctrl->full_b[st], e.chunk * p.rc,
                                     e.lora * p.b_rows[s] + (n0_local - p.b_row0[s]));
+                    } else {
+                        // The slot is free (this thread saw its release, in order, like every slot's): hand it to warps
+                        // 4-7 through a count, which -- unlike a barrier phase awaited late -- cannot be mistaken.
+                        __threadfence_block();
+                        ctrl->b_grant = w.li + 1;
                     }
                 } else {
                     mbar_arrive_expect_tx(&ctrl->full_w[st], wx_bytes);
                     tma_load_2d_hint(ring + (size_t)st * stage_bytes, &tm_w, &ctrl->full_w[st], (kb0 + w.k) * kBlockK,
                                      slice_off + n0_local, pol);
+                    if (w.it == 0) { OB_TRACE(2) }
                     uint8_t* slot = ring + (size_t)st * stage_bytes;
                     if (FP4)
                         bulk_load(slot + kWTileBytes + tn * kBlockK, p.wsf + ((size_t)n_idx * p.kblocks + (kb0 + w.k)) * kSfSlotBytes,
@@ -537,12 +551,26 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
     } else if (warp >= 4) {
         // =========================================================== segment index, H tiles, epilogue
         const int te = tid - 128;
+        // The index's loads do not depend on one another: request the sorted rows and the segment starts before the
+        // totals are summed, so that the list costs one memory round trip and not three.
+        for (int i = lane; i <= p.L; i += 32) prefetch_l1(p.meta.seg_start + i);
+        int srt_v[2] = {0, 0};                                // tn <= 256: at most two positions per thread
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int c = te + u * 128;
+            if (c < tn && t0 + c < p.M) srt_v[u] = p.meta.srt[t0 + c];
+        }
         int n_all, n_ad;
         segment_totals(p.meta, p.L, lane, n_all, n_ad);
         n_all = min(n_all, p.M);
-        for (int c = te; c < tn; c += 128) {
-            const int pos = t0 + c;
-            ctrl->rowmap[c] = pos < p.M ? position_row(p.meta, pos, p.M, n_all, n_ad) : -1;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int c = te + u * 128, pos = t0 + c;
+            if (c < tn) {
+                int row = pos < p.M ? pos : -1;
+                if (n_ad > 0 && pos < n_all) row = srt_v[u] < 0 ? 0 : (srt_v[u] > p.M - 1 ? p.M - 1 : srt_v[u]);
+                ctrl->rowmap[c] = row;
+            }
         }
         if (FUSED) {
             for (int c = te; c < 32; c += 128) ctrl->lora_pos[c] = -1;
@@ -677,31 +705,26 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
         constexpr bool stored = STORED;                       // FP8- / NVFP4-stored adapters: these warps produce the B tiles
         if (stored || !small) {
             SlotWalk w(lead);
-            RingBook book;
-            bool in_step = true;                              // te == 0: no wait on the way has run out
             for (int li = 0; li < n_steps; ++li) {
-                uint32_t parity = 0;
-                while (!w.is_b(n_base, n_steps)) {
-                    // W slots in between.  When these warps fill the B slots themselves, one thread follows EVERY slot's
-                    // release like the producer does: a waiter that skipped phases of a slot's barrier could take a
-                    // phase two ahead of the barrier for complete and overwrite a tile that is still in use.
-                    const int kw = book.acquire(w.it, w.it % p.stages, p.stages, false, parity);
-                    if (stored && te == 0 && kw != 0 && in_step && !ctrl->abort_flag &&
-                        !mbar_wait(kw == 2 ? &ctrl->empty_b[w.it % p.stages] : &ctrl->empty[w.it % p.stages], parity, limit_ns)) {
-                        record_timeout(p, ctrl, 14, w.it);
-                        in_step = false;
-                    }
-                    w.advance(false, n_base, n_steps);
-                }
+                while (!w.is_b(n_base, n_steps)) w.advance(false, n_base, n_steps);   // the W slots in between
                 const int st = w.it % p.stages;
-                const int kind = book.acquire(w.it, st, p.stages, true, parity);
                 const int hb = li % nh, hu = li / nh;
                 if (te == 0) {                                    // one thread decides, so that all 128 leave together
-                    int go = (ctrl->abort_flag || !in_step) ? 0 : 1;
-                    if (go && stored && kind != 0 &&
-                        !mbar_wait(kind == 2 ? &ctrl->empty_b[st] : &ctrl->empty[st], parity, limit_ns)) {
-                        record_timeout(p, ctrl, 14, w.it);
-                        go = 0;
+                    int go = ctrl->abort_flag ? 0 : 1;
+                    if (go && stored) {
+                        // Wait until the producer has acquired this step's slot.  (These warps start late -- after K1's
+                        // partials -- while the ring runs ahead; a wait of their own on the slot's release barrier could
+                        // meet a phase two ahead of the awaited one and never return.)
+                        const uint64_t t_start = global_timer_ns();
+                        for (uint32_t spin = 0; ctrl->b_grant <= li; ++spin) {
+                            if (ctrl->abort_flag) { go = 0; break; }
+                            if ((spin & 63u) == 63u && global_timer_ns() - t_start > limit_ns) {
+                                record_timeout(p, ctrl, 14, w.it);
+                                go = 0;
+                                break;
+                            }
+                        }
+                        __threadfence_block();
                     }
                     if (go && !small && hu > 0 && !mbar_wait(&ctrl->h_empty[hb], (uint32_t)((hu - 1) & 1), limit_ns)) {
                         record_timeout(p, ctrl, 10, li);

@@ -66,6 +66,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint64
     }
 }
 
+// Request the cache line of a global address without waiting for it.
+__device__ __forceinline__ void prefetch_l1(const void* gptr) {
+    asm volatile("prefetch.global.L1 [%0];" ::"l"(gptr));
+}
+
 // ------------------------------------------------------------------------------------------------- TMA
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

@@ -265,6 +265,28 @@ def test_stored_adapter_formats_golden(golden, fmt):
         assert float((y.float().cpu() - want_y).norm() / want_y.norm()) < 1e-2
 
 
+@pytest.mark.parametrize("fmt", ["fp8", "nvfp4"])
+@pytest.mark.parametrize("M", [1, 24])
+def test_stored_adapters_any_ring_depth_long_k(fmt, M):
+    """Stored adapters with a long K and few expand steps: the weight ring runs many slots ahead of the warps that
+    dequantize the B tiles, whatever the ring depth (3 and 5 slots included) and the K split."""
+    d = _case(4096, (256, 128), 32, 4, M, seed=31, ids_low=0)
+    op = build_fp8_op(d, max_m=32, lora_fp8=fmt == "fp8", lora_fp4=fmt == "nvfp4")
+    op.wait_ms = 200
+    idx = make_index(d["ids"], 4, 32)
+    meta = device_meta(idx, M)
+    x = d["x"].cuda()
+    ref = op(x, meta, cfg={"split2": 1, "stages": 4}).clone()
+    torch.cuda.synchronize()
+    _check_status(op)
+    for split2 in (1, 2, 4):
+        for stages in (2, 3, 5, 6):
+            y = op(x, meta, cfg={"split2": split2, "stages": stages})
+            torch.cuda.synchronize()
+            _check_status(op)
+            assert max_err_ratio(y, ref.float().cpu()) <= 8e-3, (fmt, M, split2, stages)   # one bf16 ulp: the K split moves the fp32 sum
+
+
 def test_released_slots_serve_from_the_copies_alone():
     """After release(), vLLM writes every adapter through one staging slot and requantize(index) files it under its slot
     (reference: tests/test_release_slots.py): the outputs equal those of the fully populated bf16 slots' copies."""
