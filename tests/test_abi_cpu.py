@@ -138,3 +138,22 @@ def test_tile_table_lookup_and_fallback(tmp_path, monkeypatch):
     assert tile_table.tile_for(32, 999, 512, 1, 16, "fp8") == {}
     monkeypatch.delenv("LOWBIT_PDL_CFG")
     tile_table.reload()
+
+
+def test_bench_workload_helpers():
+    """The bench's host-side arithmetic: the Zipf(1.1) prefill split covers every token and every tenant in contiguous
+    runs, and the per-format algorithmic bytes agree with the per-projection table the main line reports."""
+    import bench
+    for M in (512, 2048, 8192):
+        ids = bench.zipf_ids(M, seed=1)
+        assert ids.numel() == M and ids.dtype == torch.int32
+        counts = torch.bincount(ids.long(), minlength=bench.L_SLOTS)
+        assert int(counts.min()) >= 1 and int(counts.sum()) == M
+        top = counts.sort(descending=True).values.double()
+        assert abs(float(top[0] / top[1]) - 2 ** 1.1) < 0.15            # sizes follow 1 / rank^1.1
+        assert int((ids[1:] != ids[:-1]).sum()) == bench.L_SLOTS - 1    # one contiguous run per tenant
+    fp8_bf16 = bench.format_bytes(32, 23, "fp8", "bf16")
+    assert fp8_bf16 == sum(v["total"] for v in bench.layer_bytes(32, 23).values())
+    w_fp8 = sum(sum(w) * K for K, w in bench.PROJECTIONS.values())
+    assert fp8_bf16 - bench.format_bytes(32, 23, "nvfp4", "bf16") == int(w_fp8 * (1 - 0.5625))
+    assert bench.format_bytes(32, 23, "fp8", "nvfp4") < bench.format_bytes(32, 23, "fp8", "fp8") < fp8_bf16
