@@ -158,48 +158,62 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&b);
 }
 
-// Expand step e's B tile [128 rows x rank chunk] from a stored-format adapter into a ring slot, dequantized in
-// registers to bf16 with the scales folded in (one rounding), in the UMMA layout: thread `te` owns output row
-// n0_local + te.  FP8-stored: bf16(code * sb[l, n]); NVFP4-stored: bf16(e2m1 * block scale * bg[s, l])
-// (lowbit_lora/kernels/fp8_lora_vllm.py:249-278).  Rows past the slice's width are zero.
-__device__ __forceinline__ void fill_b_tile(const K2Params& p, const LoraStep& e, int s, int n_s, int n0_local, uint8_t* tile,
-                                            int te, int row_bytes, uint32_t swz) {
+// Expand step e's B tile [128 rows x rank chunk] from a stored-format adapter, in two halves so that a step's codes can
+// be requested one step ahead: load_b_codes() fetches thread `te`'s row of codes and scales (output row n0_local + te) into
+// registers, store_b_tile() dequantizes them to bf16 with the scales folded in (one rounding) into the ring slot in the
+// UMMA layout.  FP8-stored: bf16(code * sb[l, n]); NVFP4-stored: bf16(e2m1 * block scale * bg[s, l])
+// (lowbit_lora/kernels/fp8_lora_vllm.py:249-278).  Rows past the slice's width are zero.  The rank chunk is at most 64:
+// four groups of 16 codes.
+struct BCodes {
+    uint4 c[4];     // FP8: 16 codes each; NVFP4: .x/.y = 16 codes, .z = the block's scale byte
+    float sc;       // FP8: the row's scale; NVFP4: the matrix's global scale
+};
+
+__device__ __forceinline__ void load_b_codes(const K2Params& p, const LoraStep& e, int s, int n_s, int n0_local, int te, BCodes& r) {
     const int n = n0_local + te;
     const bool ok = n < n_s;
     const size_t row = (size_t)e.lora * n_s + (size_t)(ok ? n : 0);
-    const uint32_t row_off = (uint32_t)te * (uint32_t)row_bytes;
+    const int groups = p.rc / 16;
     if (p.lora_fmt == kLoraFp8) {
         const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.b[s]) + row * p.R + (size_t)e.chunk * p.rc);
-        const float sc = ok ? __ldg(static_cast<const float*>(p.sb[s]) + row) : 0.0f;
-        for (int g = 0; g < p.rc / 16; ++g) {                  // 16 codes -> two 16-byte chunks of bf16
-            const uint4 c = ok ? __ldg(src + g) : make_uint4(0u, 0u, 0u, 0u);
-            const uint32_t w[4] = {c.x, c.y, c.z, c.w};
-            uint32_t o[8];
+        r.sc = ok ? __ldg(static_cast<const float*>(p.sb[s]) + row) : 0.0f;
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                o[2 * q] = pack_bf16x2(k2_e4m3_value(w[q] & 0xFFu) * sc, k2_e4m3_value((w[q] >> 8) & 0xFFu) * sc);
-                o[2 * q + 1] = pack_bf16x2(k2_e4m3_value((w[q] >> 16) & 0xFFu) * sc, k2_e4m3_value(w[q] >> 24) * sc);
-            }
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                uint32_t off = row_off + (uint32_t)(2 * g + h) * 16u;
-                off ^= ((off >> 7) & swz) << 4;
-                *reinterpret_cast<uint4*>(tile + off) = make_uint4(o[4 * h], o[4 * h + 1], o[4 * h + 2], o[4 * h + 3]);
-            }
-        }
+        for (int g = 0; g < 4; ++g) r.c[g] = (ok && g < groups) ? __ldg(src + g) : make_uint4(0u, 0u, 0u, 0u);
     } else {
         const uint2* src = reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(p.b[s]) + (row * p.R + (size_t)e.chunk * p.rc) / 2);
         const uint8_t* sfp = static_cast<const uint8_t*>(p.sb[s]) + row * (p.R / 16) + (size_t)e.chunk * p.rc / 16;
-        const float bg = __ldg(p.bg + (size_t)s * p.L + e.lora);
-        for (int g = 0; g < p.rc / 16; ++g) {                  // one block of 16 codes (8 bytes) + its scale
-            const uint2 c = ok ? __ldg(src + g) : make_uint2(0u, 0u);
-            const float sf = ok ? k2_e4m3_value(__ldg(sfp + g)) : 0.0f;
-            const uint32_t w[2] = {c.x, c.y};
-            uint32_t o[8];
+        r.sc = __ldg(p.bg + (size_t)s * p.L + e.lora);
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-                const uint32_t b8 = (w[q >> 2] >> (8 * (q & 3))) & 0xFFu;      // two codes: element 2q in the low nibble
-                o[q] = pack_bf16x2(k2_e2m1_value(b8 & 15u) * sf * bg, k2_e2m1_value(b8 >> 4) * sf * bg);
+        for (int g = 0; g < 4; ++g) {
+            const bool in = ok && g < groups;
+            const uint2 c = in ? __ldg(src + g) : make_uint2(0u, 0u);
+            r.c[g] = make_uint4(c.x, c.y, in ? (uint32_t)__ldg(sfp + g) : 0u, 0u);
+        }
+    }
+}
+
+__device__ __forceinline__ void store_b_tile(const K2Params& p, const BCodes& r, uint8_t* tile, int te, int row_bytes, uint32_t swz) {
+    const uint32_t row_off = (uint32_t)te * (uint32_t)row_bytes;
+    const int groups = p.rc / 16;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        if (g < groups) {
+            uint32_t o[8];
+            if (p.lora_fmt == kLoraFp8) {                      // 16 codes -> two 16-byte chunks of bf16
+                const uint32_t w[4] = {r.c[g].x, r.c[g].y, r.c[g].z, r.c[g].w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    o[2 * q] = pack_bf16x2(k2_e4m3_value(w[q] & 0xFFu) * r.sc, k2_e4m3_value((w[q] >> 8) & 0xFFu) * r.sc);
+                    o[2 * q + 1] = pack_bf16x2(k2_e4m3_value((w[q] >> 16) & 0xFFu) * r.sc, k2_e4m3_value(w[q] >> 24) * r.sc);
+                }
+            } else {                                           // one block of 16 codes (8 bytes) + its scale
+                const float sf = k2_e4m3_value(r.c[g].z);      // (0 for rows past the slice's width: their codes are 0 too)
+                const uint32_t w[2] = {r.c[g].x, r.c[g].y};
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    const uint32_t b8 = (w[q >> 2] >> (8 * (q & 3))) & 0xFFu;      // two codes: element 2q in the low nibble
+                    o[q] = pack_bf16x2(k2_e2m1_value(b8 & 15u) * sf * r.sc, k2_e2m1_value(b8 >> 4) * sf * r.sc);
+                }
             }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -705,6 +719,8 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
         constexpr bool stored = STORED;                       // FP8- / NVFP4-stored adapters: these warps produce the B tiles
         if (stored || !small) {
             SlotWalk w(lead);
+            BCodes cur;                                       // stored adapters: this step's codes, requested a step ahead
+            if (STORED && n_steps > 0) load_b_codes(p, ctrl->steps[0], s, n_s, n0_local, te, cur);
             for (int li = 0; li < n_steps; ++li) {
                 while (!w.is_b(n_base, n_steps)) w.advance(false, n_base, n_steps);   // the W slots in between
                 const int st = w.it % p.stages;
@@ -735,7 +751,12 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (!ctrl->go_flag) break;
                 const LoraStep e = ctrl->steps[li];
-                if constexpr (STORED) fill_b_tile(p, e, s, n_s, n0_local, ring + (size_t)st * stage_bytes, te, row_bytes, swz);
+                if constexpr (STORED) {
+                    BCodes nxt = cur;
+                    if (li + 1 < n_steps) load_b_codes(p, ctrl->steps[li + 1], s, n_s, n0_local, te, nxt);   // in flight during the stores
+                    store_b_tile(p, cur, ring + (size_t)st * stage_bytes, te, row_bytes, swz);
+                    cur = nxt;
+                }
                 if (!small) {
                 uint8_t* hdst = hbuf + (size_t)hb * h_bytes;
                 for (int ch = te; ch < tn * cpr; ch += 128) {
