@@ -173,9 +173,9 @@ class VllmFusedFP8LoRA:
 
     # ------------------------------------------------------------------------------------------------- tile choice
     def tile(self, M: int, cfg: dict | None = None) -> _lib.ObTileCfg:
-        # the table's rows were swept with bf16 adapters; stored adapters run the library's own rule
-        stored = self.lora_fp8 or self.lora_fp4
-        c = {} if stored else dict(tile_for(_bucket(M), self.N, self.K, self.S, self.R, self._FMT))
+        # rows are keyed by the adapters' storage too: one swept with bf16 adapters is not applied to stored ones
+        adapters = "nvfp4" if self.lora_fp4 else "fp8" if self.lora_fp8 else "bf16"
+        c = dict(tile_for(_bucket(M), self.N, self.K, self.S, self.R, self._FMT, adapters))
         if self.split_k:
             c["split1"] = self.split_k
         if cfg:

@@ -1,6 +1,6 @@
 """Sweep the tile choices of the FP8 decode chain on this GPU and write the rows of a tile table.
 
-    python -m onebase_b200.tiles.sweep [--base fp8|nvfp4] [--out onebase_b200/tiles/qwen3_8b_<base>.jsonl] [--ms 1,2,4,8,16,32]
+    python -m onebase_b200.tiles.sweep [--base fp8|nvfp4] [--adapters bf16|fp8|nvfp4] [--out onebase_b200/tiles/qwen3_8b_<base>.jsonl] [--ms 1,2,4,8,16,32]
 
 For every decode batch size it times one Qwen3-8B decoder layer -- the four projection chains in one CUDA graph, L2
 flushed before each replay, median of the replays -- and walks each projection's choices in turn (GEMM split-K x ring
@@ -74,6 +74,8 @@ def main() -> None:
     ap.add_argument("--ms", default="1,2,4,8,16,32")
     ap.add_argument("--margin", type=float, default=0.02, help="a choice must shorten the layer by this fraction to be kept")
     ap.add_argument("--base", default="fp8", choices=["fp8", "nvfp4"], help="base format of the swept layer (the rows' fmt key)")
+    ap.add_argument("--adapters", default="bf16", choices=["bf16", "fp8", "nvfp4"],
+                    help="storage format of the adapters (the rows' adapters key; bf16 rows carry none)")
     args = ap.parse_args()
     dev = torch.device("cuda:0")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -85,12 +87,14 @@ def main() -> None:
         b_st = tuple((torch.randn(L_SLOTS, 1, n, RANK, device=dev, generator=g) * 0.01).to(torch.bfloat16) for n in widths)
         if args.base == "fp8":
             w_q = (torch.randn(N, K, device=dev, generator=g) * 0.5).to(torch.float8_e4m3fn)
-            ops[name] = VllmFusedFP8LoRA(w_q, torch.full((1,), 0.01, device=dev), a_st, b_st, max_m=32)
+            ops[name] = VllmFusedFP8LoRA(w_q, torch.full((1,), 0.01, device=dev), a_st, b_st, max_m=32,
+                                         lora_fp8=args.adapters == "fp8", lora_fp4=args.adapters == "nvfp4")
         else:   # timing does not depend on the code values: random nibbles, block scales near 1
             from onebase_b200.kernels.nvfp4_lora_vllm import VllmFusedNVFP4LoRA
             w_q = torch.randint(0, 256, (N, K // 2), device=dev, generator=g, dtype=torch.uint8)
             w_sf = torch.randint(0x30, 0x40, (N, K // 16), device=dev, generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn)
-            ops[name] = VllmFusedNVFP4LoRA(w_q, w_sf, 2688.0 / 0.1, 2688.0 / 4.0, a_st, b_st, max_m=32, rcp_approx=True)
+            ops[name] = VllmFusedNVFP4LoRA(w_q, w_sf, 2688.0 / 0.1, 2688.0 / 4.0, a_st, b_st, max_m=32, rcp_approx=True,
+                                           lora_fmt=args.adapters)
     rows = []
     for M in (int(v) for v in args.ms.split(",")):
         ids = torch.randint(0, L_SLOTS, (M,), generator=torch.Generator().manual_seed(M), dtype=torch.int32).to(dev)
@@ -121,12 +125,14 @@ def main() -> None:
                             cfgs, best_us = trial, again
         for name, (K, widths) in PROJECTIONS.items():
             assert ops[name].scratch.status()[0] == 0, ops[name].scratch.status()[:8]
-            row = {"M": M, "N": sum(widths), "K": K, "S": len(widths), "R": RANK, "fmt": args.base, **cfgs[name],
+            row = {"M": M, "N": sum(widths), "K": K, "S": len(widths), "R": RANK, "fmt": args.base,
+                   **({} if args.adapters == "bf16" else {"adapters": args.adapters}), **cfgs[name],
                    "layer_us": round(best_us, 2), "default_layer_us": round(default_us, 2), "proj": name, "tried": tried,
                    "gpu": torch.cuda.get_device_name(0)}
             rows.append(row)
             print(json.dumps(row), flush=True)
-    Path(args.out or Path(__file__).resolve().parent / f"qwen3_8b_{args.base}.jsonl").write_text("".join(json.dumps(r) + "\n" for r in rows))
+    suffix = "" if args.adapters == "bf16" else f"_{args.adapters}_adapters"
+    Path(args.out or Path(__file__).resolve().parent / f"qwen3_8b_{args.base}{suffix}.jsonl").write_text("".join(json.dumps(r) + "\n" for r in rows))
 
 
 if __name__ == "__main__":

@@ -128,7 +128,8 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
 def test_tile_table_lookup_and_fallback(tmp_path, monkeypatch):
     from onebase_b200 import tile_table
     f = tmp_path / "extra.jsonl"
-    f.write_text('{"M": 32, "N": 1000, "K": 512, "S": 1, "R": 16, "fmt": "fp8", "tn": 32, "split2": 3, "split1": 2, "stages": 4}\n')
+    f.write_text('{"M": 32, "N": 1000, "K": 512, "S": 1, "R": 16, "fmt": "fp8", "tn": 32, "split2": 3, "split1": 2, "stages": 4}\n'
+                 '{"M": 32, "N": 1000, "K": 512, "S": 1, "R": 16, "fmt": "fp8", "adapters": "nvfp4", "split2": 2}\n')
     monkeypatch.setenv("LOWBIT_PDL_CFG", str(f))
     tile_table.reload()
     assert tile_table.tile_for(32, 1000, 512, 1, 16, "fp8") == {"tn": 32, "split2": 3, "split1": 2, "stages": 4}
@@ -136,6 +137,10 @@ def test_tile_table_lookup_and_fallback(tmp_path, monkeypatch):
     assert near == {"split2": 3, "split1": 2, "stages": 4}
     assert tile_table.tile_for(2048, 1000, 512, 1, 16, "fp8") == {}   # a decode row says nothing about a prefill batch
     assert tile_table.tile_for(32, 999, 512, 1, 16, "fp8") == {}
+    # rows are per adapter storage: a bf16-adapter row is not applied to stored adapters, nor the other way round
+    assert tile_table.tile_for(32, 1000, 512, 1, 16, "fp8", "fp8") == {}
+    assert tile_table.tile_for(32, 1000, 512, 1, 16, "fp8", "nvfp4") == {"split2": 2}
+    assert tile_table.tile_for(16, 1000, 512, 1, 16, "fp8", "nvfp4") == {"split2": 2}
     monkeypatch.delenv("LOWBIT_PDL_CFG")
     tile_table.reload()
 
