@@ -21,6 +21,9 @@ Switches (environment, read at install / layer build; same names and meaning as 
   LOWBIT_COMPILE_CACHE=0  disable vLLM's compile cache instead of keying it
   LOWBIT_LORA_FP8=1 / LOWBIT_LORA_FP4=1   serve the adapters FP8-stored (e4m3, per-row scales) / NVFP4-stored from low-precision
                           copies refreshed on every slot write; LOWBIT_RELEASE_SLOTS=0 keeps vLLM's bf16 slots as well
+  LOWBIT_SEGMENT_INDEX=1  (not in the reference) build vLLM's per-step token sort / segment index with the ob_segment_index
+                          kernel instead of torch sort / unique / cumsum (LoRAKernelMeta.prepare_tensors): one launch and
+                          one small copy to the host per step
   LOWBIT_DISPATCH*, LOWBIT_HYBRIDQ, LOWBIT_LEAN_BASE, LOWBIT_TUNE_MAX_M   accepted and ignored: there is no timed
                           dispatch; tiles come from the table.
 """
@@ -45,6 +48,50 @@ def _report(line: str) -> None:
     if rep:
         with open(rep, "a") as fh:
             fh.write(f"{os.getpid()} {line}\n")
+
+
+def _device_segment_index(meta, token_lora_mapping: torch.Tensor, max_loras: int) -> None:
+    """Fill the five metadata tensors of a vLLM LoRAKernelMeta with one launch of the segment index kernel."""
+    import ctypes as C
+
+    from onebase_b200 import _lib
+    t = token_lora_mapping
+    p = lambda x: C.c_void_p(x.data_ptr())   # noqa: E731
+    _lib.call("ob_segment_index", p(t), t.numel(), max_loras, p(meta.token_lora_mapping),
+              p(meta.token_indices_sorted_by_lora_ids), p(meta.num_tokens_per_lora), p(meta.lora_token_start_loc),
+              p(meta.active_lora_ids), C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream))
+
+
+def segment_index_prepare(orig, index_fn=None):
+    """A replacement for vLLM's `LoRAKernelMeta.prepare_tensors` (vllm/lora/ops/triton_ops/lora_kernel_metadata.py:110-168)
+    that leaves the same five tensors, bit for bit and with the same statefulness (an all -1 batch resets the segment arrays
+    and keeps the token map and sorted indices), through `index_fn(meta, mapping, max_loras)` -- the ob_segment_index kernel
+    unless a test passes its own -- and then sets the host-side flags vLLM's own LoRA ops and its CUDA-graph dispatch read
+    (`no_lora_flag_cpu`, `num_active_loras_cpu` rounded up to a captured count) from ONE copy of the per-segment token
+    counts.  Inputs the kernel does not take (not int32 / not contiguous / not on a GPU / more than 256 slots) go to `orig`."""
+    import bisect
+
+    def prepare_tensors(self, token_lora_mapping: torch.Tensor) -> None:
+        t = token_lora_mapping
+        max_loras = self.active_lora_ids.numel() - 1
+        fits = (t.dtype == torch.int32 and t.is_contiguous() and t.ndim == 1 and 0 < max_loras <= 256 and
+                t.numel() <= self.token_lora_mapping.numel())
+        if not fits or (index_fn is None and not t.is_cuda):
+            return orig(self, t)
+        (index_fn or _device_segment_index)(self, t, max_loras)
+        counts = self.num_tokens_per_lora.cpu()                 # the step's only device -> host copy (it synchronizes)
+        groups = int((counts > 0).sum())                        # unique ids of the batch, the "-1" group included
+        if hasattr(self, "no_lora_flag_cpu"):
+            self.no_lora_flag_cpu[0] = groups == 0              # the kernel leaves every count 0 for an all -1 batch
+        if hasattr(self, "num_active_loras_cpu"):
+            captured = getattr(self, "captured_lora_counts", None)
+            if captured and groups > 0:
+                i = bisect.bisect_left(captured, groups)
+                if i < len(captured):
+                    groups = captured[i]
+            self.num_active_loras_cpu[0] = groups
+
+    return prepare_tensors
 
 
 def _cache_root() -> str:
@@ -245,6 +292,14 @@ def install() -> None:
         ModelOptNvFp4LinearMethod.process_weights_after_loading = nvfp4_process
     except Exception:   # noqa: BLE001
         pass
+
+    if _on("LOWBIT_SEGMENT_INDEX"):
+        try:
+            from vllm.lora.ops.triton_ops.lora_kernel_metadata import LoRAKernelMeta
+            LoRAKernelMeta.prepare_tensors = segment_index_prepare(LoRAKernelMeta.prepare_tensors)
+            _report("segment-index kernel installed in LoRAKernelMeta.prepare_tensors")
+        except Exception as e:   # noqa: BLE001 - vLLM keeps its own metadata code
+            _report(f"segment-index kernel not installed: {type(e).__name__}")
 
     direct_register_custom_op(op_name="lowbit_fused_fp8_lora", op_func=_fused, mutates_args=[], fake_impl=_fused_fake)
     fused_op = torch.ops.vllm.lowbit_fused_fp8_lora

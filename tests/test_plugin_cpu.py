@@ -136,3 +136,50 @@ def test_install_patches_and_routes_calls(plugin, monkeypatch, tmp_path):
                 elif k in c.__dict__:
                     delattr(c, k)
         monkeypatch.setattr(P, "_INSTALLED", False)
+
+
+def test_segment_index_hook_matches_vllm_metadata():
+    """LOWBIT_SEGMENT_INDEX: the replacement for LoRAKernelMeta.prepare_tensors leaves vLLM's own tensors and host flags,
+    over a sequence of batches on the SAME object (stale state included).  The kernel is stood in for by the CPU oracle
+    of the segment index (the GPU tests hold the kernel to that oracle bit for bit)."""
+    meta_mod = pytest.importorskip("vllm.lora.ops.triton_ops.lora_kernel_metadata")
+    from onebase_b200.plugin import segment_index_prepare
+    from oracle import segments as oseg
+    L, max_m = 6, 48
+    captured = [1, 2, 4, 7]
+
+    def index_fn(meta, t, max_loras):
+        assert max_loras == L
+        idx = oseg.SegmentIndex(L, max_m)
+        idx.tok.copy_(meta.token_lora_mapping)
+        idx.srt.copy_(meta.token_indices_sorted_by_lora_ids)
+        idx.prepare(t)
+        meta.token_lora_mapping.copy_(idx.tok)
+        meta.token_indices_sorted_by_lora_ids.copy_(idx.srt)
+        meta.num_tokens_per_lora.copy_(idx.seg_n)
+        meta.lora_token_start_loc.copy_(idx.seg_start)
+        meta.active_lora_ids.copy_(idx.seg_ids)
+
+    stock = meta_mod.LoRAKernelMeta.make(L, max_m, "cpu", captured_lora_counts=captured)
+    ours = meta_mod.LoRAKernelMeta.make(L, max_m, "cpu", captured_lora_counts=captured)
+    for m in (stock, ours):                                    # vLLM allocates these with torch.empty
+        m.token_lora_mapping.zero_()
+        m.token_indices_sorted_by_lora_ids.zero_()
+    hooked = segment_index_prepare(meta_mod.LoRAKernelMeta.prepare_tensors, index_fn=index_fn)
+    g = torch.Generator().manual_seed(5)
+    batches = [torch.randint(-1, L, (40,), generator=g, dtype=torch.int32), torch.full((17,), -1, dtype=torch.int32),
+               torch.full((9,), 3, dtype=torch.int32), torch.randint(0, 2, (48,), generator=g, dtype=torch.int32),
+               torch.tensor([5, -1, 5, 0], dtype=torch.int32), torch.full((3,), -1, dtype=torch.int32),
+               torch.arange(48, dtype=torch.int32) % L]
+    for t in batches:
+        stock.prepare_tensors(t)
+        hooked(ours, t)
+        n = t.numel()
+        for spec in (False, True):
+            a, b = stock.meta_args(n, spec), ours.meta_args(n, spec)
+            for x, y in zip(a, b):
+                assert torch.equal(x, y), (t.tolist(), spec)
+    # inputs the kernel does not take go to vLLM's own code
+    hooked(ours, batches[0].to(torch.int64))
+    stock.prepare_tensors(batches[0].to(torch.int64))
+    assert all(torch.equal(x, y) for x, y in zip(stock.meta_args(40, True), ours.meta_args(40, True)))
