@@ -63,6 +63,28 @@ def shard_row_sharded_lora(w_q, a_stacked, b_stacked, tp: int, rank: int):
     return w_r, a_r, tuple(b_r), b_shard
 
 
+def shard_column_nvfp4(w_q4, w_sf, a_stacked, b_stacked, tp: int, rank: int, replicate=()):
+    """Column-parallel shard of an NVFP4 base (the reference's plugin refuses NVFP4 under tensor parallelism,
+    lowbit_lora/plugin.py:199): the rank's rows of the packed codes [N, K/2] and of the linear block scales [N, K/16]; the
+    two global scales are per tensor and stay.  Returns (w_q4, w_sf, a_stacked, b_stacked)."""
+    q_r, a_r, b_r = shard_column(w_q4, a_stacked, b_stacked, tp, rank, replicate)
+    sf_r, _, _ = shard_column(w_sf.view(torch.uint8), a_stacked, b_stacked, tp, rank, replicate)
+    return q_r, sf_r.view(w_sf.dtype), a_r, b_r
+
+
+def shard_row_nvfp4(w_q4, w_sf, a_stacked, b_stacked, tp: int, rank: int):
+    """Row-parallel shard of an NVFP4 base: K elements [rank * K/tp, (rank + 1) * K/tp) are columns [lo/2, hi/2) of the
+    packed codes and [lo/16, hi/16) of the block scales (K/tp must be a multiple of 32: whole scale blocks, and code rows
+    that keep the 16-byte stride TMA needs).  The activation quantization is block-local against a static global scale, so
+    a rank's codes of its K slice equal the unsharded ones.  Returns (w_q4, w_sf, a_stacked, b_stacked)."""
+    K = w_q4.shape[1] * 2
+    assert K % tp == 0 and (K // tp) % 32 == 0, f"K = {K} does not split into {tp} shards of whole 32-element groups"
+    ks = K // tp
+    lo = rank * ks
+    return (w_q4[:, lo // 2:(lo + ks) // 2].contiguous(), w_sf[:, lo // 16:(lo + ks) // 16].contiguous(),
+            tuple(a[..., lo:lo + ks].contiguous() for a in a_stacked), tuple(b_stacked))
+
+
 def run_row_parallel_sharded(op, x_r, meta_args, out=None, cfg=None, group=None):
     """One row-parallel projection with sharded adapters on this rank: K1 on the rank's K slice, all-reduce of the fp32
     shrink partials (a few hundred KB at most), K2 with the expand on the rank's output features only, all-reduce of y.

@@ -128,3 +128,40 @@ def test_qkv_kv_replication_when_fewer_kv_heads_than_ranks():
         assert torch.equal(w_r[:8], w[rank * 8: rank * 8 + 8])
         assert torch.equal(w_r[8:16], w[32 + (rank // 2) * 8: 32 + (rank // 2) * 8 + 8])
     assert shapes == [[8, 8, 8]] * 4
+
+
+def test_nvfp4_base_shards():
+    """NVFP4 base under tensor parallelism (shard arithmetic only, the oracle standing in for the kernels): column shards
+    concatenate to the unsharded result exactly; row shards, whose activation codes equal the unsharded ones block for
+    block, sum to it up to the fp32 summation order and one bf16 rounding of each rank's partial h."""
+    from onebase_b200 import tp
+    from oracle import nvfp4 as on4
+    world = 2
+    d = configs.with_nvfp4_base(configs.draw(256, (128, 64), 16, 4, 11, seed=13, w_std=0.05, b_std=0.05))
+    A, B = ofp8.stack_slices(d["a_stacked"], d["b_stacked"])
+    full = on4.fused_projection(d["x"], d["ids"], d["w_q4"], d["w_sf"], d["w_global"], d["x_global"], A, B, d["widths"])
+    parts = []
+    for rank in range(world):
+        q_r, sf_r, a_r, b_r = tp.shard_column_nvfp4(d["w_q4"], d["w_sf"], d["a_stacked"], d["b_stacked"], world, rank)
+        assert q_r.shape == (96, 128) and sf_r.shape == (96, 16) and sf_r.dtype == d["w_sf"].dtype
+        Ar, Br = ofp8.stack_slices(a_r, b_r)
+        parts.append(on4.fused_projection(d["x"], d["ids"], q_r, sf_r, d["w_global"], d["x_global"], Ar, Br, [t.shape[2] for t in b_r]))
+    cols, off = [], 0
+    for w in d["widths"]:
+        ws = w // world
+        cols.append(torch.cat([parts[r][:, off // world: off // world + ws] for r in range(world)], 1))
+        off += w
+    assert torch.equal(torch.cat(cols, 1), full)
+    total = torch.zeros_like(full)
+    for rank in range(world):
+        q_r, sf_r, a_r, b_r = tp.shard_row_nvfp4(d["w_q4"], d["w_sf"], d["a_stacked"], d["b_stacked"], world, rank)
+        assert q_r.shape == (192, 64) and sf_r.shape == (192, 8) and a_r[0].shape[-1] == 128
+        x_r = tp.shard_input_row(d["x"], world, rank)
+        xq_full, xsf_full = on4.quant(d["x"], d["x_global"])
+        xq_r, xsf_r = on4.quant(x_r, d["x_global"])
+        assert torch.equal(xq_r, xq_full[:, rank * 64:(rank + 1) * 64]) and torch.equal(xsf_r.view(torch.uint8), xsf_full.view(torch.uint8)[:, rank * 8:(rank + 1) * 8])
+        Ar, Br = ofp8.stack_slices(a_r, b_r)
+        total += on4.fused_projection(x_r, d["ids"], q_r, sf_r, d["w_global"], d["x_global"], Ar, Br, d["widths"])
+    assert float((total - full).abs().max() / full.abs().max()) <= 2e-3
+    with pytest.raises(AssertionError):
+        tp.shard_row_nvfp4(d["w_q4"][:, :24], d["w_sf"][:, :3], d["a_stacked"], d["b_stacked"], world, 0)   # K = 48: 24 per rank
