@@ -78,6 +78,42 @@ def test_segment_index_large_batch():
         assert torch.equal(have.cpu(), want)
 
 
+def test_segment_index_hook_device_path():
+    """The replacement for vLLM's LoRAKernelMeta.prepare_tensors (LOWBIT_SEGMENT_INDEX=1) on device tensors: the five
+    tensors bit-equal to the oracle over a sequence of batches on the same object, and vLLM's host-side flags."""
+    from onebase_b200.plugin import segment_index_prepare
+    L, max_m = 6, 48
+
+    class Meta:   # the attributes of vllm/lora/ops/triton_ops/lora_kernel_metadata.py:14-60 the replacement touches
+        def __init__(self):
+            z = lambda n: torch.zeros(n, dtype=torch.int32, device="cuda")   # noqa: E731
+            self.token_lora_mapping, self.token_indices_sorted_by_lora_ids = z(max_m), z(max_m)
+            self.active_lora_ids = torch.full((L + 1,), -1, dtype=torch.int32, device="cuda")
+            self.num_tokens_per_lora, self.lora_token_start_loc = z(L + 1), z(L + 2)
+            self.no_lora_flag_cpu = torch.tensor([False])
+            self.num_active_loras_cpu = torch.tensor([0], dtype=torch.int32)
+            self.captured_lora_counts = [1, 2, 4, 7]
+
+    def never(self, t):
+        raise AssertionError("fell back to vLLM's own code")
+
+    hook = segment_index_prepare(never)
+    m, ref = Meta(), oseg.SegmentIndex(L, max_m)
+    g = torch.Generator().manual_seed(5)
+    batches = [torch.randint(-1, L, (40,), generator=g, dtype=torch.int32), torch.full((17,), -1, dtype=torch.int32),
+               torch.full((9,), 3, dtype=torch.int32), torch.arange(48, dtype=torch.int32) % L]
+    want_active = [7, 0, 1, 7]                                  # unique ids ("-1" included), rounded up to a captured count
+    for t, active in zip(batches, want_active):
+        hook(m, t.cuda())
+        ref.prepare(t)
+        n = t.numel()
+        for have, want in ((m.token_lora_mapping[:n], ref.tok[:n]), (m.token_indices_sorted_by_lora_ids[:n], ref.srt[:n]),
+                           (m.num_tokens_per_lora, ref.seg_n), (m.lora_token_start_loc, ref.seg_start),
+                           (m.active_lora_ids, ref.seg_ids)):
+            assert torch.equal(have.cpu(), want)
+        assert bool(m.no_lora_flag_cpu[0]) == bool((t == -1).all()) and int(m.num_active_loras_cpu[0]) == active
+
+
 def test_quant_codes_and_scales_bit_exact_golden(golden):
     """K1's codes and scales on the fixture the reference's own rule produced (edge rows: zeros, floor, ties, large)."""
     g = golden("fp8_quant")
