@@ -135,6 +135,12 @@ typedef struct ObTileCfg {
                                       * from 512 tokens; 256 x 256 GEMM tiles when they fill the GPU), 1 = tensor-core
                                       * shrink and, where the layer allows, 256 x 256 tiles whatever the size, 2 = the
                                       * warp-level shrink and 64..128-token tiles */
+    int32_t stream;                  /* decode batches (at most 32 tokens) of bf16 adapters: 1 = the persistent GEMM, one CTA per
+                                      * SM streaming a contiguous share of the launch's weight k-blocks across output tiles, the
+                                      * expand steps' B tiles in a ring of their own (tiles shared between CTAs are finished by
+                                      * the last CTA to arrive; tn and stages apply, split2 does not); 0 or 2 = one CTA per
+                                      * (output tile, K split), the default.  ob_resolve_tile reports which one a call takes
+                                      * (1 or 2) */
 } ObTileCfg;
 
 typedef struct ObLayer ObLayer;      /* opaque: validated descriptor + TMA tensor maps (host memory only) */
@@ -152,6 +158,14 @@ int ob_workspace_bytes(const ObWorkspaceShape* shape, size_t* bytes);
  * max_m > 32: an adapter-sorted bf16 copy of x and the tensor-core shrink's finished h; for max_m > 128 and max_l > 0: the
  * per-tenant h blocks of the large-tile prefill GEMM); ob_workspace_bytes counts them. */
 int ob_workspace_offsets(const ObWorkspaceShape* shape, size_t out[7]);
+
+/* Offset and size of ONE workspace region, the kernel-only ones included (same purpose as above: the reference's
+ * tests read its scratch tensors, e.g. `op.scratch.hp`, lowbit_lora/kernels/fp8_lora_vllm.py:321-327).
+ * OB_WS_XS: adapter-sorted bf16 copy of x [max_m, K]; OB_WS_HB: the tensor-core shrink's finished h [S][max_m][R] bf16;
+ * OB_WS_HCAT: per-tenant h blocks of the large-tile prefill GEMM.  A region the shape has no room for has 0 bytes. */
+enum { OB_WS_STATUS = 0, OB_WS_COUNTERS, OB_WS_SX, OB_WS_XQ, OB_WS_XSF, OB_WS_HP, OB_WS_PART, OB_WS_XS, OB_WS_HB, OB_WS_HCAT,
+       OB_WS_REGIONS };
+int ob_workspace_region(const ObWorkspaceShape* shape, int region, size_t* offset, size_t* bytes);
 
 /* Validate a layer and build its TMA descriptors.  Replaces VllmFusedFP8LoRA.__init__ / VllmFusedNVFP4LoRA.__init__
  * (fp8_lora_vllm.py:425-496, nvfp4_lora_vllm.py:446-502): pointer tables, slice ends, format flags. */
@@ -176,11 +190,12 @@ int ob_k1_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWor
 int ob_k2_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape,
               const ObTileCfg* cfg, int pdl, void* cuda_stream);
 
-/* K2 for callers that cannot allocate device memory for scratch: the same kernel and result as ob_k2_fp8, but its
- * split-K scratch (fp32 partial tiles, per-tile arrival counters) lives in a fixed device array inside the library
- * instead of the workspace's split-K region.  Meant for hosts that must not call cudaMalloc where this runs -- inside
- * a stream capture, on a serving thread whose memory pool is frozen after warm-up, or from a runtime that hands the
- * library nothing but its tensors -- and so cannot grow a workspace when a tile choice needs more split-K room.
+/* K2 for callers that cannot allocate device memory for scratch: the same tile-per-CTA kernel, launch geometry and
+ * result as ob_k2_fp8 with ObTileCfg.stream = 2, but its split-K scratch (fp32 partial tiles, per-tile arrival counters)
+ * lives in a fixed device array inside the library instead of the workspace's split-K region.  Meant for hosts that
+ * must not call cudaMalloc where this runs -- inside a stream capture, on a serving thread whose memory pool is frozen
+ * after warm-up, or from a runtime that hands the library nothing but its tensors -- and so cannot grow a workspace
+ * when a tile choice needs more split-K room.
  * This entry point has no counterpart in the reference (its Triton host code allocates torch tensors freely).
  *   - `workspace` must still hold what ob_k1_fp8 wrote for this batch (x_q, s_x, shrink partials) and receives the
  *     status words; its own split-K region is neither needed nor touched (a shape with max_split2 = 1 is enough).
@@ -190,7 +205,10 @@ int ob_k2_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWor
  *   - the first call on each device resolves the array's device address and zeroes its counters on `cuda_stream`;
  *     make that first call before any stream capture.  It calls no cudaMalloc / cudaFree or other allocating routine.
  *   - all calls on a device share the one array: two calls that overlap on the GPU (different streams) race.  A call
- *     leaves the counters at zero; the partial tiles keep the last call's contents and are overwritten before use. */
+ *     that completes leaves the counters at zero; the partial tiles keep the last call's contents and are overwritten
+ *     before use.  A call whose device-side wait ran out (status word 0 = OB_DEV_WAIT_TIMEOUT) may leave counters
+ *     above zero: ob_read_status, by which the host learns of it, clears the array's counters on the current device
+ *     whenever it reads a non-zero status, so call it (with that device current) before the next static call. */
 #define OB_STATIC_SCRATCH_BYTES (8u << 20)
 int ob_k2_fp8_static(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape,
                      const ObTileCfg* cfg, int pdl, void* cuda_stream);
@@ -245,7 +263,8 @@ int ob_segment_index(const int32_t* token_lora, int32_t M, int32_t L, int32_t* t
 #define OB_TRACE_EVENTS 16
 int ob_trace_buffer(void* device_u64_buffer, int64_t max_ctas);
 
-/* Copy the workspace's OB_STATUS_WORDS status words to host memory (synchronizes the stream) and clear them. */
+/* Copy the workspace's OB_STATUS_WORDS status words to host memory (synchronizes the stream) and clear them.  If word 0
+ * is not OB_DEV_OK it also zeroes the arrival counters of ob_k2_fp8_static's array on the current device. */
 int ob_read_status(void* workspace, int32_t* host_out, void* cuda_stream);
 
 #ifdef __cplusplus

@@ -16,6 +16,7 @@ OB_MAX_SLICES = 4
 OB_STATUS_WORDS = 16
 OB_BASE_FP8, OB_BASE_NVFP4 = 0, 1
 OB_LORA_BF16, OB_LORA_FP8, OB_LORA_NVFP4 = 0, 1, 2
+OB_WS = {name: i for i, name in enumerate(("status", "counters", "sx", "xq", "xsf", "hp", "part", "xs", "hb", "hcat"))}
 
 
 class ObError(RuntimeError):
@@ -49,7 +50,7 @@ class ObWorkspaceShape(C.Structure):
 
 class ObTileCfg(C.Structure):
     _fields_ = [("tn", C.c_int32), ("split2", C.c_int32), ("split1", C.c_int32), ("stages", C.c_int32),
-                ("wait_ms", C.c_int32), ("fused", C.c_int32), ("prefill", C.c_int32)]
+                ("wait_ms", C.c_int32), ("fused", C.c_int32), ("prefill", C.c_int32), ("stream", C.c_int32)]
 
 
 # every symbol include/onebase_b200.h declares: name -> (restype, argtypes)
@@ -58,6 +59,7 @@ SYMBOLS = {
     "ob_status_string": (C.c_char_p, [C.c_int]),
     "ob_workspace_bytes": (C.c_int, [C.POINTER(ObWorkspaceShape), C.POINTER(C.c_size_t)]),
     "ob_workspace_offsets": (C.c_int, [C.POINTER(ObWorkspaceShape), C.POINTER(C.c_size_t)]),
+    "ob_workspace_region": (C.c_int, [C.POINTER(ObWorkspaceShape), C.c_int, C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
     "ob_layer_create": (C.c_int, [C.POINTER(ObLayerDesc), C.POINTER(C.c_void_p)]),
     "ob_layer_destroy": (C.c_int, [C.c_void_p]),
     "ob_requant_fp8_rows": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),

@@ -133,10 +133,20 @@ __device__ void quantize_row_nvfp4(const K1Params& p, int pos, int row, int tid)
                 osc = p.rcp_approx ? rcp_approx_ftz(den) : __frcp_rn(den);
             }
             uint32_t lo = 0, hi = 0;
+            // The sign bit of a code: the torch recipe sets it for values below zero (so -0.0 and negative values under a
+            // zero block scale encode as +0), vLLM's CUDA kernel converts with cvt.rn.satfinite.e2m1x2.f32, which keeps the
+            // product's own sign bit (they encode as -0: code 8).  Each mode follows its model, bit for bit.
+            const uint32_t approx = p.rcp_approx ? 1u : 0u;
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
-                lo |= e2m1_code(__fmul_rn(v[e], osc)) << (4 * e);
-                hi |= e2m1_code(__fmul_rn(v[8 + e], osc)) << (4 * e);
+                const float a = __fmul_rn(v[e], osc), b = __fmul_rn(v[8 + e], osc);
+                uint32_t ca = e2m1_code(a), cb = e2m1_code(b);
+                if (approx) {
+                    ca = (ca & 7u) | ((__float_as_uint(a) >> 31) << 3);
+                    cb = (cb & 7u) | ((__float_as_uint(b) >> 31) << 3);
+                }
+                lo |= ca << (4 * e);
+                hi |= cb << (4 * e);
             }
             *reinterpret_cast<uint2*>(p.xq + (size_t)pos * (size_t)(p.K >> 1) + (size_t)b * 8) = make_uint2(lo, hi);
         }

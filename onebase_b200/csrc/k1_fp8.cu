@@ -17,6 +17,8 @@
 // The kernel starts with griddepcontrol.launch_dependents so that a dependent K2 may begin streaming W at once, and it
 // may itself be launched as a programmatic dependent of the preceding kernel: it reads the segment index and requests
 // its first block of A before griddepcontrol.wait, and touches x and the scratch only after it.
+#include <atomic>
+
 #include "k1_device.cuh"
 
 namespace ob {
@@ -43,9 +45,20 @@ __global__ void __launch_bounds__(kK1Threads) k1_kernel(const K1Params p) {
             if (threadIdx.x == 0) red_release_add(p.xq_ready, 1);
         }
         OB_TRACE1(3)
-        return;
+        if (!p.looped) return;
     }
     const int lane = threadIdx.x & 31;
+    if (p.looped) {
+        // One CTA per SM at most (so that a dependent GEMM's CTAs fit beside this kernel's and stream weights while it
+        // runs): every warp of the grid walks the shrink units with the grid's stride; the quantizing CTAs join after
+        // their position.
+        const long long total = (long long)p.n_pblocks * p.units_per_block;
+        const long long stride = (long long)gridDim.x * (kK1Threads / 32);
+        for (long long w = (long long)blockIdx.x * (kK1Threads / 32) + (threadIdx.x >> 5); w < total; w += stride)
+            shrink_unit<LORA_FMT>(p, (int)(w / p.units_per_block), (int)(w % p.units_per_block), lane);
+        OB_TRACE1(3)
+        return;
+    }
     const int w = ((int)blockIdx.x - p.n_quant_ctas) * (kK1Threads / 32) + (threadIdx.x >> 5);
     const int pb = w / p.units_per_block;
     if (pb >= p.n_pblocks) return;
@@ -81,6 +94,18 @@ static cudaError_t launch_k1_impl(const K1Params& p, int grid, int pdl, cudaStre
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
+    // K1 needs next to no shared memory, but it must leave the SMs it runs on configured for the LARGEST shared-memory
+    // carve-out: the split between L1 and shared memory only changes on an idle SM, so with the default (small) carve-out
+    // the dependent GEMM's CTAs (100-200 KB each) could not become resident beside K1's and the two kernels of a chain
+    // would run one after the other.
+    static std::atomic<unsigned long long> carved{0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !(carved.load() & (1ull << dev))) {
+        cudaError_t e = cudaFuncSetAttribute(k1_kernel<LORA_FMT, FP4_BASE>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                             (int)cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
+        carved.fetch_or(1ull << dev);
+    }
     if (grid == p.n_quant_ctas && p.xq_ready == nullptr && p.trace == nullptr)   // no shrink warps in this launch
         return cudaLaunchKernelEx(&cfg, k1_quant_kernel<FP4_BASE>, p);
     return cudaLaunchKernelEx(&cfg, k1_kernel<LORA_FMT, FP4_BASE>, p);

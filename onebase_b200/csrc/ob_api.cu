@@ -25,6 +25,10 @@ cudaError_t launch_fused(const K2Params& p, const K1Params& k1, const CUtensorMa
 cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream);
 cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                           dim3 grid, size_t smem, int pdl, cudaStream_t stream);
+size_t k2_stream_smem_bytes(int tn, int stages, int rc, int R, int S, int fp4);
+int k2_stream_h_tiles(int tn);
+cudaError_t launch_k2_stream(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
+                             int grid, size_t smem, int fp4, int pdl, cudaStream_t stream);
 cudaError_t launch_pack_scales(const uint8_t* linear, int K, int S, const int32_t* widths, uint8_t* packed, size_t bytes,
                                cudaStream_t stream);
 cudaError_t launch_segment_index(const int32_t* token_lora, int M, int L, int32_t* tok, int32_t* srt, int32_t* seg_n,
@@ -36,6 +40,7 @@ using namespace ob;
 namespace {
 
 constexpr size_t kSmemLimit = 226 * 1024;    // dynamic part; the kernels keep a few static words besides
+constexpr size_t kSmemStream = 216 * 1024;   // the persistent decode GEMM: leaves 10 KB of the SM for co-resident K1 CTAs
 constexpr size_t kSmemTwoPerSm = 112 * 1024;   // two CTAs of this size (+1 KB reserved each) fit one SM's 228 KB
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -170,8 +175,24 @@ int k_bytes(const ObLayerDesc& d) { return d.base_fmt == OB_BASE_NVFP4 ? d.K / 2
 
 struct Resolved {
     int tn, split1, split2, stages, m_tiles, k_per_split, pb, fused, mma_shrink, big;
+    int stream;        // the persistent decode GEMM (k2_stream.cu) serves this call; `grid_s` CTAs, `stages` ring slots
+    int grid_s;
     uint32_t wait_ms;
 };
+
+// Streaming multiprocessors of the current device (148 on a B200); 0 if it cannot be read.
+int sm_count() {
+    static std::mutex mu;
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+    std::lock_guard<std::mutex> g(mu);
+    if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) { (void)cudaGetLastError(); return 0; }
+    if (dev >= 0 && dev < 64) cached[dev] = n;
+    return n;
+}
 
 // Token tile by default: the smallest of 16..128 that covers the batch.  Prefill batches stay at 128-token tiles: two
 // such CTAs share an SM (256 TMEM columns and a two-slot ring each), so one's epilogue runs under the other's main loop,
@@ -192,7 +213,37 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     if (fp4 && r->tn > 128) return OB_ERR_TILE;
     if (!(r->tn == 16 || r->tn == 32 || r->tn == 64 || r->tn == 128 || r->tn == 256)) return OB_ERR_TILE;
     r->m_tiles = (M + r->tn - 1) / r->tn;
+    // Decode batches of bf16 adapters may take the persistent GEMM (k2_stream.cu): one CTA per SM streams a contiguous share
+    // of the launch's weight bytes.  ObTileCfg.stream = 1 (or LOWBIT_K2_STREAM=1 for every call) asks for it; 0 and 2 keep
+    // the tile-per-CTA kernel, which measured as fast or faster on a B200 at every shape of the benchmark layer (the
+    // persistent form's start-up, expand pipeline and shared-tile fix-ups cost what its weight stream gains).
+    static const bool env_stream = [] { const char* v = std::getenv("LOWBIT_K2_STREAM"); return v && v[0] == '1'; }();
+    r->stream = 0;
+    r->grid_s = 0;
+    {
+        const int want = cfg ? cfg->stream : 0;
+        const int sms = sm_count();
+        const long long units = (long long)l->n_tiles * kblocks;
+        if ((want == 1 || (env_stream && want != 2)) && !(cfg && cfg->fused) && sms > 0 &&
+            M <= kDecodeTokens && r->tn <= 32 && r->m_tiles == 1 && d.lora_fmt == kLoraBf16 && l->n_tiles <= kCounterSlots &&
+            (long long)(d.L < r->tn ? d.L : r->tn) * (d.R / l->rc) <= 256) {
+            // Ring depth: measured on a B200, the stream rate does not grow beyond 4-6 slots (HBM, not latency, bounds it), and
+            // the footprint must leave room for K1's CTAs (a few static bytes + 1 KB reserved each) on the same SM, or the
+            // two kernels of a chain cannot overlap.
+            int stages = (cfg && cfg->stages) ? cfg->stages : 4;
+            if (stages > 16) stages = 16;
+            while (stages > 3 && k2_stream_smem_bytes(r->tn, stages, l->rc, d.R, d.S, fp4 ? 1 : 0) > kSmemStream) --stages;
+            if (fp4) while (stages > 3 && 4 * r->tn + 32 * stages > 512) --stages;   // tensor memory: four accumulators + scale columns
+            if (stages >= 3 && k2_stream_smem_bytes(r->tn, stages, l->rc, d.R, d.S, fp4 ? 1 : 0) <= kSmemStream) {
+                r->stream = 1;
+                r->stages = stages;
+                r->grid_s = (int)(units < sms ? units : sms);
+                if (r->grid_s > kStreamMaxCtas) r->grid_s = kStreamMaxCtas;
+            }
+        }
+    }
     int split2 = (cfg && cfg->split2) ? cfg->split2 : 0;
+    if (r->stream) split2 = 1;
     if (split2 == 0) {   // one co-resident wave: as many CTAs as fit the GPU's 2 x 148 slots, at least 4 K blocks each
         split2 = 1;
         if (r->m_tiles == 1)
@@ -227,7 +278,9 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     if (split1 == 0) {
         const long long units = (long long)((M + pb - 1) / pb) * d.S * (d.R / 8);
         split1 = 1;
-        if (pb == 1)   // decode: as many K splits as keep the whole shrink in one wave of the GPU's 2 x 148 CTA slots (8 warps each)
+        if (pb == 1 && r->stream)   // beside the persistent GEMM the shrink runs as one CTA per SM: one unit per warp of that grid
+            while (split1 < 16 && d.K / (split1 * 2) >= 512 && units * split1 * 2 <= (long long)r->grid_s * 8) split1 *= 2;
+        else if (pb == 1)   // decode: as many K splits as keep the whole shrink in one wave of the GPU's 2 x 148 CTA slots (8 warps each)
             while (split1 < 16 && d.K / (split1 * 2) >= 512 && (units * split1 * 2 + 7) / 8 + M <= 296) split1 *= 2;
         else {         // four positions per warp: two to three waves of warps measured best (each re-reads A through L2);
                        // every CTA of K2 adds the partials again, so a projection with many output tiles wants fewer of them
@@ -242,7 +295,12 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
         while (r->split1 > 1 && (long long)(r->split1 - 1) * r->k_per_split >= d.K) --r->split1;
     r->pb = pb;
     const int rc = l->rc;
-    int stages = (cfg && cfg->stages) ? cfg->stages : 0;
+    int stages = r->stream ? r->stages : (cfg && cfg->stages) ? cfg->stages : 0;
+    if (r->stream) {
+        r->wait_ms = (cfg && cfg->wait_ms > 0) ? (uint32_t)cfg->wait_ms : 2000u;
+        r->fused = 0;
+        return OB_OK;
+    }
     if (stages == 0) {   // prefer a footprint that lets two CTAs share an SM (3+ stages; 2+ for 128-token tiles), else the deepest ring that fits
         stages = 12;
         const int floor_stages = r->tn >= 128 ? 2 : 3;
@@ -298,6 +356,7 @@ K1Params k1_params(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShap
     p.split1 = r.split1;
     p.k_per_split = r.k_per_split;
     p.n_quant_ctas = b->M;
+    p.looped = r.stream;
     p.pb = r.pb;
     p.n_pblocks = (b->M + r.pb - 1) / r.pb;
     p.units_per_block = d.S * (d.R / 8) * r.split1;
@@ -328,7 +387,12 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
                 cudaStream_t stream, bool chain = false) {
     const K1Params p = k1_params(l, b, ws, sh, r, chain);
     const long long warps = r.mma_shrink ? 0 : (long long)p.n_pblocks * p.units_per_block;
-    const long long grid = p.n_quant_ctas + (warps + 7) / 8;
+    long long grid = p.n_quant_ctas + (warps + 7) / 8;
+    if (p.looped) {   // at most one CTA per SM (never fewer than the quantizing CTAs): the warps walk the units with the grid's stride
+        const long long cap = r.grid_s > p.n_quant_ctas ? r.grid_s : p.n_quant_ctas;
+        const long long need = (warps + 7) / 8 > p.n_quant_ctas ? (warps + 7) / 8 : p.n_quant_ctas;
+        grid = need < cap ? need : cap;
+    }
     if (grid > 0x7fffffffLL) return OB_ERR_TOO_LARGE;
     cudaError_t e = launch_k1_fp8(p, (int)grid, pdl, stream);
     if (e != cudaSuccess) return (int)e;
@@ -399,7 +463,15 @@ struct K2Launch {
     bool fp4;
 };
 
-int k2_prepare(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, bool chain, K2Launch* out) {
+// `scratch` (optional): split-K partial tiles and arrival counters somewhere else than in the workspace's own split-K
+// region -- the partials then go through global memory (no cluster form) and the workspace need not have room for them.
+struct SplitScratch {
+    float* part;
+    int32_t* counters;
+};
+
+int k2_prepare(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, bool chain, K2Launch* out,
+               const SplitScratch* scratch = nullptr) {
     const ObLayerDesc& d = l->d;
     const WorkspaceLayout lay = workspace_layout(*sh);
     uint8_t* base = static_cast<uint8_t*>(ws);
@@ -433,8 +505,9 @@ int k2_prepare(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* s
     p.part = reinterpret_cast<float*>(base + lay.part);
     p.counters = reinterpret_cast<int32_t*>(base + lay.counters);
     p.status = reinterpret_cast<int32_t*>(base + lay.status);
-    p.xq_ready = chain ? p.counters + kCounterSlots : nullptr;
-    p.chain_done = chain ? p.counters + kCounterSlots + 1 : nullptr;
+    int32_t* chain_words = reinterpret_cast<int32_t*>(base + lay.counters) + kCounterSlots;
+    p.xq_ready = chain ? chain_words : nullptr;
+    p.chain_done = chain ? chain_words + 1 : nullptr;
     for (int s = 0; s < d.S; ++s) { p.b[s] = d.b[s]; p.sb[s] = d.sb[s]; }
     for (int s = 0; s < OB_MAX_SLICES; ++s) {
         p.b_row0[s] = s < d.S ? d.b_row0[s] : 0;
@@ -443,7 +516,10 @@ int k2_prepare(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* s
     p.bg = d.bg;
     p.trace = g_trace;
     p.trace_ctas = g_trace_ctas;
-    if (r.split2 > 1) {   // the partials of this call must fit the workspace's split-K region
+    if (scratch != nullptr) {
+        p.part = scratch->part;
+        p.counters = scratch->counters;
+    } else if (r.split2 > 1) {   // the partials of this call must fit the workspace's split-K region
         const size_t need = (size_t)r.split2 * (size_t)l->n_tiles * (size_t)r.tn * kTileN * sizeof(float);
         if (lay.part + need > lay.total) return OB_ERR_WORKSPACE;
     }
@@ -453,7 +529,7 @@ int k2_prepare(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* s
                          : dim3((unsigned)l->n_tiles, (unsigned)r.split2, (unsigned)r.m_tiles);
     out->fp4 = d.base_fmt == OB_BASE_NVFP4;
     out->smem = k2_fp8_smem_bytes(r.tn, r.stages, l->rc, d.R, out->fp4 ? 1 : 0);
-    p.cluster_reduce = cluster_reduce_fits(l, r, out->smem) ? 1 : 0;
+    p.cluster_reduce = (scratch == nullptr && cluster_reduce_fits(l, r, out->smem)) ? 1 : 0;
     return OB_OK;
 }
 
@@ -486,9 +562,29 @@ int k2_prefill_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceSha
     return e == cudaSuccess ? OB_OK : (int)e;
 }
 
+// The persistent decode GEMM: same parameters as the tile kernel's launch; its fp32 partial tiles (two per CTA at most: the
+// first and the last tile of a CTA's share may be shared with its neighbours) live in the workspace's split-K region.
+int k2_stream_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, int pdl,
+                   cudaStream_t stream, bool chain) {
+    K2Launch k;
+    const int st = k2_prepare(l, b, ws, sh, r, chain, &k);
+    if (st != OB_OK) return st;
+    const WorkspaceLayout lay = workspace_layout(*sh);
+    const size_t need = (size_t)2 * (size_t)r.grid_s * (size_t)r.tn * kTileN * sizeof(float);
+    if (lay.part + need > lay.total) return OB_ERR_WORKSPACE;
+    k.p.n_tiles = l->n_tiles;
+    k.p.nh = k2_stream_h_tiles(r.tn);
+    k.p.cluster_reduce = 0;
+    k.p.m_fast = 0;
+    const size_t smem = k2_stream_smem_bytes(r.tn, r.stages, l->rc, l->d.R, l->d.S, k.fp4 ? 1 : 0);
+    cudaError_t e = launch_k2_stream(k.p, l->tm_w, k.tm_x, l->tm_b, r.grid_s, smem, k.fp4 ? 1 : 0, pdl, stream);
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
+
 int k2_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, int pdl,
                 cudaStream_t stream, bool chain = false) {
     if (r.big) return k2_prefill_impl(l, b, ws, sh, r, pdl, stream);
+    if (r.stream) return k2_stream_impl(l, b, ws, sh, r, pdl, stream, chain);
     K2Launch k;
     const int st = k2_prepare(l, b, ws, sh, r, chain, &k);
     if (st != OB_OK) return st;
@@ -544,24 +640,39 @@ static __device__ __align__(256) unsigned char g_k2_static_scratch[OB_STATIC_SCR
 // Device address of the array on the current device, resolved once per device.  In host code the array's name is only a
 // stand-in symbol, not a device address, so the kernel must be given what cudaGetSymbolAddress returns.  The first call
 // on a device also zeroes the counters (a memset on the caller's stream; later launches return them to zero themselves).
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mu;
+unsigned char* g_static_addr[kMaxDevices] = {nullptr};
+
 int static_scratch_for_current_device(cudaStream_t stream, unsigned char** out) {
-    static unsigned char* addr[64] = {nullptr};
-    static std::mutex mu;
     int dev = -1;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
-    if (dev < 0 || dev >= 64) return OB_ERR_TOO_LARGE;
-    std::lock_guard<std::mutex> g(mu);
-    if (addr[dev] == nullptr) {
+    if (dev < 0 || dev >= kMaxDevices) return OB_ERR_TOO_LARGE;
+    std::lock_guard<std::mutex> g(g_static_mu);
+    if (g_static_addr[dev] == nullptr) {
         void* ptr = nullptr;
         e = cudaGetSymbolAddress(&ptr, g_k2_static_scratch);
         if (e != cudaSuccess) return (int)e;
         e = cudaMemsetAsync(ptr, 0, kStaticCounterBytes, stream);
         if (e != cudaSuccess) return (int)e;
-        addr[dev] = static_cast<unsigned char*>(ptr);
+        g_static_addr[dev] = static_cast<unsigned char*>(ptr);
     }
-    *out = addr[dev];
+    *out = g_static_addr[dev];
     return OB_OK;
+}
+
+// A launch that recorded a wait time-out may have left arrival counters of the static array above zero (a CTA that gave
+// up never arrived), and no caller can reach the array.  ob_read_status -- the call by which a host learns of the
+// time-out -- therefore clears them whenever it reads a non-zero status word on a device whose array is in use.
+cudaError_t rezero_static_counters(cudaStream_t stream) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev < 0 || dev >= kMaxDevices) return cudaSuccess;
+    std::lock_guard<std::mutex> g(g_static_mu);
+    if (g_static_addr[dev] == nullptr) return cudaSuccess;
+    return cudaMemsetAsync(g_static_addr[dev], 0, kStaticCounterBytes, stream);
 }
 
 }  // namespace
@@ -576,59 +687,27 @@ int ob_k2_fp8_static(ObLayer* layer, const ObBatch* batch, void* workspace, cons
     if (layer->d.base_fmt != OB_BASE_FP8 || layer->d.lora_fmt != OB_LORA_BF16) return OB_ERR_FORMAT;
     st = resolve_cfg(layer, batch->M, cfg, &r);
     if (st != OB_OK) return st;
+    r.stream = 0;   // this entry point runs the tile-per-CTA kernel: its split-K partials are what lives in the array
     // the workspace only has to hold what K1 wrote (and the status words): its own split-K region is not used
     st = validate_workspace(layer, workspace, shape, r.split1, 1);
     if (st != OB_OK) return st;
     if (r.big && (shape->max_l < layer->d.L || batch->ldy % 8 != 0 || !aligned16(batch->y))) r.big = 0;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
     // a prefill batch on the 256 x 256 GEMM needs no split-K scratch at all: the same launch as ob_k2_fp8
-    if (r.big) return k2_prefill_impl(layer, batch, workspace, shape, r, pdl, static_cast<cudaStream_t>(cuda_stream));
+    if (r.big) return k2_prefill_impl(layer, batch, workspace, shape, r, pdl, stream);
     const size_t need = r.split2 > 1 ? (size_t)r.split2 * (size_t)layer->n_tiles * (size_t)r.tn * kTileN * sizeof(float) : 0;
     if (need > kStaticPartBytes) return OB_ERR_TOO_LARGE;   // beyond the static scratch: use ob_k2_fp8 with a workspace
-    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
     unsigned char* scratch = nullptr;
     st = static_scratch_for_current_device(stream, &scratch);
     if (st != OB_OK) return st;
-
-    const ObLayerDesc& d = layer->d;
-    const WorkspaceLayout lay = workspace_layout(*shape);
-    uint8_t* base = static_cast<uint8_t*>(workspace);
-    CUtensorMap tm_x;
-    st = get_xmap(layer, base + lay.xq, shape->max_m, r.tn, &tm_x);
+    // the same launch as ob_k2_fp8 builds, with the split-K partial tiles and arrival counters taken from the array
+    const SplitScratch ss = {reinterpret_cast<float*>(scratch + kStaticCounterBytes), reinterpret_cast<int32_t*>(scratch)};
+    K2Launch k;
+    st = k2_prepare(layer, batch, workspace, shape, r, false, &k, &ss);
     if (st != OB_OK) return st;
-    K2Params p = {};
-    p.M = batch->M; p.N = d.N; p.K = d.K; p.S = d.S; p.R = d.R; p.L = d.L;
-    for (int s = 0; s < OB_MAX_SLICES; ++s) p.widths[s] = s < d.S ? d.widths[s] : 0;
-    p.lora_fmt = d.lora_fmt;
-    p.tn = r.tn;
-    p.split2 = r.split2;
-    p.split1 = r.split1;
-    p.kblocks = (d.K + kBlockK - 1) / kBlockK;
-    p.stages = r.stages;
-    p.rc = layer->rc;
-    p.nh = k2_fp8_h_tiles(r.tn);
-    p.max_m = shape->max_m;
-    p.wait_ms = r.wait_ms;
-    p.s_w = d.s_w;
-    p.sx = reinterpret_cast<const float*>(base + lay.sx);
-    p.hp = reinterpret_cast<const float*>(base + lay.hp);
-    p.hb = r.mma_shrink ? reinterpret_cast<const __nv_bfloat16*>(base + lay.hb) : nullptr;
-    p.meta = meta_of(batch);
-    p.y = static_cast<__nv_bfloat16*>(batch->y);
-    p.ldy = batch->ldy;
-    p.counters = reinterpret_cast<int32_t*>(scratch);                       // static scratch: arrival counters ...
-    p.part = reinterpret_cast<float*>(scratch + kStaticCounterBytes);       // ... and split-K partial tiles
-    p.status = reinterpret_cast<int32_t*>(base + lay.status);
-    for (int s = 0; s < d.S; ++s) { p.b[s] = d.b[s]; p.sb[s] = d.sb[s]; }
-    for (int s = 0; s < OB_MAX_SLICES; ++s) {
-        p.b_row0[s] = s < d.S ? d.b_row0[s] : 0;
-        p.b_rows[s] = s < d.S ? (d.b_rows[s] ? d.b_rows[s] : d.widths[s]) : 0;
-    }
-    p.bg = d.bg;
-    p.trace = nullptr;
-    p.trace_ctas = 0;
-    dim3 grid((unsigned)layer->n_tiles, (unsigned)r.split2, (unsigned)r.m_tiles);
-    cudaError_t e = launch_k2_fp8(p, layer->tm_w, tm_x, layer->tm_b, grid, k2_fp8_smem_bytes(r.tn, r.stages, layer->rc, d.R, 0),
-                                  pdl, stream);
+    k.p.trace = nullptr;
+    k.p.trace_ctas = 0;
+    cudaError_t e = launch_k2_fp8(k.p, layer->tm_w, k.tm_x, layer->tm_b, k.grid, k.smem, pdl, stream);
     return e == cudaSuccess ? OB_OK : (int)e;
 }
 
@@ -669,6 +748,19 @@ int ob_workspace_offsets(const ObWorkspaceShape* shape, size_t out[7]) {
     if (!out) return OB_ERR_NULL;
     const WorkspaceLayout l = workspace_layout(*shape);
     out[0] = l.status; out[1] = l.counters; out[2] = l.sx; out[3] = l.xq; out[4] = l.xsf; out[5] = l.hp; out[6] = l.part;
+    return OB_OK;
+}
+
+int ob_workspace_region(const ObWorkspaceShape* shape, int region, size_t* offset, size_t* bytes) {
+    size_t total;
+    int st = ob_workspace_bytes(shape, &total);
+    if (st != OB_OK) return st;
+    if (!offset || !bytes) return OB_ERR_NULL;
+    if (region < 0 || region >= OB_WS_REGIONS) return OB_ERR_SHAPE;
+    const WorkspaceLayout l = workspace_layout(*shape);
+    const size_t start[OB_WS_REGIONS + 1] = {l.status, l.counters, l.sx, l.xq, l.xsf, l.hp, l.part, l.xs, l.hb, l.hcat, l.total};
+    *offset = start[region];
+    *bytes = start[region + 1] - start[region];
     return OB_OK;
 }
 
@@ -734,6 +826,7 @@ int ob_resolve_tile(ObLayer* layer, int32_t M, const ObTileCfg* cfg, ObTileCfg* 
     out->stages = r.stages;
     out->wait_ms = (int32_t)r.wait_ms;
     out->fused = r.fused;
+    out->stream = r.stream ? 1 : 2;                          // which GEMM kernel serves the call
     out->prefill = r.big ? 1 : r.mma_shrink ? 0 : 2;       // what will run (the workspace may still veto the large tiles)
     return OB_OK;
 }
@@ -761,9 +854,10 @@ int ob_chain_fp8(ObLayer* layer, const ObBatch* batch, void* workspace, const Ob
     if (st != OB_OK) return st;
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
     if (fused_applies(layer, r)) return fused_impl(layer, batch, workspace, shape, r, stream);
-    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
+    // (persistent decode GEMM: K1 counts the positions it has quantized and K2 starts its base GEMM on that count)
+    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream, r.stream != 0);
     if (st != OB_OK) return st;
-    return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
+    return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream, r.stream != 0);
 }
 
 int ob_k1_nvfp4(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape, const ObTileCfg* cfg,
@@ -789,9 +883,10 @@ int ob_chain_nvfp4(ObLayer* layer, const ObBatch* batch, void* workspace, const 
     if (st != OB_OK) return st;
     cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
     if (fused_applies(layer, r)) return fused_impl(layer, batch, workspace, shape, r, stream);
-    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
+    // (persistent decode GEMM: K1 counts the positions it has quantized and K2 starts its base GEMM on that count)
+    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream, r.stream != 0);
     if (st != OB_OK) return st;
-    return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
+    return k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream, r.stream != 0);
 }
 
 int ob_nvfp4_packed_scale_bytes(int32_t K, int32_t S, const int32_t* widths, size_t* bytes) {
@@ -858,6 +953,10 @@ int ob_read_status(void* workspace, int32_t* host_out, void* cuda_stream) {
     cudaError_t e = cudaMemcpyAsync(host_out, workspace, sizeof(int32_t) * OB_STATUS_WORDS, cudaMemcpyDeviceToHost, stream);
     if (e == cudaSuccess) e = cudaMemsetAsync(workspace, 0, sizeof(int32_t) * OB_STATUS_WORDS, stream);
     if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    if (e == cudaSuccess && host_out[0] != OB_DEV_OK) {
+        e = rezero_static_counters(stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
+    }
     return e == cudaSuccess ? OB_OK : (int)e;
 }
 

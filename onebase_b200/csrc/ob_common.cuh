@@ -18,6 +18,7 @@ constexpr int kBigTileMinTokens = 128; // larger FP8 batches of bf16 adapters ta
 constexpr int kMmaShrinkTokens = 512;   // batches from this size on shrink on the tensor cores (bf16 adapters)
 constexpr int kDecodeTokens = 32;     // batches up to this size take the decode forms (one position per shrink warp)
 constexpr int kCounterSlots = 4096;  // split-K arrival counters in the workspace
+constexpr int kStreamMaxCtas = 256;  // most CTAs of the persistent decode GEMM (one per SM)
 constexpr int kSfSlotBytes = 2048;   // NVFP4: scale factors of 128 rows x one 256-element K slot (4 atoms of 512 bytes)
 
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -49,7 +50,11 @@ __host__ __device__ inline WorkspaceLayout workspace_layout(const ObWorkspaceSha
     const size_t n_pad = align_up((size_t)s.max_n, kTileN) + (size_t)OB_MAX_SLICES * kTileN;
     size_t m_pad = 16;                                        // split-K serves one token tile: min(max_m, 256) tokens
     while (m_pad < (size_t)s.max_m && m_pad < 256) m_pad *= 2;
-    l.part = off;     off = align_up(off + sizeof(float) * (s.max_split2 > 1 ? (size_t)s.max_split2 * m_pad * n_pad : 0), 1024);
+    // ... or the persistent decode GEMM's partial tiles: two of 32 tokens x 128 features per CTA
+    const size_t units_cap = (n_pad / kTileN) * (((size_t)s.max_k + kBlockK - 1) / kBlockK);
+    const size_t stream_part = (size_t)2 * (units_cap < (size_t)kStreamMaxCtas ? units_cap : (size_t)kStreamMaxCtas) * kDecodeTokens * kTileN;
+    const size_t split_part = s.max_split2 > 1 ? (size_t)s.max_split2 * m_pad * n_pad : 0;
+    l.part = off;     off = align_up(off + sizeof(float) * (split_part > stream_part ? split_part : stream_part), 1024);
     l.xs = off;       off = align_up(off + (s.max_m > kDecodeTokens ? (size_t)s.max_m * (size_t)s.max_k * 2 : 0), 1024);
     l.hb = off;       off = align_up(off + (s.max_m > kDecodeTokens ? (size_t)s.max_sr * (size_t)s.max_m * 2 : 0), 1024);
     const size_t lc = s.max_l < kMaxTileTenants ? (s.max_l > 0 ? s.max_l : 0) : kMaxTileTenants;
@@ -75,6 +80,7 @@ struct K1Params {
     int split1;            // K splits of the shrink
     int k_per_split;       // elements of K per split (multiple of the warp's K step)
     int n_quant_ctas;      // leading CTAs that quantize (one position each)
+    int looped;            // 1: the grid is capped at one CTA per SM; every warp walks the shrink units with the grid's stride
     int pb;                // sorted positions per shrink warp: 1 (decode) or 4
     int n_pblocks;         // ceil(M / pb)
     int units_per_block;   // shrink warps per position block: S * (R / 8) * split1
@@ -147,6 +153,7 @@ struct K2Params {
     int cluster_reduce;    // split2 > 1: the splits of a tile form one thread-block cluster and add their partials through shared memory
     int split1;            // shrink partials to sum
     int kblocks;           // ceil(K / 128)
+    int n_tiles;           // persistent decode kernel: 128-wide output tiles over all slices
     int stages;
     int rc;                // rank chunk per expand step: min(R, 64)
     int nh;                // masked H tiles in flight (expand steps the builder may run ahead of the B tiles)

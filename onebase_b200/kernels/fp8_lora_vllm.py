@@ -62,9 +62,11 @@ class Scratch:
         s.max_m, s.max_k, s.max_n, s.max_sr, s.max_split2, s.max_l = want
         nbytes = C.c_size_t()
         _lib.call("ob_workspace_bytes", C.byref(s), C.byref(nbytes))
-        offs = (C.c_size_t * 7)()
-        _lib.call("ob_workspace_offsets", C.byref(s), offs)
-        self.offsets = dict(zip(("status", "counters", "sx", "xq", "xsf", "hp", "part"), (int(v) for v in offs)))
+        self.offsets, self.sizes = {}, {}
+        for name, rid in _lib.OB_WS.items():
+            off, size = C.c_size_t(), C.c_size_t()
+            _lib.call("ob_workspace_region", C.byref(s), rid, C.byref(off), C.byref(size))
+            self.offsets[name], self.sizes[name] = int(off.value), int(size.value)
         # over-allocate so that the base can be rounded up to the 1024-byte alignment the TMA descriptors need
         raw = torch.zeros(nbytes.value + 1024, dtype=torch.uint8, device=self.device)
         skew = (-raw.data_ptr()) % 1024
@@ -86,6 +88,11 @@ class Scratch:
     def xq(self, M: int, K: int) -> torch.Tensor:
         """Per-POSITION e4m3 codes of the last call, [M, K] (position p holds the token row the sort put there)."""
         return self.region("xq", M * K).view(torch.float8_e4m3fn).view(M, K)
+
+    def hb(self, S: int, R: int) -> torch.Tensor:
+        """The tensor-core shrink's finished h of the last prefill call, bf16 [S, max_m, R] at adapter-sorted positions."""
+        max_m = self.shape.max_m
+        return self.region("hb", 2 * S * max_m * R).view(torch.bfloat16).view(S, max_m, R)
 
     def status(self, stream=None) -> list[int]:
         out = (C.c_int32 * _lib.OB_STATUS_WORDS)()
@@ -181,13 +188,13 @@ class VllmFusedFP8LoRA:
         if cfg:
             c.update(cfg)
         return _lib.ObTileCfg(c.get("tn", 0), c.get("split2", 0), c.get("split1", 0), c.get("stages", 0),
-                              c.get("wait_ms", self.wait_ms), c.get("fused", 0), c.get("prefill", 0))
+                              c.get("wait_ms", self.wait_ms), c.get("fused", 0), c.get("prefill", 0), c.get("stream", 0))
 
     def resolved_tile(self, M: int, cfg: dict | None = None) -> dict:
         """The tile choice a call of M tokens runs with, the library's own rule filled in (ob_resolve_tile)."""
         out = _lib.ObTileCfg()
         _lib.call("ob_resolve_tile", self._h, int(M), C.byref(self.tile(M, cfg)), C.byref(out))
-        return {k: getattr(out, k) for k in ("tn", "split2", "split1", "stages", "fused")}
+        return {k: getattr(out, k) for k in ("tn", "split2", "split1", "stages", "fused", "stream")}
 
     def shrink_partials(self, M: int, cfg: dict | None = None) -> torch.Tensor:
         """The fp32 shrink partials the last K1 call of M tokens wrote, [split1, S, max_m, R], as a view of the workspace:

@@ -37,6 +37,7 @@ _REGISTRY: list = []          # layer id -> op object
 _INSTALLED = False
 _CALLED = [False]
 _STATS = {"fused_layers": 0, "fallback_layers": 0}
+_LAUNCH = {"pdl": True, "pdl_max_m": 0}   # how the op launches its two kernels; filled from the environment by install()
 
 
 def _on(name: str, default: str = "0") -> bool:
@@ -68,16 +69,21 @@ def segment_index_prepare(orig, index_fn=None):
     and keeps the token map and sorted indices), through `index_fn(meta, mapping, max_loras)` -- the ob_segment_index kernel
     unless a test passes its own -- and then sets the host-side flags vLLM's own LoRA ops and its CUDA-graph dispatch read
     (`no_lora_flag_cpu`, `num_active_loras_cpu` rounded up to a captured count) from ONE copy of the per-segment token
-    counts.  Inputs the kernel does not take (not int32 / not contiguous / not on a GPU / more than 256 slots) go to `orig`."""
+    counts.  int64 mappings (what vLLM's Punica wrapper passes) are cast to int32 on the device first.  Inputs the kernel
+    does not take (another dtype, empty, not on a GPU, more than 256 slots) go to `orig`."""
     import bisect
 
     def prepare_tensors(self, token_lora_mapping: torch.Tensor) -> None:
         t = token_lora_mapping
         max_loras = self.active_lora_ids.numel() - 1
-        fits = (t.dtype == torch.int32 and t.is_contiguous() and t.ndim == 1 and 0 < max_loras <= 256 and
-                t.numel() <= self.token_lora_mapping.numel())
+        fits = (t.dtype in (torch.int32, torch.int64) and t.ndim == 1 and 0 < max_loras <= 256 and
+                0 < t.numel() <= self.token_lora_mapping.numel())
         if not fits or (index_fn is None and not t.is_cuda):
-            return orig(self, t)
+            return orig(self, t)               # (an empty mapping too: vLLM treats it as a batch without adapters)
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            # vLLM's PunicaWrapperGPU hands over a slice of its int64 `_token_lora_indices` (punica_base.py): slot ids
+            # fit 32 bits, and the cast is one small device-side copy in the same stream
+            t = t.to(torch.int32).contiguous()
         (index_fn or _device_segment_index)(self, t, max_loras)
         counts = self.num_tokens_per_lora.cpu()                 # the step's only device -> host copy (it synchronizes)
         groups = int((counts > 0).sum())                        # unique ids of the batch, the "-1" group included
@@ -94,24 +100,30 @@ def segment_index_prepare(orig, index_fn=None):
     return prepare_tensors
 
 
-def _cache_root() -> str:
-    """vLLM's compile-cache root keyed on this package's source and every LOWBIT_* setting (as the reference's
-    `_cache_root`, plugin.py:31-51): a graph compiled without the plugin would silently bypass it."""
+def _settings_digest() -> str:
+    """Twelve hex digits that change with anything that changes what a compiled graph would call: the built library, the
+    tile rows, this package's Python, and every LOWBIT_* switch except the two that only steer reporting."""
     import hashlib
     from pathlib import Path
-
-    import vllm.envs as envs
-    h = hashlib.sha256()
     pkg = Path(__file__).resolve().parent
-    for f in sorted(list(pkg.rglob("*.py")) + list(pkg.rglob("*.cu")) + list(pkg.rglob("*.cuh")) + list(pkg.rglob("*.jsonl"))):
-        h.update(str(f.relative_to(pkg)).encode())
-        h.update(f.read_bytes())
-    for k in sorted(os.environ):
-        if k.startswith("LOWBIT_") and k not in ("LOWBIT_REPORT", "LOWBIT_VERBOSE"):
-            h.update(f"{k}={os.environ[k]}\n".encode())
-    base = envs.VLLM_CACHE_ROOT
-    key = f"lowbit-{h.hexdigest()[:12]}"
-    return base if os.path.basename(base) == key else os.path.join(base, key)
+    digest = hashlib.blake2b(digest_size=6)
+    tracked = [q for pat in ("*.py", "kernels/*.py", "tiles/*.jsonl", "csrc/*.cu", "csrc/*.cuh") for q in pkg.glob(pat)]
+    for q in sorted(tracked, key=lambda q: q.as_posix()):
+        digest.update(q.relative_to(pkg).as_posix().encode() + b"\0" + q.read_bytes() + b"\0")
+    switches = {k: v for k, v in os.environ.items() if k.startswith("LOWBIT_") and k not in ("LOWBIT_REPORT", "LOWBIT_VERBOSE")}
+    digest.update(repr(sorted(switches.items())).encode())
+    return digest.hexdigest()
+
+
+def _cache_root() -> str:
+    """Where vLLM should keep graphs compiled with this plugin active: a sub-directory of its cache root named after
+    `_settings_digest()`, so that a graph compiled without the plugin (or with other switches) is never reused -- it
+    would bypass the fused op without any error (the reference keys its cache the same way, lowbit_lora/plugin.py:31-51).
+    A child process that inherits an already keyed root keeps it."""
+    import vllm.envs as envs
+    root = envs.VLLM_CACHE_ROOT
+    leaf = "lowbit-" + _settings_digest()
+    return root if os.path.basename(os.path.normpath(root)) == leaf else os.path.join(root, leaf)
 
 
 def _fused(x: torch.Tensor, layer_id: int, tok: torch.Tensor, srt: torch.Tensor, seg_n: torch.Tensor,
@@ -120,11 +132,9 @@ def _fused(x: torch.Tensor, layer_id: int, tok: torch.Tensor, srt: torch.Tensor,
         _CALLED[0] = True
         _report("op-called")
     op = _REGISTRY[layer_id]
-    pdl = _on("LOWBIT_PDL", "1")
-    max_m = int(os.environ.get("LOWBIT_PDL_MAX_M", "0") or 0)
-    if max_m and x.shape[0] > max_m:
-        pdl = False
-    return op(x, (tok, srt, seg_n, seg_start, seg_ids), pdl=pdl)
+    limit = _LAUNCH["pdl_max_m"]
+    chained = _LAUNCH["pdl"] and not (limit and x.shape[0] > limit)
+    return op(x, (tok, srt, seg_n, seg_start, seg_ids), pdl=chained)
 
 
 def _fused_fake(x: torch.Tensor, layer_id: int, tok: torch.Tensor, srt: torch.Tensor, seg_n: torch.Tensor,
@@ -142,9 +152,20 @@ def _adapters_ok(layer) -> bool:
     a, b = getattr(layer, "lora_a_stacked", None), getattr(layer, "lora_b_stacked", None)
     if a is None or b is None or not (1 <= len(a) <= 4) or len(a) != len(b):
         return False
-    if not all(t.dtype == torch.bfloat16 for t in (*a, *b)):
+    if not all(t.dtype == torch.bfloat16 and t.ndim == 4 for t in (*a, *b)):
         return False
-    return a[0].shape[2] in (16, 32, 64, 128, 256)
+    rank = a[0].shape[2]
+    # every slice: A [L,1,R,K] and B [L,1,N_s,R] with the SAME R -- vLLM's fully sharded classes keep A as [L,1,R/tp,K] and
+    # all-gather the shrink, which this op does not do
+    if any(ta.shape[2] != rank or tb.shape[3] != rank for ta, tb in zip(a, b)):
+        return False
+    return rank in (16, 32, 64, 128, 256)
+
+
+def _fully_sharded(layer) -> bool:
+    """vLLM's `fully_sharded_loras` classes (…WithShardedLoRA): their shrink output is all-gathered / their expand input
+    all-reduced between the two LoRA kernels, a collective the fused call does not contain."""
+    return any("ShardedLoRA" in c.__name__ for c in type(layer).__mro__)
 
 
 def _is_fp8_per_tensor(base, qm) -> bool:
@@ -161,45 +182,61 @@ def _is_fp8_per_tensor(base, qm) -> bool:
     return type(qm).__name__ in ("Fp8PerTensorOnlineLinearMethod", "Fp8OnlineLinearMethod", "Fp8LinearMethod")
 
 
+def _fp8_backend(qm) -> str:
+    """Name of the scaled-mm kernel object vLLM chose for this layer (the reference insists on the CUTLASS one, which
+    quantizes activations per token: lowbit_lora/plugin.py:244).  Reported per layer; LOWBIT_FP8_BACKEND_STRICT=1 makes any
+    other backend a fallback."""
+    for attr in ("fp8_linear", "kernel", "fp8_linear_op"):
+        k = getattr(qm, attr, None)
+        if k is not None:
+            return type(getattr(k, "kernel", k)).__name__
+    return "unknown"
+
+
+class _SlotWrites:
+    """Keeps an op's low-precision adapter copies in step with vLLM's slot writes on ONE layer instance, by standing in
+    for the instance's `set_lora` / `reset_lora` (what the reference does per instance too, lowbit_lora/plugin.py:89-130;
+    subclasses of the LoRA layers override these methods, hence the instance and not the class).
+
+    keep_bf16 = True   vLLM's L bf16 slots stay; after each write or reset of slot i the copy of slot i is refreshed.
+    keep_bf16 = False  (default, LOWBIT_RELEASE_SLOTS=1) vLLM's buffers are cut down to ONE staging slot: every write goes
+                       into staging slot 0 and is then filed under its real index in the copies, which become the only
+                       per-slot storage (32 rank-64 slots of an 8B model are about 10 GB of bf16 otherwise).
+    vLLM's own `set_lora(i, ...)` begins with `reset_lora(i)`; while a write is under way that inner reset must not refresh
+    the copy (it would file a zeroed slot under i and the write would then quantize twice)."""
+
+    def __init__(self, layer, op, keep_bf16: bool):
+        self.op, self.keep = op, keep_bf16
+        self.vllm_set, self.vllm_reset = layer.set_lora, layer.reset_lora
+        self.mid_write = False
+        if not keep_bf16:
+            layer.lora_a_stacked = tuple(buf.narrow(0, 0, 1).clone() for buf in layer.lora_a_stacked)
+            layer.lora_b_stacked = tuple(buf.narrow(0, 0, 1).clone() for buf in layer.lora_b_stacked)
+            op.release(layer.lora_a_stacked, layer.lora_b_stacked)
+            layer._lowbit_released = True
+            if torch.cuda.is_available():
+                torch.cuda.empty_cache()
+        layer.set_lora, layer.reset_lora = self.write, self.clear
+
+    def _vllm_index(self, index: int) -> int:
+        return index if self.keep else 0
+
+    def write(self, index, *args, **kwargs):
+        self.mid_write = True
+        try:
+            self.vllm_set(self._vllm_index(index), *args, **kwargs)
+        finally:
+            self.mid_write = False
+        self.op.requantize(index)
+
+    def clear(self, index):
+        self.vllm_reset(self._vllm_index(index))
+        if not self.mid_write:
+            self.op.requantize(index)
+
+
 def _hook_slot_writes(layer, op) -> None:
-    """Per instance: requantize a slot's low-precision copy after vLLM writes or clears it (reference: plugin.py:89-130).
-    By default (LOWBIT_RELEASE_SLOTS=0 keeps vLLM's buffers) the copies become the only per-slot storage: vLLM's bf16 slots
-    shrink to one staging slot that every write goes through."""
-    set_lora, reset_lora = layer.set_lora, layer.reset_lora
-    if _on("LOWBIT_RELEASE_SLOTS", "1"):
-        layer.lora_a_stacked = tuple(t[:1].clone() for t in layer.lora_a_stacked)
-        layer.lora_b_stacked = tuple(t[:1].clone() for t in layer.lora_b_stacked)
-        op.release(layer.lora_a_stacked, layer.lora_b_stacked)
-        if torch.cuda.is_available():
-            torch.cuda.empty_cache()
-        writing = [False]
-
-        def set_lora_s(index, *args, **kw):
-            writing[0] = True
-            try:
-                set_lora(0, *args, **kw)          # its reset_lora(0) lands in reset_lora_s
-            finally:
-                writing[0] = False
-            op.requantize(index)
-
-        def reset_lora_s(index):
-            reset_lora(0)
-            if not writing[0]:
-                op.requantize(index)              # a cleared slot: the copy of the zeroed staging slot
-
-        layer.set_lora, layer.reset_lora = set_lora_s, reset_lora_s
-        layer._lowbit_released = True
-        return
-
-    def set_lora_q(index, *args, **kw):
-        set_lora(index, *args, **kw)
-        op.requantize(index)
-
-    def reset_lora_q(index):
-        reset_lora(index)
-        op.requantize(index)
-
-    layer.set_lora, layer.reset_lora = set_lora_q, reset_lora_q
+    _SlotWrites(layer, op, keep_bf16=not _on("LOWBIT_RELEASE_SLOTS", "1"))
 
 
 def _build(layer) -> int:
@@ -215,7 +252,9 @@ def _build(layer) -> int:
     st4 = getattr(base, "_lowbit_nvfp4", None)
     max_m = layer.punica_wrapper._token_lora_indices.numel()
     fmt = "nvfp4" if _on("LOWBIT_LORA_FP4") else "fp8" if _on("LOWBIT_LORA_FP8") else "bf16"
-    if not _adapters_ok(layer):
+    if _fully_sharded(layer):
+        why = "fully sharded adapters"
+    elif not _adapters_ok(layer):
         why = "adapter buffers (dtype / slices / rank)"
     elif (getattr(layer, "tp_size", 1) != 1 or getattr(base, "bias", None) is not None) and not tp_ok:
         why = "tensor-parallel shard or bias without LOWBIT_TP=1"
@@ -231,6 +270,8 @@ def _build(layer) -> int:
             lid = len(_REGISTRY) - 1
         else:
             why = "NVFP4 weight shape"
+    elif _is_fp8_per_tensor(base, qm) and _on("LOWBIT_FP8_BACKEND_STRICT") and "Cutlass" not in _fp8_backend(qm):
+        why = f"FP8 backend {_fp8_backend(qm)} (LOWBIT_FP8_BACKEND_STRICT=1 wants vLLM's CUTLASS per-token kernel)"
     elif _is_fp8_per_tensor(base, qm):
         w_q = base.weight.t()                                   # [N, K], the storage vLLM quantized into
         widths = [t.shape[2] for t in layer.lora_b_stacked]
@@ -253,8 +294,40 @@ def _build(layer) -> int:
     else:
         _STATS["fallback_layers"] += 1
     _report(f"{type(layer).__name__} {kind if lid >= 0 else 'fallback'} {getattr(base, 'prefix', '')} "
-            f"dispatch=table{(' reason=' + why.replace(' ', '_')) if lid < 0 else ''}")
+            f"dispatch=table{(' fp8_backend=' + _fp8_backend(qm)) if lid >= 0 and kind == 'fused' else ''}"
+            f"{(' reason=' + why.replace(' ', '_')) if lid < 0 else ''}")
     return lid
+
+
+def _keep_nvfp4_checkpoint_layout() -> None:
+    """vLLM's NVFP4 backends re-layout a ModelOpt checkpoint's tensors when the weights have been loaded (swizzled block
+    scales, possibly shuffled codes).  K2 wants the checkpoint's own layout -- codes [N, K/2], linear ue4m3 block scales
+    [N, K/16] -- so a snapshot is taken just before (`layer._lowbit_nvfp4`), with the two per-tensor scales as vLLM itself
+    reduces them (the maximum over fused shards).  When the backend turns out to have left the codes untouched the snapshot
+    of the codes is dropped in favour of vLLM's tensor, so only the scales are held twice.  (The reference does the same
+    around the same method, lowbit_lora/plugin.py:155-174.)  No-op when this vLLM has no ModelOpt NVFP4 method."""
+    try:
+        from vllm.model_executor.layers.quantization.modelopt import ModelOptNvFp4LinearMethod as Method
+    except Exception:   # noqa: BLE001
+        return
+    if getattr(Method.process_weights_after_loading, "_lowbit_wrapped", False):
+        return
+    backend_relayout = Method.process_weights_after_loading
+
+    def process_weights_after_loading(self, layer):
+        codes = layer.weight.data.clone()
+        snap = {"w_q": codes, "w_sf": layer.weight_scale.data.view(torch.float8_e4m3fn).clone(),
+                "input_scale": float(layer.input_scale.max()), "weight_scale_2": float(layer.weight_scale_2.max())}
+        layer._lowbit_nvfp4 = snap
+        result = backend_relayout(self, layer)
+        after = layer.weight.data
+        same_storage_layout = after.dtype == codes.dtype and after.shape == codes.shape and after.is_contiguous()
+        if same_storage_layout and torch.equal(after, codes):
+            snap["w_q"] = after
+        return result
+
+    process_weights_after_loading._lowbit_wrapped = True
+    Method.process_weights_after_loading = process_weights_after_loading
 
 
 def install() -> None:
@@ -268,30 +341,15 @@ def install() -> None:
             os.environ["VLLM_DISABLE_COMPILE_CACHE"] = "1"
     else:
         os.environ["VLLM_DISABLE_COMPILE_CACHE"] = "1"
+    _LAUNCH["pdl"] = _on("LOWBIT_PDL", "1")
+    _LAUNCH["pdl_max_m"] = int(os.environ.get("LOWBIT_PDL_MAX_M", "0") or 0)
     import inspect
 
     import vllm.lora.layers as lora_layers
     from vllm.lora.layers.base_linear import BaseLinearLayerWithLoRA
     from vllm.utils.torch_utils import direct_register_custom_op
 
-    try:   # keep the NVFP4 checkpoint layout (codes, linear block scales) before the backend re-layouts it
-        from vllm.model_executor.layers.quantization.modelopt import ModelOptNvFp4LinearMethod
-        orig_process = ModelOptNvFp4LinearMethod.process_weights_after_loading
-
-        def nvfp4_process(self, layer):
-            layer._lowbit_nvfp4 = st = {"w_q": layer.weight.data.clone(),
-                                        "w_sf": layer.weight_scale.data.view(torch.float8_e4m3fn).clone(),
-                                        "input_scale": float(layer.input_scale.max()),
-                                        "weight_scale_2": float(layer.weight_scale_2.max())}
-            out = orig_process(self, layer)
-            w = layer.weight.data
-            if w.dtype == st["w_q"].dtype and w.shape == st["w_q"].shape and w.is_contiguous() and torch.equal(w, st["w_q"]):
-                st["w_q"] = w                                   # the backend kept the codes in place: share them
-            return out
-
-        ModelOptNvFp4LinearMethod.process_weights_after_loading = nvfp4_process
-    except Exception:   # noqa: BLE001
-        pass
+    _keep_nvfp4_checkpoint_layout()
 
     if _on("LOWBIT_SEGMENT_INDEX"):
         try:
@@ -309,13 +367,17 @@ def install() -> None:
     tp_bias = _on("LOWBIT_TP")
 
     def set_mapping(self, punica_wrapper):
+        # vLLM calls this once per wrapped layer, after the base weights are final and before any graph capture: the one
+        # point where the layer can be inspected and its op built.  The decision is kept on the instance.
         orig_set_mapping(self, punica_wrapper)
-        if "_lowbit_id" not in self.__dict__:
-            self._lowbit_id = _build(self)
+        if vars(self).get("_lowbit_id") is None:
+            vars(self)["_lowbit_id"] = _build(self)
+
+    reported_fallbacks: set = set()
 
     def _note_fallback(layer, why: str) -> None:
-        if not layer.__dict__.get("_lowbit_fb"):
-            layer.__dict__["_lowbit_fb"] = True
+        if id(layer) not in reported_fallbacks:                # one line per layer, however often it falls back
+            reported_fallbacks.add(id(layer))
             _report(f"{type(layer).__name__} runtime-fallback {why}")
 
     def fused_or_none(self, x, bias):
@@ -379,3 +441,16 @@ def install() -> None:
     _report(f"installed wrapped-apply={','.join(wrapped) or '-'}")
     if os.environ.get("LOWBIT_VERBOSE"):
         print(f"[lowbit] onebase_b200 fused FP8/NVFP4 + LoRA plugin installed (class-level apply wrapped: {wrapped})", flush=True)
+
+
+def install_pdl() -> None:
+    """Entry point `lowbit_pdl`: in the reference a separate plugin that switches the FP8 layers' decode batches to the
+    K1 -> K2 chain with programmatic dependent launch (lowbit_lora/hopper_pdl.py:311-423; active under LOWBIT_PDL=1).
+    Here the chain is how the op launches (LOWBIT_PDL=0 turns it off), so this only makes sure the plugin is installed."""
+    install()
+
+
+def install_pdl4() -> None:
+    """Entry point `lowbit_pdl4`: the reference's NVFP4 decode chain plugin (lowbit_lora/blackwell_pdl_plugin.py:149-237);
+    see install_pdl."""
+    install()

@@ -34,7 +34,7 @@ def _load() -> dict:
             row = json.loads(line)
             key = (int(row["M"]), int(row["N"]), int(row["K"]), int(row["S"]), int(row["R"]), str(row.get("fmt", "fp8")),
                    str(row.get("adapters", "bf16")))
-            table[key] = {k: int(row[k]) for k in ("tn", "split2", "split1", "stages", "fused", "prefill") if k in row}
+            table[key] = {k: int(row[k]) for k in ("tn", "split2", "split1", "stages", "fused", "prefill", "stream") if k in row}
     return table
 
 
