@@ -312,6 +312,10 @@ def main() -> None:
     ap.add_argument("--tp-form", default="partial", choices=["partial", "sharded"],
                     help="N > 1: row-parallel layers add partial LoRA terms (vLLM's default) or shard the adapters too and "
                          "all-reduce the shrink partials first")
+    ap.add_argument("--tp-comm", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: the row-parallel layers' all-reduce -- the peer-memory kernel inside the layer's CUDA graph "
+                         "(default) or NCCL between graph replays")
+    ap.add_argument("--no-config4", action="store_true", help="N > 1: skip the 72B-class layer's timings")
     ap.add_argument("--matrix", default=None, metavar="SIZES",
                     help="measure the grid of base formats x adapter storage formats at these batch sizes (comma-separated, "
                          "or 'all' for 1,2,4,8,16,32,512,2048,8192); one JSON line per cell")

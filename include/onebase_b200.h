@@ -254,6 +254,43 @@ int ob_requant_nvfp4(const void* src, int32_t l, int32_t rows, int32_t cols, voi
 int ob_segment_index(const int32_t* token_lora, int32_t M, int32_t L, int32_t* tok, int32_t* srt, int32_t* seg_n,
                      int32_t* seg_start, int32_t* seg_ids, void* cuda_stream);
 
+/* ---- All-reduce of a row-parallel layer's partial outputs over peer-mapped memory (one NVSwitch box, one process per
+ * GPU).  Replaces the NCCL all-reduce vLLM issues after a row-parallel LoRA layer (tensor_model_parallel_all_reduce,
+ * vllm/lora/layers/row_parallel_linear.py:73-76; served by the reference's plugin under LOWBIT_TP=1,
+ * lowbit_lora/plugin.py:239-245) with one stream-ordered kernel per rank that can sit inside a CUDA graph.
+ *
+ * Every rank allocates one communication buffer (device memory, zero-initialized, ob_comm_bytes(slot_bytes) bytes, where
+ * slot_bytes >= the largest payload), exports it (ob_ipc_export), hands handle + offset to the other ranks by any host
+ * channel, and maps theirs (ob_ipc_open).  ObComm.bufs[r] is rank r's buffer as mapped in THIS process (bufs[rank] = the
+ * own buffer's ordinary pointer).  All ranks must call ob_allreduce the same number of times with the same count / dtype /
+ * mode; the result is bitwise identical on all ranks (partials added in rank order, fp32 accumulation).  Waits on peers are
+ * bounded by wait_ms: when one runs out the call's output is left unwritten and ob_comm_status reports it; the ranks must
+ * then zero their buffers together before the next call.  Plain peer loads and stores only (no multicast, no TMA). */
+#define OB_MAX_RANKS 8
+#define OB_IPC_HANDLE_BYTES 64
+enum { OB_DTYPE_BF16 = 0, OB_DTYPE_F32 = 1 };
+enum { OB_AR_AUTO = 0, OB_AR_ONE_SHOT = 1, OB_AR_TWO_SHOT = 2 };   /* auto: two shots above 512 KB on more than 2 ranks */
+typedef struct ObComm {
+    int32_t world, rank;             /* 2..OB_MAX_RANKS ranks */
+    void* bufs[OB_MAX_RANKS];
+    size_t slot_bytes;               /* as given to ob_comm_bytes (a multiple of 16) */
+} ObComm;
+int ob_comm_bytes(size_t slot_bytes, size_t* bytes);
+int ob_ipc_export(const void* dev_ptr, unsigned char handle[OB_IPC_HANDLE_BYTES], size_t* offset);
+int ob_ipc_open(const unsigned char handle[OB_IPC_HANDLE_BYTES], size_t offset, void** mapped);
+int ob_ipc_close(void* mapped, size_t offset);
+/* dst[i] = sum over ranks of src[i], i < count; count * element size a multiple of 16 and <= slot_bytes; src and dst 16-byte
+ * aligned device pointers of this rank (they may be the same). */
+int ob_allreduce(const ObComm* comm, const void* src, void* dst, int64_t count, int32_t dtype, int32_t mode, int32_t wait_ms,
+                 void* cuda_stream);
+/* The same exchange for `n` ranks that all live on the CURRENT device, as ONE cooperative launch (ranks on one GPU must not
+ * be separate launches that wait for one another): for tests without a second GPU.  comms[q].bufs are ordinary pointers. */
+int ob_allreduce_emulated(const ObComm* comms, int32_t n, const void* const* src, void* const* dst, int64_t count,
+                          int32_t dtype, int32_t mode, int32_t wait_ms, void* cuda_stream);
+/* Copy the buffer's 8 state words to the host (synchronizes the stream): [0] calls completed, [3] 0 = ok / 1 = a wait ran out,
+ * [4] which wait (1 = partials, 2 = reduced slices), [5] the rank that was missing, [6] the call.  Clears [3..6]. */
+int ob_comm_status(const ObComm* comm, int32_t host_out[8], void* cuda_stream);
+
 /* In-kernel timeline for profiling (the reference has no counterpart: it profiles with torch.profiler only,
  * bench/overhead.py:111-113).  While a buffer is set, every K2 CTA stores OB_TRACE_EVENTS global-timer stamps (ns) at
  * buffer[cta * OB_TRACE_EVENTS + event], cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z); CTAs beyond

@@ -48,6 +48,15 @@ class ObWorkspaceShape(C.Structure):
                 ("max_split1", C.c_int32), ("max_split2", C.c_int32), ("max_l", C.c_int32)]
 
 
+OB_MAX_RANKS = 8
+OB_DTYPE_BF16, OB_DTYPE_F32 = 0, 1
+OB_AR_AUTO, OB_AR_ONE_SHOT, OB_AR_TWO_SHOT = 0, 1, 2
+
+
+class ObComm(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("bufs", C.c_void_p * OB_MAX_RANKS), ("slot_bytes", C.c_size_t)]
+
+
 class ObTileCfg(C.Structure):
     _fields_ = [("tn", C.c_int32), ("split2", C.c_int32), ("split1", C.c_int32), ("stages", C.c_int32),
                 ("wait_ms", C.c_int32), ("fused", C.c_int32), ("prefill", C.c_int32), ("stream", C.c_int32)]
@@ -85,6 +94,14 @@ SYMBOLS = {
                                        C.c_void_p]),
     "ob_segment_index": (C.c_int, [C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                    C.c_void_p, C.c_void_p]),
+    "ob_comm_bytes": (C.c_int, [C.c_size_t, C.POINTER(C.c_size_t)]),
+    "ob_ipc_export": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_size_t)]),
+    "ob_ipc_open": (C.c_int, [C.c_char_p, C.c_size_t, C.POINTER(C.c_void_p)]),
+    "ob_ipc_close": (C.c_int, [C.c_void_p, C.c_size_t]),
+    "ob_allreduce": (C.c_int, [C.POINTER(ObComm), C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "ob_allreduce_emulated": (C.c_int, [C.POINTER(ObComm), C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int64,
+                                        C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "ob_comm_status": (C.c_int, [C.POINTER(ObComm), C.POINTER(C.c_int32), C.c_void_p]),
     "ob_trace_buffer": (C.c_int, [C.c_void_p, C.c_int64]),
     "ob_read_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p]),
 }

@@ -26,7 +26,9 @@ namespace ob {
 constexpr int kK1Threads = 256;
 
 // One instantiation per (adapter storage, base format): each launch carries only the code of its own case.
-template <int LORA_FMT, bool FP4_BASE>
+// LOOPED: the one-CTA-per-SM form that runs beside the persistent GEMM; a function of its own, because the shared-memory
+// carve-out it needs (see launch_k1_impl) is a per-function attribute and costs the other form its L1 cache.
+template <int LORA_FMT, bool FP4_BASE, bool LOOPED>
 __global__ void __launch_bounds__(kK1Threads) k1_kernel(const K1Params p) {
     griddep_launch_dependents();
     OB_TRACE1(0)
@@ -45,10 +47,10 @@ __global__ void __launch_bounds__(kK1Threads) k1_kernel(const K1Params p) {
             if (threadIdx.x == 0) red_release_add(p.xq_ready, 1);
         }
         OB_TRACE1(3)
-        if (!p.looped) return;
+        if (!LOOPED) return;
     }
     const int lane = threadIdx.x & 31;
-    if (p.looped) {
+    if (LOOPED) {
         // One CTA per SM at most (so that a dependent GEMM's CTAs fit beside this kernel's and stream weights while it
         // runs): every warp of the grid walks the shrink units with the grid's stride; the quantizing CTAs join after
         // their position.
@@ -94,21 +96,24 @@ static cudaError_t launch_k1_impl(const K1Params& p, int grid, int pdl, cudaStre
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    // K1 needs next to no shared memory, but it must leave the SMs it runs on configured for the LARGEST shared-memory
-    // carve-out: the split between L1 and shared memory only changes on an idle SM, so with the default (small) carve-out
-    // the dependent GEMM's CTAs (100-200 KB each) could not become resident beside K1's and the two kernels of a chain
-    // would run one after the other.
-    static std::atomic<unsigned long long> carved{0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !(carved.load() & (1ull << dev))) {
-        cudaError_t e = cudaFuncSetAttribute(k1_kernel<LORA_FMT, FP4_BASE>, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                             (int)cudaSharedmemCarveoutMaxShared);
-        if (e != cudaSuccess) return e;
-        carved.fetch_or(1ull << dev);
+    if (p.looped) {
+        // Beside the persistent GEMM, K1 needs next to no shared memory but must leave the SMs it runs on configured for the
+        // LARGEST shared-memory carve-out: the split between L1 and shared memory only changes on an idle SM, so with the
+        // default (small) carve-out the dependent GEMM's CTAs (150-200 KB each) could not become resident beside K1's and
+        // the two kernels of the chain would run one after the other.  (It costs this form most of its L1 cache.)
+        static std::atomic<unsigned long long> carved{0};
+        int dev = 0;
+        if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !(carved.load() & (1ull << dev))) {
+            cudaError_t e = cudaFuncSetAttribute(k1_kernel<LORA_FMT, FP4_BASE, true>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                                 (int)cudaSharedmemCarveoutMaxShared);
+            if (e != cudaSuccess) return e;
+            carved.fetch_or(1ull << dev);
+        }
+        return cudaLaunchKernelEx(&cfg, k1_kernel<LORA_FMT, FP4_BASE, true>, p);
     }
     if (grid == p.n_quant_ctas && p.xq_ready == nullptr && p.trace == nullptr)   // no shrink warps in this launch
         return cudaLaunchKernelEx(&cfg, k1_quant_kernel<FP4_BASE>, p);
-    return cudaLaunchKernelEx(&cfg, k1_kernel<LORA_FMT, FP4_BASE>, p);
+    return cudaLaunchKernelEx(&cfg, k1_kernel<LORA_FMT, FP4_BASE, false>, p);
 }
 
 cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream) {

@@ -2,6 +2,7 @@
 // Host code only allocates host memory; device memory always belongs to the caller.
 #include <cstdio>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <new>
 #include <vector>
@@ -33,6 +34,21 @@ cudaError_t launch_pack_scales(const uint8_t* linear, int K, int S, const int32_
                                cudaStream_t stream);
 cudaError_t launch_segment_index(const int32_t* token_lora, int M, int L, int32_t* tok, int32_t* srt, int32_t* seg_n,
                                  int32_t* seg_start, int32_t* seg_ids, cudaStream_t stream);
+struct ArParams {
+    int world, rank;
+    int dtype;
+    int two_shot;
+    long long count;
+    long long slot_bytes;
+    uint32_t wait_ms;
+    const void* src;
+    void* dst;
+    uint8_t* bufs[OB_MAX_RANKS];
+};
+struct ArBatch {
+    ArParams r[OB_MAX_RANKS];
+};
+cudaError_t launch_allreduce(const ArBatch& b, int n_emulated, int grid_x, cudaStream_t stream);
 }  // namespace ob
 
 using namespace ob;
@@ -938,6 +954,126 @@ int ob_segment_index(const int32_t* token_lora, int32_t M, int32_t L, int32_t* t
     if (M < 1 || L < 1 || L > 1023) return OB_ERR_SHAPE;
     cudaError_t e = launch_segment_index(token_lora, M, L, tok, srt, seg_n, seg_start, seg_ids,
                                          static_cast<cudaStream_t>(cuda_stream));
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// all-reduce over peer-mapped memory
+namespace {
+constexpr size_t kArStateBytes = 4096;
+
+int ar_fill(const ObComm* c, const void* src, void* dst, int64_t count, int32_t dtype, int32_t mode, int32_t wait_ms, ArParams* p) {
+    if (!c || !src || !dst) return OB_ERR_NULL;
+    if (c->world < 2 || c->world > OB_MAX_RANKS || c->rank < 0 || c->rank >= c->world) return OB_ERR_SHAPE;
+    if (dtype != OB_DTYPE_BF16 && dtype != OB_DTYPE_F32) return OB_ERR_FORMAT;
+    const size_t esz = dtype == OB_DTYPE_BF16 ? 2 : 4;
+    if (count < 1 || ((size_t)count * esz) % 16 != 0) return OB_ERR_SHAPE;
+    if ((size_t)count * esz > c->slot_bytes || c->slot_bytes % 16 != 0) return OB_ERR_TOO_LARGE;
+    if (!aligned16(src) || !aligned16(dst)) return OB_ERR_ALIGN;
+    for (int r = 0; r < c->world; ++r)
+        if (!c->bufs[r] || !aligned16(c->bufs[r])) return OB_ERR_NULL;
+    if (mode != OB_AR_AUTO && mode != OB_AR_ONE_SHOT && mode != OB_AR_TWO_SHOT) return OB_ERR_TILE;
+    *p = ArParams{};
+    p->world = c->world;
+    p->rank = c->rank;
+    p->dtype = dtype;
+    p->two_shot = mode == OB_AR_TWO_SHOT || (mode == OB_AR_AUTO && c->world > 2 && (size_t)count * esz > 512 * 1024) ? 1 : 0;
+    p->count = count;
+    p->slot_bytes = (long long)c->slot_bytes;
+    p->wait_ms = wait_ms > 0 ? (uint32_t)wait_ms : 2000u;
+    p->src = src;
+    p->dst = dst;
+    for (int r = 0; r < c->world; ++r) p->bufs[r] = static_cast<uint8_t*>(c->bufs[r]);
+    return OB_OK;
+}
+
+int ar_grid(int64_t count, int32_t dtype) {
+    const long long nvec = (count * (dtype == OB_DTYPE_BF16 ? 2 : 4) + 15) / 16;
+    long long g = (nvec + 255) / 256;
+    const long long cap = nvec > 32768 ? 128 : 64;        // payloads above 512 KB: more CTAs, two vectors per thread and pass
+    return (int)(g < 1 ? 1 : g > cap ? cap : g);
+}
+}  // namespace
+
+int ob_comm_bytes(size_t slot_bytes, size_t* bytes) {
+    if (!bytes) return OB_ERR_NULL;
+    if (slot_bytes < 16 || slot_bytes % 16 != 0) return OB_ERR_SHAPE;
+    *bytes = kArStateBytes + 4 * slot_bytes;     // state and flags; two staged copies; two reduced copies
+    return OB_OK;
+}
+
+int ob_ipc_export(const void* dev_ptr, unsigned char handle[OB_IPC_HANDLE_BYTES], size_t* offset) {
+    if (!dev_ptr || !handle || !offset) return OB_ERR_NULL;
+    static_assert(sizeof(cudaIpcMemHandle_t) == OB_IPC_HANDLE_BYTES, "handle size");
+    // the handle names the whole allocation the pointer lies in: report where in it the pointer is
+    typedef CUresult (*RangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
+    void* fp = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &fp, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) {
+        (void)cudaGetLastError();
+        return OB_ERR_DRIVER;
+    }
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    const CUresult r = reinterpret_cast<RangeFn>(fp)(&base, &size, reinterpret_cast<CUdeviceptr>(dev_ptr));
+    if (r != CUDA_SUCCESS) return 1000 + (int)r;
+    cudaIpcMemHandle_t h;
+    const cudaError_t e = cudaIpcGetMemHandle(&h, reinterpret_cast<void*>(base));
+    if (e != cudaSuccess) return (int)e;
+    std::memcpy(handle, &h, sizeof(h));
+    *offset = reinterpret_cast<CUdeviceptr>(dev_ptr) - base;
+    return OB_OK;
+}
+
+int ob_ipc_open(const unsigned char handle[OB_IPC_HANDLE_BYTES], size_t offset, void** mapped) {
+    if (!handle || !mapped) return OB_ERR_NULL;
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, handle, sizeof(h));
+    void* base = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return (int)e;
+    *mapped = static_cast<unsigned char*>(base) + offset;
+    return OB_OK;
+}
+
+int ob_ipc_close(void* mapped, size_t offset) {
+    if (!mapped) return OB_ERR_NULL;
+    const cudaError_t e = cudaIpcCloseMemHandle(static_cast<unsigned char*>(mapped) - offset);
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
+
+int ob_allreduce(const ObComm* comm, const void* src, void* dst, int64_t count, int32_t dtype, int32_t mode, int32_t wait_ms,
+                 void* cuda_stream) {
+    ArBatch b = {};
+    const int st = ar_fill(comm, src, dst, count, dtype, mode, wait_ms, &b.r[0]);
+    if (st != OB_OK) return st;
+    const cudaError_t e = launch_allreduce(b, 1, ar_grid(count, dtype), static_cast<cudaStream_t>(cuda_stream));
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
+
+int ob_allreduce_emulated(const ObComm* comms, int32_t n, const void* const* src, void* const* dst, int64_t count,
+                          int32_t dtype, int32_t mode, int32_t wait_ms, void* cuda_stream) {
+    if (!comms || !src || !dst) return OB_ERR_NULL;
+    if (n < 1 || n > OB_MAX_RANKS) return OB_ERR_SHAPE;
+    ArBatch b = {};
+    for (int q = 0; q < n; ++q) {
+        const int st = ar_fill(&comms[q], src[q], dst[q], count, dtype, mode, wait_ms, &b.r[q]);
+        if (st != OB_OK) return st;
+    }
+    int grid = ar_grid(count, dtype);
+    const int sms = sm_count();
+    if (sms > 0 && grid * n > sms) grid = sms / n > 0 ? sms / n : 1;      // a cooperative launch must fit the GPU at once
+    const cudaError_t e = launch_allreduce(b, n, grid, static_cast<cudaStream_t>(cuda_stream));
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
+
+int ob_comm_status(const ObComm* comm, int32_t host_out[8], void* cuda_stream) {
+    if (!comm || !host_out || !comm->bufs[comm->rank]) return OB_ERR_NULL;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    int32_t* state = static_cast<int32_t*>(comm->bufs[comm->rank]);
+    cudaError_t e = cudaMemcpyAsync(host_out, state, sizeof(int32_t) * 8, cudaMemcpyDeviceToHost, stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(state + 3, 0, sizeof(int32_t) * 4, stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(stream);
     return e == cudaSuccess ? OB_OK : (int)e;
 }
 

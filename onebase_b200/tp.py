@@ -115,32 +115,171 @@ def all_reduce_output(y: torch.Tensor, group=None) -> torch.Tensor:
     return y
 
 
+class PeerComm:
+    """This rank's end of the peer-memory all-reduce (ob_allreduce): a zeroed communication buffer on the current device,
+    exported by CUDA IPC and mapped into every other rank of `group`; handles travel through torch.distributed (host
+    side, once).  `all_reduce(t)` is then ONE stream-ordered kernel launch, capturable in a CUDA graph, in place of the
+    NCCL call vLLM makes after a row-parallel layer (tensor_model_parallel_all_reduce, row_parallel_linear.py:73-76).
+    Every rank of the group must make the same calls in the same order."""
+
+    def __init__(self, max_bytes: int, device, group=None, wait_ms: int = 2000):
+        import ctypes as C
+
+        import torch.distributed as dist
+
+        from onebase_b200 import _lib
+        self._lib, self._C = _lib, C
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        assert 2 <= self.world <= _lib.OB_MAX_RANKS
+        self.wait_ms = wait_ms
+        self.slot_bytes = (int(max_bytes) + 15) // 16 * 16
+        size = C.c_size_t()
+        _lib.call("ob_comm_bytes", self.slot_bytes, C.byref(size))
+        with torch.cuda.device(device):
+            self.buf = torch.zeros(size.value, dtype=torch.uint8, device=device)
+            handle = C.create_string_buffer(64)
+            offset = C.c_size_t()
+            _lib.call("ob_ipc_export", C.c_void_p(self.buf.data_ptr()), handle, C.byref(offset))
+            torch.cuda.synchronize(device)                     # the zeros are in memory before any peer may write a flag
+            mine = (bytes(handle.raw), int(offset.value))
+            everyone = [None] * self.world
+            dist.all_gather_object(everyone, mine, group=group)
+            self.comm = _lib.ObComm()
+            self.comm.world, self.comm.rank, self.comm.slot_bytes = self.world, self.rank, self.slot_bytes
+            self._mapped = []
+            for r, (h, off) in enumerate(everyone):
+                if r == self.rank:
+                    self.comm.bufs[r] = self.buf.data_ptr()
+                    continue
+                ptr = C.c_void_p()
+                _lib.call("ob_ipc_open", h, off, C.byref(ptr))
+                self.comm.bufs[r] = ptr.value
+                self._mapped.append((ptr.value, off))
+        dist.barrier(group=group)                               # every rank has mapped every buffer
+
+    def all_reduce(self, t: torch.Tensor, out: torch.Tensor | None = None, mode: int = 0) -> torch.Tensor:
+        C, _lib = self._C, self._lib
+        assert t.is_cuda and t.is_contiguous() and t.dtype in (torch.bfloat16, torch.float32)
+        out = t if out is None else out
+        _lib.call("ob_allreduce", C.byref(self.comm), C.c_void_p(t.data_ptr()), C.c_void_p(out.data_ptr()), t.numel(),
+                  _lib.OB_DTYPE_BF16 if t.dtype == torch.bfloat16 else _lib.OB_DTYPE_F32, mode, self.wait_ms,
+                  C.c_void_p(torch.cuda.current_stream(t.device).cuda_stream))
+        return out
+
+    def status(self) -> list[int]:
+        C = self._C
+        st = (C.c_int32 * 8)()
+        self._lib.call("ob_comm_status", C.byref(self.comm), st, C.c_void_p(torch.cuda.current_stream(self.buf.device).cuda_stream))
+        return list(st)
+
+    def close(self) -> None:
+        for ptr, off in self._mapped:
+            self._lib.lib().ob_ipc_close(self._C.c_void_p(ptr), off)
+        self._mapped = []
+
+
 # ------------------------------------------------------------------------------------------------------ benchmark
 QWEN3_8B = {"qkv": (4096, (4096, 1024, 1024), "col"), "o": (4096, (4096,), "row"),
             "gate_up": (4096, (12288, 12288), "col"), "down": (12288, (4096,), "row")}
+# the 72B-class layer of the tensor-parallel configuration: hidden 8192, 64 query / 8 kv heads of 128, intermediate 29568
+L72B = {"qkv": (8192, (8192, 1024, 1024), "col"), "o": (8192, (8192,), "row"),
+        "gate_up": (8192, (29568, 29568), "col"), "down": (29568, (8192,), "row")}
+
+
+def time_sharded_layer(spec: dict, world: int, rank: int, dev, batch_sizes, comm, steps: int, flush) -> dict:
+    """Layer time (us, mean over `steps` graph replays, L2 flushed, max over ranks) of `spec`'s decoder layer at tensor-
+    parallel `world` for each batch size: this rank's shards are drawn directly at their shard shapes (timing only), the
+    layer -- eight fused kernels and the two peer-memory all-reduces -- is one CUDA graph per batch size."""
+    import torch.distributed as dist
+
+    from onebase_b200.kernels.fp8_lora_vllm import VllmFusedFP8LoRA
+    from onebase_b200.metadata import KernelMeta
+    max_m = max(batch_sizes)
+    g = torch.Generator(device=dev).manual_seed(1 + rank)
+    ops = {}
+    for name, (K, widths, kind) in spec.items():
+        if kind == "col":
+            kv_rep = max(1, world // 8) if name == "qkv" else 1        # kv slices are replicated when ranks outnumber kv heads
+            widths_r = tuple(w // (world if s == 0 or name != "qkv" else max(1, world // kv_rep)) for s, w in enumerate(widths))
+            K_r = K
+        else:
+            widths_r, K_r = widths, K // world
+        N_r = sum(widths_r)
+        w_q = torch.randint(0, 120, (N_r, K_r), device=dev, generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn)
+        s_w = torch.full((1,), 1e-3, device=dev)
+        a_r = tuple(((torch.rand(L_SLOTS, 1, RANK, K_r, device=dev, generator=g) * 2 - 1) / K ** 0.5).to(torch.bfloat16) for _ in widths_r)
+        b_r = tuple((torch.randn(L_SLOTS, 1, n, RANK, device=dev, generator=g) * 0.01).to(torch.bfloat16) for n in widths_r)
+        ops[name] = (VllmFusedFP8LoRA(w_q, s_w, a_r, b_r, max_m=max_m), K_r, N_r, kind)
+    out = {}
+    for M in batch_sizes:
+        ids = torch.randint(0, L_SLOTS, (M,), generator=torch.Generator().manual_seed(M), dtype=torch.int32).to(dev)
+        km = KernelMeta.make(L_SLOTS, M, dev)
+        km.prepare_tensors(ids)
+        meta = km.meta_args(M)
+        xs = {n: torch.randn(M, k, device=dev, generator=g).to(torch.bfloat16) for n, (_, k, _, _) in ops.items()}
+        ys = {n: torch.empty(M, nn, dtype=torch.bfloat16, device=dev) for n, (_, _, nn, _) in ops.items()}
+
+        def step():
+            for n in ("qkv", "o", "gate_up", "down"):
+                ops[n][0](xs[n], meta, out=ys[n])
+                if ops[n][3] == "row":
+                    comm.all_reduce(ys[n])
+
+        for _ in range(2):
+            step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        gph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gph):
+            step()
+        ts = []
+        for i in range(steps + 3):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            gph.replay()
+            e1.record()
+            e1.synchronize()
+            if i >= 3:
+                ts.append(e0.elapsed_time(e1))
+        ms = torch.tensor([statistics.fmean(ts)], device=dev)
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        out[str(M)] = round(float(ms.item()) * 1e3, 1)
+        del gph
+    st = ops["qkv"][0].scratch.status()
+    out["device_status_ok"] = st[0] == 0
+    return out
 L_SLOTS, RANK = 32, 64
 
 
 def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
-    """One Qwen3-8B decoder layer at tensor-parallel size `world` (one process per GPU, NCCL): column-parallel qkv /
-    gate_up, row-parallel o / down each followed by an all-reduce of y.  Strong scaling: the same M tokens on every N.
-    Device time per step with CUDA events (max over ranks), L2 flushed before every step."""
+    """One Qwen3-8B decoder layer at tensor-parallel size `world` (one process per GPU): column-parallel qkv / gate_up,
+    row-parallel o / down each followed by an all-reduce of y -- by default the peer-memory kernel (ob_allreduce), so the
+    whole layer (eight fused kernels + two all-reduces) is ONE CUDA graph; `--tp-comm nccl` issues NCCL all-reduces
+    between two graphs instead.  Strong scaling: the same M tokens on every N.  Before timing, rank 0's all-reduced o /
+    down outputs are checked against the unsharded op on the same seeded tensors.  Device time per step with CUDA events
+    (max over ranks), L2 flushed before every step."""
+    import datetime
+
     import torch.distributed as dist
+
     from onebase_b200.kernels.fp8_lora_vllm import VllmFusedFP8LoRA
     from onebase_b200.metadata import KernelMeta
     dev = torch.device(f"cuda:{local}")
     torch.cuda.set_device(dev)
-    import datetime
     dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))
     M = args.m
     sharded = getattr(args, "tp_form", "partial") == "sharded"   # row-parallel layers with sharded adapters
+    use_nccl = getattr(args, "tp_comm", "peer") == "nccl"
     warmup = max(3, args.warmup)
     g = torch.Generator(device=dev).manual_seed(0)            # same seed on every rank: identical full tensors, then sharded
     ids = torch.randint(0, L_SLOTS, (M,), generator=torch.Generator().manual_seed(0), dtype=torch.int32).to(dev)
+    distinct = int(torch.unique(ids).numel())
     km = KernelMeta.make(L_SLOTS, M, dev)
     km.prepare_tensors(ids)
     meta = km.meta_args(M)
-    layer = {}
+    layer, y_full = {}, {}
+    rank_bytes = {}
     for name, (K, widths, kind) in QWEN3_8B.items():
         N = sum(widths)
         w = torch.randn(N, K, device=dev, generator=g) * 0.02
@@ -152,6 +291,11 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
         b_st = tuple((torch.randn(L_SLOTS, 1, n, RANK, device=dev, generator=g) * 0.01).to(torch.bfloat16) for n in widths)
         x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
         b_shard = None
+        if kind == "row":                                        # the unsharded projection on the same tensors: the check's reference
+            full = VllmFusedFP8LoRA(w_q, s_w, a_st, b_st, max_m=M)
+            y_full[name] = full(x, meta).clone()
+            torch.cuda.synchronize()
+            del full
         if kind == "col":
             rep = (1, max(1, world // 8), max(1, world // 8)) if name == "qkv" else ()
             w_r, a_r, b_r = shard_column(w_q.view(torch.uint8), a_st, b_st, world, rank, rep)
@@ -165,86 +309,134 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
         del w_q, a_st, b_st
         op = VllmFusedFP8LoRA(w_r.view(torch.float8_e4m3fn), s_w, a_r, b_r, max_m=M, b_shard=b_shard)
         layer[name] = (op, x_r, torch.empty(M, op.N, dtype=torch.bfloat16, device=dev), kind)
+        # algorithmic bytes this rank moves for the projection: its W shard, its x, the distinct tenants' A and B shards, y
+        rank_bytes[name] = (w_r.numel() + x_r.numel() * 2 + M * op.N * 2 +
+                            distinct * (sum(t.shape[2] * t.shape[3] for t in a_r) + sum(t.shape[2] * t.shape[3] for t in b_r)) * 2)
     torch.cuda.empty_cache()
 
-    def half(names):
-        for name in names:
-            op, x, y, _ = layer[name]
-            op(x, meta, out=y)
-
-    def col_then_k1(col, row):       # sharded adapters: the column-parallel chain, then the row-parallel layer's K1
-        op, x, y, _ = layer[col]
-        op(x, meta, out=y)
-        op, x, y, _ = layer[row]
-        op(x, meta, out=y, gemm=False)
-
-    def k2_only(row):
-        op, x, y, _ = layer[row]
-        op(x, meta, out=y, shrink=False)
-
+    y_o, y_down = layer["o"][2], layer["down"][2]
     hp_o = layer["o"][0].shrink_partials(M) if sharded else None
     hp_down = layer["down"][0].shrink_partials(M) if sharded else None
+    comm = None
+    if not use_nccl:
+        largest = max(y_o.numel() * 2, y_down.numel() * 2, (hp_o.numel() * 4 if sharded else 0), (hp_down.numel() * 4 if sharded else 0))
+        comm = PeerComm(largest, dev)
+
+    def reduce(t):
+        if use_nccl:
+            dist.all_reduce(t)
+        else:
+            comm.all_reduce(t)
+
+    def chain(name, **kw):
+        op, x, y, _ = layer[name]
+        op(x, meta, out=y, **kw)
+
+    def step():
+        """The whole layer in stream order."""
+        chain("qkv")
+        if sharded:
+            chain("o", gemm=False)
+            reduce(hp_o)
+            chain("o", shrink=False)
+        else:
+            chain("o")
+        reduce(y_o)
+        chain("gate_up")
+        if sharded:
+            chain("down", gemm=False)
+            reduce(hp_down)
+            chain("down", shrink=False)
+        else:
+            chain("down")
+        reduce(y_down)
 
     def log(msg):
         if os.environ.get("LOWBIT_VERBOSE"):
             print(f"[tp rank {rank}] {msg}", flush=True)
 
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
-    y_o, y_down = layer["o"][2], layer["down"][2]
-    def eager_step():
-        if sharded:
-            col_then_k1("qkv", "o")
-            dist.all_reduce(hp_o)
-            k2_only("o")
-            dist.all_reduce(y_o)
-            col_then_k1("gate_up", "down")
-            dist.all_reduce(hp_down)
-            k2_only("down")
-            dist.all_reduce(y_down)
-        else:
-            half(("qkv", "o"))
-            dist.all_reduce(y_o)
-            half(("gate_up", "down"))
-            dist.all_reduce(y_down)
-
-    for _ in range(2):                                        # eager warm-up: kernels, scratch, NCCL communicator
-        eager_step()
+    for _ in range(2):                                        # eager warm-up: kernels, scratch, communicator
+        step()
     torch.cuda.synchronize()
     log("eager warm-up done")
-    # The kernels of each half are captured in a CUDA graph; the two all-reduces are issued between the replays (NCCL is
-    # not captured: the collective stays an ordinary stream-ordered launch).
+    # ---- correctness of the exchange before timing.  (a) The all-reduced o / down outputs against the sum of every rank's
+    # partial output, gathered by NCCL and added in rank order in fp32: exact for the peer-memory kernel, one bf16 rounding
+    # per hop off for NCCL's ring.  (b) Against the unsharded projection on the same seeded tensors: equal up to the two
+    # activation quantizations (a rank scales its K slice of a token by the slice's own amax).
+    check, exact = {}, {}
+    for name, y in (("o", y_o), ("down", y_down)):
+        op_n, x_n, _, _ = layer[name]
+        part = torch.empty_like(y)
+        if sharded:
+            op_n(x_n, meta, out=part, gemm=False)
+            reduce(op_n.shrink_partials(M))
+            op_n(x_n, meta, out=part, shrink=False)
+        else:
+            op_n(x_n, meta, out=part)
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part)
+        acc = torch.zeros_like(part, dtype=torch.float32)
+        for t in parts:
+            acc += t.float()
+        exact[name] = float((y.float() - acc.to(torch.bfloat16).float()).abs().max() / acc.abs().max())
+        ref = y_full[name].float()
+        check[name] = float((y.float() - ref).abs().max() / ref.abs().max())
+    worst = torch.tensor([max(check.values()), max(exact.values())], device=dev)
+    dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+    same = torch.stack([y_o.float().sum(), y_down.float().sum()])
+    lo, hi = same.clone(), same.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    ranks_agree = bool(torch.equal(lo, hi))                   # every rank holds the same reduced outputs
+    exact_bound = 0.0 if not use_nccl else 1e-2
+    tp_ok = float(worst[1].item()) <= exact_bound and float(worst[0].item()) <= 6e-2 and ranks_agree
+    log(f"exchange check: vs sum of partials {exact}, vs the unsharded op {check}, ranks agree = {ranks_agree}")
+
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     graphs = []
-    pieces = ([lambda: col_then_k1("qkv", "o"), lambda: k2_only("o"), lambda: col_then_k1("gate_up", "down"),
-               lambda: k2_only("down")] if sharded else [lambda: half(("qkv", "o")), lambda: half(("gate_up", "down"))])
+    if use_nccl:
+        # NCCL stays outside the graphs: the kernels of each half are captured, the collectives are issued between replays
+        pieces = ([lambda: (chain("qkv"), chain("o", gemm=False)), lambda: chain("o", shrink=False),
+                   lambda: (chain("gate_up"), chain("down", gemm=False)), lambda: chain("down", shrink=False)] if sharded
+                  else [lambda: (chain("qkv"), chain("o")), lambda: (chain("gate_up"), chain("down"))])
+    else:
+        pieces = [step]
     for piece in pieces:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             piece()
         torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        dist.barrier()
         gph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(gph):
             piece()
         graphs.append(gph)
     torch.cuda.synchronize()
+    dist.barrier()
     log("graphs captured")
-    graphed = True
 
     def run():
-        if sharded:
+        if not use_nccl:
             graphs[0].replay()
-            dist.all_reduce(hp_o)
-            graphs[1].replay()
-            dist.all_reduce(y_o)
-            graphs[2].replay()
-            dist.all_reduce(hp_down)
-            graphs[3].replay()
-            dist.all_reduce(y_down)
+        elif sharded:
+            graphs[0].replay(); dist.all_reduce(hp_o); graphs[1].replay(); dist.all_reduce(y_o)
+            graphs[2].replay(); dist.all_reduce(hp_down); graphs[3].replay(); dist.all_reduce(y_down)
         else:
-            graphs[0].replay()
-            dist.all_reduce(y_o)
-            graphs[1].replay()
-            dist.all_reduce(y_down)
+            graphs[0].replay(); dist.all_reduce(y_o); graphs[1].replay(); dist.all_reduce(y_down)
+
+    def timed(fn, steps):
+        ts = []
+        for _ in range(steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return ts
 
     for _ in range(warmup):
         flush.fill_(1)
@@ -252,35 +444,104 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
     torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
-    ts = []
-    for _ in range(args.steps):
-        flush.fill_(1)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        run()
-        e1.record()
-        e1.synchronize()
-        ts.append(e0.elapsed_time(e1))
+    ts = timed(run, args.steps)
     torch.cuda.synchronize()
     dist.barrier()
     ms = torch.tensor([statistics.fmean(ts)], device=dev)
     dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+
+    # ---- end to end: this rank's activations from pinned host memory, the layer, rank outputs back to the host
+    host_x = {n: layer[n][1].cpu().pin_memory() for n in layer}
+    host_y = {n: torch.empty(layer[n][2].shape, dtype=torch.bfloat16).pin_memory() for n in layer}
+
+    def e2e_step():
+        for n in layer:
+            layer[n][1].copy_(host_x[n], non_blocking=True)
+        run()
+        for n in layer:
+            host_y[n].copy_(layer[n][2], non_blocking=True)
+
+    for _ in range(3):
+        flush.fill_(1)
+        e2e_step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    e2e_ts = timed(e2e_step, args.steps)
+    e2e_ms = torch.tensor([statistics.fmean(e2e_ts)], device=dev)
+    dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    h2d = sum(t.numel() * 2 for t in host_x.values())
+    d2h = sum(t.numel() * 2 for t in host_y.values())
+
+    # ---- the dominant kernel on this rank: K2 of the gate_up shard, launched alone
+    op_g, x_g, y_g, _ = layer["gate_up"]
+    op_g(x_g, meta, out=y_g)
+    gk2 = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gk2):
+        op_g(x_g, meta, out=y_g, shrink=False, pdl=False)
+    k2_ms = statistics.fmean(timed(gk2.replay, 30))
+    k2_bytes = (op_g.w_q.numel() + M * op_g.K + M * op_g.N * 2 + distinct * op_g.N * RANK * 2)
+
+    # ---- the exchange alone (one all-reduce of y_o in a graph of its own), and the 72B-class layer of the tensor-parallel
+    # configuration at this N (decode M = 8, 32, 128); both with the peer-memory kernel only
+    ar_us, config4 = None, None
     status = layer["qkv"][0].scratch.status()
-    ok = torch.tensor([1 if status[0] == 0 else 0], device=dev)
+    if comm is not None:
+        g_ar = torch.cuda.CUDAGraph()                          # eight in a row: the ranks' start skew is paid once, not per call
+        with torch.cuda.graph(g_ar):
+            for _ in range(8):
+                comm.all_reduce(y_o)
+        dist.barrier()
+        ar_ms = torch.tensor([statistics.fmean(timed(g_ar.replay, 30)) / 8], device=dev)
+        dist.all_reduce(ar_ms, op=dist.ReduceOp.MAX)
+        ar_us = float(ar_ms.item()) * 1e3
+        if not getattr(args, "no_config4", False):
+            del layer, op_g, x_g, y_g, gk2, graphs
+            torch.cuda.empty_cache()
+            big = PeerComm(128 * 8192 * 2, dev)
+            config4 = time_sharded_layer(L72B, world, rank, dev, (8, 32, 128), big, 20, flush)
+            config4["workload"] = (f"72B-class decoder layer (hidden 8192, intermediate 29568) at tensor-parallel {world}, FP8 base, "
+                                   "32 bf16 tenants rank 64, one CUDA graph per batch size; layer us by decode batch size")
+            big.close()
+    ok = torch.tensor([1 if status[0] == 0 and (comm is None or comm.status()[3] == 0) and
+                       (config4 is None or config4["device_status_ok"]) else 0], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
     if rank == 0:
+        import json as _json
+        from pathlib import Path
         ms_v = float(ms.item())
+        peaks = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
+        peak, peak_kind = (float(_json.loads(peaks.read_text())["hbm_gbs"]), "measured") if peaks.exists() else (6650.0, "fallback")
+        k2_gbs = k2_bytes / (k2_ms * 1e-3) / 1e9
+        total_rank_bytes = sum(rank_bytes.values())
         print(json.dumps({
             "metric": metric, "value": M / (ms_v * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms_v, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp8_e4m3", "data": "synthetic",
             "config": {"workload": f"Qwen3-8B decoder layer at tensor-parallel {world}: column-parallel qkv / gate_up, row-parallel "
-                                   f"o / down + NCCL all-reduce of y"
+                                   f"o / down + all-reduce of y ({'NCCL' if use_nccl else 'peer-memory kernel, in the graph'})"
                                    f"{' (adapters sharded too: all-reduce of the shrink partials before the expand)' if sharded else ''}"
-                                   f"; FP8 base, decode M={M}, 32 bf16 tenants rank 64",
+                                   f"; FP8 base, decode M={M}, 32 bf16 tenants rank 64 ({distinct} distinct)",
                        "l2": "flushed by a 256 MB write before every timed step",
-                       "cuda_graph": f"{len(graphs)} graphs; the NCCL all-reduces are launched between them" if graphed else "no"},
-            "layer_us": ms_v * 1e3, "gpu_launches": 8 * args.steps,   # our kernels: four K1 + four K2 per step
+                       "cuda_graph": (f"{len(graphs)} graphs; the NCCL all-reduces are launched between them" if use_nccl
+                                      else "one graph: 8 fused kernels + 2 all-reduce kernels per rank")},
+            "layer_us": ms_v * 1e3, "allreduce_us_alone": ar_us, "config4": config4,
+            "gpu_launches": (8 if use_nccl else 10) * args.steps,   # our kernels per step: four K1, four K2 (+ two all-reduces)
             "device_status_ok": bool(ok.item()),
-            "e2e": None, "roofline": None, "cpu_baseline": None}))
+            "tp_check": {"max_abs_err_over_ymax_vs_sum_of_rank_partials": exact, "exchange_bound": exact_bound,
+                         "max_abs_err_over_ymax_vs_unsharded_op": check, "unsharded_bound": 6e-2,
+                         "note": "the unsharded op quantizes a token's activations once, a rank its K slice with the slice's own "
+                                 "scale: two FP8 roundings of the same activations, not an exchange error",
+                         "ranks_bitwise_equal": ranks_agree, "ok": tp_ok},
+            "rank_bytes_per_step": total_rank_bytes, "rank_gbs": total_rank_bytes / (ms_v * 1e-3) / 1e9,
+            "remaining_per_rank": "every rank still runs the whole shrink of the column-parallel layers (A is not sharded) "
+                                  "and K1's latency does not shrink with N",
+            "e2e": {"value": M / (float(e2e_ms.item()) * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": float(e2e_ms.item()),
+                    "how": "per rank: uploads, the layer, downloads, serial on one stream; max over ranks"},
+            "roofline": {"kernel": "k2_kernel<FP8 base, bf16 adapters> (this rank's gate_up shard, launched alone)", "bound": "hbm",
+                         "achieved": k2_gbs, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": k2_gbs / peak,
+                         "traffic": None, "bytes": k2_bytes, "us": k2_ms * 1e3},
+            "cpu_baseline": None}))
+    if comm is not None:
+        comm.close()
     dist.destroy_process_group()

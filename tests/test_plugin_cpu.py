@@ -179,7 +179,42 @@ def test_segment_index_hook_matches_vllm_metadata():
             a, b = stock.meta_args(n, spec), ours.meta_args(n, spec)
             for x, y in zip(a, b):
                 assert torch.equal(x, y), (t.tolist(), spec)
-    # inputs the kernel does not take go to vLLM's own code
-    hooked(ours, batches[0].to(torch.int64))
-    stock.prepare_tensors(batches[0].to(torch.int64))
+    # vLLM's Punica wrapper hands over a slice of its int64 index buffer: the hook serves it too (cast to int32 first)
+    calls = []
+    counting = segment_index_prepare(meta_mod.LoRAKernelMeta.prepare_tensors,
+                                     index_fn=lambda m, t, n: (calls.append(t.dtype), index_fn(m, t, n)))
+    wide = torch.zeros(64, dtype=torch.int64)
+    wide[:40] = batches[0]
+    counting(ours, wide[:40])                                  # a slice of a longer int64 buffer, as punica_base.py passes it
+    stock.prepare_tensors(wide[:40])
+    assert calls == [torch.int32]
     assert all(torch.equal(x, y) for x, y in zip(stock.meta_args(40, True), ours.meta_args(40, True)))
+    # inputs the kernel does not take go to vLLM's own code: another dtype, an empty mapping
+    def never(m, t, n):
+        raise AssertionError("the kernel path was taken")
+    refusing = segment_index_prepare(meta_mod.LoRAKernelMeta.prepare_tensors, index_fn=never)
+    refusing(ours, batches[0].to(torch.int16))
+    stock.prepare_tensors(batches[0].to(torch.int16))
+    assert all(torch.equal(x, y) for x, y in zip(stock.meta_args(40, True), ours.meta_args(40, True)))
+    refusing(ours, torch.zeros(0, dtype=torch.int32))
+    stock.prepare_tensors(torch.zeros(0, dtype=torch.int32))
+    assert all(torch.equal(x, y) for x, y in zip(stock.meta_args(4, True), ours.meta_args(4, True)))
+
+
+def test_fully_sharded_adapters_fall_back(plugin):
+    """vLLM's fully sharded LoRA classes hold A as [L,1,R/tp,K] and gather the shrink between their two LoRA kernels: a
+    rank mismatch between A and B, or such a class anywhere in the layer's type, must not build a fused op."""
+    P = plugin
+    layer = fake_layer(R=16)
+    layer.lora_a_stacked = tuple(t[:, :, :8].contiguous() for t in layer.lora_a_stacked)      # R/tp rows of A, B keeps R
+    assert P._build(layer) == -1
+
+    class ColumnParallelLinearWithShardedLoRA(types.SimpleNamespace):
+        pass
+
+    ok = fake_layer()
+    sharded = ColumnParallelLinearWithShardedLoRA(**vars(ok))
+    assert P._build(sharded) == -1
+    assert P._build(ok) >= 0
+    text = P._report_path.read_text()
+    assert "fully_sharded_adapters" in text and "adapter_buffers" in text
