@@ -39,10 +39,14 @@ if str(ROOT) not in sys.path:
 PROJECTIONS = {"qkv": (4096, (4096, 1024, 1024)), "o": (4096, (4096,)), "gate_up": (4096, (12288, 12288)),
                "down": (12288, (4096,))}
 L_SLOTS, RANK = 32, 64
-# dram__bytes_read.sum + dram__bytes_write.sum of one k2_kernel launch on gate_up at M = 32 (23 distinct tenants), from the
-# ncu capture summarised in profiles/k2_kernel_gate_up_m32.md; other batch sizes were not captured
-K2_GATE_UP_TRAFFIC = {32: 178.5e6}
 METRIC = "decode tok/s at 32 tenants through one fused FP8+LoRA decoder layer (layer us and HBM roofline % alongside)"
+
+
+def workload_name(M: int) -> str:
+    """The same string in both arms' lines (the batch is seeded: both draw the same tenants)."""
+    ids = torch.randint(0, L_SLOTS, (M,), generator=torch.Generator().manual_seed(0), dtype=torch.int32)
+    return (f"Qwen3-8B decoder layer (qkv, o, gate_up, down), FP8 per-tensor base, decode M={M}, 32 bf16 tenants rank 64 "
+            f"({int(torch.unique(ids).numel())} distinct in the batch)")
 
 
 def measured_peaks() -> tuple[float, str]:
@@ -216,38 +220,53 @@ def format_bytes(M: int, distinct: int, base: str, lora_fmt: str) -> int:
     return int(total)
 
 
+def measure_cell(base: str, lora_fmt: str, M: int, dev, flush, peak: float, kind: str) -> dict:
+    """One cell of the configurations' grid: the four-projection layer for a base format, adapter storage and batch size as
+    one CUDA graph, L2 flushed before every replay, CUDA events.  Decode batches (at most 64 tokens) draw a tenant per token
+    and report algorithmic bytes against the HBM peak; prefill batches split the tokens across the tenants by Zipf(1.1) and
+    report the base GEMM's flops against the nominal dense peak of the base format and against 2x / 4x the measured bf16
+    GEMM throughput (an FP8 / FP4 ceiling of the same silicon)."""
+    ids = zipf_ids(M) if M > 64 else None
+    layer, meta, ids = make_layer(M, dev, base=base, lora_fmt=lora_fmt, ids=ids)
+    run_layer(layer, meta)
+    torch.cuda.synchronize()
+    status = [int(layer[n][0].scratch.status()[0]) for n in PROJECTIONS]
+    g = graph_of(lambda: run_layer(layer, meta))
+    steps = 30 if M <= 64 else 10
+    us = statistics.fmean(time_events(g.replay, steps, 3, flush)) * 1e3
+    distinct = int(torch.unique(ids).numel())
+    nbytes = format_bytes(M, distinct, base, lora_fmt)
+    flops = sum(2.0 * M * sum(w) * K for K, w in PROJECTIONS.values())
+    line = {"base": base, "adapters": lora_fmt, "M": M, "distinct": distinct, "layer_us": round(us, 1),
+            "tokens_per_s": round(M / us * 1e6), "device_status": status}
+    if M <= 64:
+        line.update({"bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1), "hbm_frac": round(nbytes / us / 1e3 / peak, 3),
+                     "hbm_frac_of_nominal_8tbs": round(nbytes / us / 1e3 / 8000.0, 3), "peak_gbs": peak, "peak_kind": kind})
+    else:
+        bf16 = measured_bf16_tflops()
+        mult = 2.0 if base == "fp8" else 4.0
+        line.update({"base_gemm_gflop": round(flops / 1e9, 1), "pflops": round(flops / us / 1e9, 3),
+                     "frac_of_nominal": round(flops / us / 1e9 / (4.5 if base == "fp8" else 9.0), 3),
+                     "frac_of_measured_bf16_x%d" % int(mult): (round(flops / us / 1e6 / (bf16 * mult), 3) if bf16 else None)})
+    del layer, g
+    torch.cuda.empty_cache()
+    return line
+
+
+def measured_bf16_tflops() -> float | None:
+    f = ROOT / "MEASURED_PEAKS.json"
+    return float(json.loads(f.read_text())["bf16_tflops"]) if f.exists() else None
+
+
 def matrix_case(args, dev) -> None:
-    """The configurations' grid, one JSON line per cell: base format x adapter storage x batch size; decode batches draw a
-    tenant per token, prefill batches (more than 64 tokens) split the tokens across the tenants by Zipf(1.1).  Each cell
-    is the four-projection layer as one CUDA graph, L2 flushed before every replay, CUDA events."""
+    """The configurations' grid, one JSON line per cell: base format x adapter storage x batch size."""
     peak, kind = measured_peaks()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     cells = [("fp8", "bf16"), ("nvfp4", "bf16"), ("fp8", "fp8"), ("nvfp4", "fp8"), ("nvfp4", "nvfp4")]
     sizes = [int(v) for v in args.matrix.split(",")] if args.matrix != "all" else [1, 2, 4, 8, 16, 32, 512, 2048, 8192]
     for base, lora_fmt in cells:
         for M in sizes:
-            ids = zipf_ids(M) if M > 64 else None
-            layer, meta, ids = make_layer(M, dev, base=base, lora_fmt=lora_fmt, ids=ids)
-            run_layer(layer, meta)
-            torch.cuda.synchronize()
-            status = [int(layer[n][0].scratch.status()[0]) for n in PROJECTIONS]
-            g = graph_of(lambda: run_layer(layer, meta))
-            steps = 30 if M <= 64 else 10
-            us = statistics.fmean(time_events(g.replay, steps, 3, flush)) * 1e3
-            distinct = int(torch.unique(ids).numel())
-            nbytes = format_bytes(M, distinct, base, lora_fmt)
-            flops = sum(2.0 * M * sum(w) * K for K, w in PROJECTIONS.values())
-            line = {"matrix": True, "base": base, "adapters": lora_fmt, "M": M, "distinct": distinct, "layer_us": round(us, 1),
-                    "tokens_per_s": round(M / us * 1e6), "device_status": status}
-            if M <= 64:
-                line.update({"bytes": nbytes, "gbs": round(nbytes / us / 1e3, 1), "hbm_frac": round(nbytes / us / 1e3 / peak, 3),
-                             "peak_gbs": peak, "peak_kind": kind})
-            else:
-                line.update({"base_gemm_gflop": round(flops / 1e9, 1), "pflops": round(flops / us / 1e9, 3),
-                             "frac_of_nominal": round(flops / us / 1e9 / (4.5 if base == "fp8" else 9.0), 3)})
-            print(json.dumps(line), flush=True)
-            del layer, g
-            torch.cuda.empty_cache()
+            print(json.dumps(dict(measure_cell(base, lora_fmt, M, dev, flush, peak, kind), matrix=True)), flush=True)
 
 
 def graph_of(fn) -> "torch.cuda.CUDAGraph":
@@ -263,10 +282,14 @@ def graph_of(fn) -> "torch.cuda.CUDAGraph":
     return g
 
 
-def cpu_layer_seconds(M: int, reps: int, threads: int) -> tuple[float, str]:
-    """The CPU oracle on one layer (all four projections), same shapes and distributions; median seconds per pass."""
-    from oracle import configs, fp8 as ofp8
+def cpu_layer_seconds(M: int, reps: int, threads: int) -> tuple[float, str, str]:
+    """The reference's CPU torch path on one layer (all four projections), same shapes and distributions; median seconds
+    per pass.  Runs the reference's own `reference_multi` (its per-token Python loop timed as written) when its modules
+    were put under oracle/_ref by `python -m oracle.build_ref`, else the oracle's restatement of it.  Returns
+    (seconds, sample description, "reference" | "port")."""
+    from oracle import build_ref, configs, fp8 as ofp8
     torch.set_num_threads(threads)
+    ref = build_ref.load()
     ds = {}
     for i, (name, (K, widths)) in enumerate(PROJECTIONS.items()):
         d = configs.with_fp8_base(configs.draw(K, widths, RANK, L_SLOTS, M, seed=i, ids_low=0))
@@ -276,10 +299,17 @@ def cpu_layer_seconds(M: int, reps: int, threads: int) -> tuple[float, str]:
     for r in range(reps + 1):
         t0 = time.perf_counter()
         for name, d in ds.items():
-            ofp8.fused_projection(d["x"], d["ids"], d["w_q"], d["s_w"], d["A"], d["B"], d["widths"])
+            if ref is not None:
+                ref[0].reference_multi(d["x"], d["ids"], d["w_q"], d["s_w"], d["A"], d["B"], list(d["widths"]), 1.0)
+            else:
+                ofp8.fused_projection(d["x"], d["ids"], d["w_q"], d["s_w"], d["A"], d["B"], d["widths"])
         if r:
             ts.append(time.perf_counter() - t0)
-    return statistics.median(ts), f"one Qwen3-8B layer (4 projections), M={M}, 32 slots rank 64, {reps} timed passes after 1 warm-up"
+    kind = "reference" if ref is not None else "port"
+    what = ("the reference's own reference_multi (lowbit_lora/kernels/fp8_lora_multi.py:295-314), per-token loop as written"
+            if ref is not None else "the oracle's restatement of reference_multi")
+    return (statistics.median(ts),
+            f"one Qwen3-8B layer (4 projections), M={M}, 32 slots rank 64, {reps} timed passes after 1 warm-up; {what}", kind)
 
 
 def reference_arm(args, rank: int) -> None:
@@ -288,13 +318,13 @@ def reference_arm(args, rank: int) -> None:
     threads = os.cpu_count() or 1
     M = args.m
     steps = max(1, min(args.steps, 3))
-    sec, sample = cpu_layer_seconds(M, steps, threads)
+    sec, sample, kind = cpu_layer_seconds(M, steps, threads)
     value = M / sec
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": steps,
             "warmup": 1, "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp32 (CPU dequantize-and-matmul)", "data": "synthetic",
-            "config": {"workload": f"Qwen3-8B decoder layer, FP8 base, decode M={M}, 32 tenants rank 64"},
-            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample},
+            "config": {"workload": workload_name(M), "how": "the reference's CPU torch path on this host's cores"},
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": threads, "kind": kind, "sample": sample},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
 
@@ -307,14 +337,15 @@ def main() -> None:
     ap.add_argument("--m", type=int, default=32, help="decode batch (tokens per step)")
     ap.add_argument("--impl", default="onebase_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-tables", action="store_true", help="skip the decode / prefill tables beside the headline cell")
     ap.add_argument("--base", default="fp8", choices=["fp8", "nvfp4"], help="base format of the --profile case")
     ap.add_argument("--lora-fmt", default="bf16", choices=["bf16", "fp8", "nvfp4"], help="adapter storage of the --profile case")
     ap.add_argument("--tp-form", default="partial", choices=["partial", "sharded"],
                     help="N > 1: row-parallel layers add partial LoRA terms (vLLM's default) or shard the adapters too and "
                          "all-reduce the shrink partials first")
-    ap.add_argument("--tp-comm", default="peer", choices=["peer", "nccl"],
+    ap.add_argument("--tp-comm", default="peer", choices=["peer", "fused", "nccl"],
                     help="N > 1: the row-parallel layers' all-reduce -- the peer-memory kernel inside the layer's CUDA graph "
-                         "(default) or NCCL between graph replays")
+                         "(default; measured fastest), the same exchange fused into K2's epilogue, or NCCL between graph replays")
     ap.add_argument("--no-config4", action="store_true", help="N > 1: skip the 72B-class layer's timings")
     ap.add_argument("--matrix", default=None, metavar="SIZES",
                     help="measure the grid of base formats x adapter storage formats at these batch sizes (comma-separated, "
@@ -429,6 +460,7 @@ def main() -> None:
         print(f"[bench] pipelined end-to-end step unavailable ({type(exc).__name__}: {exc}); timing the serial form", file=sys.stderr)
         e2e_step, e2e_kind = e2e_serial, "serial: uploads, one graph replay, downloads"
     e2e_ms = statistics.fmean(time_events(e2e_step, args.steps, warmup, flush))
+    e2e_serial_ms = statistics.fmean(time_events(e2e_serial, args.steps, warmup, flush))
     sampler.stop_flag = True
     sampler.join(timeout=2)
     status = layer["qkv"][0].scratch.status()
@@ -444,24 +476,34 @@ def main() -> None:
         "metric": METRIC, "value": M / (ms * 1e-3), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3",
         "data": "synthetic",
-        "config": {"workload": f"Qwen3-8B decoder layer (qkv, o, gate_up, down), FP8 per-tensor base, decode M={M}, "
-                               f"32 bf16 tenants rank 64 ({distinct} distinct in the batch), K1->K2 PDL chains in one CUDA graph",
+        "config": {"workload": workload_name(M), "how": "K1->K2 PDL chains of the four projections in one CUDA graph",
                    "l2": "flushed by a 256 MB write before every timed replay"},
         "layer_us": ms * 1e3, "layer_us_median": statistics.median(ts) * 1e3, "projection_us": per_proj,
         "layer_bytes": total_bytes, "layer_gbs": total_bytes / (ms * 1e-3) / 1e9,
         "layer_frac_of_peak": total_bytes / (ms * 1e-3) / 1e9 / peak,
         "roofline": {"kernel": "k2_kernel<FP8 base, bf16 adapters> (gate_up, launched alone)", "bound": "hbm", "achieved": k2_gbs, "peak": peak,
-                     "peak_kind": peak_kind, "unit": "GB/s", "frac": k2_gbs / peak, "traffic": K2_GATE_UP_TRAFFIC.get(M) if distinct == 23 else None, "bytes": k2_bytes,
+                     "peak_kind": peak_kind, "unit": "GB/s", "frac": k2_gbs / peak, "traffic": None,
+                     "traffic_note": "DRAM bytes are not readable from inside the run; one ncu capture of this launch "
+                                     "(k2_kernel, gate_up, M = 32) read 178.5 MB against 174.85 MB algorithmic",
+                     "bytes": k2_bytes,
                      "us": k2_ms * 1e3, "k1_us_alone": k1_ms * 1e3},
         "e2e": {"value": M / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": e2e_ms, "how": e2e_kind},
+                "ms_per_step": e2e_ms, "how": e2e_kind,
+                "serial": {"value": M / (e2e_serial_ms * 1e-3), "ms_per_step": e2e_serial_ms,
+                           "how": "uploads, one graph replay, downloads, one after the other on one stream"}},
         "gpu_launches": 8 * args.steps,
         "clocks": sampler.result(),
     }
+    if not args.no_tables:
+        # the rest of the metric beside the headline cell: decode at M = 1 / 8 / 32 and one prefill batch, both base formats
+        del layer, graph
+        torch.cuda.empty_cache()
+        line["decode_table"] = [measure_cell(b, "bf16", m, dev, flush, peak, peak_kind) for b in ("fp8", "nvfp4") for m in (1, 8, 32)]
+        line["prefill_table"] = [measure_cell(b, "bf16", 2048, dev, flush, peak, peak_kind) for b in ("fp8", "nvfp4")]
     if not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        sec, sample = cpu_layer_seconds(M, 2, threads)
-        line["cpu_baseline"] = {"value": M / sec, "unit": "tokens/s", "cores": threads, "kind": "port", "sample": sample}
+        sec, sample, kind = cpu_layer_seconds(M, 2, threads)
+        line["cpu_baseline"] = {"value": M / sec, "unit": "tokens/s", "cores": threads, "kind": kind, "sample": sample}
     print(json.dumps(line))
 
 

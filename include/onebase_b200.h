@@ -287,6 +287,16 @@ int ob_allreduce(const ObComm* comm, const void* src, void* dst, int64_t count, 
  * be separate launches that wait for one another): for tests without a second GPU.  comms[q].bufs are ordinary pointers. */
 int ob_allreduce_emulated(const ObComm* comms, int32_t n, const void* const* src, void* const* dst, int64_t count,
                           int32_t dtype, int32_t mode, int32_t wait_ms, void* cuda_stream);
+/* A row-parallel projection with its all-reduce: K1, then K2 whose epilogue stages each finished output tile in this rank's
+ * communication buffer, announces it to the peers with a per-tile flag, waits (bounded) for every rank's copy of that tile
+ * and stores the sum -- the exchange of vLLM's row-parallel LoRA layers (row_parallel_linear.py:73-76) without a launch of
+ * its own and without a second pass over y.  Bitwise the same result as the chain followed by ob_allreduce (same rank
+ * order, fp32 accumulation).  Serves decode batches (at most 32 tokens) on the tile-per-CTA kernel for either base
+ * format; any other call runs the chain and then the stand-alone kernel (y must then be dense: ldy = N).  Counts as one
+ * call of the communication buffer on every rank, like ob_allreduce. */
+int ob_chain_allreduce(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape, const ObTileCfg* cfg,
+                       const ObComm* comm, void* cuda_stream);
+
 /* Copy the buffer's 8 state words to the host (synchronizes the stream): [0] calls completed, [3] 0 = ok / 1 = a wait ran out,
  * [4] which wait (1 = partials, 2 = reduced slices), [5] the rank that was missing, [6] the call.  Clears [3..6]. */
 int ob_comm_status(const ObComm* comm, int32_t host_out[8], void* cuda_stream);

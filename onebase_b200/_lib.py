@@ -101,6 +101,8 @@ SYMBOLS = {
     "ob_allreduce": (C.c_int, [C.POINTER(ObComm), C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
     "ob_allreduce_emulated": (C.c_int, [C.POINTER(ObComm), C.c_int32, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int64,
                                         C.c_int32, C.c_int32, C.c_int32, C.c_void_p]),
+    "ob_chain_allreduce": (C.c_int, [C.c_void_p, C.POINTER(ObBatch), C.c_void_p, C.POINTER(ObWorkspaceShape), C.POINTER(ObTileCfg),
+                                     C.POINTER(ObComm), C.c_void_p]),
     "ob_comm_status": (C.c_int, [C.POINTER(ObComm), C.POINTER(C.c_int32), C.c_void_p]),
     "ob_trace_buffer": (C.c_int, [C.c_void_p, C.c_int64]),
     "ob_read_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p]),

@@ -13,7 +13,8 @@
 //                            [3] status (0 ok, 1 = a wait ran out), [4..6] which wait / rank / call, [7] CTAs finished
 //     [1 KB, 2 KB)   flags   int32[world]: flags[r] = last epoch for which rank r's data is ready (written BY rank r)
 //     [2 KB, 3 KB)   flags2  int32[world]: two-shot form: rank r's reduced slice is ready
-//     [4 KB, ...)    data[2][slot] then red[2][slot]: the staged partials (by epoch parity) and the reduced slices
+//     [4 KB, 16 KB)  per-tile flags int32[world][384] of the all-reduce fused into K2's epilogue (k2_gemm.cu)
+//     [16 KB, ...)   data[2][slot] then red[2][slot]: the staged partials (by epoch parity) and the reduced slices
 // One call on rank q:  (1) every CTA copies its share of `src` into data[epoch & 1] of its OWN buffer; the last CTA to
 // finish that (an arrival counter -- no CTA waits for another CTA of its grid) publishes flags[q] = epoch in every
 // peer's buffer with a system-scope release.  (2) every CTA waits, bounded, until its own buffer's flags[r] >= epoch for
@@ -29,13 +30,11 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
-#include "../../include/onebase_b200.h"
+#include "ob_common.cuh"
 
 namespace ob {
 
 constexpr int kArThreads = 256;
-constexpr int kArStateBytes = 4096;
-constexpr int kArFlagsOff = 1024, kArFlags2Off = 2048;
 
 struct ArParams {
     int world, rank;

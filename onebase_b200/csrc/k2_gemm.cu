@@ -225,6 +225,71 @@ __device__ __forceinline__ void store_b_tile(const K2Params& p, const BCodes& r,
     }
 }
 
+// ---- all-reduce fused into the epilogue (see K2Params.ar_*).  System-scope flag and data accesses as in allreduce.cu.
+__device__ __forceinline__ void ar_st_release_sys(int32_t* p, int32_t v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int32_t ar_ld_acquire_sys(const int32_t* p) {
+    int32_t v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint4 ar_ld_peer16(const void* p) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+
+// Called by the 128 epilogue threads of the CTA that holds the FINISHED values of output tile `tile` once they are staged
+// (bf16, [token row][N]) in this rank's communication buffer: announce the tile to every rank, wait (bounded) for every
+// rank's copy of it, add the copies in rank order with fp32 accumulation, store y.  Same arithmetic as the stand-alone
+// all-reduce kernel, so the results are bitwise equal to "K2, then ob_allreduce".
+__device__ void ar_finish_tile(const K2Params& p, K2Ctrl* ctrl, int te, int tile, int32_t epoch, int tn, int slice_off, int n0_local,
+                               int n_s, uint64_t limit_ns) {
+    uint8_t* own = p.ar_bufs[p.ar_rank];
+    const size_t data_off = (size_t)kArStateBytes + (size_t)(epoch & 1) * (size_t)p.ar_slot_bytes;
+    asm volatile("bar.sync 1, 128;" ::: "memory");            // every thread's staged values precede the announcement
+    if (te < p.ar_world) {
+        __threadfence();
+        ar_st_release_sys(reinterpret_cast<int32_t*>(p.ar_bufs[te] + kArTileFlagsOff) + p.ar_rank * kArMaxTiles + tile, epoch);
+        const int32_t* flag = reinterpret_cast<const int32_t*>(own + kArTileFlagsOff) + te * kArMaxTiles + tile;
+        const uint64_t t0 = global_timer_ns();
+        bool ok = false;
+        for (uint32_t spin = 0;; ++spin) {
+            if (ar_ld_acquire_sys(flag) - epoch >= 0) { ok = true; break; }
+            if ((spin & 63u) == 63u && global_timer_ns() - t0 > limit_ns) break;
+        }
+        if (!ok) record_timeout(p, ctrl, 20 + te, tile);     // 20 + the rank whose tile did not arrive
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (ctrl->abort_flag) return;
+    for (int idx = te; idx < tn * (kTileN / 8); idx += 128) {
+        const int c = idx / (kTileN / 8), n8 = (idx % (kTileN / 8)) * 8;
+        const int row = ctrl->rowmap[c];
+        const int left = n_s - (n0_local + n8);
+        if (row < 0 || left <= 0) continue;
+        const size_t off = data_off + ((size_t)row * p.N + (size_t)(slice_off + n0_local + n8)) * 2;
+        uint4 v[OB_MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < OB_MAX_RANKS; ++r)
+            if (r < p.ar_world) v[r] = ar_ld_peer16(p.ar_bufs[r] + off);
+        float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int r = 0; r < OB_MAX_RANKS; ++r)
+            if (r < p.ar_world) {
+                acc[0] += bf16_lo(v[r].x); acc[1] += bf16_hi(v[r].x); acc[2] += bf16_lo(v[r].y); acc[3] += bf16_hi(v[r].y);
+                acc[4] += bf16_lo(v[r].z); acc[5] += bf16_hi(v[r].z); acc[6] += bf16_lo(v[r].w); acc[7] += bf16_hi(v[r].w);
+            }
+        __nv_bfloat16* yr = p.y + (int64_t)row * p.ldy + slice_off + n0_local + n8;
+        if (left >= 8 && (((uintptr_t)yr) & 15) == 0) {
+            *reinterpret_cast<uint4*>(yr) = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
+                                                      pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
+        } else {
+            for (int u = 0; u < 8 && u < left; ++u) yr[u] = __float2bfloat16_rn(acc[u]);
+        }
+    }
+}
+
 // Fused decode form: the warps of every CTA except the producer and the MMA issuer claim the shrink kernel's work
 // (positions to quantize, then shrink units) from two counters before they take up their GEMM roles.  A claimed piece of
 // work never waits for another CTA, so the launch cannot deadlock however its CTAs are scheduled.
@@ -823,6 +888,13 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
             const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
             const bool has_lora = n_steps > 0;
             float* part = p.part + ((size_t)tile_lin * p.split2 + j) * (size_t)tn * kTileN;
+            // fused all-reduce: finished values go to this rank's staged copy ([token row][N] bf16) instead of y
+            const bool ar = p.ar_world > 0;
+            const int32_t ar_epoch = ar ? *reinterpret_cast<const volatile int32_t*>(p.ar_bufs[p.ar_rank]) + 1 : 0;
+            __nv_bfloat16* ydst = ar ? reinterpret_cast<__nv_bfloat16*>(p.ar_bufs[p.ar_rank] + kArStateBytes +
+                                                                      (size_t)(ar_epoch & 1) * (size_t)p.ar_slot_bytes)
+                                     : p.y;
+            const int64_t yld = ar ? (int64_t)p.N : p.ldy;
             {
                 for (int c0 = 0; c0 < tn; c0 += 16) {
                     uint32_t r0[16], r1[16];
@@ -835,7 +907,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                         float v = __uint_as_float(r0[c]) * (ctrl->sx[c0 + c] * s_w);
                         if (has_lora) v += __uint_as_float(r1[c]);
                         if (p.split2 == 1) {
-                            if (row >= 0 && n_ok) p.y[(int64_t)row * p.ldy + n_glob] = __float2bfloat16_rn(v);
+                            if (row >= 0 && n_ok) ydst[(int64_t)row * yld + n_glob] = __float2bfloat16_rn(v);
                         } else if (p.cluster_reduce) {
                             reinterpret_cast<float*>(ring)[(c0 + c) * kTileN + n_local] = v;   // the ring is idle by now
                         } else {
@@ -844,6 +916,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                     }
                 }
             }
+            if (ar && p.split2 == 1) ar_finish_tile(p, ctrl, te, tile_lin, ar_epoch, tn, slice_off, n0_local, n_s, limit_ns);
             if (p.split2 > 1 && !p.cluster_reduce) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");    // all 128 threads' partials precede the arrival below
                 if (te == 0) {
@@ -876,7 +949,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                             const int c = cb + u * 4 + tg;
                             const int row = c < tn ? ctrl->rowmap[c] : -1;
                             if (row >= 0) {
-                                __nv_bfloat16* yr = p.y + (int64_t)row * p.ldy + slice_off + n0_local + n4;
+                                __nv_bfloat16* yr = ydst + (int64_t)row * yld + slice_off + n0_local + n4;
                                 const int left = n_s - (n0_local + n4);
                                 if (left > 0) yr[0] = __float2bfloat16_rn(acc[u].x);
                                 if (left > 1) yr[1] = __float2bfloat16_rn(acc[u].y);
@@ -886,6 +959,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                         }
                     }
                     if (te == 0) p.counters[tile_lin] = 0;
+                    if (ar) ar_finish_tile(p, ctrl, te, tile_lin, ar_epoch, tn, slice_off, n0_local, n_s, limit_ns);
                 }
             }
         }
@@ -934,6 +1008,16 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);
+    }
+    if (p.ar_world > 0 && tid == 0) {               // fused all-reduce: the last CTA of the launch advances the call count
+        int32_t* state = reinterpret_cast<int32_t*>(p.ar_bufs[p.ar_rank]);
+        const int32_t epoch = *reinterpret_cast<volatile int32_t*>(state) + 1;
+        __threadfence();
+        if (atomicAdd(state + 7, 1) == (int)(gridDim.x * gridDim.y * gridDim.z) - 1) {
+            state[7] = 0;
+            __threadfence();
+            *reinterpret_cast<volatile int32_t*>(state) = epoch;
+        }
     }
     if (FUSED && tid == 0) {                        // the last CTA of the launch clears the work counters for the next call
         const int total = (int)(gridDim.x * gridDim.y * gridDim.z);

@@ -487,7 +487,7 @@ struct SplitScratch {
 };
 
 int k2_prepare(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* sh, const Resolved& r, bool chain, K2Launch* out,
-               const SplitScratch* scratch = nullptr) {
+               const SplitScratch* scratch = nullptr, const ObComm* fused_ar = nullptr) {
     const ObLayerDesc& d = l->d;
     const WorkspaceLayout lay = workspace_layout(*sh);
     uint8_t* base = static_cast<uint8_t*>(ws);
@@ -545,7 +545,13 @@ int k2_prepare(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* s
                          : dim3((unsigned)l->n_tiles, (unsigned)r.split2, (unsigned)r.m_tiles);
     out->fp4 = d.base_fmt == OB_BASE_NVFP4;
     out->smem = k2_fp8_smem_bytes(r.tn, r.stages, l->rc, d.R, out->fp4 ? 1 : 0);
-    p.cluster_reduce = (scratch == nullptr && cluster_reduce_fits(l, r, out->smem)) ? 1 : 0;
+    p.cluster_reduce = (scratch == nullptr && fused_ar == nullptr && cluster_reduce_fits(l, r, out->smem)) ? 1 : 0;
+    if (fused_ar != nullptr) {      // the all-reduce of a row-parallel layer's output, inside the epilogue
+        p.ar_world = fused_ar->world;
+        p.ar_rank = fused_ar->rank;
+        p.ar_slot_bytes = (long long)fused_ar->slot_bytes;
+        for (int q = 0; q < fused_ar->world; ++q) p.ar_bufs[q] = static_cast<uint8_t*>(fused_ar->bufs[q]);
+    }
     return OB_OK;
 }
 
@@ -960,8 +966,6 @@ int ob_segment_index(const int32_t* token_lora, int32_t M, int32_t L, int32_t* t
 // ---------------------------------------------------------------------------------------------------------------
 // all-reduce over peer-mapped memory
 namespace {
-constexpr size_t kArStateBytes = 4096;
-
 int ar_fill(const ObComm* c, const void* src, void* dst, int64_t count, int32_t dtype, int32_t mode, int32_t wait_ms, ArParams* p) {
     if (!c || !src || !dst) return OB_ERR_NULL;
     if (c->world < 2 || c->world > OB_MAX_RANKS || c->rank < 0 || c->rank >= c->world) return OB_ERR_SHAPE;
@@ -994,6 +998,50 @@ int ar_grid(int64_t count, int32_t dtype) {
     return (int)(g < 1 ? 1 : g > cap ? cap : g);
 }
 }  // namespace
+
+// Can K2's epilogue carry the all-reduce of this call?  Decode batches on the tile-per-CTA kernel, features in whole 16-byte
+// groups, one flag per output tile, and the [M, N] bf16 partial must fit a slot of the communication buffer.
+static bool fused_allreduce_applies(const ObLayer* l, const ObBatch* b, const Resolved& r, const ObComm* c) {
+    if (r.big || r.stream || r.m_tiles != 1 || r.tn > kDecodeTokens) return false;
+    if (l->n_tiles > kArMaxTiles || l->d.N % 8 != 0) return false;
+    for (int s = 0; s < l->d.S; ++s)
+        if (l->d.widths[s] % 8 != 0) return false;
+    return (size_t)b->M * (size_t)l->d.N * 2 <= c->slot_bytes;
+}
+
+int ob_chain_allreduce(ObLayer* layer, const ObBatch* batch, void* workspace, const ObWorkspaceShape* shape, const ObTileCfg* cfg,
+                       const ObComm* comm, void* cuda_stream) {
+    if (!comm) return OB_ERR_NULL;
+    if (comm->world < 2 || comm->world > OB_MAX_RANKS || comm->rank < 0 || comm->rank >= comm->world || comm->slot_bytes % 16 != 0)
+        return OB_ERR_SHAPE;
+    for (int q = 0; q < comm->world; ++q)
+        if (!comm->bufs[q] || !aligned16(comm->bufs[q])) return OB_ERR_NULL;
+    if (!layer) return OB_ERR_NULL;
+    Resolved r;
+    int st = prepare_call(layer, batch, workspace, shape, cfg, &r, layer->d.base_fmt);
+    if (st != OB_OK) return st;
+    cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+    const int wait_ms = (cfg && cfg->wait_ms > 0) ? cfg->wait_ms : 2000;
+    if (!fused_allreduce_applies(layer, batch, r, comm)) {
+        // the chain as usual, then the stand-alone all-reduce kernel over y (which must then be a dense [M, N] matrix)
+        if (batch->ldy != layer->d.N || !aligned16(batch->y)) return OB_ERR_ALIGN;
+        if (fused_applies(layer, r)) st = fused_impl(layer, batch, workspace, shape, r, stream);
+        else {
+            st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream, r.stream != 0);
+            if (st == OB_OK) st = k2_fp8_impl(layer, batch, workspace, shape, r, 1, stream, r.stream != 0);
+        }
+        if (st != OB_OK) return st;
+        return ob_allreduce(comm, batch->y, batch->y, (int64_t)batch->M * layer->d.N, OB_DTYPE_BF16, OB_AR_AUTO, wait_ms, cuda_stream);
+    }
+    st = k1_fp8_impl(layer, batch, workspace, shape, r, 1, stream);
+    if (st != OB_OK) return st;
+    K2Launch k;
+    st = k2_prepare(layer, batch, workspace, shape, r, false, &k, nullptr, comm);
+    if (st != OB_OK) return st;
+    cudaError_t e = k.fp4 ? launch_k2_nvfp4(k.p, layer->tm_w, k.tm_x, layer->tm_b, k.grid, k.smem, 1, stream)
+                          : launch_k2_fp8(k.p, layer->tm_w, k.tm_x, layer->tm_b, k.grid, k.smem, 1, stream);
+    return e == cudaSuccess ? OB_OK : (int)e;
+}
 
 int ob_comm_bytes(size_t slot_bytes, size_t* bytes) {
     if (!bytes) return OB_ERR_NULL;

@@ -19,7 +19,11 @@ constexpr int kMmaShrinkTokens = 512;   // batches from this size on shrink on t
 constexpr int kDecodeTokens = 32;     // batches up to this size take the decode forms (one position per shrink warp)
 constexpr int kCounterSlots = 4096;  // split-K arrival counters in the workspace
 constexpr int kStreamMaxCtas = 256;  // most CTAs of the persistent decode GEMM (one per SM)
-constexpr int kSfSlotBytes = 2048;   // NVFP4: scale factors of 128 rows x one 256-element K slot (4 atoms of 512 bytes)
+constexpr int kSfSlotBytes = 2048;
+// Peer-memory all-reduce: layout of a rank's communication buffer (see allreduce.cu)
+constexpr int kArStateBytes = 16384;  // state words, rank flags, per-tile flags; the staged copies follow
+constexpr int kArFlagsOff = 1024, kArFlags2Off = 2048, kArTileFlagsOff = 4096;
+constexpr int kArMaxTiles = 384;      // per-tile flags [world][kArMaxTiles] of the all-reduce fused into K2's epilogue   // NVFP4: scale factors of 128 rows x one 256-element K slot (4 atoms of 512 bytes)
 
 __host__ __device__ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
@@ -186,6 +190,12 @@ struct K2Params {
     int shrink_units;      // fused: position blocks x units per block
     unsigned long long* trace;   // optional timeline buffer (null: off)
     long long trace_ctas;
+    // All-reduce fused into the epilogue (row-parallel layers under tensor parallelism; ar_world = 0: off): a finished tile is
+    // staged in this rank's communication buffer, announced to every peer by a per-tile flag, and the CTA then adds the
+    // ranks' copies of ITS tile in rank order and stores y -- no separate all-reduce launch, no second pass over y.
+    int ar_world, ar_rank;
+    long long ar_slot_bytes;
+    uint8_t* ar_bufs[OB_MAX_RANKS];
 };
 
 // Warp-wide: n_all = sum of seg_n, n_ad = sum of seg_n over segments whose slot id >= 0 (L+1 segments).

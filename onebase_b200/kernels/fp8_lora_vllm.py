@@ -218,14 +218,18 @@ class VllmFusedFP8LoRA:
         return b, y
 
     def __call__(self, x, meta_args, out=None, cfg: dict | None = None, pdl: bool = True, shrink: bool = True,
-                 gemm: bool = True):
+                 gemm: bool = True, allreduce=None):
         """y = x W^T (FP8, x quantized per token as vLLM does) + every tenant's expansion.  pdl=False runs the same two
-        kernels serialized; shrink=False / gemm=False run one kernel alone (breakdowns and tests)."""
+        kernels serialized; shrink=False / gemm=False run one kernel alone (breakdowns and tests).  allreduce = a
+        tp.PeerComm: this is a row-parallel shard and y is summed over the ranks inside K2's epilogue (ob_chain_allreduce)."""
         b, y = self._batch(x, meta_args, out)
         t = self.tile(b.M, cfg)
         ws, sh = C.c_void_p(self.scratch.ptr), C.byref(self.scratch.shape)
         st = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
-        if shrink and gemm and pdl:
+        if allreduce is not None:
+            assert shrink and gemm and y.is_contiguous()
+            _lib.call("ob_chain_allreduce", self._h, C.byref(b), ws, sh, C.byref(t), C.byref(allreduce.comm), st)
+        elif shrink and gemm and pdl:
             _lib.call(self._CHAIN, self._h, C.byref(b), ws, sh, C.byref(t), st)
         else:
             if shrink:

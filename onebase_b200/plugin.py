@@ -36,7 +36,7 @@ import torch
 _REGISTRY: list = []          # layer id -> op object
 _INSTALLED = False
 _CALLED = [False]
-_STATS = {"fused_layers": 0, "fallback_layers": 0}
+_STATS = {"fused_layers": 0, "fallback_layers": 0, "segment_index_kernel": 0, "segment_index_stock": 0}
 _LAUNCH = {"pdl": True, "pdl_max_m": 0}   # how the op launches its two kernels; filled from the environment by install()
 
 
@@ -79,12 +79,14 @@ def segment_index_prepare(orig, index_fn=None):
         fits = (t.dtype in (torch.int32, torch.int64) and t.ndim == 1 and 0 < max_loras <= 256 and
                 0 < t.numel() <= self.token_lora_mapping.numel())
         if not fits or (index_fn is None and not t.is_cuda):
+            _STATS["segment_index_stock"] += 1
             return orig(self, t)               # (an empty mapping too: vLLM treats it as a batch without adapters)
         if t.dtype != torch.int32 or not t.is_contiguous():
             # vLLM's PunicaWrapperGPU hands over a slice of its int64 `_token_lora_indices` (punica_base.py): slot ids
             # fit 32 bits, and the cast is one small device-side copy in the same stream
             t = t.to(torch.int32).contiguous()
         (index_fn or _device_segment_index)(self, t, max_loras)
+        _STATS["segment_index_kernel"] += 1
         counts = self.num_tokens_per_lora.cpu()                 # the step's only device -> host copy (it synchronizes)
         groups = int((counts > 0).sum())                        # unique ids of the batch, the "-1" group included
         if hasattr(self, "no_lora_flag_cpu"):

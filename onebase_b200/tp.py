@@ -271,6 +271,7 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
     M = args.m
     sharded = getattr(args, "tp_form", "partial") == "sharded"   # row-parallel layers with sharded adapters
     use_nccl = getattr(args, "tp_comm", "peer") == "nccl"
+    fuse_ar = getattr(args, "tp_comm", "peer") == "fused" and not sharded   # the all-reduce inside K2's epilogue
     warmup = max(3, args.warmup)
     g = torch.Generator(device=dev).manual_seed(0)            # same seed on every rank: identical full tensors, then sharded
     ids = torch.randint(0, L_SLOTS, (M,), generator=torch.Generator().manual_seed(0), dtype=torch.int32).to(dev)
@@ -339,17 +340,23 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
             chain("o", gemm=False)
             reduce(hp_o)
             chain("o", shrink=False)
+            reduce(y_o)
+        elif fuse_ar:
+            chain("o", allreduce=comm)
         else:
             chain("o")
-        reduce(y_o)
+            reduce(y_o)
         chain("gate_up")
         if sharded:
             chain("down", gemm=False)
             reduce(hp_down)
             chain("down", shrink=False)
+            reduce(y_down)
+        elif fuse_ar:
+            chain("down", allreduce=comm)
         else:
             chain("down")
-        reduce(y_down)
+            reduce(y_down)
 
     def log(msg):
         if os.environ.get("LOWBIT_VERBOSE"):
@@ -518,14 +525,15 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
             "warmup": warmup, "ms_per_step": ms_v, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp8_e4m3", "data": "synthetic",
             "config": {"workload": f"Qwen3-8B decoder layer at tensor-parallel {world}: column-parallel qkv / gate_up, row-parallel "
-                                   f"o / down + all-reduce of y ({'NCCL' if use_nccl else 'peer-memory kernel, in the graph'})"
+                                   f"o / down + all-reduce of y ({'NCCL' if use_nccl else 'over peer memory inside K2 epilogues' if fuse_ar else 'peer-memory kernel, in the graph'})"
                                    f"{' (adapters sharded too: all-reduce of the shrink partials before the expand)' if sharded else ''}"
                                    f"; FP8 base, decode M={M}, 32 bf16 tenants rank 64 ({distinct} distinct)",
                        "l2": "flushed by a 256 MB write before every timed step",
                        "cuda_graph": (f"{len(graphs)} graphs; the NCCL all-reduces are launched between them" if use_nccl
+                                      else "one graph: 8 fused kernels per rank, the two all-reduces inside K2's epilogues" if fuse_ar
                                       else "one graph: 8 fused kernels + 2 all-reduce kernels per rank")},
             "layer_us": ms_v * 1e3, "allreduce_us_alone": ar_us, "config4": config4,
-            "gpu_launches": (8 if use_nccl else 10) * args.steps,   # our kernels per step: four K1, four K2 (+ two all-reduces)
+            "gpu_launches": (8 if use_nccl or fuse_ar else 10) * args.steps,   # our kernels per step: four K1, four K2 (+ two all-reduces)
             "device_status_ok": bool(ok.item()),
             "tp_check": {"max_abs_err_over_ymax_vs_sum_of_rank_partials": exact, "exchange_bound": exact_bound,
                          "max_abs_err_over_ymax_vs_unsharded_op": check, "unsharded_bound": 6e-2,

@@ -1,4 +1,4 @@
-"""The plugin inside a real vLLM engine (opt-in: ONEBASE_VLLM_ENGINE_TEST=1; needs vLLM and ~2 minutes).
+"""The plugin inside a real vLLM engine (runs whenever vLLM imports; ONEBASE_VLLM_ENGINE_TEST=0 skips it; ~2 minutes a case).
 
 A child process builds a small random-init Qwen3-architecture checkpoint (2 layers, hidden 1024, GQA 8/2) and three
 random rank-16 LoRA adapters under a temporary directory -- bf16 weights that vLLM quantizes online to per-tensor FP8, or
@@ -6,7 +6,9 @@ a ModelOpt NVFP4 checkpoint (packed e2m1 codes, linear ue4m3 block scales, weigh
 the oracle's recipe --, starts `vllm.LLM(..., enable_lora=True)` in eager mode with the plugin installed, and wraps every LoRA linear class that overrides `apply` so that each call runs BOTH
 the fused path and vLLM's own path on the same input.  Checked: every LoRA linear layer was taken over (no fallback), the
 opaque op was called, and the two paths agree within the output bound on every call of a mixed batch (prefill and decode,
-one request without an adapter).  The engine runs in a child process so that its memory pool and process groups do not
+one request without an adapter).  A third case runs the FP8 engine with LOWBIT_SEGMENT_INDEX=1, i.e. with vLLM's per-step
+token sort / segment index built by the ob_segment_index kernel, and checks that the kernel path was really taken on the
+mappings vLLM's Punica wrapper passes.  The engine runs in a child process so that its memory pool and process groups do not
 outlive the test.
 """
 import os
@@ -21,6 +23,9 @@ pytestmark = pytest.mark.gpu
 CHILD = textwrap.dedent('''
     import collections, inspect, json, os, sys, tempfile
     BASE = sys.argv[1]                                   # "fp8": online per-tensor FP8; "nvfp4": a ModelOpt NVFP4 checkpoint
+    if BASE.endswith("+segidx"):                         # ... "+segidx": the segment index kernel behind vLLM's metadata
+        BASE = BASE[:-7]
+        os.environ["LOWBIT_SEGMENT_INDEX"] = "1"
     os.environ.setdefault("VLLM_ENABLE_V1_MULTIPROCESSING", "0")
     os.environ["LOWBIT_FUSED"] = "1"
     work = tempfile.mkdtemp(prefix="ob_vllm_")
@@ -109,12 +114,14 @@ CHILD = textwrap.dedent('''
     rep = open(os.environ["LOWBIT_REPORT"]).read().splitlines()
     print("RESULT " + json.dumps({"fused": sum(" fused" in l for l in rep), "fallback": sum("fallback" in l for l in rep),
                                   "op_called": any("op-called" in l for l in rep), "generated": [len(o.outputs[0].token_ids) for o in outs],
-                                  "max_err": {k: max(v) for k, v in errs.items()}, "calls": {k: len(v) for k, v in errs.items()}}))
+                                  "max_err": {k: max(v) for k, v in errs.items()}, "calls": {k: len(v) for k, v in errs.items()},
+                                  "segment_index": {"installed": any("segment-index kernel installed" in l for l in rep),
+                                                    "kernel": plugin._STATS["segment_index_kernel"], "stock": plugin._STATS["segment_index_stock"]}}))
 ''')
 
 
-@pytest.mark.skipif(os.environ.get("ONEBASE_VLLM_ENGINE_TEST") != "1", reason="opt-in: set ONEBASE_VLLM_ENGINE_TEST=1 (starts a vLLM engine)")
-@pytest.mark.parametrize("base", ["fp8", "nvfp4"])
+@pytest.mark.skipif(os.environ.get("ONEBASE_VLLM_ENGINE_TEST") == "0", reason="ONEBASE_VLLM_ENGINE_TEST=0 (starts a vLLM engine)")
+@pytest.mark.parametrize("base", ["fp8", "nvfp4", "fp8+segidx"])
 def test_plugin_inside_vllm_engine(base):
     import json
     pytest.importorskip("vllm")
@@ -128,3 +135,5 @@ def test_plugin_inside_vllm_engine(base):
     assert r["generated"] == [8] * 6, r
     assert r["max_err"] and all(c > 0 for c in r["calls"].values()), r
     assert max(r["max_err"].values()) <= 2e-2, r                                 # fused vs vLLM's own path, same inputs
+    if base.endswith("+segidx"):
+        assert r["segment_index"]["installed"] and r["segment_index"]["kernel"] > 0, r
