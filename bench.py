@@ -402,7 +402,7 @@ def main() -> None:
         g1 = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g1):
             op(x, meta, out=y)
-        per_proj[name] = statistics.median(time_events(g1.replay, 30, 5, flush)) * 1e3
+        per_proj[name] = statistics.fmean(time_events(g1.replay, 30, 5, flush)) * 1e3
     op, x, y = layer["gate_up"]
     op(x, meta, out=y)
     k2_ms = statistics.fmean(time_events(graph_of(lambda: op(x, meta, out=y, shrink=False, pdl=False)).replay, 50, 5, flush))

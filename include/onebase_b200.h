@@ -48,6 +48,7 @@ extern "C" {
 #define OB_DEV_WAIT_TIMEOUT 1    /* a bounded wait ran out; words 1..7 say where */
 
 enum { OB_BASE_FP8 = 0, OB_BASE_NVFP4 = 1 };
+enum { OB_X_PLAIN = 0, OB_X_SILU_MUL = 1 };
 enum { OB_LORA_BF16 = 0, OB_LORA_FP8 = 1, OB_LORA_NVFP4 = 2 };
 
 #define OB_MAX_SLICES 4
@@ -105,6 +106,17 @@ typedef struct ObBatch {
     const int32_t* seg_n;            /* [L+1] tokens per segment                     num_tokens_per_lora */
     const int32_t* seg_start;        /* [L+2] segment start offsets                  lora_token_start_loc */
     const int32_t* seg_ids;          /* [L+1] slot id per segment, -1 padded         active_lora_ids */
+    /* The ops either side of the projection, fused (all optional; zero / null = off):
+     *   x_op = OB_X_SILU_MUL   the projection's input is silu(gate) * up of the preceding merged projection: x is its
+     *        output [M, 2K] (gate | up, row pitch ldx >= 2K) and K1 forms bf16(bf16(silu(g)) * u) on the fly -- vLLM's
+     *        SiluAndMul (vllm/model_executor/layers/activation.py, forward_native) without its pass over memory -- before
+     *        quantizing and shrinking it.  For down_proj.
+     *   residual   [M, N] bf16, row pitch ldr: K2 stores y = bf16(bf16(acc) + residual) -- the "x + residual" of vLLM's
+     *        fused add + RMSNorm that follows o_proj and down_proj (vllm/model_executor/layers/layernorm.py,
+     *        forward_native: the sum in fp32, rounded to the residual's dtype).  May be the same memory as y. */
+    int32_t x_op;
+    const void* residual;
+    int64_t ldr;
 } ObBatch;
 
 /* Capacity of a shared workspace (what the reference's Scratch.ensure / _Work.ensure grow,

@@ -16,6 +16,7 @@ OB_MAX_SLICES = 4
 OB_STATUS_WORDS = 16
 OB_BASE_FP8, OB_BASE_NVFP4 = 0, 1
 OB_LORA_BF16, OB_LORA_FP8, OB_LORA_NVFP4 = 0, 1, 2
+OB_X_PLAIN, OB_X_SILU_MUL = 0, 1
 OB_WS = {name: i for i, name in enumerate(("status", "counters", "sx", "xq", "xsf", "hp", "part", "xs", "hb", "hcat"))}
 
 
@@ -40,6 +41,7 @@ class ObBatch(C.Structure):
     _fields_ = [
         ("M", C.c_int32), ("x", C.c_void_p), ("ldx", C.c_int64), ("y", C.c_void_p), ("ldy", C.c_int64),
         ("tok", C.c_void_p), ("srt", C.c_void_p), ("seg_n", C.c_void_p), ("seg_start", C.c_void_p), ("seg_ids", C.c_void_p),
+        ("x_op", C.c_int32), ("residual", C.c_void_p), ("ldr", C.c_int64),
     ]
 
 

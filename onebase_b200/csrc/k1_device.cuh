@@ -38,6 +38,29 @@ __device__ __forceinline__ uint2 quant8(const uint4& v, float sx) {
     return o;
 }
 
+// Eight consecutive elements k .. k+7 of the projection's INPUT row as bf16 pairs.  Plain: the row of x itself.  SiLU * mul
+// (down_proj): x holds the merged gate | up output [2K]; the input is silu(gate) * up, formed as vLLM's SiluAndMul forms
+// it: silu in fp32, rounded to bf16, times up, rounded to bf16 (activation.py, forward_native).
+// XOP is a template parameter: the plain kernels must not carry the activation's code (after an L2 flush every
+// instruction line of a launch is a cold fetch, and K1 sits on the chain's critical path).
+template <bool XOP>
+__device__ __forceinline__ uint4 x_load8(const K1Params& p, const __nv_bfloat16* xrow, int k) {
+    const uint4 g = __ldg(reinterpret_cast<const uint4*>(xrow + k));
+    if (!XOP) return g;
+    const uint4 u = __ldg(reinterpret_cast<const uint4*>(xrow + p.K + k));
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float g0 = bf16_lo(gw[i]), g1 = bf16_hi(gw[i]);
+        const __nv_bfloat162 s2 = __floats2bfloat162_rn(__fdiv_rn(g0, 1.0f + expf(-g0)), __fdiv_rn(g1, 1.0f + expf(-g1)));
+        const uint32_t sb = *reinterpret_cast<const uint32_t*>(&s2);
+        const __nv_bfloat162 r2 = __floats2bfloat162_rn(bf16_lo(sb) * bf16_lo(uw[i]), bf16_hi(sb) * bf16_hi(uw[i]));
+        o[i] = *reinterpret_cast<const uint32_t*>(&r2);
+    }
+    return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 // The row of x that tile position `pos` stands for (warp-wide call).
 __device__ __forceinline__ int row_of_position(const K1Params& p, int pos, int lane) {
     const int sorted_row = p.meta.srt[pos];            // requested together with the segment index (one latency, not two)
@@ -48,17 +71,17 @@ __device__ __forceinline__ int row_of_position(const K1Params& p, int pos, int l
 }
 
 // NT threads (tid in [0, NT)) that meet at named barrier BAR quantize row `row` of x into position `pos`.
-template <int NT, int BAR>
+template <int NT, int BAR, bool XOP = false>
 __device__ void quantize_row(const K1Params& p, int pos, int row, int tid) {
     __shared__ float s_part[NT / 32];
     __shared__ float s_scale;
     const int lane = tid & 31, warp = tid >> 5;
-    const uint4* xr = reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.ldx);
+    const __nv_bfloat16* xr = p.x + (int64_t)row * p.ldx;
     const int nvec = p.K >> 3;
     // Pass 1: every load of the row in flight at once (the loop is short code: a row has at most a few vectors per thread).
     float amax = 0.0f;
 #pragma unroll 4
-    for (int i = tid; i < nvec; i += NT) amax = fmaxf(amax, amax8(__ldg(xr + i)));
+    for (int i = tid; i < nvec; i += NT) amax = fmaxf(amax, amax8(x_load8<XOP>(p, xr, i * 8)));
 #pragma unroll
     for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if (lane == 0) s_part[warp] = amax;
@@ -76,7 +99,7 @@ __device__ void quantize_row(const K1Params& p, int pos, int row, int tid) {
     // Pass 2 re-reads the row (it is in L1 now) in a rolled loop: the eight IEEE divisions per vector are long code, and a
     // batch runs this code on few SMs, so every instruction line of an unrolled copy would be fetched cold.
 #pragma unroll 1
-    for (int i = tid; i < nvec; i += NT) out[i] = quant8(__ldg(xr + i), sx);
+    for (int i = tid; i < nvec; i += NT) out[i] = quant8(x_load8<XOP>(p, xr, i * 8), sx);
     named_bar_sync<BAR, NT>();                        // s_part / s_scale may be reused by the group's next position
 }
 
@@ -105,10 +128,10 @@ __device__ __forceinline__ float e4m3_to_float(uint32_t code) {
 // rcp(sf * rcp(gs)) : 0, code = e2m1_rn(x * out_scale); codes packed two per byte (element 2i in the low nibble).  One
 // thread per block.  The scales go straight into K2's scale-factor atoms: [token tile][K slot][128-token block][MMA][r%32]
 // [r/32][4], r = position within the token tile.
-template <int NT>
+template <int NT, bool XOP = false>
 __device__ void quantize_row_nvfp4(const K1Params& p, int pos, int row, int tid) {
     const float gs = __ldg(p.x_global);
-    const uint4* xr = reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.ldx);
+    const __nv_bfloat16* xr = p.x + (int64_t)row * p.ldx;
     const float rcp6 = p.rcp_approx ? rcp_approx_ftz(6.0f) : __frcp_rn(6.0f);
     const float rgs = p.rcp_approx ? rcp_approx_ftz(gs) : __frcp_rn(gs);
     const int nblocks = p.K >> 4;
@@ -119,8 +142,8 @@ __device__ void quantize_row_nvfp4(const K1Params& p, int pos, int row, int tid)
         uint32_t sf_code = 0;
         if (b < nblocks) {
             float v[16];
-            unpack8(__ldg(xr + 2 * b), *reinterpret_cast<float(*)[8]>(&v[0]));
-            unpack8(__ldg(xr + 2 * b + 1), *reinterpret_cast<float(*)[8]>(&v[8]));
+            unpack8(x_load8<XOP>(p, xr, 16 * b), *reinterpret_cast<float(*)[8]>(&v[0]));
+            unpack8(x_load8<XOP>(p, xr, 16 * b + 8), *reinterpret_cast<float(*)[8]>(&v[8]));
             float vmax = 0.0f;
 #pragma unroll
             for (int e = 0; e < 16; ++e) vmax = fmaxf(vmax, fabsf(v[e]));
@@ -246,7 +269,7 @@ __device__ __forceinline__ float post_scale(const K1Params& p, int lora, int s, 
 // One pass of a warp: 8 rank rows [k0, k1) of adapter `lora`, slice s, times the `nt` (<= 4) tokens whose x rows are
 // rows[0..nt); writes the split-K partial hp[j][s][pos0 + t][rg*8 .. +8].  bf16 adapters.  The first block of A is
 // requested before the wait on the preceding kernel (A is static); x is read and hp written only after it.
-template <int FMT>
+template <int FMT, bool XOP = false>
 __device__ __forceinline__ void shrink_pass(const K1Params& p, int lora, int s, int rg, int j, int k0, int k1, int pos0,
                                                  const int* rows, int nt, int lane) {
     const ARows<FMT> a(p, lora, s, rg);
@@ -268,7 +291,7 @@ __device__ __forceinline__ void shrink_pass(const K1Params& p, int lora, int s, 
 #pragma unroll
         for (int t = 0; t < 4; ++t) {
             if (t < nt && act) {
-                unpack8(__ldg(reinterpret_cast<const uint4*>(xrow[t] + k)), xf[t]);
+                unpack8(x_load8<XOP>(p, xrow[t], k), xf[t]);
             } else {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) xf[t][e] = 0.0f;
@@ -308,7 +331,7 @@ __device__ __forceinline__ void fma8(float (&acc)[8], const uint4 (&av)[8], cons
 
 // Decode form of the pass (one token): two K steps of A in flight per lane (8 KB per warp), both requested before the wait
 // on the preceding kernel.  8 lane-partials -> lanes 0..7 hold the 8 rank rows' sums (2 butterfly + 3 transposing steps).
-template <int FMT>
+template <int FMT, bool XOP = false>
 __device__ __forceinline__ void shrink_pass1(const K1Params& p, int lora, int s, int rg, int j, int k0, int k1, int pos,
                                                   int row, int lane) {
     const ARows<FMT> a(p, lora, s, rg);
@@ -325,9 +348,9 @@ __device__ __forceinline__ void shrink_pass1(const K1Params& p, int lora, int s,
     for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
     for (int k = kl; k < k1; k += 512) {
         float x0[8], x1[8];
-        unpack8(__ldg(reinterpret_cast<const uint4*>(xrow + k)), x0);
+        unpack8(x_load8<XOP>(p, xrow, k), x0);
         if (k + 256 < k1) {
-            unpack8(__ldg(reinterpret_cast<const uint4*>(xrow + k + 256)), x1);
+            unpack8(x_load8<XOP>(p, xrow, k + 256), x1);
         } else {
 #pragma unroll
             for (int e = 0; e < 8; ++e) x1[e] = 0.0f;
@@ -359,7 +382,7 @@ __device__ __forceinline__ void shrink_pass1(const K1Params& p, int lora, int s,
 // One warp-wide read of the segment index gives the batch totals and the segment (adapter) of each of the warp's
 // positions; the positions' token rows are requested at the same time.  Then one pass per run of positions that share
 // an adapter.
-template <int FMT>
+template <int FMT, bool XOP = false>
 __device__ void shrink_unit(const K1Params& p, int pb, int u, int lane) {
     const int p0 = pb * p.pb;
     int rows[4];
@@ -403,7 +426,7 @@ __device__ void shrink_unit(const K1Params& p, int pb, int u, int lane) {
     const int k0 = j * p.k_per_split;
     const int k1 = min(p.K, k0 + p.k_per_split);
     if (p.pb == 1) {
-        if (lora_of[0] >= 0) shrink_pass1<FMT>(p, lora_of[0], s, rg, j, k0, k1, p0, rows[0], lane);
+        if (lora_of[0] >= 0) shrink_pass1<FMT, XOP>(p, lora_of[0], s, rg, j, k0, k1, p0, rows[0], lane);
         return;
     }
     int q = 0;
@@ -411,7 +434,7 @@ __device__ void shrink_unit(const K1Params& p, int pb, int u, int lane) {
         const int lora = lora_of[q];
         int nt = 1;
         while (q + nt < np && lora_of[q + nt] == lora) ++nt;
-        if (lora >= 0) shrink_pass<FMT>(p, lora, s, rg, j, k0, k1, p0 + q, rows + q, nt, lane);
+        if (lora >= 0) shrink_pass<FMT, XOP>(p, lora, s, rg, j, k0, k1, p0 + q, rows + q, nt, lane);
         q += nt;
     }
 }

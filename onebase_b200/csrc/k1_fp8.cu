@@ -28,19 +28,20 @@ constexpr int kK1Threads = 256;
 // One instantiation per (adapter storage, base format): each launch carries only the code of its own case.
 // LOOPED: the one-CTA-per-SM form that runs beside the persistent GEMM; a function of its own, because the shared-memory
 // carve-out it needs (see launch_k1_impl) is a per-function attribute and costs the other form its L1 cache.
-template <int LORA_FMT, bool FP4_BASE, bool LOOPED>
-__global__ void __launch_bounds__(kK1Threads) k1_kernel(const K1Params p) {
+// XOP: the projection's input is formed from x on the fly (OB_X_SILU_MUL); plain launches run an instantiation without it.
+template <int LORA_FMT, bool FP4_BASE, bool LOOPED, bool XOP>
+__global__ void __launch_bounds__(kK1Threads, XOP ? 2 : 0) k1_kernel(const K1Params p) {
     griddep_launch_dependents();
     OB_TRACE1(0)
     if ((int)blockIdx.x < p.n_quant_ctas) {
         const int row = row_of_position(p, blockIdx.x, threadIdx.x & 31);
         griddep_wait();                               // x comes from the preceding kernel; the scratch may still be read by it
-        if (FP4_BASE) quantize_row_nvfp4<kK1Threads>(p, blockIdx.x, row, threadIdx.x);
-        else quantize_row<kK1Threads, 0>(p, blockIdx.x, row, threadIdx.x);
+        if (FP4_BASE) quantize_row_nvfp4<kK1Threads, XOP>(p, blockIdx.x, row, threadIdx.x);
+        else quantize_row<kK1Threads, 0, XOP>(p, blockIdx.x, row, threadIdx.x);
         if (p.xs != nullptr) {                        // the tensor-core shrink reads x in position order by TMA
-            const uint4* xr = reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.ldx);
+            const __nv_bfloat16* xr = p.x + (int64_t)row * p.ldx;
             uint4* xo = reinterpret_cast<uint4*>(p.xs + (size_t)blockIdx.x * (size_t)p.K);
-            for (int i = threadIdx.x; i < (p.K >> 3); i += kK1Threads) xo[i] = __ldg(xr + i);
+            for (int i = threadIdx.x; i < (p.K >> 3); i += kK1Threads) xo[i] = x_load8<XOP>(p, xr, i * 8);
         }
         if (p.xq_ready != nullptr) {          // chain: tell K2 that this position's codes and scale are in memory
             __syncthreads();
@@ -57,14 +58,14 @@ __global__ void __launch_bounds__(kK1Threads) k1_kernel(const K1Params p) {
         const long long total = (long long)p.n_pblocks * p.units_per_block;
         const long long stride = (long long)gridDim.x * (kK1Threads / 32);
         for (long long w = (long long)blockIdx.x * (kK1Threads / 32) + (threadIdx.x >> 5); w < total; w += stride)
-            shrink_unit<LORA_FMT>(p, (int)(w / p.units_per_block), (int)(w % p.units_per_block), lane);
+            shrink_unit<LORA_FMT, XOP>(p, (int)(w / p.units_per_block), (int)(w % p.units_per_block), lane);
         OB_TRACE1(3)
         return;
     }
     const int w = ((int)blockIdx.x - p.n_quant_ctas) * (kK1Threads / 32) + (threadIdx.x >> 5);
     const int pb = w / p.units_per_block;
     if (pb >= p.n_pblocks) return;
-    shrink_unit<LORA_FMT>(p, pb, w % p.units_per_block, lane);
+    shrink_unit<LORA_FMT, XOP>(p, pb, w % p.units_per_block, lane);
     OB_TRACE1(3)
 }
 
@@ -78,9 +79,9 @@ __global__ void __launch_bounds__(kK1Threads, 4) k1_quant_kernel(const K1Params 
     if (FP4_BASE) quantize_row_nvfp4<kK1Threads>(p, blockIdx.x, row, threadIdx.x);
     else quantize_row<kK1Threads, 0>(p, blockIdx.x, row, threadIdx.x);
     if (p.xs != nullptr) {
-        const uint4* xr = reinterpret_cast<const uint4*>(p.x + (int64_t)row * p.ldx);
+        const __nv_bfloat16* xr = p.x + (int64_t)row * p.ldx;
         uint4* xo = reinterpret_cast<uint4*>(p.xs + (size_t)blockIdx.x * (size_t)p.K);
-        for (int i = threadIdx.x; i < (p.K >> 3); i += kK1Threads) xo[i] = __ldg(xr + i);
+        for (int i = threadIdx.x; i < (p.K >> 3); i += kK1Threads) xo[i] = x_load8<false>(p, xr, i * 8);
     }
 }
 
@@ -104,16 +105,17 @@ static cudaError_t launch_k1_impl(const K1Params& p, int grid, int pdl, cudaStre
         static std::atomic<unsigned long long> carved{0};
         int dev = 0;
         if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !(carved.load() & (1ull << dev))) {
-            cudaError_t e = cudaFuncSetAttribute(k1_kernel<LORA_FMT, FP4_BASE, true>, cudaFuncAttributePreferredSharedMemoryCarveout,
+            cudaError_t e = cudaFuncSetAttribute(k1_kernel<LORA_FMT, FP4_BASE, true, false>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                                  (int)cudaSharedmemCarveoutMaxShared);
             if (e != cudaSuccess) return e;
             carved.fetch_or(1ull << dev);
         }
-        return cudaLaunchKernelEx(&cfg, k1_kernel<LORA_FMT, FP4_BASE, true>, p);
+        return cudaLaunchKernelEx(&cfg, k1_kernel<LORA_FMT, FP4_BASE, true, false>, p);
     }
+    if (p.x_op != OB_X_PLAIN) return cudaLaunchKernelEx(&cfg, k1_kernel<LORA_FMT, FP4_BASE, false, true>, p);
     if (grid == p.n_quant_ctas && p.xq_ready == nullptr && p.trace == nullptr)   // no shrink warps in this launch
         return cudaLaunchKernelEx(&cfg, k1_quant_kernel<FP4_BASE>, p);
-    return cudaLaunchKernelEx(&cfg, k1_kernel<LORA_FMT, FP4_BASE, false>, p);
+    return cudaLaunchKernelEx(&cfg, k1_kernel<LORA_FMT, FP4_BASE, false, false>, p);
 }
 
 cudaError_t launch_k1_fp8(const K1Params& p, int grid, int pdl, cudaStream_t stream) {

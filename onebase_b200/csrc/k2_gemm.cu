@@ -62,6 +62,7 @@ struct K2Ctrl {
     float sx[256];
     int rowmap[256];
     LoraStep steps[kMaxLoraIters];
+    uint64_t code_full[12];   // stored adapters: the step's codes and scales have landed in the slot
 };
 static_assert(sizeof(K2Ctrl) <= kCtrlBytes, "control block too large");
 
@@ -153,6 +154,15 @@ __device__ __forceinline__ float k2_e4m3_value(uint32_t code) {
     return __half2float(__ushort_as_half((unsigned short)(h2 & 0xFFFFu)));
 }
 
+// The value K2 stores for an accumulated fp32 result: bf16(acc), or with a residual stream bf16(bf16(acc) + residual): the
+// "x + residual" of vLLM's fused add + RMSNorm (layernorm.py, forward_native: fp32 sum of the two bf16 tensors).
+template <bool EXTRA>
+__device__ __forceinline__ __nv_bfloat16 k2_out(const K2Params& p, float v, int64_t row, int64_t col) {
+    const __nv_bfloat16 y = __float2bfloat16_rn(v);
+    if (!EXTRA || p.residual == nullptr) return y;
+    return __float2bfloat16_rn(__bfloat162float(y) + __bfloat162float(p.residual[row * p.ldr + col]));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
     __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&b);
@@ -192,6 +202,41 @@ __device__ __forceinline__ void load_b_codes(const K2Params& p, const LoraStep& 
     }
 }
 
+// The same row of codes and scales out of the ring slot, where the producer's bulk copies put them: codes of row r at
+// slot + 8192 + r * (R or R/2) bytes, scales (fp32 per row, or one ue4m3 byte per 16 elements) at slot + 16384.  (The rank
+// chunk is the whole rank in this form.)
+__device__ __forceinline__ void load_b_codes_smem(const K2Params& p, const LoraStep& e, int s, int n_s, int n0_local, int te,
+                                                  const uint8_t* slot, BCodes& r) {
+    const bool ok = n0_local + te < n_s;
+    const int groups = p.rc / 16;
+    if (p.lora_fmt == kLoraFp8) {
+        const uint4* src = reinterpret_cast<const uint4*>(slot + 8192 + (size_t)te * p.R);
+        r.sc = ok ? *reinterpret_cast<const float*>(slot + 16384 + (size_t)te * 4) : 0.0f;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) r.c[g] = (ok && g < groups) ? src[g] : make_uint4(0u, 0u, 0u, 0u);
+    } else {
+        const uint2* src = reinterpret_cast<const uint2*>(slot + 8192 + (size_t)te * (p.R / 2));
+        const uint8_t* sfp = slot + 16384 + (size_t)te * (p.R / 16);
+        r.sc = __ldg(p.bg + (size_t)s * p.L + e.lora);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const bool in = ok && g < groups;
+            const uint2 c = in ? src[g] : make_uint2(0u, 0u);
+            r.c[g] = make_uint4(c.x, c.y, in ? (uint32_t)sfp[g] : 0u, 0u);
+        }
+    }
+}
+
+// Four e2m1 codes (the nibbles of the low 16 bits of w4) -> four bf16 values of bf16(value * block scale * global), through
+// byte tables of the block's eight magnitudes: two byte permutes pick the low and the high bytes of the four results,
+// two more interleave them, the codes' sign bits are ORed in.
+__device__ __forceinline__ void e2m1x4_lookup(uint32_t w4, const uint32_t (&lo)[2], const uint32_t (&hi)[2], uint32_t& out01, uint32_t& out23) {
+    const uint32_t sel = w4 & 0x7777u;
+    const uint32_t L = __byte_perm(lo[0], lo[1], sel), H = __byte_perm(hi[0], hi[1], sel);
+    out01 = __byte_perm(L, H, 0x5140u) | ((w4 & 0x8u) << 12) | ((w4 & 0x80u) << 24);
+    out23 = __byte_perm(L, H, 0x7362u) | ((w4 & 0x800u) << 4) | ((w4 & 0x8000u) << 16);
+}
+
 __device__ __forceinline__ void store_b_tile(const K2Params& p, const BCodes& r, uint8_t* tile, int te, int row_bytes, uint32_t swz) {
     const uint32_t row_off = (uint32_t)te * (uint32_t)row_bytes;
     const int groups = p.rc / 16;
@@ -208,12 +253,16 @@ __device__ __forceinline__ void store_b_tile(const K2Params& p, const BCodes& r,
                 }
             } else {                                           // one block of 16 codes (8 bytes) + its scale
                 const float sf = k2_e4m3_value(r.c[g].z);      // (0 for rows past the slice's width: their codes are 0 too)
-                const uint32_t w[2] = {r.c[g].x, r.c[g].y};
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    const uint32_t b8 = (w[q >> 2] >> (8 * (q & 3))) & 0xFFu;      // two codes: element 2q in the low nibble
-                    o[q] = pack_bf16x2(k2_e2m1_value(b8 & 15u) * sf * r.sc, k2_e2m1_value(b8 >> 4) * sf * r.sc);
-                }
+                // the block's eight magnitudes bf16((value * block scale) * global) -- the reference's order of the two
+                // products, one fp32 rounding -- as byte tables
+                const uint32_t m01 = pack_bf16x2(0.0f, (0.5f * sf) * r.sc), m23 = pack_bf16x2((1.0f * sf) * r.sc, (1.5f * sf) * r.sc);
+                const uint32_t m45 = pack_bf16x2((2.0f * sf) * r.sc, (3.0f * sf) * r.sc), m67 = pack_bf16x2((4.0f * sf) * r.sc, (6.0f * sf) * r.sc);
+                const uint32_t lo[2] = {__byte_perm(m01, m23, 0x6420u), __byte_perm(m45, m67, 0x6420u)};
+                const uint32_t hi[2] = {__byte_perm(m01, m23, 0x7531u), __byte_perm(m45, m67, 0x7531u)};
+                e2m1x4_lookup(r.c[g].x, lo, hi, o[0], o[1]);   // element 2q in the low nibble of byte q: nibble order = element order
+                e2m1x4_lookup(r.c[g].x >> 16, lo, hi, o[2], o[3]);
+                e2m1x4_lookup(r.c[g].y, lo, hi, o[4], o[5]);
+                e2m1x4_lookup(r.c[g].y >> 16, lo, hi, o[6], o[7]);
             }
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
@@ -281,7 +330,9 @@ __device__ void ar_finish_tile(const K2Params& p, K2Ctrl* ctrl, int te, int tile
                 acc[4] += bf16_lo(v[r].z); acc[5] += bf16_hi(v[r].z); acc[6] += bf16_lo(v[r].w); acc[7] += bf16_hi(v[r].w);
             }
         __nv_bfloat16* yr = p.y + (int64_t)row * p.ldy + slice_off + n0_local + n8;
-        if (left >= 8 && (((uintptr_t)yr) & 15) == 0) {
+        if (p.residual != nullptr) {
+            for (int u = 0; u < 8 && u < left; ++u) yr[u] = k2_out<true>(p, acc[u], row, slice_off + n0_local + n8 + u);
+        } else if (left >= 8 && (((uintptr_t)yr) & 15) == 0) {
             *reinterpret_cast<uint4*>(yr) = make_uint4(pack_bf16x2(acc[0], acc[1]), pack_bf16x2(acc[2], acc[3]),
                                                       pack_bf16x2(acc[4], acc[5]), pack_bf16x2(acc[6], acc[7]));
         } else {
@@ -315,7 +366,9 @@ __device__ __forceinline__ void fused_shrink_units(const K2Params& p, const K1Pa
     }
 }
 
-template <bool FP4, bool STORED, bool FUSED>
+// EXTRA: the launch adds a residual stream in its stores; every other launch runs an instantiation without that code (a
+// launch's instruction lines are cold fetches after an L2 flush, and the per-element branches lengthen the epilogue).
+template <bool FP4, bool STORED, bool FUSED, bool EXTRA>
 __global__ void __launch_bounds__(kK2Threads, 2)
 k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
               const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
@@ -368,6 +421,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
             mbar_init(&ctrl->full_b[i], 1);
             mbar_init(&ctrl->empty[i], 1);
             mbar_init(&ctrl->empty_b[i], 1);
+            if (STORED) mbar_init(&ctrl->code_full[i], 1);
         }
         for (int i = 0; i < 8; ++i) {
             mbar_init(&ctrl->h_full[i], 1);
@@ -481,6 +535,22 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                     } else {
                         // The slot is free (this thread saw its release, in order, like every slot's): hand it to warps
                         // 4-7 through a count, which -- unlike a barrier phase awaited late -- cannot be mistaken.
+                        if (p.b_staged) {
+                            // ... with the step's codes and scales already on their way into the slot's upper half (the
+                            // dequantized tile will overwrite them only after every thread has taken its row into
+                            // registers): the ring's depth, not one step, is how far the adapter bytes run ahead.
+                            const LoraStep e = ctrl->steps[w.li];
+                            const uint32_t rows = (uint32_t)min(kTileN, n_s - n0_local);
+                            const size_t row0 = (size_t)e.lora * n_s + (size_t)n0_local;
+                            uint8_t* slot = ring + (size_t)st * stage_bytes;
+                            const uint32_t code_bytes = p.lora_fmt == kLoraFp8 ? rows * (uint32_t)p.R : rows * (uint32_t)p.R / 2;
+                            const uint32_t scale_bytes = p.lora_fmt == kLoraFp8 ? rows * 4u : rows * (uint32_t)p.R / 16;
+                            const size_t code_off = p.lora_fmt == kLoraFp8 ? row0 * p.R : row0 * p.R / 2;
+                            const size_t scale_off = p.lora_fmt == kLoraFp8 ? row0 * 4 : row0 * p.R / 16;
+                            mbar_arrive_expect_tx(&ctrl->code_full[st], code_bytes + scale_bytes);
+                            bulk_load(slot + 8192, static_cast<const uint8_t*>(p.b[s]) + code_off, code_bytes, &ctrl->code_full[st]);
+                            bulk_load(slot + 16384, static_cast<const uint8_t*>(p.sb[s]) + scale_off, scale_bytes, &ctrl->code_full[st]);
+                        }
                         __threadfence_block();
                         ctrl->b_grant = w.li + 1;
                     }
@@ -785,7 +855,9 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
         if (stored || !small) {
             SlotWalk w(lead);
             BCodes cur;                                       // stored adapters: this step's codes, requested a step ahead
-            if (STORED && n_steps > 0) load_b_codes(p, ctrl->steps[0], s, n_s, n0_local, te, cur);
+            const bool staged = STORED && p.b_staged != 0;    // ... or brought into the slot by the producer's bulk copies
+            uint32_t par_c = 0;                               // per slot: phase of its code barrier
+            if (STORED && !staged && n_steps > 0) load_b_codes(p, ctrl->steps[0], s, n_s, n0_local, te, cur);
             for (int li = 0; li < n_steps; ++li) {
                 while (!w.is_b(n_base, n_steps)) w.advance(false, n_base, n_steps);   // the W slots in between
                 const int st = w.it % p.stages;
@@ -806,6 +878,10 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                             }
                         }
                         __threadfence_block();
+                        if (go && staged && !mbar_wait(&ctrl->code_full[st], (par_c >> st) & 1u, limit_ns)) {
+                            record_timeout(p, ctrl, 17, w.it);
+                            go = 0;
+                        }
                     }
                     if (go && !small && hu > 0 && !mbar_wait(&ctrl->h_empty[hb], (uint32_t)((hu - 1) & 1), limit_ns)) {
                         record_timeout(p, ctrl, 10, li);
@@ -817,10 +893,17 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                 if (!ctrl->go_flag) break;
                 const LoraStep e = ctrl->steps[li];
                 if constexpr (STORED) {
-                    BCodes nxt = cur;
-                    if (li + 1 < n_steps) load_b_codes(p, ctrl->steps[li + 1], s, n_s, n0_local, te, nxt);   // in flight during the stores
-                    store_b_tile(p, cur, ring + (size_t)st * stage_bytes, te, row_bytes, swz);
-                    cur = nxt;
+                    if (staged) {
+                        par_c ^= 1u << st;
+                        load_b_codes_smem(p, e, s, n_s, n0_local, te, ring + (size_t)st * stage_bytes, cur);
+                        asm volatile("bar.sync 1, 128;" ::: "memory");    // every row is in registers before the tile overwrites the codes
+                        store_b_tile(p, cur, ring + (size_t)st * stage_bytes, te, row_bytes, swz);
+                    } else {
+                        BCodes nxt = cur;
+                        if (li + 1 < n_steps) load_b_codes(p, ctrl->steps[li + 1], s, n_s, n0_local, te, nxt);   // in flight during the stores
+                        store_b_tile(p, cur, ring + (size_t)st * stage_bytes, te, row_bytes, swz);
+                        cur = nxt;
+                    }
                 }
                 if (!small) {
                 uint8_t* hdst = hbuf + (size_t)hb * h_bytes;
@@ -889,7 +972,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
             const bool has_lora = n_steps > 0;
             float* part = p.part + ((size_t)tile_lin * p.split2 + j) * (size_t)tn * kTileN;
             // fused all-reduce: finished values go to this rank's staged copy ([token row][N] bf16) instead of y
-            const bool ar = p.ar_world > 0;
+            const bool ar = p.ar_world > 0;   // a run-time flag in every instantiation: measured faster than compiling it out
             const int32_t ar_epoch = ar ? *reinterpret_cast<const volatile int32_t*>(p.ar_bufs[p.ar_rank]) + 1 : 0;
             __nv_bfloat16* ydst = ar ? reinterpret_cast<__nv_bfloat16*>(p.ar_bufs[p.ar_rank] + kArStateBytes +
                                                                       (size_t)(ar_epoch & 1) * (size_t)p.ar_slot_bytes)
@@ -907,7 +990,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                         float v = __uint_as_float(r0[c]) * (ctrl->sx[c0 + c] * s_w);
                         if (has_lora) v += __uint_as_float(r1[c]);
                         if (p.split2 == 1) {
-                            if (row >= 0 && n_ok) ydst[(int64_t)row * yld + n_glob] = __float2bfloat16_rn(v);
+                            if (row >= 0 && n_ok) ydst[(int64_t)row * yld + n_glob] = ar ? __float2bfloat16_rn(v) : k2_out<EXTRA>(p, v, row, n_glob);
                         } else if (p.cluster_reduce) {
                             reinterpret_cast<float*>(ring)[(c0 + c) * kTileN + n_local] = v;   // the ring is idle by now
                         } else {
@@ -949,12 +1032,13 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                             const int c = cb + u * 4 + tg;
                             const int row = c < tn ? ctrl->rowmap[c] : -1;
                             if (row >= 0) {
-                                __nv_bfloat16* yr = ydst + (int64_t)row * yld + slice_off + n0_local + n4;
+                                const int64_t col = slice_off + n0_local + n4;
+                                __nv_bfloat16* yr = ydst + (int64_t)row * yld + col;
                                 const int left = n_s - (n0_local + n4);
-                                if (left > 0) yr[0] = __float2bfloat16_rn(acc[u].x);
-                                if (left > 1) yr[1] = __float2bfloat16_rn(acc[u].y);
-                                if (left > 2) yr[2] = __float2bfloat16_rn(acc[u].z);
-                                if (left > 3) yr[3] = __float2bfloat16_rn(acc[u].w);
+                                const float vv[4] = {acc[u].x, acc[u].y, acc[u].z, acc[u].w};
+#pragma unroll
+                                for (int e = 0; e < 4; ++e)
+                                    if (left > e) yr[e] = ar ? __float2bfloat16_rn(vv[e]) : k2_out<EXTRA>(p, vv[e], row, col + e);
                             }
                         }
                     }
@@ -987,7 +1071,10 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
                 if (row >= 0) {
                     __nv_bfloat16* yr = p.y + (int64_t)row * p.ldy + slice_off + n0_local + n4;
                     const int left = n_s - (n0_local + n4);
-                    if (left >= 4 && (((uintptr_t)yr) & 7) == 0) {
+                    if (EXTRA && p.residual != nullptr) {
+                        const float vv[4] = {acc.x, acc.y, acc.z, acc.w};
+                        for (int e = 0; e < 4 && e < left; ++e) yr[e] = k2_out<true>(p, vv[e], row, slice_off + n0_local + n4 + e);
+                    } else if (left >= 4 && (((uintptr_t)yr) & 7) == 0) {
                         __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
                         *reinterpret_cast<uint2*>(yr) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
                     } else {
@@ -1009,7 +1096,7 @@ k2_kernel(const K2Params p, const __grid_constant__ CUtensorMap tm_w, const __gr
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);
     }
-    if (p.ar_world > 0 && tid == 0) {               // fused all-reduce: the last CTA of the launch advances the call count
+    if (p.ar_world > 0 && tid == 0) {      // fused all-reduce: the last CTA of the launch advances the call count
         int32_t* state = reinterpret_cast<int32_t*>(p.ar_bufs[p.ar_rank]);
         const int32_t epoch = *reinterpret_cast<volatile int32_t*>(state) + 1;
         __threadfence();
@@ -1043,7 +1130,7 @@ size_t k2_fp8_smem_bytes(int tn, int stages, int rc, int R, int fp4) {
     return 1024 + (size_t)stages * (kWTileBytes + (size_t)tn * kBlockK + sf) + aux + kCtrlBytes;
 }
 
-template <bool FP4, bool STORED, bool FUSED>
+template <bool FP4, bool STORED, bool FUSED, bool EXTRA = false>
 static cudaError_t launch_k2_impl(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                                   dim3 grid, size_t smem, int pdl, cudaStream_t stream, const K1Params& k1) {
     static int configured_for[64] = {0};
@@ -1052,9 +1139,9 @@ static cudaError_t launch_k2_impl(const K2Params& p, const CUtensorMap& tm_w, co
     if (e != cudaSuccess) return e;
     if (dev >= 0 && dev < 64 && !configured_for[dev]) {
         cudaFuncAttributes fa;                    // the opt-in limit covers static + dynamic shared memory
-        e = cudaFuncGetAttributes(&fa, k2_kernel<FP4, STORED, FUSED>);
+        e = cudaFuncGetAttributes(&fa, k2_kernel<FP4, STORED, FUSED, EXTRA>);
         if (e != cudaSuccess) return e;
-        e = cudaFuncSetAttribute(k2_kernel<FP4, STORED, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        e = cudaFuncSetAttribute(k2_kernel<FP4, STORED, FUSED, EXTRA>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  227 * 1024 - (int)fa.sharedSizeBytes);
         if (e != cudaSuccess) return e;
         configured_for[dev] = 1;
@@ -1080,13 +1167,13 @@ static cudaError_t launch_k2_impl(const K2Params& p, const CUtensorMap& tm_w, co
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    return cudaLaunchKernelEx(&cfg, k2_kernel<FP4, STORED, FUSED>, p, tm_w, tm_x, tm_b[0], tm_b[1], tm_b[2], tm_b[3], k1);
+    return cudaLaunchKernelEx(&cfg, k2_kernel<FP4, STORED, FUSED, EXTRA>, p, tm_w, tm_x, tm_b[0], tm_b[1], tm_b[2], tm_b[3], k1);
 }
 
 // How many clusters of `split2` CTAs (grid y) of this kernel the current device keeps resident at once; 0 on error.
 template <bool FP4, bool STORED>
 static int max_clusters_impl(int split2, size_t smem) {
-    cudaError_t e = cudaFuncSetAttribute(k2_kernel<FP4, STORED, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(k2_kernel<FP4, STORED, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e != cudaSuccess) return 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(64, (unsigned)split2, 1);
@@ -1100,7 +1187,7 @@ static int max_clusters_impl(int split2, size_t smem) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    e = cudaOccupancyMaxActiveClusters(&n, k2_kernel<FP4, STORED, false>, &cfg);
+    e = cudaOccupancyMaxActiveClusters(&n, k2_kernel<FP4, STORED, false, false>, &cfg);
     if (e != cudaSuccess) { (void)cudaGetLastError(); return 0; }
     return n;
 }
@@ -1113,6 +1200,9 @@ int k2_max_active_clusters(int fp4, int stored, int split2, size_t smem) {
 cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                           dim3 grid, size_t smem, int pdl, cudaStream_t stream) {
     const K1Params none = {};
+    if (p.residual != nullptr)
+        return p.lora_fmt == kLoraBf16 ? launch_k2_impl<false, false, false, true>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream, none)
+                                       : launch_k2_impl<false, true, false, true>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream, none);
     return p.lora_fmt == kLoraBf16 ? launch_k2_impl<false, false, false>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream, none)
                                    : launch_k2_impl<false, true, false>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream, none);
 }
@@ -1120,6 +1210,9 @@ cudaError_t launch_k2_fp8(const K2Params& p, const CUtensorMap& tm_w, const CUte
 cudaError_t launch_k2_nvfp4(const K2Params& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap* tm_b,
                             dim3 grid, size_t smem, int pdl, cudaStream_t stream) {
     const K1Params none = {};
+    if (p.residual != nullptr)
+        return p.lora_fmt == kLoraBf16 ? launch_k2_impl<true, false, false, true>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream, none)
+                                       : launch_k2_impl<true, true, false, true>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream, none);
     return p.lora_fmt == kLoraBf16 ? launch_k2_impl<true, false, false>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream, none)
                                    : launch_k2_impl<true, true, false>(p, tm_w, tm_x, tm_b, grid, smem, pdl, stream, none);
 }

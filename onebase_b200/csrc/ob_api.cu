@@ -173,7 +173,9 @@ int validate_batch(const ObLayer* l, const ObBatch* b) {
     if (!l || !b) return OB_ERR_NULL;
     if (b->M < 1 || b->M > l->d.max_m) return OB_ERR_BATCH;
     if (!b->x || !b->y || !b->tok || !b->srt || !b->seg_n || !b->seg_start || !b->seg_ids) return OB_ERR_NULL;
-    if (!aligned16(b->x) || b->ldx < l->d.K || b->ldx % 8 != 0) return OB_ERR_ALIGN;
+    if (b->x_op != OB_X_PLAIN && b->x_op != OB_X_SILU_MUL) return OB_ERR_FORMAT;
+    if (!aligned16(b->x) || b->ldx < (b->x_op == OB_X_SILU_MUL ? 2 : 1) * (int64_t)l->d.K || b->ldx % 8 != 0) return OB_ERR_ALIGN;
+    if (b->residual && ((reinterpret_cast<uintptr_t>(b->residual) & 1u) || b->ldr < l->d.N)) return OB_ERR_ALIGN;
     if ((reinterpret_cast<uintptr_t>(b->y) & 1u) || b->ldy < l->d.N) return OB_ERR_ALIGN;
     return OB_OK;
 }
@@ -378,6 +380,7 @@ K1Params k1_params(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShap
     p.units_per_block = d.S * (d.R / 8) * r.split1;
     p.x = static_cast<const __nv_bfloat16*>(b->x);
     p.ldx = b->ldx;
+    p.x_op = b->x_op;
     p.meta = meta_of(b);
     for (int s = 0; s < d.S; ++s) { p.a[s] = d.a[s]; p.sa[s] = d.sa[s]; }
     p.ag = d.ag;
@@ -518,6 +521,8 @@ int k2_prepare(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* s
     p.meta = meta_of(b);
     p.y = static_cast<__nv_bfloat16*>(b->y);
     p.ldy = b->ldy;
+    p.residual = static_cast<const __nv_bfloat16*>(b->residual);
+    p.ldr = b->ldr;
     p.part = reinterpret_cast<float*>(base + lay.part);
     p.counters = reinterpret_cast<int32_t*>(base + lay.counters);
     p.status = reinterpret_cast<int32_t*>(base + lay.status);
@@ -530,6 +535,12 @@ int k2_prepare(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* s
         p.b_rows[s] = s < d.S ? (d.b_rows[s] ? d.b_rows[s] : d.widths[s]) : 0;
     }
     p.bg = d.bg;
+    {   // stored adapters: bulk copies of a step's codes need whole-rank chunks and 16-byte granular rows
+        static const bool unstaged = [] { const char* v = std::getenv("LOWBIT_B_UNSTAGED"); return v && v[0] == '1'; }();
+        bool ok = d.lora_fmt != kLoraBf16 && d.R == l->rc && !unstaged;
+        for (int s = 0; s < d.S; ++s) ok = ok && d.widths[s] % 16 == 0;
+        p.b_staged = ok ? 1 : 0;
+    }
     p.trace = g_trace;
     p.trace_ctas = g_trace_ctas;
     if (scratch != nullptr) {
@@ -646,6 +657,15 @@ int prepare_call(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape*
     if (l->d.base_fmt != base_fmt) return OB_ERR_FORMAT;
     st = resolve_cfg(l, b->M, cfg, r);
     if (st != OB_OK) return st;
+    if (b->residual != nullptr) {                // the residual add lives in the tile kernel's stores
+        r->big = 0;
+        r->stream = 0;
+        r->fused = 0;
+    }
+    if (b->x_op != OB_X_PLAIN) {                 // the input transform lives in the two-CTAs-per-SM K1 only
+        r->fused = 0;
+        r->stream = 0;
+    }
     if (r->big && (!sh || sh->max_l < l->d.L)) r->big = 0;
     if (r->big && (b->ldy % 8 != 0 || !aligned16(b->y))) r->big = 0;   // its epilogue stores 16 bytes at a time
     return validate_workspace(l, ws, sh, r->split1, r->split2);

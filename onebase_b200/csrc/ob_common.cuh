@@ -90,6 +90,7 @@ struct K1Params {
     int units_per_block;   // shrink warps per position block: S * (R / 8) * split1
     const __nv_bfloat16* x;
     int64_t ldx;
+    int x_op;              // OB_X_SILU_MUL: x is [M, 2K] (gate | up) and the projection's input is bf16(bf16(silu(g)) * u)
     Meta meta;
     const void* a[OB_MAX_SLICES];
     const void* sa[OB_MAX_SLICES];
@@ -170,11 +171,14 @@ struct K2Params {
     Meta meta;
     __nv_bfloat16* y;
     int64_t ldy;
+    const __nv_bfloat16* residual;   // y = bf16(bf16(acc) + residual) (null: plain store)
+    int64_t ldr;
     float* part;
     int32_t* counters;
     int32_t* status;
     const void* b[OB_MAX_SLICES];
     const void* sb[OB_MAX_SLICES];
+    int b_staged;          // stored adapters: a step's codes and scales come by bulk copy into its ring slot (see k2_gemm.cu)
     int b_row0[OB_MAX_SLICES];   // first output feature of each slice whose B rows this rank holds (0 unless B is sharded)
     int b_rows[OB_MAX_SLICES];   // number of those rows (the slice's width unless B is sharded)
     const float* bg;

@@ -205,24 +205,31 @@ class VllmFusedFP8LoRA:
         return self.scratch.region("hp", 4 * n).view(torch.float32).view(split1, self.S, max_m, self.R)
 
     # ------------------------------------------------------------------------------------------------- the call
-    def _batch(self, x, meta_args, out):
+    def _batch(self, x, meta_args, out, silu_mul: bool = False, residual=None):
         tok, srt, seg_n, seg_start, seg_ids = meta_args[:5]
         M = x.shape[0]
-        assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[1] == self.K and x.stride(1) == 1
+        assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+        assert x.shape[1] == (2 * self.K if silu_mul else self.K)
         y = out if out is not None else torch.empty(M, self.N, dtype=torch.bfloat16, device=x.device)
         assert y.dtype == torch.bfloat16 and y.stride(1) == 1
         for t in (tok, srt, seg_n, seg_start, seg_ids):
             assert t.dtype == torch.int32 and t.is_cuda
         b = _lib.ObBatch(M, x.data_ptr(), x.stride(0), y.data_ptr(), y.stride(0), tok.data_ptr(), srt.data_ptr(),
                          seg_n.data_ptr(), seg_start.data_ptr(), seg_ids.data_ptr())
+        b.x_op = _lib.OB_X_SILU_MUL if silu_mul else _lib.OB_X_PLAIN
+        if residual is not None:
+            assert residual.dtype == torch.bfloat16 and residual.shape == (M, self.N) and residual.stride(1) == 1
+            b.residual, b.ldr = residual.data_ptr(), residual.stride(0)
         return b, y
 
     def __call__(self, x, meta_args, out=None, cfg: dict | None = None, pdl: bool = True, shrink: bool = True,
-                 gemm: bool = True, allreduce=None):
+                 gemm: bool = True, allreduce=None, silu_mul: bool = False, residual=None):
         """y = x W^T (FP8, x quantized per token as vLLM does) + every tenant's expansion.  pdl=False runs the same two
         kernels serialized; shrink=False / gemm=False run one kernel alone (breakdowns and tests).  allreduce = a
-        tp.PeerComm: this is a row-parallel shard and y is summed over the ranks inside K2's epilogue (ob_chain_allreduce)."""
-        b, y = self._batch(x, meta_args, out)
+        tp.PeerComm: this is a row-parallel shard and y is summed over the ranks inside K2's epilogue (ob_chain_allreduce).
+        silu_mul=True: x is the merged gate | up output [M, 2K] and the projection's input is silu(gate) * up, formed inside
+        K1 (down_proj).  residual = [M, N] bf16: K2 stores y + residual, the new residual stream (o_proj, down_proj)."""
+        b, y = self._batch(x, meta_args, out, silu_mul, residual)
         t = self.tile(b.M, cfg)
         ws, sh = C.c_void_p(self.scratch.ptr), C.byref(self.scratch.shape)
         st = C.c_void_p(torch.cuda.current_stream(x.device).cuda_stream)
