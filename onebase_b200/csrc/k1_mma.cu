@@ -201,7 +201,7 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
         const bool direct = p.split1 == 1;                     // no partials: the accumulator row is the finished h
         const bool cat = p.hcat != nullptr;                    // per-tenant blocks, pre-divided by the output scale
         __nv_bfloat16* cdst = cat ? p.hcat + ((size_t)s * p.max_m + (size_t)pos) * ((size_t)p.lc * p.R) : nullptr;
-        const float inv = (cat && pos < p.M) ? 1.0f / (__ldcg(p.sx + pos) * __ldg(p.s_w)) : 0.0f;
+        const float inv = (cat && pos < p.M) ? 1.0f / ((p.sx ? __ldcg(p.sx + pos) : 1.0f) * __ldg(p.s_w)) : 0.0f;   // NVFP4 base: one scale for every token
         for (int pass = 0; pass < n_pass; ++pass) {
             const int g0 = pass * group, ng = min(group, n_list - g0);
             int go = 1;

@@ -17,7 +17,13 @@ int k2_fp8_h_tiles(int tn);
 int k2_max_active_clusters(int fp4, int stored, int split2, size_t smem);
 cudaError_t launch_k1_mma(const K1mParams& p, const CUtensorMap& tm_xs, const CUtensorMap* tm_a, dim3 grid, cudaStream_t stream);
 cudaError_t launch_k2_prefill(const K2pParams& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap& tm_h,
-                              const CUtensorMap* tm_b, dim3 grid, int pdl, cudaStream_t stream);
+                              const CUtensorMap* tm_b, dim3 grid, int fp4, int pdl, cudaStream_t stream);
+int k2_prefill_max_steps();
+cudaError_t launch_k2_prefill_pair(const K2pParams& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap& tm_h,
+                                   const CUtensorMap* tm_b, int pairs, int fp4, int pdl, cudaStream_t stream);
+int k2_prefill_pair_capacity(int fp4);
+int k2_prefill_pair_max_steps();
+int k2_prefill_pair_rows(int fp4);
 cudaError_t launch_requant_fp8(const void* src, long long rows, int cols, void* codes, float* scales, cudaStream_t stream);
 cudaError_t launch_requant_nvfp4(const void* src, int l, int rows, int cols, void* packed, void* sf, float* inv_global,
                                  unsigned int* amax_bits, cudaStream_t stream);
@@ -119,8 +125,8 @@ struct ObLayer {
     CUtensorMap tm_w;
     CUtensorMap tm_b[OB_MAX_SLICES];
     CUtensorMap tm_a[OB_MAX_SLICES];   // bf16 adapters: A of each slice as [L * R, K], for the tensor-core shrink
-    bool big_ok;                       // FP8 base, bf16 adapters of rank >= 64, slice widths in multiples of 256:
-    CUtensorMap tm_w2;                 //   the 256 x 256 prefill GEMM applies; W and B in 256-row boxes
+    bool big_ok;                       // bf16 adapters of rank >= 64, slice widths in multiples of 256 (NVFP4 base: 128):
+    CUtensorMap tm_w2;                 //   the large-tile prefill GEMM applies; FP8 base: W and B in 256-row boxes
     CUtensorMap tm_b2[OB_MAX_SLICES];
     std::mutex mu;
     std::vector<XMap> xmaps;      // x_q maps by (workspace region, rows, token tile)
@@ -228,7 +234,7 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     r->tn = (cfg && cfg->tn) ? cfg->tn : default_tn(M);
     // NVFP4: the scale factors share tensor memory with the accumulators; 64-token tiles leave room for two CTAs per SM
     if (fp4 && r->tn > 64 && !(cfg && cfg->tn)) r->tn = 64;
-    if (fp4 && r->tn > 128) return OB_ERR_TILE;
+    if (fp4 && r->tn > 128) return OB_ERR_TILE;   // (the large-tile prefill GEMM has its own 256-token tile: `big` below)
     if (!(r->tn == 16 || r->tn == 32 || r->tn == 64 || r->tn == 128 || r->tn == 256)) return OB_ERR_TILE;
     r->m_tiles = (M + r->tn - 1) / r->tn;
     // Decode batches of bf16 adapters may take the persistent GEMM (k2_stream.cu): one CTA per SM streams a contiguous share
@@ -285,9 +291,10 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     static const bool no_big = [] { const char* v = std::getenv("LOWBIT_PREFILL_SMALL_TILES"); return v && v[0] == '1'; }();
     // ... and unless its 256 x 256 tiles would leave most of the 148 SMs idle (one CTA per SM): then k2_gemm.cu's 128 x 128
     // tiles, four times as many, are the better fit.
-    const long long big_tiles = (long long)((M + 255) / 256) * (d.N / 256);
+    const long long big_tiles = (long long)((M + 255) / 256) * (d.N / (fp4 ? 128 : 256));
+    const long long big_steps = 2LL * (d.L < kMaxTileTenants ? d.L : kMaxTileTenants) * (d.R / 64);   // a tile's expand steps at most
     r->big = (!no_big && r->mma_shrink && l->big_ok && M > kBigTileMinTokens && !(cfg && cfg->tn) &&
-              (pf == 1 || big_tiles >= 120)) ? 1 : 0;
+              big_steps <= k2_prefill_max_steps() && (pf == 1 || big_tiles >= 120)) ? 1 : 0;
     if (split1 == 0 && r->mma_shrink) {   // one wave of (128-position tile, slice, K split) CTAs, at least 256 elements each
         const int tiles = ((M + 127) / 128) * d.S;
         split1 = 1;
@@ -389,8 +396,8 @@ K1Params k1_params(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShap
     p.hp = reinterpret_cast<float*>(base + lay.hp);
     p.max_m = sh->max_m;
     p.base_fmt = d.base_fmt;
-    p.tn = r.tn;
-    p.nblk = r.tn > 128 ? 2 : 1;
+    p.tn = (r.big && d.base_fmt == OB_BASE_NVFP4) ? 256 : r.tn;   // the activation scales are laid out per token tile of K2
+    p.nblk = p.tn > 128 ? 2 : 1;
     p.kslots = (d.K + 255) / 256;
     p.rcp_approx = d.quant_rcp_approx;
     p.x_global = d.x_global;
@@ -437,8 +444,9 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     if (r.big) {
         m.hcat = reinterpret_cast<__nv_bfloat16*>(base + lay.hcat);
         m.lc = d.L < kMaxTileTenants ? d.L : kMaxTileTenants;
-        m.sx = reinterpret_cast<const float*>(base + lay.sx);
-        m.s_w = d.s_w;
+        const bool fp4 = d.base_fmt == OB_BASE_NVFP4;     // NVFP4: the output scale is alpha = 1 / (x_global * w_global) alone
+        m.sx = fp4 ? nullptr : reinterpret_cast<const float*>(base + lay.sx);
+        m.s_w = fp4 ? d.alpha : d.s_w;
     }
     if ((long long)((b->M + 127) / 128) * d.S > kCounterSlots) return OB_ERR_TOO_LARGE;
     dim3 mgrid((unsigned)((b->M + 127) / 128), (unsigned)d.S, (unsigned)r.split1);
@@ -571,27 +579,53 @@ int k2_prefill_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceSha
     const ObLayerDesc& d = l->d;
     const WorkspaceLayout lay = workspace_layout(*sh);
     uint8_t* base = static_cast<uint8_t*>(ws);
+    // Slices in whole tiles of the pair kernel (256 features with an NVFP4 base, 512 with FP8): CTA pairs (k2_prefill2.cu)
+    // unless LOWBIT_PREFILL_PAIRS=0
+    static const bool no_pairs = [] { const char* v = std::getenv("LOWBIT_PREFILL_PAIRS"); return v && v[0] == '0'; }();
+    const int is_fp4 = d.base_fmt == OB_BASE_NVFP4 ? 1 : 0;
+    const int pair_rows = k2_prefill_pair_rows(is_fp4);
+    bool pairs = !no_pairs;
+    for (int s = 0; s < d.S; ++s) pairs = pairs && d.widths[s] % pair_rows == 0;
+    // FP8 base: measured on a B200 the pair kernel wins on the short-K projections (qkv, gate_up: 3-7 %) and loses on the
+    // long-K one (down, K = 12288: its few, long tiles quantize worse over 74 pairs than over 148 single CTAs)
+    if (!is_fp4 && d.K > 8192) pairs = false;
+    const int pair_cap = pairs ? k2_prefill_pair_capacity(is_fp4) : 0;
+    pairs = pairs && pair_cap > 0;
+    if (std::getenv("LOWBIT_VERBOSE")) std::fprintf(stderr, "[onebase_b200] prefill GEMM: pairs=%d (resident pairs %d)\n", (int)pairs, pair_cap);
     CUtensorMap tm_x, tm_h;
-    int st = get_xmap(l, base + lay.xq, sh->max_m, 256, &tm_x);
+    int st = get_xmap(l, base + lay.xq, sh->max_m, pairs ? 128 : 256, &tm_x);
     if (st == OB_OK) st = get_xmap(l, base + lay.hcat, sh->max_m, -2, &tm_h);
     if (st != OB_OK) return st;
     K2pParams p = {};
     p.M = b->M; p.N = d.N; p.K = d.K; p.S = d.S; p.R = d.R; p.L = d.L;
     for (int s = 0; s < OB_MAX_SLICES; ++s) p.widths[s] = s < d.S ? d.widths[s] : 0;
-    p.kblocks = (d.K + kBlockK - 1) / kBlockK;
+    const bool fp4 = d.base_fmt == OB_BASE_NVFP4;
+    p.kblocks = (k_bytes(d) + kBlockK - 1) / kBlockK;
     p.stages = 3;
+    p.wsf = static_cast<const uint8_t*>(d.w_sf);
+    p.xsf = base + lay.xsf;
     p.lc = d.L < kMaxTileTenants ? d.L : kMaxTileTenants;
     p.max_m = sh->max_m;
     p.wait_ms = r.wait_ms;
-    p.s_w = d.s_w;
-    p.sx = reinterpret_cast<const float*>(base + lay.sx);
+    p.s_w = fp4 ? d.alpha : d.s_w;               // NVFP4: one output scale, no per-token factor
+    p.sx = fp4 ? nullptr : reinterpret_cast<const float*>(base + lay.sx);
     p.meta = meta_of(b);
     p.y = static_cast<__nv_bfloat16*>(b->y);
     p.ldy = b->ldy;
     p.status = reinterpret_cast<int32_t*>(base + lay.status);
-    if (d.N / 256 > 65535) return OB_ERR_TOO_LARGE;
-    dim3 grid((unsigned)((b->M + 255) / 256), 1u, (unsigned)(d.N / 256));
-    cudaError_t e = launch_k2_prefill(p, l->tm_w2, tm_x, tm_h, l->tm_b2, grid, pdl, stream);
+    if (pairs) {
+        const long long ptiles = (long long)((b->M + 255) / 256) * (d.N / pair_rows);
+        const int n = (int)(ptiles < pair_cap ? ptiles : pair_cap);
+        cudaError_t e = launch_k2_prefill_pair(p, l->tm_w, tm_x, tm_h, l->tm_b, n, is_fp4, pdl, stream);
+        return e == cudaSuccess ? OB_OK : (int)e;
+    }
+    const int rows = fp4 ? 128 : 256;            // output features per CTA
+    const long long tiles = (long long)((b->M + 255) / 256) * (d.N / rows);
+    const int sms = sm_count();
+    if (tiles > 0x7fffffffLL || sms <= 0) return OB_ERR_TOO_LARGE;
+    dim3 grid((unsigned)(tiles < sms ? tiles : sms), 1u, 1u);   // persistent: one CTA per SM walks the tiles
+    cudaError_t e = fp4 ? launch_k2_prefill(p, l->tm_w, tm_x, tm_h, l->tm_b, grid, 1, pdl, stream)
+                        : launch_k2_prefill(p, l->tm_w2, tm_x, tm_h, l->tm_b2, grid, 0, pdl, stream);
     return e == cudaSuccess ? OB_OK : (int)e;
 }
 
@@ -832,9 +866,10 @@ int ob_layer_create(const ObLayerDesc* desc, ObLayer** out) {
             }
         }
     }
-    l->big_ok = desc->base_fmt == OB_BASE_FP8 && desc->lora_fmt == OB_LORA_BF16 && desc->R >= 64 && !b_sharded(*desc);
-    for (int s = 0; s < desc->S; ++s) l->big_ok = l->big_ok && desc->widths[s] % 256 == 0;
-    if (st == OB_OK && l->big_ok) {
+    l->big_ok = desc->lora_fmt == OB_LORA_BF16 && desc->R >= 64 && !b_sharded(*desc);
+    for (int s = 0; s < desc->S; ++s) l->big_ok = l->big_ok && desc->widths[s] % (desc->base_fmt == OB_BASE_NVFP4 ? 128 : 256) == 0;
+    if (desc->base_fmt == OB_BASE_NVFP4 && desc->K % 256 != 0) l->big_ok = false;   // whole 256-element k-blocks
+    if (st == OB_OK && l->big_ok && desc->base_fmt == OB_BASE_FP8) {
         st = encode_2d(&l->tm_w2, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, desc->w_q, (uint64_t)desc->K, (uint64_t)desc->N, (uint64_t)desc->K,
                        kBlockK, 256);
         for (int s = 0; s < OB_MAX_SLICES && st == OB_OK; ++s) {

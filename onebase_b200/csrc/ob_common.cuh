@@ -14,7 +14,7 @@ constexpr int kTileN = 128;          // output features per GEMM tile (rows of W
 constexpr int kBlockK = 128;         // bytes of K per ring stage row (one 128-byte swizzle row)
 constexpr int kMaxLoraIters = 512;   // capacity of a CTA's list of (segment, rank chunk) expand steps
 constexpr int kMaxTileTenants = 128;  // tenants with a position in one 128-position block
-constexpr int kBigTileMinTokens = 128; // larger FP8 batches of bf16 adapters take the 256 x 256 prefill GEMM
+constexpr int kBigTileMinTokens = 128; // larger batches of bf16 adapters take the large-tile prefill GEMM (k2_prefill.cu)
 constexpr int kMmaShrinkTokens = 512;   // batches from this size on shrink on the tensor cores (bf16 adapters)
 constexpr int kDecodeTokens = 32;     // batches up to this size take the decode forms (one position per shrink warp)
 constexpr int kCounterSlots = 4096;  // split-K arrival counters in the workspace
@@ -131,12 +131,14 @@ struct K1mParams {
     int32_t* status;
 };
 
-// The 256 x 256 prefill GEMM (k2_prefill.cu): FP8 base, bf16 adapters.
+// The large-tile prefill GEMM (k2_prefill.cu): FP8 base 256 x 256, NVFP4 base 128 x 256; bf16 adapters.
 struct K2pParams {
     int M, N, K, S, R, L;
     int widths[OB_MAX_SLICES];
-    int kblocks;           // ceil(K / 128)
+    int kblocks;           // 128-byte k-blocks of a W row: ceil(K / 128), NVFP4 ceil(K / 256)
     int stages;
+    const uint8_t* wsf;    // NVFP4: packed W block scales [128-row tile][k-block][2 KB]
+    const uint8_t* xsf;    // NVFP4: K1's activation block scales [256-token tile][k-block][2][2 KB]
     int lc;                // list entries per position in hcat
     int max_m;
     uint32_t wait_ms;

@@ -194,7 +194,7 @@ class VllmFusedFP8LoRA:
         """The tile choice a call of M tokens runs with, the library's own rule filled in (ob_resolve_tile)."""
         out = _lib.ObTileCfg()
         _lib.call("ob_resolve_tile", self._h, int(M), C.byref(self.tile(M, cfg)), C.byref(out))
-        return {k: getattr(out, k) for k in ("tn", "split2", "split1", "stages", "fused", "stream")}
+        return {k: getattr(out, k) for k in ("tn", "split2", "split1", "stages", "fused", "stream", "prefill")}
 
     def shrink_partials(self, M: int, cfg: dict | None = None) -> torch.Tensor:
         """The fp32 shrink partials the last K1 call of M tokens wrote, [split1, S, max_m, R], as a view of the workspace:

@@ -99,8 +99,9 @@ class VllmFusedNVFP4LoRA(VllmFusedFP8LoRA):
         float8_e4m3fn, read back out of the scale-factor atoms)."""
         K = self.K
         xq = self.scratch.region("xq", M * (K // 2)).view(M, K // 2)
-        t = self.tile(M)
-        tn = tn or t.tn or min(64, max(16, 1 << (M - 1).bit_length()))   # the library's default token tile for an NVFP4 base
+        if tn is None:   # the token tile the library's own rule gave the last call; 256 under the large-tile prefill GEMM
+            rt = self.resolved_tile(M)
+            tn = 256 if rt["prefill"] == 1 else rt["tn"]
         nblk = 2 if tn > 128 else 1
         kslots = (K + 255) // 256
         m_tiles = (M + tn - 1) // tn

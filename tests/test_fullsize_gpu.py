@@ -47,8 +47,9 @@ def _sample_rows(widths, g_cpu, per_slice=48):
     return torch.cat(glob), local
 
 
-@pytest.mark.parametrize("name", list(PROJECTIONS))
-@pytest.mark.parametrize("M", [32, 300])
+# M = 1000 on gate_up gives every CTA pair of the prefill GEMM several tiles; M = 2500 on down does the same for the
+# single-CTA form (the long-K projection keeps it): the persistent loops' hand-overs between tiles are exercised.
+@pytest.mark.parametrize("name,M", [(n, m) for m in (32, 300) for n in PROJECTIONS] + [("gate_up", 1000), ("down", 2500)])
 def test_full_size_projection_sampled_features(name, M):
     K, widths, N, w_q, s_w, a_st, b_st, g, Op = _layer(name, seed=len(name) * 100 + M)
     op = Op(w_q, s_w, a_st, b_st, max_m=M)
@@ -92,10 +93,12 @@ def test_full_size_projection_sampled_features(name, M):
 
 
 @pytest.mark.parametrize("name", ["qkv", "down"])
-@pytest.mark.parametrize("M", [32, 300])
-def test_full_size_nvfp4_projection_sampled_features(name, M):
+@pytest.mark.parametrize("M,cfg", [(32, None), (300, None), (300, {"prefill": 1}), (1000, None)])
+def test_full_size_nvfp4_projection_sampled_features(name, M, cfg):
     """The same check with an NVFP4 base.  The weight codes and block scales are random (every nibble and every scale byte
-    of 0.5..1.9 is a valid weight); both sides consume the same bytes, so parity does not depend on how they were made."""
+    of 0.5..1.9 is a valid weight); both sides consume the same bytes, so parity does not depend on how they were made.
+    M = 300 runs the 64-token tiles by default and the large-tile prefill GEMM (128 features x 256 tokens) when asked;
+    M = 1000 takes the large tiles by the library's own rule."""
     from onebase_b200.kernels.nvfp4_lora_vllm import VllmFusedNVFP4LoRA
     from oracle import nvfp4 as on4
     K, widths = PROJECTIONS[name]
@@ -116,14 +119,16 @@ def test_full_size_nvfp4_projection_sampled_features(name, M):
     idx = oseg.SegmentIndex(L, M)
     idx.prepare(ids)
     meta = device_meta(idx, M)
-    y = op(x, meta)
-    y2 = op(x, meta)
+    y = op(x, meta, cfg=cfg)
+    y2 = op(x, meta, cfg=cfg)
     torch.cuda.synchronize()
     assert op.scratch.status()[0] == 0, op.scratch.status()[:8]
     assert torch.equal(y, y2)
+    big = op.resolved_tile(M, cfg)["prefill"] == 1
+    assert big == (cfg is not None or M >= 1000)
     rows, _ = oseg.resolve_positions(M, *idx.args(M))
     q_ref, sf_ref = on4.quant(x_cpu, x_global)
-    xq, xsf = op.codes(M)
+    xq, xsf = op.codes(M, tn=256 if big else None)
     assert torch.equal(xq.cpu(), q_ref[rows])
     assert torch.equal(xsf.view(torch.uint8).cpu(), sf_ref.view(torch.uint8)[rows])
     sel, local = _sample_rows(widths, g_cpu)
