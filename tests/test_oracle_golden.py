@@ -140,3 +140,26 @@ def test_resolve_positions_padding_and_stale():
     idx.prepare(torch.full((6,), -1, dtype=torch.int32))                 # no adapter: stale sort must be ignored
     rows, ads = segments.resolve_positions(6, *idx.args(6))
     assert rows.tolist() == list(range(6)) and ads.tolist() == [-1] * 6
+
+
+def test_port_equals_the_references_own_modules_when_built():
+    """`python -m oracle.build_ref` puts the reference's three source files under oracle/_ref (git-ignored).  Where that
+    copy exists -- the build machine, and any box the snapshot travels to -- the restatement must agree with the
+    reference's own functions on freshly drawn inputs, not only with the committed fixtures."""
+    from oracle import build_ref, configs
+    ref = build_ref.load()
+    if ref is None:
+        pytest.skip("oracle/_ref has not been built on this machine")
+    ref8, ref4 = ref
+    d = configs.with_fp8_base(configs.draw(512, (256, 128), 16, 4, 24, seed=11, ids_low=-1))
+    A, B = fp8.stack_slices(d["a_stacked"], d["b_stacked"])
+    want = ref8.reference_multi(d["x"], d["ids"], d["w_q"], d["s_w"], A, B, list(d["widths"]), 1.0)
+    got = fp8.fused_projection(d["x"], d["ids"], d["w_q"], d["s_w"], A, B, d["widths"])
+    assert float((got - want.float()).abs().max()) <= 2e-5 * float(want.float().abs().max())
+    x = torch.randn(8, 256, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16)
+    gs = ref4.global_scale_for(x.float())
+    assert gs == nvfp4.global_scale_for(x.float())
+    q_ref, sf_ref = ref4.nvfp4_quant_torch(x, gs)
+    q, sf = nvfp4.quant(x, gs)
+    assert torch.equal(q, q_ref) and torch.equal(u8(sf), u8(sf_ref))
+    assert torch.equal(nvfp4.dequant(q, sf, gs), ref4.nvfp4_dequant_torch(q_ref, sf_ref, gs))
