@@ -252,6 +252,94 @@ def time_sharded_layer(spec: dict, world: int, rank: int, dev, batch_sizes, comm
 L_SLOTS, RANK = 32, 64
 
 
+def nvfp4_layer_check(world: int, rank: int, dev, comm, M: int, steps: int, flush) -> dict:
+    """The Qwen3-8B layer with an NVFP4 base at tensor-parallel `world`: every rank draws the same full tensors (random
+    codes and block scales: both sides consume the same bytes), keeps its column / row shard (`shard_column_nvfp4`,
+    `shard_row_nvfp4`), runs the layer -- eight fused kernels and the two peer-memory all-reduces -- as one CUDA graph, and
+    checks (a) its all-reduced o / down outputs against the rank-ordered sum of every rank's partial output, gathered by
+    NCCL (exact), (b) them against the unsharded NVFP4 op on the same tensors: the activation quantization is block-local
+    against a static global scale, so sharding K changes only the summation order.  Returns errors and the layer time."""
+    import torch.distributed as dist
+
+    from onebase_b200.kernels.nvfp4_lora_vllm import VllmFusedNVFP4LoRA
+    from onebase_b200.metadata import KernelMeta
+    g = torch.Generator(device=dev).manual_seed(5)
+    ids = torch.randint(0, L_SLOTS, (M,), generator=torch.Generator().manual_seed(0), dtype=torch.int32).to(dev)
+    km = KernelMeta.make(L_SLOTS, M, dev)
+    km.prepare_tensors(ids)
+    meta = km.meta_args(M)
+    w_global = 2688.0 / 0.1
+    layer, y_full = {}, {}
+    for name, (K, widths, kind) in QWEN3_8B.items():
+        N = sum(widths)
+        w_q4 = torch.randint(0, 256, (N, K // 2), device=dev, generator=g, dtype=torch.uint8)
+        w_sf = torch.randint(0x30, 0x40, (N, K // 16), device=dev, generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn)
+        a_st = tuple(((torch.rand(L_SLOTS, 1, RANK, K, device=dev, generator=g) * 2 - 1) / K ** 0.5).to(torch.bfloat16) for _ in widths)
+        b_st = tuple((torch.randn(L_SLOTS, 1, n, RANK, device=dev, generator=g) * 0.01).to(torch.bfloat16) for n in widths)
+        x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+        x_global = float(448.0 * 6.0 / x.float().abs().amax().clamp_min(1e-12))
+        if kind == "row":
+            full = VllmFusedNVFP4LoRA(w_q4, w_sf, w_global, x_global, a_st, b_st, max_m=M)
+            y_full[name] = full(x, meta).clone()
+            torch.cuda.synchronize()
+            del full
+            q_r, sf_r, a_r, b_r = shard_row_nvfp4(w_q4, w_sf, a_st, b_st, world, rank)
+            x_r = shard_input_row(x, world, rank)
+        else:
+            rep = (1, max(1, world // 8), max(1, world // 8)) if name == "qkv" else ()
+            q_r, sf_r, a_r, b_r = shard_column_nvfp4(w_q4, w_sf, a_st, b_st, world, rank, rep)
+            x_r = x
+        del w_q4, w_sf, a_st, b_st
+        op = VllmFusedNVFP4LoRA(q_r, sf_r, w_global, x_global, a_r, b_r, max_m=M)
+        layer[name] = (op, x_r, torch.empty(M, op.N, dtype=torch.bfloat16, device=dev), kind)
+    torch.cuda.empty_cache()
+
+    def step():
+        for n in ("qkv", "o", "gate_up", "down"):
+            op, x_n, y_n, kind = layer[n]
+            op(x_n, meta, out=y_n)
+            if kind == "row":
+                comm.all_reduce(y_n)
+
+    for _ in range(2):
+        step()
+    torch.cuda.synchronize()
+    exact, check = {}, {}
+    for n in ("o", "down"):
+        op, x_n, y_n, _ = layer[n]
+        part = torch.empty_like(y_n)
+        op(x_n, meta, out=part)
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part)
+        acc = torch.zeros_like(part, dtype=torch.float32)
+        for t in parts:
+            acc += t.float()
+        exact[n] = float((y_n.float() - acc.to(torch.bfloat16).float()).abs().max() / acc.abs().max())
+        ref = y_full[n].float()
+        check[n] = float((y_n.float() - ref).abs().max() / ref.abs().max())
+    dist.barrier()
+    gph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gph):
+        step()
+    ts = []
+    for i in range(steps + 3):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        gph.replay()
+        e1.record()
+        e1.synchronize()
+        if i >= 3:
+            ts.append(e0.elapsed_time(e1))
+    ms = torch.tensor([statistics.fmean(ts), max(exact.values()), max(check.values())], device=dev)
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    st = layer["qkv"][0].scratch.status()
+    return {"layer_us": round(float(ms[0].item()) * 1e3, 1), "max_abs_err_over_ymax_vs_sum_of_rank_partials": float(ms[1].item()),
+            "max_abs_err_over_ymax_vs_unsharded_op": float(ms[2].item()), "unsharded_bound": 2e-2,
+            "ok": float(ms[1].item()) == 0.0 and float(ms[2].item()) <= 2e-2 and st[0] == 0,
+            "workload": f"Qwen3-8B decoder layer, NVFP4 base, tensor-parallel {world}, decode M={M}, 32 bf16 tenants rank 64"}
+
+
 def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
     """One Qwen3-8B decoder layer at tensor-parallel size `world` (one process per GPU): column-parallel qkv / gate_up,
     row-parallel o / down each followed by an all-reduce of y -- by default the peer-memory kernel (ob_allreduce), so the
@@ -490,7 +578,7 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
 
     # ---- the exchange alone (one all-reduce of y_o in a graph of its own), and the 72B-class layer of the tensor-parallel
     # configuration at this N (decode M = 8, 32, 128); both with the peer-memory kernel only
-    ar_us, config4 = None, None
+    ar_us, config4, nvfp4_tp = None, None, None
     status = layer["qkv"][0].scratch.status()
     if comm is not None:
         g_ar = torch.cuda.CUDAGraph()                          # eight in a row: the ranks' start skew is paid once, not per call
@@ -509,6 +597,7 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
             config4["workload"] = (f"72B-class decoder layer (hidden 8192, intermediate 29568) at tensor-parallel {world}, FP8 base, "
                                    "32 bf16 tenants rank 64, one CUDA graph per batch size; layer us by decode batch size")
             big.close()
+            nvfp4_tp = nvfp4_layer_check(world, rank, dev, comm, M, 20, flush)
     ok = torch.tensor([1 if status[0] == 0 and (comm is None or comm.status()[3] == 0) and
                        (config4 is None or config4["device_status_ok"]) else 0], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
@@ -532,7 +621,7 @@ def bench_tp(args, rank: int, world: int, local: int, metric: str) -> None:
                        "cuda_graph": (f"{len(graphs)} graphs; the NCCL all-reduces are launched between them" if use_nccl
                                       else "one graph: 8 fused kernels per rank, the two all-reduces inside K2's epilogues" if fuse_ar
                                       else "one graph: 8 fused kernels + 2 all-reduce kernels per rank")},
-            "layer_us": ms_v * 1e3, "allreduce_us_alone": ar_us, "config4": config4,
+            "layer_us": ms_v * 1e3, "allreduce_us_alone": ar_us, "config4": config4, "nvfp4_tp": nvfp4_tp,
             "gpu_launches": (8 if use_nccl or fuse_ar else 10) * args.steps,   # our kernels per step: four K1, four K2 (+ two all-reduces)
             "device_status_ok": bool(ok.item()),
             "tp_check": {"max_abs_err_over_ymax_vs_sum_of_rank_partials": exact, "exchange_bound": exact_bound,
