@@ -117,7 +117,10 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
     }
     __syncthreads();
     const int n_list = ctrl->n_list;
-    if (n_list == 0 || n_ksteps == 0) return;                 // no tenant in this tile (uniform: nothing was allocated)
+    if (n_list == 0 || n_ksteps == 0) {                       // no tenant in this tile (uniform: nothing was allocated)
+        griddep_wait();                                       // this grid must not be complete before the grid it depends on is
+        return;
+    }
     const int n_pass = (n_list + group - 1) / group;
     const int first_group = min(n_list, group);
     uint32_t tmem_cols = 32;
@@ -201,6 +204,9 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
         const bool direct = p.split1 == 1;                     // no partials: the accumulator row is the finished h
         const bool cat = p.hcat != nullptr;                    // per-tenant blocks, pre-divided by the output scale
         __nv_bfloat16* cdst = cat ? p.hcat + ((size_t)s * p.max_m + (size_t)pos) * ((size_t)p.lc * p.R) : nullptr;
+        // (the per-token scales come from the quantizing kernel this launch is a programmatic dependent of: they may be read
+        // only after griddepcontrol.wait, which every thread that reads them executes itself)
+        griddep_wait();
         const float inv = (cat && pos < p.M) ? 1.0f / ((p.sx ? __ldcg(p.sx + pos) : 1.0f) * __ldg(p.s_w)) : 0.0f;   // NVFP4 base: one scale for every token
         for (int pass = 0; pass < n_pass; ++pass) {
             const int g0 = pass * group, ng = min(group, n_list - g0);
