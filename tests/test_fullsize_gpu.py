@@ -140,3 +140,102 @@ def test_full_size_nvfp4_projection_sampled_features(name, M, cfg):
     got = y[:, sel.cuda()]
     err = max_err_ratio(got, ref)
     assert err <= TOL, f"{name} M={M}: max-abs-err / ||y||inf = {err:.3e}"
+
+
+def _zipf_ids(M, seed=0, exponent=1.1):
+    """Contiguous requests whose sizes follow Zipf(1.1) over the L tenants, in a seeded tenant order (the prefill batches
+    of the NVFP4 configuration)."""
+    g = torch.Generator().manual_seed(seed)
+    share = 1.0 / torch.arange(1, L + 1, dtype=torch.float64) ** exponent
+    exact = share / share.sum() * M
+    counts = exact.floor().long()
+    order = torch.argsort(exact - counts, descending=True)
+    counts[order[: M - int(counts.sum())]] += 1
+    return torch.repeat_interleave(torch.randperm(L, generator=g).to(torch.int32), counts)
+
+
+def _dequantized_like_the_store(stacked, fmt):
+    """What the kernels see of adapters stored as `fmt` (the reference's AdapterStore.dequantized,
+    lowbit_lora/kernels/adapter_store.py:82-94), per slice as fp32 [L, rows, cols]."""
+    from oracle import nvfp4 as on4
+    out = []
+    for t in stacked:
+        m = t[:, 0].cpu()
+        if fmt == "bf16":
+            out.append(m.float())
+        elif fmt == "fp8":
+            codes, scale = ofp8.store_rows_fp8(m)
+            out.append(codes.float() * scale[..., None])
+        else:
+            out.append(on4.dequant_stack(*on4.quant_stack(m)))
+    return out
+
+
+@pytest.mark.parametrize("adapters", ["bf16", "fp8", "nvfp4"])
+@pytest.mark.parametrize("M", [512, 2048])
+def test_config2_nvfp4_base_stored_adapters_zipf_prefill(adapters, M):
+    """Configuration 2 at full size: NVFP4 base, adapters stored as bf16 / FP8 / NVFP4, a prefill batch split across the
+    32 tenants by Zipf(1.1), under the library's own tile rule; the o projection (4096 -> 4096) on sampled features."""
+    from onebase_b200.kernels.nvfp4_lora_vllm import VllmFusedNVFP4LoRA
+    from oracle import nvfp4 as on4
+    K, widths = PROJECTIONS["o"]
+    N = sum(widths)
+    g = torch.Generator(device="cuda").manual_seed(1000 + M)
+    w_q4 = torch.randint(0, 256, (N, K // 2), device="cuda", generator=g, dtype=torch.uint8)
+    w_sf = torch.randint(0x30, 0x40, (N, K // 16), device="cuda", generator=g, dtype=torch.uint8).view(torch.float8_e4m3fn)
+    a_st = tuple(((torch.rand(L, 1, R, K, device="cuda", generator=g) * 2 - 1) / K ** 0.5).to(torch.bfloat16) for _ in widths)
+    b_st = tuple((torch.randn(L, 1, n, R, device="cuda", generator=g) * 0.01).to(torch.bfloat16) for n in widths)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    x_cpu = x.cpu()
+    w_global, x_global = 2688.0 / 0.1, on4.global_scale_for(x_cpu.float())
+    op = VllmFusedNVFP4LoRA(w_q4, w_sf, w_global, x_global, a_st, b_st, max_m=M, lora_fmt=adapters)
+    ids = _zipf_ids(M, seed=M)
+    idx = oseg.SegmentIndex(L, M)
+    idx.prepare(ids)
+    meta = device_meta(idx, M)
+    y = op(x, meta)
+    y2 = op(x, meta)
+    torch.cuda.synchronize()
+    assert op.scratch.status()[0] == 0, op.scratch.status()[:8]
+    assert torch.equal(y, y2)
+    g_cpu = torch.Generator().manual_seed(M)
+    sel, local = _sample_rows(widths, g_cpu)
+    a_deq = _dequantized_like_the_store(a_st, adapters)
+    b_deq = [t[:, loc] for t, loc in zip(_dequantized_like_the_store(b_st, adapters), local)]
+    A, B = torch.cat(a_deq, 1), torch.cat(b_deq, 1)
+    ref = on4.fused_projection(x_cpu, ids, w_q4[sel.cuda()].cpu(), w_sf.view(torch.uint8)[sel.cuda()].cpu().view(torch.float8_e4m3fn),
+                               w_global, x_global, A, B, [len(loc) for loc in local])
+    err = max_err_ratio(y[:, sel.cuda()], ref)
+    assert err <= TOL, f"adapters {adapters} M={M}: max-abs-err / ||y||inf = {err:.3e}"
+
+
+@pytest.mark.parametrize("name,M", [("o", 512), ("gate_up", 2048)])
+def test_fp8_base_zipf_prefill_default_rule(name, M):
+    """FP8 base, bf16 adapters, Zipf(1.1) prefill batches under the library's OWN rule (no tile override): M = 512 on o
+    stays on the small tiles with the tensor-core shrink, M = 2048 on gate_up takes the large-tile kernels."""
+    K, widths, N, w_q, s_w, a_st, b_st, g, Op = _layer(name, seed=31 + M)
+    op = Op(w_q, s_w, a_st, b_st, max_m=M)
+    ids = _zipf_ids(M, seed=M + 1)
+    idx = oseg.SegmentIndex(L, M)
+    idx.prepare(ids)
+    meta = device_meta(idx, M)
+    x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+    y = op(x, meta)
+    y2 = op(x, meta)
+    torch.cuda.synchronize()
+    assert op.scratch.status()[0] == 0, op.scratch.status()[:8]
+    assert torch.equal(y, y2)
+    assert (op.resolved_tile(M)["prefill"] == 1) == (name == "gate_up")
+    x_cpu = x.cpu()
+    rows, _ = oseg.resolve_positions(M, *idx.args(M))
+    q_ref, sx_ref = ofp8.quant_per_token(x_cpu)
+    assert torch.equal(op.scratch.xq(M, K).view(torch.uint8).cpu(), q_ref.view(torch.uint8)[rows])
+    assert torch.equal(op.scratch.sx(M).cpu().view(torch.int32), sx_ref[rows].view(torch.int32))
+    g_cpu = torch.Generator().manual_seed(M)
+    sel, local = _sample_rows(widths, g_cpu)
+    a_red = tuple(t.cpu() for t in a_st)
+    b_red = tuple(t[:, :, loc.to(t.device)].cpu() for t, loc in zip(b_st, local))
+    A, B = ofp8.stack_slices(a_red, b_red)
+    ref = ofp8.fused_projection(x_cpu, ids, w_q.view(torch.uint8)[sel.cuda()].cpu().view(torch.float8_e4m3fn), s_w.cpu(), A, B, [len(loc) for loc in local])
+    err = max_err_ratio(y[:, sel.cuda()], ref)
+    assert err <= TOL, f"{name} M={M}: max-abs-err / ||y||inf = {err:.3e}"
