@@ -312,6 +312,68 @@ def cpu_layer_seconds(M: int, reps: int, threads: int) -> tuple[float, str, str]
             f"one Qwen3-8B layer (4 projections), M={M}, 32 slots rank 64, {reps} timed passes after 1 warm-up; {what}", kind)
 
 
+def reference_gpu_layer(layer, meta, M: int, flush, steps: int) -> dict:
+    """The reference's own GPU path for the same layer on this GPU: its `VllmFusedFP8LoRA` (serialized Triton launches,
+    the form its plugin runs wherever its PDL chain is not available) built over the SAME tensors, the four projections
+    captured in one CUDA graph, L2 flushed before every replay, CUDA events.  Its outputs are checked against this
+    repository's on the way.  Part of the reference leg: nothing of the product path runs through it."""
+    from oracle import build_ref
+    RefOp = build_ref.load_gpu_op()
+    if RefOp is None:
+        return {"unavailable": "the reference's modules are not under oracle/_ref (python -m oracle.build_ref) or do not import"}
+    try:
+        ref, outs, errs = {}, {}, {}
+        for name, (op, x, y) in layer.items():
+            ref[name] = RefOp(op.w_q, op.s_w, op.a_stacked, op.b_stacked, max_m=M)
+            outs[name] = torch.empty_like(y)
+
+        def run_ref():
+            for name in ("qkv", "o", "gate_up", "down"):
+                ref[name](layer[name][1], meta, out=outs[name])
+
+        for _ in range(3):                                    # Triton compiles here
+            run_ref()
+        torch.cuda.synchronize()
+        for name, (op, x, y) in layer.items():
+            ours = op(x, meta).float()
+            errs[name] = float((outs[name].float() - ours).abs().max() / ours.abs().max())
+        g = graph_of(run_ref)
+        ts = time_events(g.replay, steps, 5, flush)
+        per = {}
+        for name in layer:
+            g1 = graph_of(lambda n=name: ref[n](layer[n][1], meta, out=outs[n]))
+            per[name] = statistics.fmean(time_events(g1.replay, 20, 3, flush)) * 1e3
+        return {"layer_us": statistics.fmean(ts) * 1e3, "projection_us": per, "max_abs_err_over_ymax_vs_this_repo": errs,
+                "how": "lowbit_lora.kernels.fp8_lora_vllm.VllmFusedFP8LoRA (Triton _shrink_vllm + _gemm_vllm, its own tile "
+                       "tables) from oracle/_ref, same tensors, one CUDA graph, L2 flushed, CUDA events",
+                "triton": __import__("triton").__version__}
+    except Exception as exc:   # noqa: BLE001 - the reference's kernels may not compile for this GPU
+        return {"unavailable": f"{type(exc).__name__}: {exc}"[:300]}
+
+
+def reference_gpu_in_child(M: int, steps: int) -> dict:
+    """`reference_gpu_layer` in a process of its own: a compile error, a time-out or a fault in the reference's kernels
+    then costs this one object, not the run's line."""
+    import subprocess
+    cmd = [sys.executable, os.path.abspath(__file__), "--reference-gpu-child", "--m", str(M), "--steps", str(steps)]
+    try:
+        out = subprocess.run(cmd, capture_output=True, text=True, timeout=420)
+        rows = [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
+        if out.returncode != 0 or not rows:
+            return {"unavailable": f"child exited {out.returncode}: {out.stderr.strip()[-200:]}"}
+        return json.loads(rows[-1])
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "the reference's kernels did not finish within 420 s"}
+
+
+def reference_gpu_child(args) -> None:
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    layer, meta, _ = make_layer(args.m, dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    print(json.dumps(reference_gpu_layer(layer, meta, args.m, flush, args.steps)))
+
+
 def reference_arm(args, rank: int) -> None:
     if rank != 0:
         return
@@ -338,6 +400,10 @@ def main() -> None:
     ap.add_argument("--impl", default="onebase_b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-tables", action="store_true", help="skip the decode / prefill tables beside the headline cell")
+    ap.add_argument("--no-reference-gpu", action="store_true",
+                    help="skip the `reference_gpu` object: the reference's own Triton kernels (out of oracle/_ref) timed on "
+                         "the same layer and GPU in a child process, beside the CPU baseline")
+    ap.add_argument("--reference-gpu-child", action="store_true", help=argparse.SUPPRESS)
     ap.add_argument("--base", default="fp8", choices=["fp8", "nvfp4"], help="base format of the --profile case")
     ap.add_argument("--lora-fmt", default="bf16", choices=["bf16", "fp8", "nvfp4"], help="adapter storage of the --profile case")
     ap.add_argument("--tp-form", default="partial", choices=["partial", "sharded"],
@@ -357,6 +423,9 @@ def main() -> None:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.reference_gpu_child:
+        reference_gpu_child(args)
+        return
     if args.impl == "reference":
         reference_arm(args, rank)
         return
@@ -494,6 +563,10 @@ def main() -> None:
         "gpu_launches": 8 * args.steps,
         "clocks": sampler.result(),
     }
+    if not args.no_reference_gpu:
+        line["reference_gpu"] = reference_gpu_in_child(M, min(args.steps, 50))
+        if "layer_us" in line["reference_gpu"]:
+            line["reference_gpu"]["reference_over_this_repo"] = line["reference_gpu"]["layer_us"] / line["layer_us"]
     if not args.no_tables:
         # the rest of the metric beside the headline cell: decode at M = 1 / 8 / 32 and one prefill batch, both base formats
         del layer, graph

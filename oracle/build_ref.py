@@ -3,7 +3,7 @@ benchmarks on a machine without the reference checkout can time the reference it
 
     python -m oracle.build_ref [<reference checkout>]        (default: /root/reference)
 
-The reference is pure Python: "building" it means copying the three modules that hold its CPU path
+The reference is pure Python: "building" it means copying the modules that hold its CPU path
 (lowbit_lora/kernels/{fp8_lora_multi, nvfp4_lora_vllm, common}.py: `reference_multi`, `reference`, the NVFP4 torch
 recipes and the e4m3 helper they import) with their empty package markers into oracle/_ref/, which is git-ignored like
 any other built artefact: the sources never enter this repository's history.  `load()` imports them from there; it
@@ -20,6 +20,8 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 REF_DIR = HERE / "_ref"
 MODULES = ("fp8_lora_multi", "nvfp4_lora_vllm", "common")
+# ... and, for the opt-in GPU timing of the reference's own kernels (bench.py --reference-gpu), its Triton op for vLLM
+GPU_MODULES = ("fp8_lora_vllm", "adapter_store")
 
 
 def build(reference: str | Path = "/root/reference") -> Path | None:
@@ -30,7 +32,7 @@ def build(reference: str | Path = "/root/reference") -> Path | None:
     dst.mkdir(parents=True, exist_ok=True)
     (REF_DIR / "lowbit_lora" / "__init__.py").write_text("")
     (dst / "__init__.py").write_text("")
-    for m in MODULES:
+    for m in MODULES + tuple(m for m in GPU_MODULES if (src / f"{m}.py").exists()):
         shutil.copyfile(src / f"{m}.py", dst / f"{m}.py")
     return REF_DIR
 
@@ -45,6 +47,17 @@ def load():
         return (importlib.import_module("lowbit_lora.kernels.fp8_lora_multi"),
                 importlib.import_module("lowbit_lora.kernels.nvfp4_lora_vllm"))
     except Exception:   # noqa: BLE001 - e.g. no triton on this machine: the caller falls back to the restatement
+        return None
+
+
+def load_gpu_op():
+    """The reference's `VllmFusedFP8LoRA` class (its serialized Triton launches `_shrink_vllm` + `_gemm_vllm`,
+    lowbit_lora/kernels/fp8_lora_vllm.py:416-765) out of the built copy, or None."""
+    if load() is None or not (REF_DIR / "lowbit_lora" / "kernels" / "fp8_lora_vllm.py").exists():
+        return None
+    try:
+        return importlib.import_module("lowbit_lora.kernels.fp8_lora_vllm").VllmFusedFP8LoRA
+    except Exception:   # noqa: BLE001
         return None
 
 
