@@ -1,7 +1,7 @@
 """Oracle (test infrastructure): put the reference's OWN torch path for the fused projection next to the oracle, so that
 benchmarks on a machine without the reference checkout can time the reference itself and not only its restatement.
 
-    python -m oracle.build_ref [<reference checkout>]        (default: /root/reference)
+    python -m oracle.build_ref [<reference checkout>]        (default: $ONEBASE_REFERENCE_DIR, else the build container's mount)
 
 The reference is pure Python: "building" it means copying the modules that hold its CPU path
 (lowbit_lora/kernels/{fp8_lora_multi, nvfp4_lora_vllm, common}.py: `reference_multi`, `reference`, the NVFP4 torch
@@ -13,6 +13,7 @@ the same files); only their torch functions are called.
 from __future__ import annotations
 
 import importlib
+import os
 import shutil
 import sys
 from pathlib import Path
@@ -24,7 +25,10 @@ MODULES = ("fp8_lora_multi", "nvfp4_lora_vllm", "common")
 GPU_MODULES = ("fp8_lora_vllm", "adapter_store")
 
 
-def build(reference: str | Path = "/root/reference") -> Path | None:
+DEFAULT_REFERENCE = os.environ.get("ONEBASE_REFERENCE_DIR", "/root/reference")
+
+
+def build(reference: str | Path = DEFAULT_REFERENCE) -> Path | None:
     src = Path(reference) / "lowbit_lora" / "kernels"
     if not all((src / f"{m}.py").exists() for m in MODULES):
         return None
@@ -62,5 +66,5 @@ def load_gpu_op():
 
 
 if __name__ == "__main__":
-    out = build(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    out = build(sys.argv[1] if len(sys.argv) > 1 else DEFAULT_REFERENCE)
     print(out if out else "reference checkout not found: nothing built")
