@@ -6,9 +6,10 @@
 //
 // Why pairs: the single-CTA kernel of k2_prefill.cu takes 54 KB (NVFP4; FP8 64 KB) of operands into shared memory per
 // 16.8 MFLOP and its tensor pipe idles most of the time -- a ring slot costs its single-thread roles a fixed ~0.8 us
-// (every wait, copy issue, tcgen05.cp / mma / commit costs its issuing thread 50-250 cycles), whatever the slot holds.
-// A pair does twice the flops per slot: each CTA supplies its own 128 rows of W and only HALF of the token tile (the MMA
-// reads the other half out of the partner's shared memory), so a CTA takes in 38 KB for the same 16.8 MFLOP: W [128 x
+// (every wait, copy issue, tcgen05.cp / mma / commit costs its issuing thread 50-250 cycles), whatever the slot holds,
+// and only three such slots fit.  In a pair each CTA supplies its own 128 rows of W and only HALF of the token tile (the
+// MMA reads the other half out of the partner's shared memory), so a CTA takes in 38 KB for the same 16.8 MFLOP -- five
+// slots fit, and with the tokens on the accumulator's lanes the epilogue needs no staging: W [128 x
 // 128 B], x_q [128 tokens x 128 B], its tokens' block scales (2 KB) and the W block scales of all 256 features (4 KB;
 // every CTA needs the scales of all of B's rows in its own tensor memory).  No load is multicast.
 //
