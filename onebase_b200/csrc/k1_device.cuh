@@ -103,6 +103,55 @@ __device__ void quantize_row(const K1Params& p, int pos, int row, int tid) {
     named_bar_sync<BAR, NT>();                        // s_part / s_scale may be reused by the group's next position
 }
 
+// The same quantization for the prefill launches' one-row CTAs, with the row held in registers between the two passes
+// (NV vectors of 8 elements per thread: K <= 8 * NV * NT) and the adapter-sorted bf16 copy written from the same
+// registers: thousands of such CTAs keep the code warm, so the unrolled second pass costs no cold fetches, and a row
+// of up to 4096 elements needs so few registers that eight CTAs share an SM.
+template <int NT, int BAR, int NV>
+__device__ void quantize_row_regs(const K1Params& p, int pos, int row, int tid) {
+    __shared__ float s_part[NT / 32];
+    __shared__ float s_scale;
+    const int lane = tid & 31, warp = tid >> 5;
+    const __nv_bfloat16* xr = p.x + (int64_t)row * p.ldx;
+    const int nvec = p.K >> 3;
+    uint4 v[NV];
+    float amax = 0.0f;
+#pragma unroll
+    for (int q = 0; q < NV; ++q) {
+        const int i = tid + q * NT;
+        v[q] = i < nvec ? __ldg(reinterpret_cast<const uint4*>(xr + i * 8)) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int q = 0; q < NV; ++q) amax = fmaxf(amax, amax8(v[q]));
+#pragma unroll
+    for (int o = 16; o; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) s_part[warp] = amax;
+    if (p.xs != nullptr) {                            // the tensor-core shrink reads x in position order by TMA
+        uint4* xo = reinterpret_cast<uint4*>(p.xs + (size_t)pos * (size_t)p.K);
+#pragma unroll
+        for (int q = 0; q < NV; ++q) {
+            const int i = tid + q * NT;
+            if (i < nvec) xo[i] = v[q];
+        }
+    }
+    named_bar_sync<BAR, NT>();
+    if (tid == 0) {
+        float m = s_part[0];
+        for (int w = 1; w < NT / 32; ++w) m = fmaxf(m, s_part[w]);
+        const float sx = fmaxf(__fdiv_rn(m, kFp8Max), kMinTokenScale);
+        s_scale = sx;
+        p.sx[pos] = sx;
+    }
+    named_bar_sync<BAR, NT>();
+    const float sx = s_scale;
+    uint2* out = reinterpret_cast<uint2*>(p.xq + (size_t)pos * (size_t)p.K);
+#pragma unroll
+    for (int q = 0; q < NV; ++q) {
+        const int i = tid + q * NT;
+        if (i < nvec) out[i] = quant8(v[q], sx);
+    }
+}
+
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
     f[0] = bf16_lo(v.x); f[1] = bf16_hi(v.x); f[2] = bf16_lo(v.y); f[3] = bf16_hi(v.y);
     f[4] = bf16_lo(v.z); f[5] = bf16_hi(v.z); f[6] = bf16_lo(v.w); f[7] = bf16_hi(v.w);
@@ -128,7 +177,9 @@ __device__ __forceinline__ float e4m3_to_float(uint32_t code) {
 // rcp(sf * rcp(gs)) : 0, code = e2m1_rn(x * out_scale); codes packed two per byte (element 2i in the low nibble).  One
 // thread per block.  The scales go straight into K2's scale-factor atoms: [token tile][K slot][128-token block][MMA][r%32]
 // [r/32][4], r = position within the token tile.
-template <int NT, bool XOP = false>
+// COPY: also write the row's bf16 values to the adapter-sorted copy p.xs (prefill: the tensor-core shrink's input) from
+// the vectors just loaded, instead of a second pass over the row.
+template <int NT, bool XOP = false, bool COPY = false>
 __device__ void quantize_row_nvfp4(const K1Params& p, int pos, int row, int tid) {
     const float gs = __ldg(p.x_global);
     const __nv_bfloat16* xr = p.x + (int64_t)row * p.ldx;
@@ -142,8 +193,14 @@ __device__ void quantize_row_nvfp4(const K1Params& p, int pos, int row, int tid)
         uint32_t sf_code = 0;
         if (b < nblocks) {
             float v[16];
-            unpack8(x_load8<XOP>(p, xr, 16 * b), *reinterpret_cast<float(*)[8]>(&v[0]));
-            unpack8(x_load8<XOP>(p, xr, 16 * b + 8), *reinterpret_cast<float(*)[8]>(&v[8]));
+            const uint4 u0 = x_load8<XOP>(p, xr, 16 * b), u1 = x_load8<XOP>(p, xr, 16 * b + 8);
+            if (COPY && p.xs != nullptr) {
+                uint4* xo = reinterpret_cast<uint4*>(p.xs + (size_t)pos * (size_t)p.K) + 2 * b;
+                xo[0] = u0;
+                xo[1] = u1;
+            }
+            unpack8(u0, *reinterpret_cast<float(*)[8]>(&v[0]));
+            unpack8(u1, *reinterpret_cast<float(*)[8]>(&v[8]));
             float vmax = 0.0f;
 #pragma unroll
             for (int e = 0; e < 16; ++e) vmax = fmaxf(vmax, fabsf(v[e]));

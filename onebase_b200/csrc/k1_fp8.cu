@@ -76,13 +76,24 @@ __global__ void __launch_bounds__(kK1Threads, 4) k1_quant_kernel(const K1Params 
     griddep_launch_dependents();
     const int row = row_of_position(p, blockIdx.x, threadIdx.x & 31);
     griddep_wait();
-    if (FP4_BASE) quantize_row_nvfp4<kK1Threads>(p, blockIdx.x, row, threadIdx.x);
+    if (FP4_BASE) quantize_row_nvfp4<kK1Threads, false, true>(p, blockIdx.x, row, threadIdx.x);
     else quantize_row<kK1Threads, 0>(p, blockIdx.x, row, threadIdx.x);
-    if (p.xs != nullptr) {
+    if (!FP4_BASE && p.xs != nullptr) {
         const __nv_bfloat16* xr = p.x + (int64_t)row * p.ldx;
         uint4* xo = reinterpret_cast<uint4*>(p.xs + (size_t)blockIdx.x * (size_t)p.K);
         for (int i = threadIdx.x; i < (p.K >> 3); i += kK1Threads) xo[i] = x_load8<false>(p, xr, i * 8);
     }
+}
+
+// The FP8 base's form of it with the row in registers (NV vectors per thread): one read of x serves the amax, the codes
+// and the sorted copy; rows of up to 4096 elements run eight CTAs per SM (the launch is bound by how many rows an SM has
+// in flight, not by bytes).
+template <int NV>
+__global__ void __launch_bounds__(kK1Threads, NV <= 2 ? 8 : 4) k1_quant_regs_kernel(const K1Params p) {
+    griddep_launch_dependents();
+    const int row = row_of_position(p, blockIdx.x, threadIdx.x & 31);
+    griddep_wait();
+    quantize_row_regs<kK1Threads, 0, NV>(p, blockIdx.x, row, threadIdx.x);
 }
 
 template <int LORA_FMT, bool FP4_BASE>
@@ -113,8 +124,11 @@ static cudaError_t launch_k1_impl(const K1Params& p, int grid, int pdl, cudaStre
         return cudaLaunchKernelEx(&cfg, k1_kernel<LORA_FMT, FP4_BASE, true, false>, p);
     }
     if (p.x_op != OB_X_PLAIN) return cudaLaunchKernelEx(&cfg, k1_kernel<LORA_FMT, FP4_BASE, false, true>, p);
-    if (grid == p.n_quant_ctas && p.xq_ready == nullptr && p.trace == nullptr)   // no shrink warps in this launch
+    if (grid == p.n_quant_ctas && p.xq_ready == nullptr && p.trace == nullptr) {   // no shrink warps in this launch
+        if (!FP4_BASE && p.K <= 16 * kK1Threads) return cudaLaunchKernelEx(&cfg, k1_quant_regs_kernel<2>, p);
+        if (!FP4_BASE && p.K <= 48 * kK1Threads) return cudaLaunchKernelEx(&cfg, k1_quant_regs_kernel<6>, p);
         return cudaLaunchKernelEx(&cfg, k1_quant_kernel<FP4_BASE>, p);
+    }
     return cudaLaunchKernelEx(&cfg, k1_kernel<LORA_FMT, FP4_BASE, false, false>, p);
 }
 
