@@ -182,11 +182,17 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
                     tc_fence_after();
                     const uint32_t xa = smem_u32(ring + (size_t)st * stage_bytes);
                     const uint64_t dx = umma_smem_desc(xa, 1024, 2);
-                    for (int g = 0; g < ng; ++g) {
+                    // The tenants' A tiles lie one after the other in the slot and their accumulators side by side in tensor
+                    // memory, so up to 256 / R of them are ONE B operand: an MMA of N = (tenants in the batch) x R columns
+                    // instead of one MMA per tenant (every tcgen05.mma costs its issuer some 60 cycles).
+                    const int batch = 256 / p.R > 0 ? 256 / p.R : 1;
+                    for (int g = 0; g < ng; g += batch) {
+                        const int nb = min(batch, ng - g);
+                        const uint32_t idesc_b = nb == 1 ? idesc : umma_idesc(1, 1, kMmaTile, (uint32_t)(nb * p.R));
                         const uint64_t da = umma_smem_desc(xa + kMmaXBytes + (uint32_t)(g * a_bytes), 1024, 2);
 #pragma unroll
                         for (int kk = 0; kk < kMmaKStep / 16; ++kk)
-                            umma_f16(tmem_base + (uint32_t)(g * p.R), dx + (uint64_t)(kk * 2), da + (uint64_t)(kk * 2), idesc,
+                            umma_f16(tmem_base + (uint32_t)(g * p.R), dx + (uint64_t)(kk * 2), da + (uint64_t)(kk * 2), idesc_b,
                                      (ks > 0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit(&ctrl->empty[st]);
