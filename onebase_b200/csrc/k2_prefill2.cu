@@ -58,8 +58,7 @@ struct P2Meta {
 };
 
 struct P2Ctrl {
-    uint64_t full[5];                // this CTA's operands of the slot have landed
-    uint64_t peer_full[5];           // rank 0 only: the partner's have
+    uint64_t full[5];                // this CTA's operands of the slot have landed (rank 0: and the partner's, relayed)
     uint64_t sf_ready[5];            // rank 0 only (NVFP4): the slot's scale factors are in both CTAs' tensor memory
     uint64_t empty[5];               // the pair's MMAs on the slot are done (arrives in both CTAs)
     uint64_t meta_full[2];
@@ -129,8 +128,7 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
 
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(&ctrl->full[i], 1);
-            mbar_init(&ctrl->peer_full[i], 1);
+            mbar_init(&ctrl->full[i], rank == 0 ? 2 : 1);     // rank 0: its own transaction + the partner's "landed" arrival
             mbar_init(&ctrl->sf_ready[i], 1);
             mbar_init(&ctrl->empty[i], 1);
         }
@@ -251,8 +249,7 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
                         landed = !ctrl->abort_flag && mbar_wait(&ctrl->sf_ready[st], (sf_par >> st) & 1u, limit_ns);
                         sf_par ^= 1u << st;
                     } else {
-                        landed = !ctrl->abort_flag && mbar_wait(&ctrl->full[st], par, limit_ns) &&
-                                 mbar_wait_cluster(&ctrl->peer_full[st], par, limit_ns);
+                        landed = !ctrl->abort_flag && mbar_wait_cluster(&ctrl->full[st], par, limit_ns);
                     }
                     if (!landed) {
                         if (!ctrl->abort_flag) p2_timeout(p, ctrl, 4, it);
@@ -291,8 +288,7 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
                 for (int li = 0; li < n_steps; ++li, ++it) {
                     const int st = it % kStages;
                     const uint32_t par = (uint32_t)((it / kStages) & 1);
-                    if (ctrl->abort_flag || !mbar_wait(&ctrl->full[st], par, limit_ns) ||
-                        !mbar_wait_cluster(&ctrl->peer_full[st], par, limit_ns)) {
+                    if (ctrl->abort_flag || !mbar_wait_cluster(&ctrl->full[st], par, limit_ns)) {
                         if (!ctrl->abort_flag) p2_timeout(p, ctrl, 6, it);
                         ok = false;
                         break;
@@ -333,7 +329,7 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
                             ok = false;
                             break;
                         }
-                        mbar_arrive_remote(cluster_peer_addr(smem_u32(&ctrl->peer_full[st]), 0));
+                        mbar_arrive_remote(cluster_peer_addr(smem_u32(&ctrl->full[st]), 0));
                     }
                 }
             }
@@ -356,8 +352,7 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
                 for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
                     const int st = it % kStages;
                     const uint32_t par = (uint32_t)((it / kStages) & 1);
-                    if (ctrl->abort_flag || !mbar_wait(&ctrl->full[st], par, limit_ns) ||
-                        !mbar_wait_cluster(&ctrl->peer_full[st], par, limit_ns)) {
+                    if (ctrl->abort_flag || !mbar_wait_cluster(&ctrl->full[st], par, limit_ns)) {
                         if (!ctrl->abort_flag) p2_timeout(p, ctrl, 13, it);
                         ok = false;
                         break;
@@ -379,8 +374,7 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
                 for (int li = 0; li < n_steps && ok; ++li, ++it) {
                     const int st = it % kStages;
                     const uint32_t par = (uint32_t)((it / kStages) & 1);
-                    if (ctrl->abort_flag || !mbar_wait(&ctrl->full[st], par, limit_ns) ||
-                        !mbar_wait_cluster(&ctrl->peer_full[st], par, limit_ns)) {
+                    if (ctrl->abort_flag || !mbar_wait_cluster(&ctrl->full[st], par, limit_ns)) {
                         if (!ctrl->abort_flag) p2_timeout(p, ctrl, 15, it);
                         ok = false;
                     }
