@@ -10,6 +10,13 @@
 // stacked adapters.  Output: the split-K partials hp[split][slice][position][rank] (fp32) that K2 adds in split order,
 // the same array the CUDA-core shrink writes.  Computes what lowbit_lora/kernels/fp8_lora_vllm.py:72-120 computes.
 //
+// K splits: the splits of a (tile, slice) are ONE thread-block cluster where the launch allows (2 or 4 splits, the
+// rank divisible among them, one accumulator pass): each CTA leaves its positions' own-tenant rows (fp32) in its idle
+// ring, the cluster meets at a barrier, and split j adds rows j * 128 / splits ... of all the splits in split order over
+// distributed shared memory and writes the finished h -- no partials in the workspace, no arrival counter, no last
+// arriver that reduces alone (that tail took 7 of the kernel's 25 us).  Otherwise the partials go through the
+// workspace: the splits count their arrivals and the last one adds them, in the same order.
+//
 // Warp roles: 0 = TMA producer, 1 = MMA issuer (and the owner of the tensor-memory allocation), 2..5 = epilogue (warp w
 // reads the 32 accumulator lanes w % 4 may touch).  Every wait is bounded; a wait that runs out records where in the
 // workspace's status words and the CTA leaves without storing.
@@ -122,6 +129,7 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
         return;
     }
     const int n_pass = (n_list + group - 1) / group;
+    const bool csum = p.cluster != 0 && n_pass == 1 && p.split1 > 1;      // the same in every CTA of the cluster (same tile)
     const int first_group = min(n_list, group);
     uint32_t tmem_cols = 32;
     while (tmem_cols < (uint32_t)(first_group * p.R)) tmem_cols *= 2;
@@ -263,6 +271,12 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
                         }
                         reinterpret_cast<uint4*>(hdst + c0)[0] = make_uint4(o[0], o[1], o[2], o[3]);
                         reinterpret_cast<uint4*>(hdst + c0)[1] = make_uint4(o[4], o[5], o[6], o[7]);
+                    } else if (own && csum) {             // the row stays in this CTA's (idle) ring for the cluster's sum
+                        float4* sr = reinterpret_cast<float4*>(ring) + ((size_t)row * p.R + c0) / 4;
+#pragma unroll
+                        for (int v = 0; v < 4; ++v)
+                            sr[v] = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
                     } else if (own) {
 #pragma unroll
                         for (int v = 0; v < 4; ++v)
@@ -276,7 +290,7 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctrl->acc_empty);
         }
-        if (!direct) {
+        if (!direct && !csum) {
             // The K splits of a (tile, slice) count their arrivals; the last one adds the partials in split order and writes
             // the finished h once, so that K2's CTAs -- one per output tile -- need not each add them again.
             const int te = tid - 64;
@@ -347,6 +361,47 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
     if (ctrl->abort_flag) __nanosleep(200000);
     tc_fence_before();
     __syncthreads();
+    if (p.cluster != 0) {
+        // ---- the cluster's sum (see the header).  Both barriers are unconditional: a CTA whose wait ran out still joins
+        // them (its rows are then garbage, but the status words say so), and no CTA leaves while a partner reads its ring.
+        __syncwarp();
+        cluster_sync_all();
+        if (csum && warp >= 2 && !ctrl->abort_flag) {
+            const int te = tid - 64;
+            const int rank = (int)blockIdx.z;                 // cluster = the grid's z extent: rank = split index
+            const int rows_per = kMmaTile / p.split1, tpr = p.split1;          // rows this CTA finishes; threads per row
+            const int row = rank * rows_per + te / tpr, sub = te % tpr;
+            const int cols = p.R / tpr, c_lo = sub * cols;                     // a multiple of 4 columns per thread
+            const int pos = t0 + row, mine = ctrl->gidx[row];
+            const bool cat = p.hcat != nullptr;
+            const bool valid = mine >= 0 && pos < p.M;
+            if (cat && pos < p.max_m) {                       // zeros for the block's other entries, shared among the row's threads
+                __nv_bfloat16* cdst = p.hcat + ((size_t)s * p.max_m + (size_t)pos) * ((size_t)p.lc * p.R);
+                for (int li = sub; li < n_list; li += tpr) {
+                    if (valid && li == mine) continue;
+                    uint4* d4 = reinterpret_cast<uint4*>(cdst + (size_t)li * p.R);
+                    for (int c = 0; c < p.R / 8; ++c) d4[c] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            if (valid) {
+                const float osc = cat ? 1.0f / ((p.sx ? __ldcg(p.sx + pos) : 1.0f) * __ldg(p.s_w)) : 1.0f;
+                __nv_bfloat16* odst = cat ? p.hcat + ((size_t)s * p.max_m + (size_t)pos) * ((size_t)p.lc * p.R) + (size_t)mine * p.R
+                                          : p.hb + ((size_t)s * p.max_m + (size_t)pos) * p.R;
+                const uint32_t own_addr = smem_u32(ring) + (uint32_t)(((size_t)row * p.R + c_lo) * 4);
+                for (int c = 0; c < cols; c += 4) {
+                    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int q = 0; q < p.split1; ++q) {      // split order: the same sum as the workspace path
+                        const float4 v = ld_cluster_f4(cluster_peer_addr(own_addr + (uint32_t)(c * 4), (uint32_t)q));
+                        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+                    }
+                    __nv_bfloat162 b0 = __floats2bfloat162_rn(acc.x * osc, acc.y * osc), b1 = __floats2bfloat162_rn(acc.z * osc, acc.w * osc);
+                    *reinterpret_cast<uint2*>(odst + c_lo + c) = make_uint2(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1));
+                }
+            }
+        }
+        __syncwarp();
+        cluster_sync_all();
+    }
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);
@@ -371,11 +426,15 @@ cudaError_t launch_k1_mma(const K1mParams& p, const CUtensorMap& tm_xs, const CU
     cfg.blockDim = dim3(kMmaThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // always a programmatic dependent of K1
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;                  // the K splits of a (tile, slice) as one cluster
+    attr[1].val.clusterDim.x = 1;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = grid.z;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = p.cluster ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, k1_mma_kernel, p, tm_xs, tm_a[0], tm_a[1], tm_a[2], tm_a[3]);
 }
 

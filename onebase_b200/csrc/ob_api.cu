@@ -299,6 +299,9 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
         const int tiles = ((M + 127) / 128) * d.S;
         split1 = 1;
         while (split1 < 16 && tiles * (split1 * 2) <= 148 && d.K / (split1 * 2) >= 256) split1 *= 2;
+        // four splits are one cluster that sums over shared memory; eight go through the workspace and their last arriver:
+        // unless that halves a long K (1024 elements or more per split), four measured faster
+        if (split1 == 8 && d.K / 8 < 1024 && d.R % 16 == 0) split1 = 4;
     }
     if (split1 == 0) {
         const long long units = (long long)((M + pb - 1) / pb) * d.S * (d.R / 8);
@@ -448,6 +451,13 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
         m.sx = fp4 ? nullptr : reinterpret_cast<const float*>(base + lay.sx);
         m.s_w = fp4 ? d.alpha : d.s_w;
     }
+    // 2 or 4 splits whose share of the rank is whole float4s: one thread-block cluster per (tile, slice), sums over
+    // distributed shared memory (LOWBIT_SHRINK_GLOBAL_SUM=1 keeps the workspace partials and the arrival counters).
+    // Clusters of 8 measured slower than the workspace path: a cluster sits inside one GPC with one such CTA per SM, so
+    // few of them are resident at once.
+    static const bool global_sum = [] { const char* v = std::getenv("LOWBIT_SHRINK_GLOBAL_SUM"); return v && v[0] == '1'; }();
+    m.cluster = (!global_sum && (r.split1 == 2 || r.split1 == 4) && d.R % (4 * r.split1) == 0 &&
+                 (size_t)128 * d.R * 4 <= (size_t)m.ring_bytes) ? 1 : 0;
     if ((long long)((b->M + 127) / 128) * d.S > kCounterSlots) return OB_ERR_TOO_LARGE;
     dim3 mgrid((unsigned)((b->M + 127) / 128), (unsigned)d.S, (unsigned)r.split1);
     e = launch_k1_mma(m, tm_xs, l->tm_a, mgrid, stream);

@@ -129,6 +129,8 @@ struct K1mParams {
     const float* s_w;      // [1]
     int32_t* counters;     // one arrival counter per (position tile, slice); zero between launches
     int32_t* status;
+    int cluster;           // the K splits of a (tile, slice) were launched as one thread-block cluster (grid z): their partial
+                           // rows are added over distributed shared memory instead of the workspace and the counters
 };
 
 // The large-tile prefill GEMM (k2_prefill.cu): FP8 base 256 x 256, NVFP4 base 128 x 256; bf16 adapters.
