@@ -52,14 +52,19 @@ def test_decode_shrink_partials_sum_to_oracle_h(K, widths, R, L, M, cfg):
     assert err <= 2e-5 * scale + 1e-7, f"max |hp sum - h| = {err:.3e} against ||h||inf = {scale:.3e}"
 
 
-def test_prefill_tensor_core_shrink_h_equals_oracle_h():
-    K, widths, R, L, M = 1024, (256, 512), 64, 8, 300
+@pytest.mark.parametrize("K,split1", [(1024, 0), (1024, 1), (1024, 2), (4096, 8)])
+def test_prefill_tensor_core_shrink_h_equals_oracle_h(K, split1):
+    """split1 = 0: the library's rule (four K splits here: one thread-block cluster that sums over distributed shared
+    memory); 1: no split (the accumulator row is the finished h); 2: a cluster of two; 8 (on a longer K): partials through
+    the workspace and the arrival counter, the last arriver adds them."""
+    widths, R, L, M = (256, 512), 64, 8, 300
     d = configs.with_fp8_base(configs.draw(K, widths, R, L, M, seed=4, ids_low=-1))
     ids = configs.zipf_request_ids(M, L, seed=6, mean_len=25)
     ids[40:70] = -1
     op = build_fp8_op(d, max_m=M)
     idx = make_index(ids, L, M)
-    op(d["x"].cuda(), device_meta(idx, M), cfg={"prefill": 1, "tn": 128}, gemm=False)   # tensor-core shrink -> finished h
+    cfg = {"prefill": 1, "tn": 128, **({"split1": split1} if split1 else {})}
+    op(d["x"].cuda(), device_meta(idx, M), cfg=cfg, gemm=False)   # tensor-core shrink -> finished h
     torch.cuda.synchronize()
     assert op.scratch.status()[0] == 0
     hb = op.scratch.hb(len(widths), R).float().cpu()[:, :M].permute(1, 0, 2)
@@ -67,7 +72,10 @@ def test_prefill_tensor_core_shrink_h_equals_oracle_h():
     want = _oracle_h(d, ids)[rows]
     has = ids[rows] >= 0
     got, ref = hb[has], want[has]
-    # bf16 of an fp32 sum taken in another order: equal to the oracle's rounding or its neighbour
+    # bf16 of an fp32 sum taken in another order: equal to the oracle's rounding or its neighbour.  `ref` is the unrounded
+    # fp32 value, so a neighbour of its rounding lies up to 1.5 bf16 spacings away, and a spacing is at most 2^-7 |ref|.
+    # (Elements that are small against their own terms also carry the fp32 sums' reordering error: 2e-5 of |h|inf.)
     ulp = ref.abs().clamp_min(1e-30) * 2.0 ** -7
-    assert bool(((got - ref).abs() <= ulp).all()), float(((got - ref).abs() / ulp).max())
+    slack = 2e-5 * float(ref.abs().max())
+    assert bool(((got - ref).abs() <= 1.5 * ulp + slack).all()), float(((got - ref).abs() / (1.5 * ulp + slack)).max())
     assert float((got != ref.to(torch.bfloat16).float()).float().mean()) < 0.02
