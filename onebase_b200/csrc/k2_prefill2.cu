@@ -128,7 +128,9 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
 
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
-            mbar_init(&ctrl->full[i], rank == 0 ? 2 : 1);     // rank 0: its own transaction + the partner's "landed" arrival
+            // rank 0, NVFP4: its own transaction + the partner's relayed "landed" arrival; FP8: one arrival whose
+            // transaction count covers both CTAs' bytes (the partner's tensor loads complete on this barrier directly)
+            mbar_init(&ctrl->full[i], (FP4 && rank == 0) ? 2 : 1);
             mbar_init(&ctrl->sf_ready[i], 1);
             mbar_init(&ctrl->empty[i], 1);
         }
@@ -176,11 +178,22 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
                         break;
                     }
                     uint8_t* slot = ring + (size_t)st * kSlot;
-                    mbar_arrive_expect_tx(&ctrl->full[st], (uint32_t)kSlot);
+                    if (FP4) {
+                        mbar_arrive_expect_tx(&ctrl->full[st], (uint32_t)kSlot);
 #pragma unroll
-                    for (int h = 0; h < kHalves; ++h)
-                        tma_load_2d(slot + h * kP2WBytes, &tm_w, &ctrl->full[st], kb * 128, tl.slice_off + row0 + h * 256);
-                    tma_load_2d(slot + kXOff, &tm_x, &ctrl->full[st], kb * 128, tl.t0 + (int)rank * 128);
+                        for (int h = 0; h < kHalves; ++h)
+                            tma_load_2d(slot + h * kP2WBytes, &tm_w, &ctrl->full[st], kb * 128, tl.slice_off + row0 + h * 256);
+                        tma_load_2d(slot + kXOff, &tm_x, &ctrl->full[st], kb * 128, tl.t0 + (int)rank * 128);
+                    } else {
+                        // FP8: every load is a tensor load, so both CTAs' bytes are counted on rank 0's barrier and no relay
+                        // stands between the partner's data and the MMAs
+                        const uint32_t bar0 = cluster_peer_addr(smem_u32(&ctrl->full[st]), 0);
+                        if (rank == 0) mbar_arrive_expect_tx(&ctrl->full[st], (uint32_t)(2 * kSlot));
+#pragma unroll
+                        for (int h = 0; h < kHalves; ++h)
+                            tma_load_2d_pair(slot + h * kP2WBytes, &tm_w, bar0, kb * 128, tl.slice_off + row0 + h * 256);
+                        tma_load_2d_pair(slot + kXOff, &tm_x, bar0, kb * 128, tl.t0 + (int)rank * 128);
+                    }
                     if (FP4) {
                         // scales: this CTA's 128 tokens (the MMA's A rows), then both 128-feature tiles of W (every CTA needs
                         // the scales of all of B's 256 rows in its own tensor memory)
@@ -212,12 +225,21 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
                     // B_l: this CTA's 128 features of each half.  h: the step's 128-token block belongs to ONE CTA of the pair
                     // (block b = rank b's tokens); the other CTA's rows of the M = 256 MMA must add nothing, so it fetches a
                     // box that lies wholly outside the tensor, which TMA fills with zeros.
-                    mbar_arrive_expect_tx(&ctrl->full[st], (uint32_t)(kXOff + kP2XBytes));
+                    const int h_row = (int)e.block == (int)rank ? tl.s * p.max_m + tl.t0 + (int)e.block * 128 : p.S * p.max_m + 128;
+                    if (FP4) {
+                        mbar_arrive_expect_tx(&ctrl->full[st], (uint32_t)(kXOff + kP2XBytes));
 #pragma unroll
-                    for (int h = 0; h < kHalves; ++h)
-                        tma_load_2d(slot + h * kP2WBytes, tmb, &ctrl->full[st], (int)e.chunk * 64, (int)e.lora * tl.n_s + row0 + h * 256);
-                    tma_load_2d(slot + kXOff, &tm_h, &ctrl->full[st], (int)e.entry * p.R + (int)e.chunk * 64,
-                                (int)e.block == (int)rank ? tl.s * p.max_m + tl.t0 + (int)e.block * 128 : p.S * p.max_m + 128);
+                        for (int h = 0; h < kHalves; ++h)
+                            tma_load_2d(slot + h * kP2WBytes, tmb, &ctrl->full[st], (int)e.chunk * 64, (int)e.lora * tl.n_s + row0 + h * 256);
+                        tma_load_2d(slot + kXOff, &tm_h, &ctrl->full[st], (int)e.entry * p.R + (int)e.chunk * 64, h_row);
+                    } else {
+                        const uint32_t bar0 = cluster_peer_addr(smem_u32(&ctrl->full[st]), 0);
+                        if (rank == 0) mbar_arrive_expect_tx(&ctrl->full[st], (uint32_t)(2 * (kXOff + kP2XBytes)));
+#pragma unroll
+                        for (int h = 0; h < kHalves; ++h)
+                            tma_load_2d_pair(slot + h * kP2WBytes, tmb, bar0, (int)e.chunk * 64, (int)e.lora * tl.n_s + row0 + h * 256);
+                        tma_load_2d_pair(slot + kXOff, &tm_h, bar0, (int)e.entry * p.R + (int)e.chunk * 64, h_row);
+                    }
                 }
             }
         }
@@ -307,8 +329,9 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
                 }
                 if (ok) umma_commit_pair(&ctrl->acc_full, 3);
             }
-        } else if (lane == 0) {
-            // =========================================================== relay: this CTA's slot has landed -> rank 0's barrier
+        } else if (FP4 && lane == 0) {
+            // =========================================================== relay (NVFP4: the scale copies are not tensor loads and
+            // can only complete on a barrier of their own CTA): this CTA's slot has landed -> rank 0's barrier
             int it = 0;
             bool ok = true;
             for (int t = pair, i = 0; t < n_tiles && ok; t += n_pairs, ++i) {
