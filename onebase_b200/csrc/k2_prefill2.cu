@@ -13,8 +13,10 @@
 // 128 B], x_q [128 tokens x 128 B], its tokens' block scales (2 KB) and the W block scales of all 256 features (4 KB;
 // every CTA needs the scales of all of B's rows in its own tensor memory).  No load is multicast.
 //
-// Per CTA (256 threads): warp 0 = TMA producer of the CTA's own operands; warp 1 = in the pair's rank-0 CTA the MMA
-// issuer for both, in the rank-1 CTA a relay that forwards "my slot has landed" to rank 0's barrier; warp 2 = tile
+// Per CTA (256 threads): warp 0 = TMA producer of the CTA's own operands -- every load a tensor load of the
+// cta_group::2 form, whose bytes are counted on the slot barrier of the pair's rank-0 CTA, so one wait there covers
+// both CTAs' operands (the block scales are fetched as 8 x 256-byte boxes of a [rows, 256] byte tensor for that
+// reason); warp 1 = in the pair's rank-0 CTA the MMA issuer for both; warp 2 = tile
 // scout (row map, output scale, expand steps; both CTAs compute the same list); warps 3..6 = epilogue of the CTA's own
 // 128 tokens (straight from tensor memory to y);
 // warp 7 = in rank 0 the scale copier (tcgen05.cp of a slot's scale factors into both CTAs' tensor memory).  The issuer's commits arrive on the slot-free and accumulator-full barriers of BOTH CTAs
@@ -58,7 +60,7 @@ struct P2Meta {
 };
 
 struct P2Ctrl {
-    uint64_t full[5];                // this CTA's operands of the slot have landed (rank 0: and the partner's, relayed)
+    uint64_t full[5];                // rank 0's: both CTAs' operands of the slot have landed (rank 1's is unused)
     uint64_t sf_ready[5];            // rank 0 only (NVFP4): the slot's scale factors are in both CTAs' tensor memory
     uint64_t empty[5];               // the pair's MMAs on the slot are done (arrives in both CTAs)
     uint64_t meta_full[2];
@@ -109,7 +111,8 @@ __global__ void __launch_bounds__(kP2Threads, 1)
 k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                        const __grid_constant__ CUtensorMap tm_h, const __grid_constant__ CUtensorMap tm_b0,
                        const __grid_constant__ CUtensorMap tm_b1, const __grid_constant__ CUtensorMap tm_b2,
-                       const __grid_constant__ CUtensorMap tm_b3) {
+                       const __grid_constant__ CUtensorMap tm_b3, const __grid_constant__ CUtensorMap tm_wsf,
+                       const __grid_constant__ CUtensorMap tm_xsf) {
     extern __shared__ uint8_t smem_raw[];
     // (the dynamic shared memory starts at the same offset in both CTAs of a pair: the MMA applies one descriptor to both)
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -128,9 +131,9 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
 
     if (tid == 0) {
         for (int i = 0; i < kStages; ++i) {
-            // rank 0, NVFP4: its own transaction + the partner's relayed "landed" arrival; FP8: one arrival whose
-            // transaction count covers both CTAs' bytes (the partner's tensor loads complete on this barrier directly)
-            mbar_init(&ctrl->full[i], (FP4 && rank == 0) ? 2 : 1);
+            // rank 0's: one arrival whose transaction count covers both CTAs' bytes (every load is a tensor load, and the
+            // partner's complete on this barrier directly); rank 1's is never used
+            mbar_init(&ctrl->full[i], 1);
             mbar_init(&ctrl->sf_ready[i], 1);
             mbar_init(&ctrl->empty[i], 1);
         }
@@ -178,31 +181,22 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
                         break;
                     }
                     uint8_t* slot = ring + (size_t)st * kSlot;
-                    if (FP4) {
-                        mbar_arrive_expect_tx(&ctrl->full[st], (uint32_t)kSlot);
+                    // every load is a tensor load, so both CTAs' bytes are counted on rank 0's barrier and no relay stands
+                    // between the partner's data and the MMAs
+                    const uint32_t bar0 = cluster_peer_addr(smem_u32(&ctrl->full[st]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(&ctrl->full[st], (uint32_t)(2 * kSlot));
 #pragma unroll
-                        for (int h = 0; h < kHalves; ++h)
-                            tma_load_2d(slot + h * kP2WBytes, &tm_w, &ctrl->full[st], kb * 128, tl.slice_off + row0 + h * 256);
-                        tma_load_2d(slot + kXOff, &tm_x, &ctrl->full[st], kb * 128, tl.t0 + (int)rank * 128);
-                    } else {
-                        // FP8: every load is a tensor load, so both CTAs' bytes are counted on rank 0's barrier and no relay
-                        // stands between the partner's data and the MMAs
-                        const uint32_t bar0 = cluster_peer_addr(smem_u32(&ctrl->full[st]), 0);
-                        if (rank == 0) mbar_arrive_expect_tx(&ctrl->full[st], (uint32_t)(2 * kSlot));
-#pragma unroll
-                        for (int h = 0; h < kHalves; ++h)
-                            tma_load_2d_pair(slot + h * kP2WBytes, &tm_w, bar0, kb * 128, tl.slice_off + row0 + h * 256);
-                        tma_load_2d_pair(slot + kXOff, &tm_x, bar0, kb * 128, tl.t0 + (int)rank * 128);
-                    }
+                    for (int h = 0; h < kHalves; ++h)
+                        tma_load_2d_pair(slot + h * kP2WBytes, &tm_w, bar0, kb * 128, tl.slice_off + row0 + h * 256);
+                    tma_load_2d_pair(slot + kXOff, &tm_x, bar0, kb * 128, tl.t0 + (int)rank * 128);
                     if (FP4) {
-                        // scales: this CTA's 128 tokens (the MMA's A rows), then both 128-feature tiles of W (every CTA needs
-                        // the scales of all of B's 256 rows in its own tensor memory)
+                        // scales, as 8 x 256-byte rows of a [rows, 256] byte tensor per 2 KB atom: this CTA's 128 tokens (the
+                        // MMA's A rows), then both 128-feature tiles of W (every CTA needs the scales of all of B's 256 rows in
+                        // its own tensor memory)
                         uint8_t* sf = slot + kXOff + kP2XBytes;
-                        bulk_load(sf, p.xsf + (((size_t)tl.m_idx * p.kblocks + kb) * 2 + rank) * kSfSlotBytes, kSfSlotBytes, &ctrl->full[st]);
-                        bulk_load(sf + kSfSlotBytes, p.wsf + ((size_t)(tl.n_idx * 2) * p.kblocks + kb) * kSfSlotBytes, kSfSlotBytes,
-                                  &ctrl->full[st]);
-                        bulk_load(sf + 2 * kSfSlotBytes, p.wsf + ((size_t)(tl.n_idx * 2 + 1) * p.kblocks + kb) * kSfSlotBytes, kSfSlotBytes,
-                                  &ctrl->full[st]);
+                        tma_load_2d_pair(sf, &tm_xsf, bar0, 0, ((tl.m_idx * p.kblocks + kb) * 2 + (int)rank) * 8);
+                        tma_load_2d_pair(sf + kSfSlotBytes, &tm_wsf, bar0, 0, ((tl.n_idx * 2) * p.kblocks + kb) * 8);
+                        tma_load_2d_pair(sf + 2 * kSfSlotBytes, &tm_wsf, bar0, 0, ((tl.n_idx * 2 + 1) * p.kblocks + kb) * 8);
                     }
                 }
                 if (!ok) break;
@@ -226,20 +220,12 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
                     // (block b = rank b's tokens); the other CTA's rows of the M = 256 MMA must add nothing, so it fetches a
                     // box that lies wholly outside the tensor, which TMA fills with zeros.
                     const int h_row = (int)e.block == (int)rank ? tl.s * p.max_m + tl.t0 + (int)e.block * 128 : p.S * p.max_m + 128;
-                    if (FP4) {
-                        mbar_arrive_expect_tx(&ctrl->full[st], (uint32_t)(kXOff + kP2XBytes));
+                    const uint32_t bar0 = cluster_peer_addr(smem_u32(&ctrl->full[st]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(&ctrl->full[st], (uint32_t)(2 * (kXOff + kP2XBytes)));
 #pragma unroll
-                        for (int h = 0; h < kHalves; ++h)
-                            tma_load_2d(slot + h * kP2WBytes, tmb, &ctrl->full[st], (int)e.chunk * 64, (int)e.lora * tl.n_s + row0 + h * 256);
-                        tma_load_2d(slot + kXOff, &tm_h, &ctrl->full[st], (int)e.entry * p.R + (int)e.chunk * 64, h_row);
-                    } else {
-                        const uint32_t bar0 = cluster_peer_addr(smem_u32(&ctrl->full[st]), 0);
-                        if (rank == 0) mbar_arrive_expect_tx(&ctrl->full[st], (uint32_t)(2 * (kXOff + kP2XBytes)));
-#pragma unroll
-                        for (int h = 0; h < kHalves; ++h)
-                            tma_load_2d_pair(slot + h * kP2WBytes, tmb, bar0, (int)e.chunk * 64, (int)e.lora * tl.n_s + row0 + h * 256);
-                        tma_load_2d_pair(slot + kXOff, &tm_h, bar0, (int)e.entry * p.R + (int)e.chunk * 64, h_row);
-                    }
+                    for (int h = 0; h < kHalves; ++h)
+                        tma_load_2d_pair(slot + h * kP2WBytes, tmb, bar0, (int)e.chunk * 64, (int)e.lora * tl.n_s + row0 + h * 256);
+                    tma_load_2d_pair(slot + kXOff, &tm_h, bar0, (int)e.entry * p.R + (int)e.chunk * 64, h_row);
                 }
             }
         }
@@ -328,33 +314,6 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
                     umma_commit_pair(&ctrl->empty[st], 3);
                 }
                 if (ok) umma_commit_pair(&ctrl->acc_full, 3);
-            }
-        } else if (FP4 && lane == 0) {
-            // =========================================================== relay (NVFP4: the scale copies are not tensor loads and
-            // can only complete on a barrier of their own CTA): this CTA's slot has landed -> rank 0's barrier
-            int it = 0;
-            bool ok = true;
-            for (int t = pair, i = 0; t < n_tiles && ok; t += n_pairs, ++i) {
-                int n_slots = p.kblocks;
-                for (int phase = 0; phase < 2 && ok; ++phase) {
-                    if (phase == 1) {
-                        if (!mbar_wait(&ctrl->meta_full[i & 1], (uint32_t)((i >> 1) & 1), limit_ns)) {
-                            p2_timeout(p, ctrl, 11, it);
-                            ok = false;
-                            break;
-                        }
-                        n_slots = ctrl->meta[i & 1].n_steps;
-                    }
-                    for (int q = 0; q < n_slots; ++q, ++it) {
-                        const int st = it % kStages;
-                        if (ctrl->abort_flag || !mbar_wait(&ctrl->full[st], (uint32_t)((it / kStages) & 1), limit_ns)) {
-                            if (!ctrl->abort_flag) p2_timeout(p, ctrl, 12, it);
-                            ok = false;
-                            break;
-                        }
-                        mbar_arrive_remote(cluster_peer_addr(smem_u32(&ctrl->full[st]), 0));
-                    }
-                }
             }
         }
     } else if (warp == 7) {
@@ -586,15 +545,18 @@ static int pair_capacity() {
 int k2_prefill_pair_capacity(int fp4) { return fp4 ? pair_capacity<true>() : pair_capacity<false>(); }
 
 cudaError_t launch_k2_prefill_pair(const K2pParams& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap& tm_h,
-                                   const CUtensorMap* tm_b, int pairs, int fp4, int pdl, cudaStream_t stream) {
+                                   const CUtensorMap* tm_b, const CUtensorMap* tm_sf, int pairs, int fp4, int pdl,
+                                   cudaStream_t stream) {
+    // tm_sf: NVFP4 base only, the packed W block scales and the workspace's token block scales as [rows, 256] byte tensors
     cudaLaunchConfig_t cfg;
     cudaLaunchAttribute attr[2];
     if (fp4) {
         pair_launch_config<true>(&cfg, attr, pairs, pdl, stream);
-        return cudaLaunchKernelEx(&cfg, k2_prefill_pair_kernel<true>, p, tm_w, tm_x, tm_h, tm_b[0], tm_b[1], tm_b[2], tm_b[3]);
+        return cudaLaunchKernelEx(&cfg, k2_prefill_pair_kernel<true>, p, tm_w, tm_x, tm_h, tm_b[0], tm_b[1], tm_b[2], tm_b[3], tm_sf[0],
+                                  tm_sf[1]);
     }
     pair_launch_config<false>(&cfg, attr, pairs, pdl, stream);
-    return cudaLaunchKernelEx(&cfg, k2_prefill_pair_kernel<false>, p, tm_w, tm_x, tm_h, tm_b[0], tm_b[1], tm_b[2], tm_b[3]);
+    return cudaLaunchKernelEx(&cfg, k2_prefill_pair_kernel<false>, p, tm_w, tm_x, tm_h, tm_b[0], tm_b[1], tm_b[2], tm_b[3], tm_w, tm_w);
 }
 
 }  // namespace ob

@@ -20,7 +20,8 @@ cudaError_t launch_k2_prefill(const K2pParams& p, const CUtensorMap& tm_w, const
                               const CUtensorMap* tm_b, dim3 grid, int fp4, int pdl, cudaStream_t stream);
 int k2_prefill_max_steps();
 cudaError_t launch_k2_prefill_pair(const K2pParams& p, const CUtensorMap& tm_w, const CUtensorMap& tm_x, const CUtensorMap& tm_h,
-                                   const CUtensorMap* tm_b, int pairs, int fp4, int pdl, cudaStream_t stream);
+                                   const CUtensorMap* tm_b, const CUtensorMap* tm_sf, int pairs, int fp4, int pdl,
+                                   cudaStream_t stream);
 int k2_prefill_pair_capacity(int fp4);
 int k2_prefill_pair_max_steps();
 int k2_prefill_pair_rows(int fp4);
@@ -85,9 +86,9 @@ EncodeTiledFn encode_fn() {
 }
 
 // 2-D row-major tensor [rows, inner] of `elem_bytes` elements -> tiled map with box [box_rows, box_inner], swizzle by the
-// box's inner bytes (32 / 64 / 128).
+// box's inner bytes (32 / 64 / 128); `linear` asks for an unswizzled box (rows of up to 256 elements, back to back).
 int encode_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t inner, uint64_t rows,
-              uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows) {
+              uint64_t pitch_bytes, uint32_t box_inner, uint32_t box_rows, bool linear = false) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return OB_ERR_DRIVER;
     const uint32_t inner_bytes = box_inner * (uint32_t)elem_bytes;
@@ -95,7 +96,8 @@ int encode_2d(CUtensorMap* tm, CUtensorMapDataType dt, int elem_bytes, const voi
                             : inner_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
                             : inner_bytes == 32 ? CU_TENSOR_MAP_SWIZZLE_32B
                                                 : CU_TENSOR_MAP_SWIZZLE_NONE;
-    if (sw == CU_TENSOR_MAP_SWIZZLE_NONE) return OB_ERR_SHAPE;
+    if (linear) sw = CU_TENSOR_MAP_SWIZZLE_NONE;
+    if ((sw == CU_TENSOR_MAP_SWIZZLE_NONE && !linear) || box_inner > 256 || box_rows > 256) return OB_ERR_SHAPE;
     cuuint64_t gdim[2] = {inner, rows};
     cuuint64_t gstride[1] = {pitch_bytes};
     cuuint32_t box[2] = {box_inner, box_rows};
@@ -128,6 +130,7 @@ struct ObLayer {
     bool big_ok;                       // bf16 adapters of rank >= 64, slice widths in multiples of 256 (NVFP4 base: 128):
     CUtensorMap tm_w2;                 //   the large-tile prefill GEMM applies; FP8 base: W and B in 256-row boxes
     CUtensorMap tm_b2[OB_MAX_SLICES];
+    CUtensorMap tm_wsf;                //   NVFP4 base: the packed W block scales as a [rows, 256] byte tensor (8 rows per atom)
     std::mutex mu;
     std::vector<XMap> xmaps;      // x_q maps by (workspace region, rows, token tile)
 };
@@ -361,7 +364,9 @@ int get_xmap(ObLayer* l, const void* xq, int rows, int tn, CUtensorMap* out) {
     m.rows = rows;
     m.tn = tn;
     const uint64_t lc = (uint64_t)(l->d.L < kMaxTileTenants ? l->d.L : kMaxTileTenants);
-    int st = tn == -2   // the shrink's per-tenant h blocks [S * rows, lc * R] bf16: 64-element x 128-row boxes
+    int st = tn == -4   // NVFP4 activation block scales as a [rows, 256] byte tensor: one 2 KB atom = an unswizzled 8-row box
+                 ? encode_2d(&m.tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, xq, 256, (uint64_t)rows, 256, 256, 8, true)
+             : tn == -2   // the shrink's per-tenant h blocks [S * rows, lc * R] bf16: 64-element x 128-row boxes
                  ? encode_2d(&m.tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, xq, lc * (uint64_t)l->d.R, (uint64_t)l->d.S * (uint64_t)rows,
                              lc * (uint64_t)l->d.R * 2, 64, 128)
              : tn < 0   // the adapter-sorted bf16 copy of x: 64-element x 128-row boxes for the tensor-core shrink
@@ -624,9 +629,14 @@ int k2_prefill_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceSha
     p.ldy = b->ldy;
     p.status = reinterpret_cast<int32_t*>(base + lay.status);
     if (pairs) {
+        CUtensorMap tm_sf[2] = {l->tm_wsf, l->tm_w};
+        if (is_fp4) {
+            st = get_xmap(l, base + lay.xsf, (int)((lay.hp - lay.xsf) / 256), -4, &tm_sf[1]);
+            if (st != OB_OK) return st;
+        }
         const long long ptiles = (long long)((b->M + 255) / 256) * (d.N / pair_rows);
         const int n = (int)(ptiles < pair_cap ? ptiles : pair_cap);
-        cudaError_t e = launch_k2_prefill_pair(p, l->tm_w, tm_x, tm_h, l->tm_b, n, is_fp4, pdl, stream);
+        cudaError_t e = launch_k2_prefill_pair(p, l->tm_w, tm_x, tm_h, l->tm_b, tm_sf, n, is_fp4, pdl, stream);
         return e == cudaSuccess ? OB_OK : (int)e;
     }
     const int rows = fp4 ? 128 : 256;            // output features per CTA
@@ -888,6 +898,9 @@ int ob_layer_create(const ObLayerDesc* desc, ObLayer** out) {
                            (uint64_t)desc->L * (uint64_t)desc->widths[ss], (uint64_t)desc->R * 2, 64, 256);
         }
     }
+    if (st == OB_OK && l->big_ok && desc->base_fmt == OB_BASE_NVFP4)
+        st = encode_2d(&l->tm_wsf, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, desc->w_sf, 256,
+                       (uint64_t)l->n_tiles * (uint64_t)((desc->K + 255) / 256) * (kSfSlotBytes / 256), 256, 256, 8, true);
     if (st != OB_OK) {
         delete l;
         return st;
