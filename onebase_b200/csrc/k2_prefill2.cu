@@ -13,12 +13,12 @@
 // 128 B], x_q [128 tokens x 128 B], its tokens' block scales (2 KB) and the W block scales of all 256 features (4 KB;
 // every CTA needs the scales of all of B's rows in its own tensor memory).  No load is multicast.
 //
-// Per CTA (256 threads): warp 0 = TMA producer of the CTA's own operands -- every load a tensor load of the
+// Per CTA (384 threads): warp 0 = TMA producer of the CTA's own operands -- every load a tensor load of the
 // cta_group::2 form, whose bytes are counted on the slot barrier of the pair's rank-0 CTA, so one wait there covers
 // both CTAs' operands (the block scales are fetched as 8 x 256-byte boxes of a [rows, 256] byte tensor for that
 // reason); warp 1 = in the pair's rank-0 CTA the MMA issuer for both; warp 2 = tile
-// scout (row map, output scale, expand steps; both CTAs compute the same list); warps 3..6 = epilogue of the CTA's own
-// 128 tokens (straight from tensor memory to y);
+// scout (row map, output scale, expand steps; both CTAs compute the same list); warps 3..6 and 8..11 = epilogue of the CTA's own
+// 128 tokens (straight from tensor memory to y; two warps per lane quarter, half of the features each);
 // warp 7 = in rank 0 the scale copier (tcgen05.cp of a slot's scale factors into both CTAs' tensor memory).  The issuer's commits arrive on the slot-free and accumulator-full barriers of BOTH CTAs
 // (tcgen05.commit ... multicast::cluster, an arrival, not a load).  The kernel is persistent: a pair walks the launch's
 // tiles; accumulators are single-buffered (256 columns + 5 x 48 scale columns), the five-slot ring runs ahead into the
@@ -34,7 +34,7 @@
 
 namespace ob {
 
-constexpr int kP2Threads = 256;
+constexpr int kP2Threads = 384;
 constexpr int kP2Tokens = 256;               // tokens per tile: 128 per CTA (the MMA's M)
 constexpr int kP2WBytes = 128 * 128;         // 128 rows of W (or B_l) of a slot
 constexpr int kP2XBytes = 128 * 128;         // this CTA's half of the token tile
@@ -66,7 +66,7 @@ struct P2Ctrl {
     uint64_t meta_full[2];
     uint64_t meta_empty[2];
     uint64_t acc_full;               // arrives in both CTAs
-    uint64_t acc_empty;              // rank 0 only: both CTAs' epilogue warps (8 arrivals)
+    uint64_t acc_empty;              // rank 0 only: both CTAs' epilogue warps (16 arrivals)
     uint32_t tmem_base;
     volatile int abort_flag;
     int go_flag;
@@ -139,10 +139,10 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&ctrl->meta_full[i], 1);
-            mbar_init(&ctrl->meta_empty[i], 4);
+            mbar_init(&ctrl->meta_empty[i], 8);
         }
         mbar_init(&ctrl->acc_full, 1);
-        mbar_init(&ctrl->acc_empty, 8);
+        mbar_init(&ctrl->acc_empty, 16);
         ctrl->abort_flag = 0;
         fence_mbar_init();
     }
@@ -426,9 +426,11 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
             if (lane == 0) mbar_arrive(&ctrl->meta_full[i & 1]);
         }
     } else {
-        // =========================================================== epilogue (warps 3..6): this CTA's 128 tokens -> y
+        // =========================================================== epilogue (warps 3..6 and 8..11): this CTA's 128 tokens -> y
+        // Two warps per 32-lane quarter of tensor memory, one per half of the tile's features.
         const int te = tid - 96;
         const int q = warp & 3;                               // the 32 tensor-memory lanes this warp may read
+        const int c_beg = warp >= 8 ? kRows / 2 : 0, c_end = c_beg + kRows / 2;
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
         const uint32_t acc_empty_addr = cluster_peer_addr(smem_u32(&ctrl->acc_empty), 0);
         for (int t = pair, i = 0; t < n_tiles; t += n_pairs, ++i) {
@@ -445,41 +447,75 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
                 }
                 ctrl->go_flag = go;
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             const int go = ctrl->go_flag;
-            asm volatile("bar.sync 1, 128;" ::: "memory");    // everyone has read the flag before its next writer runs
+            asm volatile("bar.sync 1, 256;" ::: "memory");    // everyone has read the flag before its next writer runs
             if (!go) break;
             tc_fence_after();
             const P2Tile tl = p2_tile<FP4>(p, t, m_tiles);
             // Thread = one token (tensor-memory lane); a load brings 32 consecutive features of it, 64 contiguous bytes of
-            // the token's row in y: four 16-byte stores straight from registers, no staging, no barrier between the warps.
+            // the token's row in y.  Stored as they come, a warp's store instruction would touch 32 rows with 16 bytes each and
+            // the tile's read-out is bound by the store unit (measured: 18 k cycles per 512-feature tile, a third of the
+            // kernel, spent with the tensor pipe idle).  So every four lanes transpose their 4 x 4 sixteen-byte pieces first
+            // (two shuffle stages): lane j of a group then holds piece j of each of the group's four tokens, and a store
+            // instruction writes 64 contiguous bytes of 8 rows.  No staging in shared memory, no barrier between the warps.
+            // Two register buffers: the next load is in flight while this one is converted and stored.
             const int c_tok = (int)rank * 128 + q * 32 + lane;
             const int row = mt.rowmap[c_tok];
             const float sc = mt.scale[c_tok];
-            __nv_bfloat16* yrow = p.y + (int64_t)(row < 0 ? 0 : row) * p.ldy + tl.slice_off + tl.n0_local;
+            const int lj = lane & 3;
+            __nv_bfloat16* yr4[4];
+            bool live4[4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const int rr = __shfl_sync(0xffffffffu, row, (lane & ~3) + r);
+                live4[r] = rr >= 0;
+                yr4[r] = p.y + (int64_t)(rr < 0 ? 0 : rr) * p.ldy + tl.slice_off + tl.n0_local + lj * 8;
+            }
+            auto store32 = [&](const uint32_t (&r)[32], int c0) {
+                uint32_t o[16];                               // o[4 v + u]: piece v (8 features), register u
+#pragma unroll
+                for (int u = 0; u < 16; ++u) {
+                    const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[2 * u]) * sc, __uint_as_float(r[2 * u + 1]) * sc);
+                    o[u] = *reinterpret_cast<const uint32_t*>(&b2);
+                }
+#pragma unroll
+                for (int v = 0; v < 2; ++v)                   // 2 x 2 blocks of pieces change places between lanes j and j ^ 2
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t send = (lj & 2) ? o[v * 4 + u] : o[(v + 2) * 4 + u];
+                        const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 2);
+                        if (lj & 2) o[v * 4 + u] = recv; else o[(v + 2) * 4 + u] = recv;
+                    }
+#pragma unroll
+                for (int v = 0; v < 4; v += 2)                // then the pieces inside each block between lanes j and j ^ 1
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t send = (lj & 1) ? o[v * 4 + u] : o[(v + 1) * 4 + u];
+                        const uint32_t recv = __shfl_xor_sync(0xffffffffu, send, 1);
+                        if (lj & 1) o[v * 4 + u] = recv; else o[(v + 1) * 4 + u] = recv;
+                    }
+#pragma unroll
+                for (int r4 = 0; r4 < 4; ++r4)                // o[4 r4 ..]: piece lj of the group's token r4
+                    if (live4[r4])
+                        *reinterpret_cast<uint4*>(yr4[r4] + c0) = make_uint4(o[r4 * 4], o[r4 * 4 + 1], o[r4 * 4 + 2], o[r4 * 4 + 3]);
+            };
+            uint32_t ra[32], rb[32];
+            tmem_ld32(tmem_base + lane_addr + (uint32_t)c_beg, ra);
 #pragma unroll 1
-            for (int c0 = 0; c0 < kRows; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + lane_addr + (uint32_t)c0, r);
+            for (int c0 = c_beg; c0 < c_end; c0 += 64) {
                 tmem_ld_wait();
-                if (c0 + 32 >= kRows) {                       // tensor memory has been read: the next tile's MMAs may start
+                tmem_ld32(tmem_base + lane_addr + (uint32_t)(c0 + 32), rb);
+                store32(ra, c0);
+                tmem_ld_wait();
+                if (c0 + 64 < c_end) {
+                    tmem_ld32(tmem_base + lane_addr + (uint32_t)(c0 + 64), ra);
+                } else {                                      // tensor memory has been read: the next tile's MMAs may start
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive_remote(acc_empty_addr);
                 }
-                if (row >= 0) {
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint32_t o[4];
-#pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * u]) * sc,
-                                                                            __uint_as_float(r[v * 8 + 2 * u + 1]) * sc);
-                            o[u] = *reinterpret_cast<const uint32_t*>(&b2);
-                        }
-                        *reinterpret_cast<uint4*>(yrow + c0 + v * 8) = make_uint4(o[0], o[1], o[2], o[3]);
-                    }
-                }
+                store32(rb, c0 + 32);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctrl->meta_empty[i & 1]);

@@ -601,9 +601,6 @@ int k2_prefill_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceSha
     const int pair_rows = k2_prefill_pair_rows(is_fp4);
     bool pairs = !no_pairs;
     for (int s = 0; s < d.S; ++s) pairs = pairs && d.widths[s] % pair_rows == 0;
-    // FP8 base: measured on a B200 the pair kernel wins on the short-K projections (qkv, gate_up: 3-7 %) and loses on the
-    // long-K one (down, K = 12288: its few, long tiles quantize worse over 74 pairs than over 148 single CTAs)
-    if (!is_fp4 && d.K > 8192) pairs = false;
     const int pair_cap = pairs ? k2_prefill_pair_capacity(is_fp4) : 0;
     pairs = pairs && pair_cap > 0;
     if (std::getenv("LOWBIT_VERBOSE")) std::fprintf(stderr, "[onebase_b200] prefill GEMM: pairs=%d (resident pairs %d)\n", (int)pairs, pair_cap);
