@@ -13,13 +13,13 @@
 // 128 B], x_q [128 tokens x 128 B], its tokens' block scales (2 KB) and the W block scales of all 256 features (4 KB;
 // every CTA needs the scales of all of B's rows in its own tensor memory).  No load is multicast.
 //
-// Per CTA (384 threads): warp 0 = TMA producer of the CTA's own operands -- every load a tensor load of the
+// Per CTA (448 threads): warp 0 = TMA producer of the CTA's own operands -- every load a tensor load of the
 // cta_group::2 form, whose bytes are counted on the slot barrier of the pair's rank-0 CTA, so one wait there covers
 // both CTAs' operands (the block scales are fetched as 8 x 256-byte boxes of a [rows, 256] byte tensor for that
 // reason); warp 1 = in the pair's rank-0 CTA the MMA issuer for both; warp 2 = tile
 // scout (row map, output scale, expand steps; both CTAs compute the same list); warps 3..6 and 8..11 = epilogue of the CTA's own
 // 128 tokens (straight from tensor memory to y; two warps per lane quarter, half of the features each);
-// warp 7 = in rank 0 the scale copier (tcgen05.cp of a slot's scale factors into both CTAs' tensor memory).  The issuer's commits arrive on the slot-free and accumulator-full barriers of BOTH CTAs
+// warps 7, 12, 13 = in rank 0 the scale copiers (tcgen05.cp of a slot's scale factors into both CTAs' tensor memory).  The issuer's commits arrive on the slot-free and accumulator-full barriers of BOTH CTAs
 // (tcgen05.commit ... multicast::cluster, an arrival, not a load).  The kernel is persistent: a pair walks the launch's
 // tiles; accumulators are single-buffered (256 columns + 5 x 48 scale columns), the five-slot ring runs ahead into the
 // next tile while the epilogue drains.  The LoRA expand is folded into the accumulator as in k2_prefill.cu: per
@@ -34,7 +34,7 @@
 
 namespace ob {
 
-constexpr int kP2Threads = 384;
+constexpr int kP2Threads = 448;
 constexpr int kP2Tokens = 256;               // tokens per tile: 128 per CTA (the MMA's M)
 constexpr int kP2WBytes = 128 * 128;         // 128 rows of W (or B_l) of a slot
 constexpr int kP2XBytes = 128 * 128;         // this CTA's half of the token tile
@@ -134,7 +134,7 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
             // rank 0's: one arrival whose transaction count covers both CTAs' bytes (every load is a tensor load, and the
             // partner's complete on this barrier directly); rank 1's is never used
             mbar_init(&ctrl->full[i], 1);
-            mbar_init(&ctrl->sf_ready[i], 1);
+            mbar_init(&ctrl->sf_ready[i], 3);   // one commit per copier thread
             mbar_init(&ctrl->empty[i], 1);
         }
         for (int i = 0; i < 2; ++i) {
@@ -316,10 +316,13 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
                 if (ok) umma_commit_pair(&ctrl->acc_full, 3);
             }
         }
-    } else if (warp == 7) {
-        // =========================================================== scale copier (NVFP4, rank 0): a k-block slot's scale
-        // factors -> both CTAs' tensor memory, ahead of the MMAs.  A thread of its own because every tcgen05 instruction costs
-        // its issuer some 50 cycles: twelve copies and four MMAs per slot from one thread would bound the main loop.
+    } else if (warp == 7 || warp >= 12) {
+        // =========================================================== scale copiers (NVFP4, rank 0; warps 7, 12, 13): a k-block
+        // slot's scale factors -> both CTAs' tensor memory, ahead of the MMAs.  Threads of their own because every tcgen05
+        // instruction costs its issuer some 50 cycles: twelve copies per slot from one thread (with its wait and commit, 920
+        // cycles) bounded the main loop, whose four MMAs take the tensor pipe some 540.  Copier 0 moves the tokens' scales,
+        // copiers 1 and 2 those of the two 128-feature halves of W: four copies each per slot.
+        const int cpi = warp == 7 ? 0 : warp - 11;
         if (FP4 && lane == 0 && rank == 0) {
             int it = 0;
             bool ok = true;
@@ -344,10 +347,8 @@ k2_prefill_pair_kernel(const K2pParams p, const __grid_constant__ CUtensorMap tm
                     const uint32_t sft = tmem_base + 256u + (uint32_t)(st * kP2SfCols);
 #pragma unroll
                     for (int k = 0; k < 4; ++k) {
-                        const uint32_t ta = sft + (uint32_t)k * 4u, tb = sft + 16u + (uint32_t)k * 8u;
-                        tmem_cp_sf_pair(ta, sf_smem_desc(sfs + (uint32_t)k * 512u));
-                        tmem_cp_sf_pair(tb, sf_smem_desc(sfs + kSfSlotBytes + (uint32_t)k * 512u));
-                        tmem_cp_sf_pair(tb + 4u, sf_smem_desc(sfs + 2 * kSfSlotBytes + (uint32_t)k * 512u));
+                        const uint32_t dst = cpi == 0 ? sft + (uint32_t)k * 4u : sft + 16u + (uint32_t)k * 8u + (uint32_t)(cpi - 1) * 4u;
+                        tmem_cp_sf_pair(dst, sf_smem_desc(sfs + (uint32_t)cpi * kSfSlotBytes + (uint32_t)k * 512u));
                     }
                     umma_commit_pair(&ctrl->sf_ready[st], 1);      // (arrives in rank 0 only)
                 }
