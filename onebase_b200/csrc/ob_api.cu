@@ -292,12 +292,13 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     // Larger batches go to the 256 x 256 prefill GEMM unless the caller names a token tile (LOWBIT_PREFILL_SMALL_TILES=1
     // keeps k2_gemm.cu's tiles); prepare_call() drops the choice again when the workspace has no room for its h blocks.
     static const bool no_big = [] { const char* v = std::getenv("LOWBIT_PREFILL_SMALL_TILES"); return v && v[0] == '1'; }();
-    // ... and unless its 256 x 256 tiles would leave most of the 148 SMs idle (one CTA per SM): then k2_gemm.cu's 128 x 128
-    // tiles, four times as many, are the better fit.
+    // (LOWBIT_PREFILL_MIN_TILES=n sends launches of fewer than n 256-token tiles back to k2_gemm.cu's 128 x 128 tiles; with
+    // the CTA-pair kernel the large tiles measured equal or faster from 512 tokens on for every projection, so n = 1)
+    static const int min_big_tiles = [] { const char* v = std::getenv("LOWBIT_PREFILL_MIN_TILES"); return v ? std::atoi(v) : 1; }();
     const long long big_tiles = (long long)((M + 255) / 256) * (d.N / (fp4 ? 128 : 256));
     const long long big_steps = 2LL * (d.L < kMaxTileTenants ? d.L : kMaxTileTenants) * (d.R / 64);   // a tile's expand steps at most
     r->big = (!no_big && r->mma_shrink && l->big_ok && M > kBigTileMinTokens && !(cfg && cfg->tn) &&
-              big_steps <= k2_prefill_max_steps() && (pf == 1 || big_tiles >= 120)) ? 1 : 0;
+              big_steps <= k2_prefill_max_steps() && (pf == 1 || big_tiles >= min_big_tiles)) ? 1 : 0;
     if (split1 == 0 && r->mma_shrink) {   // one wave of (128-position tile, slice, K split) CTAs, at least 256 elements each
         const int tiles = ((M + 127) / 128) * d.S;
         split1 = 1;
