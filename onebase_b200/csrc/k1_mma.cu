@@ -32,6 +32,7 @@ constexpr int kMmaXBytes = kMmaTile * kMmaKStep * 2;       // 16 KB
 constexpr int kMmaMaxCols = 512;       // tensor-memory columns: R per tenant in flight
 constexpr int kMmaMaxStages = 8;
 constexpr int kMmaMaxList = 128;       // tenants with a position in one tile
+constexpr int kMmaMaxSeg = 257;        // segments of a batch: at most 256 tenants and the positions without one
 
 struct K1mCtrl {
     uint64_t full[kMmaMaxStages];
@@ -41,6 +42,9 @@ struct K1mCtrl {
     uint32_t tmem_base;
     volatile int abort_flag;
     int n_list;
+    int wi_tile;                       // this CTA's work item: position tile and first list entry of its tenant group
+    int wi_g0;
+    int wait_before_exit;
     int last_flag;
     int lora[kMmaMaxList];             // the tile's tenants in segment order
     short gidx[kMmaTile];              // list entry of each position (-1: no adapter)
@@ -57,6 +61,9 @@ __device__ __forceinline__ void k1m_timeout(const K1mParams& p, K1mCtrl* c, int 
     }
 }
 
+// GROUPS: a tile's tenants are dealt out to several CTAs (p.tg_cap of them each); false: one CTA per tile, the grid's x is
+// the tile (two instantiations: the one-CTA-per-tile form compiled with the group logic beside it measured slower).
+template <bool GROUPS>
 __global__ void __launch_bounds__(kMmaThreads, 1)
 k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, const __grid_constant__ CUtensorMap tm_a0,
               const __grid_constant__ CUtensorMap tm_a1, const __grid_constant__ CUtensorMap tm_a2,
@@ -68,7 +75,19 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     griddep_launch_dependents();
     const uint64_t limit_ns = (uint64_t)p.wait_ms * 1000000ull;
-    const int t0 = blockIdx.x * kMmaTile, s = blockIdx.y, j = blockIdx.z;
+    // Work item, slice and K split of this CTA, numbered so that CTAs are dispatched in work-item order (the grid's x runs
+    // fastest): the CTAs beyond the launch's last item -- the grid is the host's upper bound -- then come last instead of
+    // taking SMs ahead of working ones.  A cluster is the grid's z extent (rank = split), so only x and y are folded there.
+    int wi, s, j;
+    if (!GROUPS) {                                            // one CTA per tile: every CTA has a work item
+        wi = (int)blockIdx.x; s = (int)blockIdx.y; j = (int)blockIdx.z;
+    } else if (p.cluster) {
+        const int lin = (int)(blockIdx.x + gridDim.x * blockIdx.y);
+        j = (int)blockIdx.z; s = lin % p.S; wi = lin / p.S;
+    } else {
+        int lin = (int)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z));
+        j = lin % p.split1; lin /= p.split1; s = lin % p.S; wi = lin / p.S;
+    }
     const int k0 = j * p.k_per_split, k1 = min(p.K, k0 + p.k_per_split);
     const int n_ksteps = k1 > k0 ? (k1 - k0 + kMmaKStep - 1) / kMmaKStep : 0;
     const int a_bytes = p.R * kMmaKStep * 2;                  // one tenant's A tile of a ring slot
@@ -91,21 +110,65 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
     }
     for (int c = tid; c < kMmaTile; c += kMmaThreads) ctrl->gidx[c] = -1;
     __syncthreads();
-    // ---- the tile's tenants, from the segment index (static during the preceding kernels)
+    // ---- this CTA's work item and the tile's tenants, from the segment index (static during the preceding kernels)
     if (warp == 2) {
         int n_all, n_ad;
         segment_totals(p.meta, p.L, lane, n_all, n_ad);
         n_all = min(n_all, p.M);
+        // (tile, tenant group) number wi in tile order.  First and last tile of every segment go to shared memory;
+        // then a lane is one tile of a batch of 32 and counts the segments that cover it.
+        const int n_tiles = (p.M + kMmaTile - 1) / kMmaTile, w = wi;
+        // (the two arrays follow the control block, in launches with groups only: with them the one-CTA-per-tile launch's
+        // shared memory crossed 196 KB and its K1b measured 10-16 us slower on the long-K projection)
+        const int n_seg = GROUPS ? min(p.L + 1, kMmaMaxSeg) : 0;
+        int* seg_first = reinterpret_cast<int*>(ctrl + 1);
+        int* seg_last = seg_first + kMmaMaxSeg;
+        for (int i = lane; i < n_seg; i += 32) {
+            const int lora = __ldg(p.meta.seg_ids + i), n = __ldg(p.meta.seg_n + i), sst = __ldg(p.meta.seg_start + i);
+            const int end = min(sst + n, n_all);
+            const bool ok = lora >= 0 && lora < p.L && n > 0 && sst >= 0 && sst < end;
+            seg_first[i] = ok ? sst / kMmaTile : 0x7fffffff;
+            seg_last[i] = ok ? (end - 1) / kMmaTile : -1;
+        }
+        __syncwarp();
+        int acc = 0, tile = -1, first = 0;
+        if (!GROUPS) {                                        // one CTA per tile: the work item is the tile
+            tile = (w < n_tiles && n_ad > 0) ? w : -1;
+            acc = 0;
+        }
+        for (int tb = 0; GROUPS && tb < n_tiles && tile < 0 && n_ad > 0; tb += 32) {
+            const int t = tb + lane;
+            int cnt = 0;
+            for (int i = 0; i < n_seg; ++i) cnt += (seg_first[i] <= t && t <= seg_last[i]) ? 1 : 0;
+            const int items = t < n_tiles ? (min(cnt, kMmaMaxList) + p.tg_cap - 1) / p.tg_cap : 0;
+            int pre = items;                                  // inclusive prefix over the batch's tiles
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, pre, o);
+                if (lane >= o) pre += v;
+            }
+            const uint32_t hit = __ballot_sync(0xffffffffu, w >= acc + pre - items && w < acc + pre);
+            if (hit) {
+                const int src = __ffs(hit) - 1;
+                tile = tb + src;
+                first = (w - acc - __shfl_sync(0xffffffffu, pre - items, src)) * p.tg_cap;
+            }
+            acc += __shfl_sync(0xffffffffu, pre, 31);
+        }
+        // a CTA beyond the launch's last work item leaves at once -- unless the launch has none at all: then nobody else
+        // would keep this grid from completing before the grid it depends on
+        if (lane == 0) ctrl->wait_before_exit = (tile < 0 && acc == 0) ? 1 : 0;
         int total = 0;
-        if (n_ad > 0) {
+        if (tile >= 0) {
+            const int t0w = tile * kMmaTile;
             for (int base = 0; base <= p.L; base += 32) {
                 const int i = base + lane;
                 int lora = -1, lo = 0, hi = 0;
                 if (i <= p.L) {
                     lora = p.meta.seg_ids[i];
                     const int cnt = p.meta.seg_n[i], sst = p.meta.seg_start[i];
-                    lo = max(sst, t0);
-                    hi = min(min(sst + cnt, t0 + kMmaTile), n_all);
+                    lo = max(sst, t0w);
+                    hi = min(min(sst + cnt, t0w + kMmaTile), n_all);
                     if (cnt <= 0 || sst < 0) lora = -1;
                 }
                 const bool ok = lora >= 0 && lora < p.L && lo < hi;
@@ -114,18 +177,25 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
                     const int idx = total + __popc(mask & ((1u << lane) - 1u));
                     if (idx < kMmaMaxList) {
                         ctrl->lora[idx] = lora;
-                        for (int pos = lo; pos < hi; ++pos) ctrl->gidx[pos - t0] = (short)idx;
+                        for (int pos = lo; pos < hi; ++pos) ctrl->gidx[pos - t0w] = (short)idx;
                     }
                 }
                 total += __popc(mask);
             }
         }
-        if (lane == 0) ctrl->n_list = min(total, kMmaMaxList);
+        if (lane == 0) {
+            ctrl->n_list = min(total, kMmaMaxList);
+            ctrl->wi_tile = tile;
+            ctrl->wi_g0 = first;
+        }
     }
     __syncthreads();
-    const int n_list = ctrl->n_list;
-    if (n_list == 0 || n_ksteps == 0) {                       // no tenant in this tile (uniform: nothing was allocated)
-        griddep_wait();                                       // this grid must not be complete before the grid it depends on is
+    const int t0 = ctrl->wi_tile * kMmaTile;
+    const int g_lo = GROUPS ? ctrl->wi_g0 : 0;                // list entries [g_lo, g_lo + n_list) are this CTA's tenants
+    const int n_list = ctrl->wi_tile < 0 ? 0 : GROUPS ? min(p.tg_cap, ctrl->n_list - g_lo) : ctrl->n_list;
+    if (n_list <= 0 || n_ksteps == 0) {                       // the launch has fewer work items than CTAs (or no tenant at all)
+        // this grid must not be complete before the grid it depends on is: the CTAs with a work item see to that
+        if (!GROUPS || n_ksteps == 0 || ctrl->wait_before_exit) griddep_wait();
         return;
     }
     const int n_pass = (n_list + group - 1) / group;
@@ -164,7 +234,7 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
                     tma_load_2d(slot, &tm_xs, &ctrl->full[st], k0 + ks * kMmaKStep, t0);
                     for (int g = 0; g < ng; ++g)
                         tma_load_2d(slot + kMmaXBytes + (size_t)g * a_bytes, tma, &ctrl->full[st], k0 + ks * kMmaKStep,
-                                    ctrl->lora[g0 + g] * p.R);
+                                    ctrl->lora[g_lo + g0 + g] * p.R);
                 }
             }
         }
@@ -236,7 +306,7 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
             if (!go) break;
             tc_fence_after();
             for (int g = 0; g < ng; ++g) {
-                const bool own = mine == g0 + g && pos < p.M;
+                const bool own = mine == g_lo + g0 + g && pos < p.M;
                 if (cat && direct) {                          // every row of the block: the tenant's rows scaled, zeros elsewhere
                     for (int c0 = 0; c0 < p.R; c0 += 16) {
                         uint32_t r[16];
@@ -250,7 +320,7 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
                             o[v] = *reinterpret_cast<uint32_t*>(&b);
                         }
                         if (pos < p.max_m) {
-                            uint4* d4 = reinterpret_cast<uint4*>(cdst + (size_t)(g0 + g) * p.R + c0);
+                            uint4* d4 = reinterpret_cast<uint4*>(cdst + (size_t)(g_lo + g0 + g) * p.R + c0);
                             d4[0] = make_uint4(o[0], o[1], o[2], o[3]);
                             d4[1] = make_uint4(o[4], o[5], o[6], o[7]);
                         }
@@ -297,20 +367,20 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (te == 0) {
                 int old;
-                asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + blockIdx.x * p.S + s) : "memory");
+                asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + wi * p.S + s) : "memory");
                 ctrl->last_flag = (old == p.split1 - 1) ? 1 : 0;
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (ctrl->last_flag && !ctrl->abort_flag && cat && pos < p.max_m) {
-                // zeros for the block's other entries first; the position's own entry is written below
-                for (int li = 0; li < n_list; ++li) {
+                // zeros for the group's other entries first; the position's own entry is written below
+                for (int li = g_lo; li < g_lo + n_list; ++li) {
                     if (li == mine && pos < p.M) continue;
                     uint4* d4 = reinterpret_cast<uint4*>(cdst + (size_t)li * p.R);
                     for (int c = 0; c < p.R / 8; ++c) d4[c] = make_uint4(0u, 0u, 0u, 0u);
                 }
             }
             if (ctrl->last_flag && !ctrl->abort_flag) {
-                if (mine >= 0 && pos < p.M) {
+                if (mine >= g_lo && mine < g_lo + n_list && pos < p.M) {
                     __nv_bfloat16* odst = cat ? cdst + (size_t)mine * p.R : hdst;
                     const float osc = cat ? inv : 1.0f;
                     const size_t jstride = (size_t)p.S * p.max_m * p.R;
@@ -353,7 +423,7 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
                         }
                     }
                 }
-                if (te == 0) p.counters[blockIdx.x * p.S + s] = 0;
+                if (te == 0) p.counters[wi * p.S + s] = 0;
             }
         }
     }
@@ -374,10 +444,10 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
             const int cols = p.R / tpr, c_lo = sub * cols;                     // a multiple of 4 columns per thread
             const int pos = t0 + row, mine = ctrl->gidx[row];
             const bool cat = p.hcat != nullptr;
-            const bool valid = mine >= 0 && pos < p.M;
-            if (cat && pos < p.max_m) {                       // zeros for the block's other entries, shared among the row's threads
+            const bool valid = mine >= g_lo && mine < g_lo + n_list && pos < p.M;
+            if (cat && pos < p.max_m) {                       // zeros for the group's other entries, shared among the row's threads
                 __nv_bfloat16* cdst = p.hcat + ((size_t)s * p.max_m + (size_t)pos) * ((size_t)p.lc * p.R);
-                for (int li = sub; li < n_list; li += tpr) {
+                for (int li = g_lo + sub; li < g_lo + n_list; li += tpr) {
                     if (valid && li == mine) continue;
                     uint4* d4 = reinterpret_cast<uint4*>(cdst + (size_t)li * p.R);
                     for (int c = 0; c < p.R / 8; ++c) d4[c] = make_uint4(0u, 0u, 0u, 0u);
@@ -408,16 +478,20 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
     }
 }
 
-size_t k1_mma_smem_bytes(int ring_bytes) { return 1024 + (size_t)ring_bytes + sizeof(K1mCtrl) + 64; }
+size_t k1_mma_smem_bytes(int ring_bytes, bool groups) {
+    return 1024 + (size_t)ring_bytes + sizeof(K1mCtrl) + 64 + (groups ? 2 * kMmaMaxSeg * sizeof(int) : 0);
+}
 
 cudaError_t launch_k1_mma(const K1mParams& p, const CUtensorMap& tm_xs, const CUtensorMap* tm_a, dim3 grid, cudaStream_t stream) {
     static int configured_for[64] = {0};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    const size_t smem = k1_mma_smem_bytes(p.ring_bytes);
+    const size_t smem = k1_mma_smem_bytes(p.ring_bytes, p.tg_cap < kMmaMaxList);
     if (dev >= 0 && dev < 64 && !configured_for[dev]) {
-        e = cudaFuncSetAttribute(k1_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+        e = cudaFuncSetAttribute(k1_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+        if (e != cudaSuccess) return e;
+        e = cudaFuncSetAttribute(k1_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
         if (e != cudaSuccess) return e;
         configured_for[dev] = 1;
     }
@@ -435,7 +509,8 @@ cudaError_t launch_k1_mma(const K1mParams& p, const CUtensorMap& tm_xs, const CU
     attr[1].val.clusterDim.z = grid.z;
     cfg.attrs = attr;
     cfg.numAttrs = p.cluster ? 2 : 1;
-    return cudaLaunchKernelEx(&cfg, k1_mma_kernel, p, tm_xs, tm_a[0], tm_a[1], tm_a[2], tm_a[3]);
+    if (p.tg_cap < kMmaMaxList) return cudaLaunchKernelEx(&cfg, k1_mma_kernel<true>, p, tm_xs, tm_a[0], tm_a[1], tm_a[2], tm_a[3]);
+    return cudaLaunchKernelEx(&cfg, k1_mma_kernel<false>, p, tm_xs, tm_a[0], tm_a[1], tm_a[2], tm_a[3]);
 }
 
 }  // namespace ob

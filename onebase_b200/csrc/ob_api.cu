@@ -1,5 +1,6 @@
 // The C ABI (include/onebase_b200.h): argument validation, launch geometry, TMA descriptor construction, launches.
 // Host code only allocates host memory; device memory always belongs to the caller.
+#include <algorithm>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -230,6 +231,14 @@ int default_tn(int M) {
     return tn;
 }
 
+// Tenants with a position in one 128-position tile of an adapter-sorted batch, estimated for L tenants of equal size:
+// 128 L / M of them and one more that straddles the tile's edge.
+int shrink_tenants_per_tile(int L, int M) { return (int)std::min<long long>(L, (128LL * L + M - 1) / M + 1); }
+// Tenants per CTA of the tensor-core shrink.  Tiles of six or more tenants are dealt out in groups of kMmaShrinkGroup
+// to CTAs of their own (measured at 512 tokens over 32 tenants: K1 55-75 -> 32-52 us per projection); with fewer
+// tenants per tile one CTA per tile measured better (no CTAs without a work item, one pass over the segment index).
+int shrink_group_cap(int L, int M) { return shrink_tenants_per_tile(L, M) >= 6 ? kMmaShrinkGroup : kMaxTileTenants; }
+
 int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     const ObLayerDesc& d = l->d;
     const bool fp4 = d.base_fmt == OB_BASE_NVFP4;
@@ -299,8 +308,11 @@ int resolve_cfg(const ObLayer* l, int M, const ObTileCfg* cfg, Resolved* r) {
     const long long big_steps = 2LL * (d.L < kMaxTileTenants ? d.L : kMaxTileTenants) * (d.R / 64);   // a tile's expand steps at most
     r->big = (!no_big && r->mma_shrink && l->big_ok && M > kBigTileMinTokens && !(cfg && cfg->tn) &&
               big_steps <= k2_prefill_max_steps() && (pf == 1 || big_tiles >= min_big_tiles)) ? 1 : 0;
-    if (split1 == 0 && r->mma_shrink) {   // one wave of (128-position tile, slice, K split) CTAs, at least 256 elements each
-        const int tiles = ((M + 127) / 128) * d.S;
+    if (split1 == 0 && r->mma_shrink) {   // one wave of (128-position tile, tenant group, slice, K split) CTAs, at least 256 elements each
+        // (tenant groups per tile, where the shrink deals a tile's tenants out to several CTAs: see shrink_group_cap)
+        const int cap = shrink_group_cap(d.L, M);
+        const int groups = (shrink_tenants_per_tile(d.L, M) + cap - 1) / cap;
+        const int tiles = ((M + 127) / 128) * groups * d.S;
         split1 = 1;
         while (split1 < 16 && tiles * (split1 * 2) <= 148 && d.K / (split1 * 2) >= 256) split1 *= 2;
         // four splits are one cluster that sums over shared memory; eight go through the workspace and their last arriver:
@@ -444,6 +456,7 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     m.split1 = r.split1;
     m.k_per_split = r.k_per_split;
     m.ring_bytes = 192 * 1024;
+    m.tg_cap = shrink_group_cap(d.L, b->M);
     m.wait_ms = r.wait_ms;
     m.meta = meta_of(b);
     m.hp = reinterpret_cast<float*>(base + lay.hp);
@@ -464,8 +477,15 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     static const bool global_sum = [] { const char* v = std::getenv("LOWBIT_SHRINK_GLOBAL_SUM"); return v && v[0] == '1'; }();
     m.cluster = (!global_sum && (r.split1 == 2 || r.split1 == 4) && d.R % (4 * r.split1) == 0 &&
                  (size_t)128 * d.R * 4 <= (size_t)m.ring_bytes) ? 1 : 0;
-    if ((long long)((b->M + 127) / 128) * d.S > kCounterSlots) return OB_ERR_TOO_LARGE;
-    dim3 mgrid((unsigned)((b->M + 127) / 128), (unsigned)d.S, (unsigned)r.split1);
+    // work items (tile, tenant group): sum over tiles of ceil(tenants / cap) <= (pairs + tiles (cap - 1)) / cap with
+    // pairs = (tile, tenant) incidences <= segments + tiles - 1 (a tile boundary is crossed by one segment at most), and
+    // never more than ceil(min(L, 128) / cap) per tile
+    const long long mtiles = (b->M + 127) / 128;
+    const long long per_tile_max = ((d.L < kMaxTileTenants ? d.L : kMaxTileTenants) + m.tg_cap - 1) / m.tg_cap;
+    const long long pairs = std::min<long long>(d.L, b->M) + mtiles - 1;
+    const long long items = std::min(mtiles * per_tile_max, (pairs + mtiles * (m.tg_cap - 1)) / m.tg_cap);
+    if (items * d.S > kCounterSlots || items > 0x7fffffffLL) return OB_ERR_TOO_LARGE;
+    dim3 mgrid((unsigned)items, (unsigned)d.S, (unsigned)r.split1);
     e = launch_k1_mma(m, tm_xs, l->tm_a, mgrid, stream);
     return e == cudaSuccess ? OB_OK : (int)e;
 }

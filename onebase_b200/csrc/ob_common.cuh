@@ -15,6 +15,7 @@ constexpr int kBlockK = 128;         // bytes of K per ring stage row (one 128-b
 constexpr int kMaxLoraIters = 512;   // capacity of a CTA's list of (segment, rank chunk) expand steps
 constexpr int kMaxTileTenants = 128;  // tenants with a position in one 128-position block
 constexpr int kBigTileMinTokens = 128; // larger batches of bf16 adapters take the large-tile prefill GEMM (k2_prefill.cu)
+constexpr int kMmaShrinkGroup = 4;      // tenants of a 128-position tile per CTA of the tensor-core shrink
 constexpr int kMmaShrinkTokens = 512;   // batches from this size on shrink on the tensor cores (bf16 adapters)
 constexpr int kDecodeTokens = 32;     // batches up to this size take the decode forms (one position per shrink warp)
 constexpr int kCounterSlots = 4096;  // split-K arrival counters in the workspace
@@ -129,6 +130,7 @@ struct K1mParams {
     const float* s_w;      // [1]
     int32_t* counters;     // one arrival counter per (position tile, slice); zero between launches
     int32_t* status;
+    int tg_cap;            // tenants of a tile per CTA (work item = tile x tenant group; grid x = the host's bound on their number)
     int cluster;           // the K splits of a (tile, slice) were launched as one thread-block cluster (grid z): their partial
                            // rows are added over distributed shared memory instead of the workspace and the counters
 };
