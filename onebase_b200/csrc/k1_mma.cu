@@ -118,10 +118,11 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
         // (tile, tenant group) number wi in tile order.  First and last tile of every segment go to shared memory;
         // then a lane is one tile of a batch of 32 and counts the segments that cover it.
         const int n_tiles = (p.M + kMmaTile - 1) / kMmaTile, w = wi;
-        // (the two arrays follow the control block, in launches with groups only: with them the one-CTA-per-tile launch's
-        // shared memory crossed 196 KB and its K1b measured 10-16 us slower on the long-K projection)
+        // (the two arrays lie in the still idle operand ring, not in the control block: a launch whose shared memory crosses
+        // 196 KB measured 10-16 us slower -- the SM then has no first-level cache left.  The fence below orders this warp's
+        // accesses before the TMA writes that follow the block's barrier.)
         const int n_seg = GROUPS ? min(p.L + 1, kMmaMaxSeg) : 0;
-        int* seg_first = reinterpret_cast<int*>(ctrl + 1);
+        int* seg_first = reinterpret_cast<int*>(ring);
         int* seg_last = seg_first + kMmaMaxSeg;
         for (int i = lane; i < n_seg; i += 32) {
             const int lora = __ldg(p.meta.seg_ids + i), n = __ldg(p.meta.seg_n + i), sst = __ldg(p.meta.seg_start + i);
@@ -157,6 +158,7 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
         }
         // a CTA beyond the launch's last work item leaves at once -- unless the launch has none at all: then nobody else
         // would keep this grid from completing before the grid it depends on
+        if (GROUPS) fence_proxy_async_smem();
         if (lane == 0) ctrl->wait_before_exit = (tile < 0 && acc == 0) ? 1 : 0;
         int total = 0;
         if (tile >= 0) {
@@ -478,16 +480,14 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
     }
 }
 
-size_t k1_mma_smem_bytes(int ring_bytes, bool groups) {
-    return 1024 + (size_t)ring_bytes + sizeof(K1mCtrl) + 64 + (groups ? 2 * kMmaMaxSeg * sizeof(int) : 0);
-}
+size_t k1_mma_smem_bytes(int ring_bytes) { return 1024 + (size_t)ring_bytes + sizeof(K1mCtrl) + 64; }
 
 cudaError_t launch_k1_mma(const K1mParams& p, const CUtensorMap& tm_xs, const CUtensorMap* tm_a, dim3 grid, cudaStream_t stream) {
     static int configured_for[64] = {0};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return e;
-    const size_t smem = k1_mma_smem_bytes(p.ring_bytes, p.tg_cap < kMmaMaxList);
+    const size_t smem = k1_mma_smem_bytes(p.ring_bytes);
     if (dev >= 0 && dev < 64 && !configured_for[dev]) {
         e = cudaFuncSetAttribute(k1_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
         if (e != cudaSuccess) return e;
