@@ -283,7 +283,8 @@ def e2e_object(M, h2d, d2h, stream_ms, step_ms, step_kind, serial_ms) -> dict:
         head.update(value=M / (stream_ms * 1e-3), ms_per_step=stream_ms,
                     how="steady state, two steps in flight: step i+1 uploads and step i-1 downloads while step i computes "
                         "(three streams, two buffer sets, upload / layer / download graphs ordered by events); all steps "
-                        "timed as one region; no L2 flush inside it (a step streams 193 MB of weights through a 126 MB L2)",
+                        "timed as one region; no L2 flush inside it (a step streams 193 MB of weights and the tenants' adapters "
+                        "through a 126 MB L2; what survives from the step before can put this below `value`'s flushed step)",
                     single_step=single, serial=serial)
     else:
         head.update(value=single["value"], ms_per_step=step_ms, how=single["how"], serial=serial)

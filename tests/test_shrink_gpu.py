@@ -52,14 +52,17 @@ def test_decode_shrink_partials_sum_to_oracle_h(K, widths, R, L, M, cfg):
     assert err <= 2e-5 * scale + 1e-7, f"max |hp sum - h| = {err:.3e} against ||h||inf = {scale:.3e}"
 
 
-@pytest.mark.parametrize("K,split1", [(1024, 0), (1024, 1), (1024, 2), (4096, 8)])
-def test_prefill_tensor_core_shrink_h_equals_oracle_h(K, split1):
+@pytest.mark.parametrize("K,split1,L", [(1024, 0, 8), (1024, 1, 8), (1024, 2, 8), (4096, 8, 8),
+                                         (1024, 0, 32), (1024, 1, 32), (1024, 2, 32), (4096, 8, 32)])
+def test_prefill_tensor_core_shrink_h_equals_oracle_h(K, split1, L):
     """split1 = 0: the library's rule (four K splits here: one thread-block cluster that sums over distributed shared
     memory); 1: no split (the accumulator row is the finished h); 2: a cluster of two; 8 (on a longer K): partials through
-    the workspace and the arrival counter, the last arriver adds them."""
-    widths, R, L, M = (256, 512), 64, 8, 300
+    the workspace and the arrival counter, the last arriver adds them.  L = 8: one CTA per 128-position tile; L = 32: the
+    host expects six or more tenants per tile and deals each tile's tenants out four at a time to CTAs of their own
+    (a grid sized by the host's bound, some CTAs without a work item)."""
+    widths, R, M = (256, 512), 64, 300
     d = configs.with_fp8_base(configs.draw(K, widths, R, L, M, seed=4, ids_low=-1))
-    ids = configs.zipf_request_ids(M, L, seed=6, mean_len=25)
+    ids = configs.zipf_request_ids(M, L, seed=6, mean_len=25 if L == 8 else 9)
     ids[40:70] = -1
     op = build_fp8_op(d, max_m=M)
     idx = make_index(ids, L, M)
