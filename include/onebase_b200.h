@@ -46,6 +46,9 @@ extern "C" {
 /* device-side status word 0 (ob_read_status) */
 #define OB_DEV_OK 0
 #define OB_DEV_WAIT_TIMEOUT 1    /* a bounded wait ran out; words 1..7 say where */
+#define OB_DEV_BAD_INDEX 2       /* the segment index holds more (tile, tenant) incidences than disjoint contiguous segments
+                                    can: the tensor-core shrink's launch did not cover them; word 2 = work items found,
+                                    word 3 = work items launched */
 
 enum { OB_BASE_FP8 = 0, OB_BASE_NVFP4 = 1 };
 enum { OB_X_PLAIN = 0, OB_X_SILU_MUL = 1 };

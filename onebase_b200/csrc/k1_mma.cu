@@ -137,7 +137,10 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
             tile = (w < n_tiles && n_ad > 0) ? w : -1;
             acc = 0;
         }
-        for (int tb = 0; GROUPS && tb < n_tiles && tile < 0 && n_ad > 0; tb += 32) {
+        // (the CTA of the grid's last work item counts on to the end: more items than the host's bound allowed for means the
+        // index is not made of disjoint contiguous segments, and the status words say so instead of a silently short h)
+        const bool count_all = GROUPS && w == (int)gridDim.x - 1 && s == 0 && j == 0;
+        for (int tb = 0; GROUPS && tb < n_tiles && (tile < 0 || count_all) && n_ad > 0; tb += 32) {
             const int t = tb + lane;
             int cnt = 0;
             for (int i = 0; i < n_seg; ++i) cnt += (seg_first[i] <= t && t <= seg_last[i]) ? 1 : 0;
@@ -148,7 +151,7 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
                 const int v = __shfl_up_sync(0xffffffffu, pre, o);
                 if (lane >= o) pre += v;
             }
-            const uint32_t hit = __ballot_sync(0xffffffffu, w >= acc + pre - items && w < acc + pre);
+            const uint32_t hit = tile < 0 ? __ballot_sync(0xffffffffu, w >= acc + pre - items && w < acc + pre) : 0u;
             if (hit) {
                 const int src = __ffs(hit) - 1;
                 tile = tb + src;
@@ -158,6 +161,11 @@ k1_mma_kernel(const K1mParams p, const __grid_constant__ CUtensorMap tm_xs, cons
         }
         // a CTA beyond the launch's last work item leaves at once -- unless the launch has none at all: then nobody else
         // would keep this grid from completing before the grid it depends on
+        if (count_all && acc > (int)gridDim.x && lane == 0 && atomicCAS(p.status, OB_DEV_OK, OB_DEV_BAD_INDEX) == OB_DEV_OK) {
+            p.status[1] = 150;
+            p.status[2] = acc;
+            p.status[3] = (int)gridDim.x;
+        }
         if (GROUPS) fence_proxy_async_smem();
         if (lane == 0) ctrl->wait_before_exit = (tile < 0 && acc == 0) ? 1 : 0;
         int total = 0;

@@ -482,7 +482,7 @@ int k1_fp8_impl(ObLayer* l, const ObBatch* b, void* ws, const ObWorkspaceShape* 
     // never more than ceil(min(L, 128) / cap) per tile
     const long long mtiles = (b->M + 127) / 128;
     const long long per_tile_max = ((d.L < kMaxTileTenants ? d.L : kMaxTileTenants) + m.tg_cap - 1) / m.tg_cap;
-    const long long pairs = std::min<long long>(d.L, b->M) + mtiles - 1;
+    const long long pairs = std::min<long long>(d.L + 1, b->M) + mtiles - 1;   // (L + 1: every entry of the index)
     const long long items = std::min(mtiles * per_tile_max, (pairs + mtiles * (m.tg_cap - 1)) / m.tg_cap);
     if (items * d.S > kCounterSlots || items > 0x7fffffffLL) return OB_ERR_TOO_LARGE;
     dim3 mgrid((unsigned)items, (unsigned)d.S, (unsigned)r.split1);
